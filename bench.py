@@ -1,0 +1,438 @@
+#!/usr/bin/env python
+"""Benchmark of the W8A8 linear-layer hot path on B200.
+
+Workload (N=1): the Qwen3-8B decode GEMM set -- M in {1,4,16} tokens times the five projections
+QKV 4096->6144, O 4096->4096, gate_up 4096->24576, down 12288->4096, lm_head 4096->151936 --
+each as `quantize` (bf16 activations -> int8 + per-token scale) followed by `linear`
+(int8 x int8 -> int32, dequantizing epilogue -> bf16).  One step = one pass over all 15.
+Seeded synthetic tensors: activations bf16 N(0,1) with 8 outlier channels x20, weights fp32
+N(0,0.02) quantized per output channel.  Metric: algorithmic HBM bytes per second.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N>1 runs under torchrun: tensor-parallel shards (QKV/gate_up/lm_head split by output channel,
+O/down split along K with a bf16 NCCL all-reduce of the [M,4096] outputs).
+`--impl reference` times the CPU restatement of the reference's CPU-integer path (oracle/) on
+the host cores.  Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SHAPES = [("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 24576), ("down", 12288, 4096),
+          ("lm_head", 4096, 151936)]
+DECODE_M = [1, 4, 16]
+PREFILL_M = [129, 512, 4096]
+ROW_SPLIT = {"o", "down"}  # sharded along K under tensor parallelism, all-reduce after
+METRIC = "W8A8 decode GEMM set (Qwen3-8B shapes, M in {1,4,16}): algorithmic HBM GB/s"
+WORKLOAD = "configs[1]: quantize+linear over 5 Qwen3-8B projections x M in {1,4,16}"
+
+# DRAM bytes per launch of the dominant kernel from one ncu capture of this command
+# (profiles/gemv_dp4a_decode_set.md), averaged over the launches of one step; None until captured.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def linear_bytes(M, K, N):
+    return N * K + 4 * N + M * K + 4 * M + 2 * M * N
+
+
+def quant_bytes(M, K):
+    return 2 * M * K + M * K + 4 * M
+
+
+def shard(name, K, N, tp):
+    if tp == 1:
+        return K, N
+    return (K // tp, N) if name in ROW_SPLIT else (K, N // tp)
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 0.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            try:
+                import torch
+                pr = torch.cuda.get_device_properties(index)
+                bus = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+                self.h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _sample(self):
+        nv = self.nv
+        try:
+            self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+            r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+            names = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+                     "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                     "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+                     "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+            for k, bit in names.items():
+                if r & bit:
+                    self.reasons.add(k)
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self._sample()
+            time.sleep(0.005)
+
+    def start(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread:
+            self._sample()
+            self._stop.set()
+            self._thread.join()
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def make_weights_device(torch, K, N, seed):
+    """fp32 N(0,0.02) -> per-output-channel symmetric int8 (tools/prepare.py:79-81), generated on the device."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.empty((N, K), dtype=torch.int8, device="cuda")
+    s = torch.empty((N,), dtype=torch.float32, device="cuda")
+    rows = max(1, (64 << 20) // K)
+    for r0 in range(0, N, rows):
+        w = torch.randn((min(rows, N - r0), K), generator=g, device="cuda", dtype=torch.float32) * 0.02
+        sc = w.abs().amax(1, keepdim=True).clamp(min=1e-8) / 127.0
+        q[r0:r0 + w.shape[0]] = torch.round(w / sc).clamp(-127, 127).to(torch.int8)
+        s[r0:r0 + w.shape[0]] = sc.flatten()
+    return q, s
+
+
+def make_activations_device(torch, M, K, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn((M, K), generator=g, device="cuda", dtype=torch.float32)
+    cols = torch.randperm(K, generator=g, device="cuda")[:8]
+    x[:, cols] *= 20.0
+    return x.to(torch.bfloat16)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from inferrous_b200 import ops
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    tp = world
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ops.init(local)
+    hbm_peak, _, peak_kind = measured_peaks()
+
+    # ---- resident weights (model state) and per-(M,shape) activation/output buffers ----
+    mats, bufs = {}, {}
+    for i, (name, K, N) in enumerate(SHAPES):
+        k, n = shard(name, K, N, tp)
+        wq, ws = make_weights_device(torch, k, n, seed=1000 + 10 * i + rank)
+        mats[name] = ops.Matrix(wq, ws)
+    for M in DECODE_M:
+        for i, (name, K, N) in enumerate(SHAPES):
+            k, n = shard(name, K, N, tp)
+            bufs[(M, name)] = dict(
+                x=make_activations_device(torch, M, k, seed=7 * M + i + 100 * rank),
+                q=torch.empty((M, k), dtype=torch.int8, device="cuda"),
+                s=torch.empty((M,), dtype=torch.float32, device="cuda"),
+                y=torch.empty((M, n), dtype=torch.bfloat16, device="cuda"),
+                hx=torch.empty((M, k), dtype=torch.bfloat16).pin_memory(),
+                hy=torch.empty((M, n), dtype=torch.bfloat16).pin_memory())
+            bufs[(M, name)]["hx"].copy_(bufs[(M, name)]["x"])
+    torch.cuda.synchronize()
+
+    step_bytes = 0
+    for M in DECODE_M:
+        for name, K, N in SHAPES:
+            k, n = shard(name, K, N, tp)
+            step_bytes += linear_bytes(M, k, n) + quant_bytes(M, k)
+    total_bytes = step_bytes * world  # every rank moves the same amount
+
+    gemv_events = []  # (kernel family, bytes, start, end) per linear launch of the timed region
+
+    def step(record=False, host_io=False):
+        for M in DECODE_M:
+            for name, K, N in SHAPES:
+                b = bufs[(M, name)]
+                k, n = shard(name, K, N, tp)
+                if host_io:
+                    b["x"].copy_(b["hx"], non_blocking=True)
+                ops.quantize(b["x"], b["q"], b["s"])
+                if record:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                ops.linear_quantized(b["q"], b["s"], mats[name], b["y"])
+                if record:
+                    e1.record()
+                    gemv_events.append(("gemv_dp4a" if M <= 4 else "gemv_mma", linear_bytes(M, k, n), e0, e1))
+                if world > 1 and name in ROW_SPLIT:
+                    dist.all_reduce(b["y"])
+                if host_io:
+                    b["hy"].copy_(b["y"], non_blocking=True)
+
+    def timed(fn, steps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([t0.elapsed_time(t1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            dist.barrier()
+        return float(ms.item())
+
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed(lambda: step(record=True), args.steps)
+    clocks = sampler.stop()
+    ms_per_step = ms / args.steps
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel family, from the per-launch events of the timed region ----
+    fam = {}
+    for name, nbytes, e0, e1 in gemv_events:
+        d = fam.setdefault(name, [0, 0.0, 0])
+        d[0] += nbytes
+        d[1] += e0.elapsed_time(e1) * 1e-3
+        d[2] += 1
+    dominant = max(fam, key=lambda k: fam[k][1])
+    dom_bytes, dom_s, dom_n = fam[dominant]
+    achieved = dom_bytes / dom_s / 1e9
+    roofline = {"bound": "hbm", "kernel": dominant, "achieved": round(achieved, 1), "peak": hbm_peak, "peak_kind": peak_kind,
+                "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "algorithmic_bytes_per_launch": dom_bytes // dom_n, "avg_launch_us": round(dom_s / dom_n * 1e6, 2),
+                "launches": dom_n,
+                "other_kernels": {k: {"achieved": round(v[0] / v[1] / 1e9, 1), "frac": round(v[0] / v[1] / 1e9 / hbm_peak, 4),
+                                      "launches": v[2]} for k, v in fam.items() if k != dominant}}
+
+    # ---- end to end: host buffers in, host buffers out, through the same calls ----
+    for _ in range(3):
+        step(host_io=True)
+    e2e_ms = timed(lambda: step(host_io=True), args.steps) / args.steps
+    h2d = sum(2 * M * shard(n_, K, N, tp)[0] for M in DECODE_M for n_, K, N in SHAPES)
+    d2h = sum(2 * M * shard(n_, K, N, tp)[1] for M in DECODE_M for n_, K, N in SHAPES)
+    e2e = {"value": round(total_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4),
+           "note": "activations from pinned host memory and outputs back to it every step; weights resident (model state)"}
+
+    extra = {}
+    if world == 1 and not args.no_extra:
+        extra["per_shape"] = per_shape_table(torch, ops, mats, bufs, hbm_peak)
+        extra["prefill"] = prefill_table(torch, ops, mats)
+        body = sum(r["us"] for r in extra["per_shape"] if r["M"] == 1 and r["shape"] != "lm_head")
+        head = sum(r["us"] for r in extra["per_shape"] if r["M"] == 1 and r["shape"] == "lm_head")
+        extra["decode_linear_only_tok_s_estimate"] = round(1e6 / (36 * body + head), 1)
+
+    out = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+           "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+           "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8xint8->int32 (bf16 in/out)",
+           "data": "synthetic", "impl": "ours",
+           "config": {"workload": WORKLOAD, "shapes": {n: [K, N] for n, K, N in SHAPES}, "M": DECODE_M,
+                      "parallelism": f"tp{world}" if world > 1 else "single",
+                      "l2": f"weights ({sum(shard(n, K, N, tp)[0] * shard(n, K, N, tp)[1] for n, K, N in SHAPES) >> 20} MiB streamed per "
+                            "pass, each matrix revisited only after all the others) exceed the 126 MB L2; no flush",
+                      "bytes_per_step": step_bytes},
+           "roofline": roofline, "e2e": e2e, "gpu_launches": 2 * len(SHAPES) * len(DECODE_M) * args.steps, "clocks": clocks}
+    if world == 1 and not args.no_cpu:
+        out["cpu_baseline"] = cpu_baseline(torch, mats, bufs, reps=3)
+    out.update(extra)
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def time_launch(torch, fn, iters, flush):
+    """Median device time of fn() with an L2 flush before every timed launch."""
+    ts = []
+    for _ in range(iters):
+        flush.add_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    return statistics.median(ts)
+
+
+def per_shape_table(torch, ops, mats, bufs, hbm_peak):
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+    rows = []
+    for M in DECODE_M:
+        for name, K, N in SHAPES:
+            b = bufs[(M, name)]
+            us = time_launch(torch, lambda: ops.linear_quantized(b["q"], b["s"], mats[name], b["y"]), 20, flush)
+            gbs = linear_bytes(M, K, N) / us / 1e3
+            rows.append({"shape": name, "M": M, "us": round(us, 2), "GB/s": round(gbs, 1), "frac_hbm": round(gbs / hbm_peak, 3)})
+    del flush
+    return rows
+
+
+def prefill_table(torch, ops, mats):
+    """Tensor-core regime, reported beside the headline: quantize + GEMM at M in {129,512,4096}."""
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+    rows = []
+    for M in PREFILL_M:
+        for name, K, N in SHAPES:
+            x = make_activations_device(torch, M, K, seed=M)
+            q = torch.empty((M, K), dtype=torch.int8, device="cuda")
+            s = torch.empty((M,), dtype=torch.float32, device="cuda")
+            y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+            ops.quantize(x, q, s)
+            ops.linear_quantized(q, s, mats[name], y)
+            us = time_launch(torch, lambda: ops.linear_quantized(q, s, mats[name], y), 5, flush)
+            rows.append({"shape": name, "M": M, "us": round(us, 1), "TOPS": round(2.0 * M * N * K / us / 1e6, 1),
+                         "GB/s": round(linear_bytes(M, K, N) / us / 1e3, 1)})
+            del x, q, s, y
+    del flush
+    return rows
+
+
+def cpu_step(oracle, host, threads):
+    for M in DECODE_M:
+        for name, K, N in SHAPES:
+            x, w, ws = host[(M, name)]
+            q, s = oracle.quantize(x)
+            oracle.linear(q, s, w, ws, threads=threads)
+
+
+def host_copies(torch, mats, bufs):
+    host = {}
+    wh = {name: (m.w.cpu().numpy(), m.scale.cpu().numpy()) for name, m in mats.items()}
+    for (M, name), b in bufs.items():
+        host[(M, name)] = (b["x"].float().cpu().numpy(), *wh[name])
+    return host
+
+
+def cpu_baseline(torch, mats, bufs, reps):
+    from oracle import oracle
+    host = host_copies(torch, mats, bufs)
+    threads = oracle.hw_threads()
+    cpu_step(oracle, host, threads)
+    t = time.perf_counter()
+    for _ in range(reps):
+        cpu_step(oracle, host, threads)
+    dt = (time.perf_counter() - t) / reps
+    nbytes = sum(linear_bytes(M, K, N) + quant_bytes(M, K) for M in DECODE_M for _, K, N in SHAPES)
+    return {"value": round(nbytes / dt / 1e9, 2), "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{reps} full steps (all 15 quantize+linear pairs) of the same workload, {threads} host threads",
+            "s_per_step": round(dt, 4)}
+
+
+def run_reference(args):
+    """The reference's CPU-integer path (tools/operator_fixtures.py:43-44,54), restated in C (oracle/), on all host threads."""
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    from oracle import oracle
+    threads = oracle.hw_threads()
+    rng = np.random.default_rng(0)
+    host = {}
+    wh = {}
+    for name, K, N in SHAPES:
+        # uniform int8 codes: the integer product's speed does not depend on the value distribution
+        w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+        wh[name] = (w, (rng.random(N, dtype=np.float32) * 1e-3 + 1e-4).astype(np.float32))
+    for M in DECODE_M:
+        for name, K, N in SHAPES:
+            x = oracle.bf16(rng.standard_normal((M, K), dtype=np.float32))
+            x[:, rng.choice(K, 8, replace=False)] *= 20
+            host[(M, name)] = (oracle.bf16(x), *wh[name])
+    t = time.perf_counter()
+    cpu_step(oracle, host, threads)
+    first = time.perf_counter() - t
+    # keep the whole run within a few minutes whatever K and W were asked for
+    args.warmup = max(0, min(args.warmup - 1, int(30 / first)))
+    args.steps = max(1, min(args.steps, int(150 / first)))
+    for _ in range(args.warmup):
+        cpu_step(oracle, host, threads)
+    t = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(oracle, host, threads)
+    dt = (time.perf_counter() - t) / args.steps
+    nbytes = sum(linear_bytes(M, K, N) + quant_bytes(M, K) for M in DECODE_M for _, K, N in SHAPES)
+    v = round(nbytes / dt / 1e9, 2)
+    sample = f"full step (all 15 quantize+linear pairs), {threads} host threads, C restatement of the reference's CPU-integer path"
+    print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": args.gpus,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
+                      "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+                      "dtype": "int8xint8->int32 (bf16 in/out)", "data": "synthetic",
+                      "config": {"workload": WORKLOAD, "shapes": {n: [K, N] for n, K, N in SHAPES}, "M": DECODE_M},
+                      "cpu_baseline": {"value": v, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+                      "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the per-shape and prefill tables")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--shapes", default="", help="comma-separated subset of the five projections (profiling runs)")
+    ap.add_argument("--ms", default="", help="comma-separated subset of the token counts (profiling runs)")
+    args = ap.parse_args()
+    global SHAPES, DECODE_M, WORKLOAD
+    if args.shapes:
+        keep = args.shapes.split(",")
+        SHAPES = [s for s in SHAPES if s[0] in keep]
+        WORKLOAD += f" [subset: shapes={args.shapes}]"
+    if args.ms:
+        DECODE_M = [int(m) for m in args.ms.split(",")]
+        WORKLOAD += f" [subset: M={args.ms}]"
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,159 @@
+/*
+ * w8a8.h -- C ABI of the B200 (sm_100a) W8A8 linear-layer library.
+ *
+ * The library stands where the inferrous-qwen3 host runtime calls the kernel
+ * launchers that its `#[cuda_module]` macro generates (src/kernels.rs:322-323,
+ * invoked as `module.KERNEL(&stream, LaunchConfig, args...)`, e.g. src/gpu.rs:351-360).
+ * Each entry point below names the reference launcher(s) it replaces.
+ *
+ * Conventions (they restate the reference's own, docs/qwen3-8b-w8a8/safety.md):
+ *  - every pointer is a DEVICE pointer owned by the caller unless stated otherwise;
+ *    inputs and outputs never alias; all buffers outlive the queued work;
+ *  - `stream` is a cudaStream_t / CUstream passed as void*; all work is queued on
+ *    it, nothing synchronises, nothing touches the default stream;
+ *  - launch calls allocate nothing, read no device memory from the host and are
+ *    safe inside stream capture once w8a8_init() has run for the device;
+ *  - every kernel executes `griddepcontrol.wait` before its first access to a
+ *    buffer another kernel may produce, so programmatic graph edges
+ *    (src/graph.rs:63-127, src/kernels.rs:173-184) stay legal;
+ *  - activations are row-major [M,K]; weights are row-major [N,K] int8 (K contiguous)
+ *    with one f32 scale per output channel; outputs are row-major [M,N];
+ *  - activation element type is selectable: W8A8_BF16 (2-byte storage) or W8A8_F32
+ *    (the reference's carrier: f32 buffers that hold bf16-representable values,
+ *    src/gpu.rs:16).  Results are the same values in either carrier;
+ *  - every function returns a w8a8_status_t; nothing throws, traps or aborts.
+ */
+#ifndef W8A8_H
+#define W8A8_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    W8A8_OK = 0,
+    W8A8_ERR_BAD_ARG = 1,      /* null pointer, non-positive size, unknown enum */
+    W8A8_ERR_ALIGNMENT = 2,    /* K not a multiple of 128, pointer not 16-byte aligned */
+    W8A8_ERR_UNSUPPORTED = 3,  /* shape outside what the chosen kernel variant handles */
+    W8A8_ERR_CUDA = 4,         /* a CUDA runtime/driver call failed; see w8a8_last_cuda_error */
+    W8A8_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait expired (reported by w8a8_device_status) */
+    W8A8_ERR_NOT_INITIALIZED = 6 /* w8a8_init() has not run for the current device */
+} w8a8_status_t;
+
+typedef enum { W8A8_BF16 = 0, W8A8_F32 = 1 } w8a8_dtype_t;
+
+/* Kernel selection for w8a8_linear_ex.  AUTO is what w8a8_linear uses and mirrors the
+ * regime switch of GpuModel::linear_quantized (src/gpu.rs:450-509). */
+typedef enum {
+    W8A8_VARIANT_AUTO = 0,
+    W8A8_VARIANT_NAIVE = 1,      /* one thread per output; the on-GPU oracle (role of `linear`, src/kernels.rs:808-845) */
+    W8A8_VARIANT_GEMV_DP4A = 2,  /* M <= 4: 16-byte weight streaming + dp4a + in-CTA split-K */
+    W8A8_VARIANT_GEMV_MMA = 3,   /* M <= 64: 16-byte weight streaming + warp-level int8 MMA */
+    W8A8_VARIANT_GEMM_TCGEN05 = 4 /* any M: TMA-staged tiles + tcgen05.mma kind::i8 into TMEM */
+} w8a8_variant_t;
+
+/* Immutable weight matrix handle: device pointers, shape and the TMA descriptor of the
+ * [N,K] matrix (replaces gpu::Matrix{w,map,scale,k,n}, src/gpu.rs:43-49, and
+ * tensor::map, src/tensor.rs:5-39). */
+typedef struct w8a8_weight *w8a8_weight_t;
+
+/* ---- library / device set-up -------------------------------------------------------- */
+
+/* Loads kernels and sets their attributes on `device` (replaces device::load(&ctx),
+ * src/gpu.rs:250).  Call once per device before any launch and before stream capture. */
+int w8a8_init(int device);
+/* Library version, "major.minor.patch". */
+const char *w8a8_version(void);
+const char *w8a8_status_string(int status);
+/* Text of the last failing CUDA call on this host thread ("" if none). */
+const char *w8a8_last_cuda_error(void);
+/* Reads (and clears) the device-side status word of the current device: 0, or
+ * W8A8_ERR_DEVICE_TIMEOUT with *detail = code of the wait that gave up.  Synchronises `stream`. */
+int w8a8_device_status(void *stream, uint32_t *detail);
+
+/* ---- weights ------------------------------------------------------------------------ */
+
+/* Wraps caller-owned device buffers w[N,K] int8 and w_scale[N] f32.  No copy is made.
+ * Replaces the Matrix construction at src/gpu.rs:258-299.  K % 128 == 0, w 128-byte aligned. */
+int w8a8_weight_create(const int8_t *w, const float *w_scale, int N, int K, w8a8_weight_t *out);
+int w8a8_weight_destroy(w8a8_weight_t weight);
+int w8a8_weight_shape(w8a8_weight_t weight, int *N, int *K);
+
+/* ---- activation quantizers ---------------------------------------------------------- */
+
+/* `quantize` (src/kernels.rs:415-452; host wrapper src/gpu.rs:424-449):
+ * scale[m] = max(1e-8, max_k |x[m,k]|) / 127;  q[m,k] = rne(clamp(x[m,k] / scale[m], +-127)).
+ * ldx = row stride of x in elements (>= K). */
+int w8a8_quantize(const void *x, int dtype, int M, int K, int64_t ldx, int8_t *q, float *scale,
+                  void *stream);
+
+/* `quantize_with_max` (src/kernels.rs:455-475; src/gpu.rs:377-390): the row maximum is
+ * given as f32 bit patterns, maxima[m] (as produced by the swiglu entry points). */
+int w8a8_quantize_with_max(const void *x, int dtype, const uint32_t *maxima, int M, int K, int64_t ldx,
+                           int8_t *q, float *scale, void *stream);
+
+/* `norm_quantize` (src/kernels.rs:479-576; src/gpu.rs:340-363), any K % 128 == 0:
+ * y = bf16((x * rsqrt(mean(x^2) + eps)) * gamma), then quantize(y).  gamma has the same
+ * element type as x.  y_out (optional, may be NULL) receives the bf16 row the codes were
+ * made from; maxima_reset (optional) gets 1e-8f bits per row, as the reference resets
+ * the SwiGLU maximum there (src/kernels.rs:566). */
+int w8a8_rmsnorm_quantize(const void *x, const void *gamma, int dtype, float eps, int M, int K, int64_t ldx,
+                          int8_t *q, float *scale, void *y_out, uint32_t *maxima_reset, void *stream);
+
+/* `swiglu` (src/kernels.rs:2172-2190; src/gpu.rs:768-778): act = bf16((g / (1 + exp(-g))) * u).
+ * gate/up are [M,I] with row stride ld (elements); a [M,2I] gate|up buffer is passed as
+ * gate = base, up = base + I, ld = 2I.  maxima (optional): atomic max of |act| bit patterns per row;
+ * the caller resets it (w8a8_rmsnorm_quantize does). */
+int w8a8_swiglu(const void *gate, const void *up, int dtype, int M, int I, int64_t ld, void *act,
+                uint32_t *maxima, void *stream);
+
+/* SwiGLU fused with the quantizer of the down-projection input (replaces the prefill pair
+ * `swiglu` + `quantize`, src/gpu.rs:768-778 + :377-398).  act_out is optional. */
+int w8a8_swiglu_quantize(const void *gate, const void *up, int dtype, int M, int I, int64_t ld, int8_t *q,
+                         float *scale, void *act_out, void *stream);
+
+/* `residual` (src/kernels.rs:2163-2170; src/gpu.rs:510-517): out = bf16(a + b), n elements. */
+int w8a8_residual(const void *a, const void *b, int dtype, size_t n, void *out, void *stream);
+
+/* ---- the W8A8 product + dequantizing epilogue --------------------------------------- */
+
+/* GpuModel::linear_quantized / linear_residual (src/gpu.rs:450-509, :364-423), i.e. the kernels
+ * `linear`, `linear_splitk`, `linear_tiled`, `linear_large`, `linear_residual`, `residual`:
+ *   acc[m,n] = sum_k q[m,k] * w[n,k]            (int32, exact)
+ *   y[m,n]   = bf16((f32(acc) * a_scale[m]) * w_scale[n])
+ *   combined[m,n] = bf16(residual[m,n] + y[m,n])   when residual != NULL
+ * y may be NULL when combined is requested and the un-summed projection is not needed.
+ * The regime (decode GEMV / tensor-core GEMM) is chosen from M. */
+int w8a8_linear(const int8_t *q, const float *a_scale, w8a8_weight_t weight, int M, const void *residual,
+                void *y, void *combined, int dtype, void *stream);
+/* Same with an explicit kernel variant (tests: every variant must equal the naive one). */
+int w8a8_linear_ex(const int8_t *q, const float *a_scale, w8a8_weight_t weight, int M, const void *residual,
+                   void *y, void *combined, int dtype, int variant, void *stream);
+
+/* `linear_pair` / `linear_triple` (src/kernels.rs:698-806; src/gpu.rs:571-590): up to three
+ * sibling projections of the same quantized activations in one launch (Q, K, V).
+ * All weights share K.  M <= 16. */
+int w8a8_linear_grouped(const int8_t *q, const float *a_scale, const w8a8_weight_t *weights, int count, int M,
+                        void *const *outs, int dtype, void *stream);
+
+/* `linear_swiglu` (src/kernels.rs:621-695; src/gpu.rs:730-745): gate and up projections that
+ * share every activation load, then act = bf16(silu(bf16 g) * bf16 u) and an atomic max of
+ * |act| bit patterns into maxima[m].  gate_out / up_out are optional.  M <= 16. */
+int w8a8_linear_gate_up_swiglu(const int8_t *q, const float *a_scale, w8a8_weight_t w_gate, w8a8_weight_t w_up,
+                               int M, void *gate_out, void *up_out, void *act, uint32_t *maxima, int dtype,
+                               void *stream);
+
+/* Raw int32 accumulators acc[M,N] of the product (debug / parity: the reference's tests
+ * hold these bit-exact through its CPU-integer fixtures, tools/operator_fixtures.py:54). */
+int w8a8_linear_acc_i32(const int8_t *q, w8a8_weight_t weight, int M, int32_t *acc, int variant, void *stream);
+
+/* `rounding_probe` (src/kernels.rs:326-333): out[i] = rne(clamp(x[i], +-127)) as int8. */
+int w8a8_rounding_probe(const float *x, int8_t *out, size_t n, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* W8A8_H */

@@ -1,0 +1,72 @@
+"""ctypes binding of include/w8a8.h.  Every symbol the header declares is bound here."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libw8a8.so"
+
+OK = 0
+BF16, F32 = 0, 1
+VARIANT_AUTO, VARIANT_NAIVE, VARIANT_GEMV_DP4A, VARIANT_GEMV_MMA, VARIANT_GEMM_TCGEN05 = range(5)
+
+_vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+
+# name -> (restype, argtypes); mirrors include/w8a8.h one to one
+SIGNATURES = {
+    "w8a8_init": (_i, [_i]),
+    "w8a8_version": (C.c_char_p, []),
+    "w8a8_status_string": (C.c_char_p, [_i]),
+    "w8a8_last_cuda_error": (C.c_char_p, []),
+    "w8a8_device_status": (_i, [_vp, C.POINTER(C.c_uint32)]),
+    "w8a8_weight_create": (_i, [_vp, _vp, _i, _i, C.POINTER(_vp)]),
+    "w8a8_weight_destroy": (_i, [_vp]),
+    "w8a8_weight_shape": (_i, [_vp, C.POINTER(_i), C.POINTER(_i)]),
+    "w8a8_quantize": (_i, [_vp, _i, _i, _i, _i64, _vp, _vp, _vp]),
+    "w8a8_quantize_with_max": (_i, [_vp, _i, _vp, _i, _i, _i64, _vp, _vp, _vp]),
+    "w8a8_rmsnorm_quantize": (_i, [_vp, _vp, _i, _f, _i, _i, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "w8a8_swiglu": (_i, [_vp, _vp, _i, _i, _i, _i64, _vp, _vp, _vp]),
+    "w8a8_swiglu_quantize": (_i, [_vp, _vp, _i, _i, _i, _i64, _vp, _vp, _vp, _vp]),
+    "w8a8_residual": (_i, [_vp, _vp, _i, _sz, _vp, _vp]),
+    "w8a8_linear": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp]),
+    "w8a8_linear_ex": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp]),
+    "w8a8_linear_grouped": (_i, [_vp, _vp, C.POINTER(_vp), _i, _i, C.POINTER(_vp), _i, _vp]),
+    "w8a8_linear_gate_up_swiglu": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp]),
+    "w8a8_linear_acc_i32": (_i, [_vp, _vp, _i, _vp, _i, _vp]),
+    "w8a8_rounding_probe": (_i, [_vp, _vp, _sz, _vp]),
+}
+
+
+class W8A8Error(RuntimeError):
+    def __init__(self, status: int, where: str, detail: str = ""):
+        self.status = status
+        super().__init__(f"{where}: status {status} ({detail})")
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load libw8a8.so.  Raises if it has not been built: there is no fallback path."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise FileNotFoundError(
+                f"{LIB_PATH} is missing: build it with `python -m inferrous_b200.build` (needs nvcc). "
+                "There is no CPU or PyTorch fallback.")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        lib = load()
+        msg = lib.w8a8_status_string(status).decode()
+        if status == 4:
+            msg += ": " + lib.w8a8_last_cuda_error().decode()
+        raise W8A8Error(status, where, msg)

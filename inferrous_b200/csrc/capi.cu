@@ -1,0 +1,337 @@
+// The C ABI (include/w8a8.h): argument validation, regime selection, status reporting.
+//
+// Regime selection mirrors GpuModel::linear_quantized (crates/inferrous-qwen3/src/gpu.rs:450-509),
+// which switches kernels on the token count: 1 -> linear, 2..31 -> linear_splitk,
+// 32..255 -> linear_tiled, >= 256 (and N >= 4096) -> linear_large.  Here:
+//   M <= 4   gemv_dp4a        (weight streaming, dp4a)
+//   M <= 16  gemv_mma         (weight streaming, warp-level int8 MMA)
+//   else     gemm_tcgen05     (TMA + tcgen05.mma kind::i8 + TMEM)
+#include "../../include/w8a8.h"
+#include "internal.h"
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+namespace w8a8 {
+
+namespace {
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+    bool ready = false;
+    int sms = 0;
+    uint32_t *status = nullptr;  // 2 words: [0] wait code, [1] detail
+};
+DeviceState g_dev[kMaxDevices];
+std::mutex g_mu;
+thread_local char g_err[256] = "";
+
+int fail_cuda(cudaError_t e, const char *what) {
+    snprintf(g_err, sizeof g_err, "%s: %s", what, cudaGetErrorString(e));
+    return W8A8_ERR_CUDA;
+}
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int current_ready_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    return g_dev[dev].ready ? dev : -1;
+}
+}  // namespace
+
+int sm_count() {
+    int dev = current_ready_device();
+    return dev < 0 ? 148 : g_dev[dev].sms;
+}
+uint32_t *device_status_ptr() {
+    int dev = current_ready_device();
+    return dev < 0 ? nullptr : g_dev[dev].status;
+}
+cudaError_t read_device_status(cudaStream_t s, uint32_t out[2]) {
+    uint32_t *p = device_status_ptr();
+    if (!p) return cudaErrorInitializationError;
+    cudaError_t e = cudaMemcpyAsync(out, p, 8, cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return e;
+    if ((e = cudaMemsetAsync(p, 0, 8, s)) != cudaSuccess) return e;
+    return cudaStreamSynchronize(s);
+}
+
+}  // namespace w8a8
+
+using namespace w8a8;
+
+#define REQUIRE(cond, code) \
+    do {                    \
+        if (!(cond)) return (code); \
+    } while (0)
+#define CUDA_OK(expr, what)                              \
+    do {                                                 \
+        cudaError_t e__ = (expr);                        \
+        if (e__ != cudaSuccess) return fail_cuda(e__, what); \
+    } while (0)
+
+extern "C" {
+
+const char *w8a8_version(void) { return "0.1.0"; }
+
+const char *w8a8_status_string(int status) {
+    switch (status) {
+        case W8A8_OK: return "ok";
+        case W8A8_ERR_BAD_ARG: return "bad argument";
+        case W8A8_ERR_ALIGNMENT: return "alignment: K must be a multiple of 128 and pointers 16-byte aligned";
+        case W8A8_ERR_UNSUPPORTED: return "shape not supported by the requested kernel variant";
+        case W8A8_ERR_CUDA: return "CUDA call failed";
+        case W8A8_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait expired";
+        case W8A8_ERR_NOT_INITIALIZED: return "w8a8_init() has not run for the current device";
+        default: return "unknown status";
+    }
+}
+
+const char *w8a8_last_cuda_error(void) { return g_err; }
+
+int w8a8_init(int device) {
+    REQUIRE(device >= 0 && device < kMaxDevices, W8A8_ERR_BAD_ARG);
+    std::lock_guard<std::mutex> lock(g_mu);
+    CUDA_OK(cudaSetDevice(device), "cudaSetDevice");
+    DeviceState &d = g_dev[device];
+    if (d.ready) return W8A8_OK;
+    cudaDeviceProp prop;
+    CUDA_OK(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties");
+    if (prop.major != 10) {
+        snprintf(g_err, sizeof g_err, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+        return W8A8_ERR_CUDA;
+    }
+    d.sms = prop.multiProcessorCount;
+    CUDA_OK(cudaMalloc(&d.status, 8), "cudaMalloc(status)");
+    CUDA_OK(cudaMemset(d.status, 0, 8), "cudaMemset(status)");
+    CUDA_OK(init_quantize(), "init_quantize");
+    CUDA_OK(init_gemv(), "init_gemv");
+    CUDA_OK(init_gemm_tcgen05(), "init_gemm_tcgen05");
+    d.ready = true;
+    return W8A8_OK;
+}
+
+int w8a8_device_status(void *stream, uint32_t *detail) {
+    REQUIRE(current_ready_device() >= 0, W8A8_ERR_NOT_INITIALIZED);
+    uint32_t words[2] = {0, 0};
+    CUDA_OK(read_device_status((cudaStream_t)stream, words), "read_device_status");
+    if (detail) *detail = words[0] ? ((words[0] << 24) | (words[1] & 0xffffffu)) : 0;
+    return words[0] ? W8A8_ERR_DEVICE_TIMEOUT : W8A8_OK;
+}
+
+// ---- weights ---------------------------------------------------------------------------
+
+int w8a8_weight_create(const int8_t *w, const float *w_scale, int N, int K, w8a8_weight_t *out) {
+    REQUIRE(w && w_scale && out && N > 0 && K > 0, W8A8_ERR_BAD_ARG);
+    REQUIRE(K % 128 == 0 && (reinterpret_cast<uintptr_t>(w) & 127u) == 0 && aligned16(w_scale), W8A8_ERR_ALIGNMENT);
+    int dev = current_ready_device();
+    REQUIRE(dev >= 0, W8A8_ERR_NOT_INITIALIZED);
+    w8a8_weight *wt = new (std::nothrow) w8a8_weight();
+    REQUIRE(wt, W8A8_ERR_BAD_ARG);
+    wt->magic = kWeightMagic;
+    wt->device = dev;
+    wt->w = w;
+    wt->w_scale = w_scale;
+    wt->N = N;
+    wt->K = K;
+    wt->has_maps = false;
+    cudaError_t e = make_weight_maps(wt);
+    if (e != cudaSuccess) {
+        delete wt;
+        return fail_cuda(e, "cuTensorMapEncodeTiled(weight)");
+    }
+    *out = wt;
+    return W8A8_OK;
+}
+
+int w8a8_weight_destroy(w8a8_weight_t weight) {
+    REQUIRE(weight && weight->magic == kWeightMagic, W8A8_ERR_BAD_ARG);
+    weight->magic = 0;
+    delete weight;
+    return W8A8_OK;
+}
+
+int w8a8_weight_shape(w8a8_weight_t weight, int *N, int *K) {
+    REQUIRE(weight && weight->magic == kWeightMagic, W8A8_ERR_BAD_ARG);
+    if (N) *N = weight->N;
+    if (K) *K = weight->K;
+    return W8A8_OK;
+}
+
+// ---- quantizers ------------------------------------------------------------------------
+
+static int check_dtype(int dtype) { return dtype == W8A8_BF16 || dtype == W8A8_F32; }
+static int elem_vec(int dtype) { return dtype == W8A8_BF16 ? 8 : 4; }
+
+static int quant_common(QuantArgs &a, void *stream) {
+    REQUIRE(check_dtype(a.dtype), W8A8_ERR_BAD_ARG);
+    REQUIRE(a.x && a.q && a.scale && a.M > 0 && a.K > 0 && a.ld >= a.K, W8A8_ERR_BAD_ARG);
+    REQUIRE(a.K % 128 == 0 && a.ld % elem_vec(a.dtype) == 0, W8A8_ERR_ALIGNMENT);
+    REQUIRE(aligned16(a.x) && aligned16(a.q) && (reinterpret_cast<uintptr_t>(a.scale) & 3u) == 0, W8A8_ERR_ALIGNMENT);
+    REQUIRE(a.x2 == nullptr || aligned16(a.x2), W8A8_ERR_ALIGNMENT);
+    REQUIRE(a.y_out == nullptr || aligned16(a.y_out), W8A8_ERR_ALIGNMENT);
+    REQUIRE(a.K <= 24576, W8A8_ERR_UNSUPPORTED);
+    REQUIRE(current_ready_device() >= 0, W8A8_ERR_NOT_INITIALIZED);
+    CUDA_OK(launch_quantize(a, (cudaStream_t)stream), "launch_quantize");
+    return W8A8_OK;
+}
+
+int w8a8_quantize(const void *x, int dtype, int M, int K, int64_t ldx, int8_t *q, float *scale, void *stream) {
+    QuantArgs a{};
+    a.mode = QUANT_PLAIN; a.dtype = dtype; a.x = x; a.ld = ldx; a.M = M; a.K = K; a.q = q; a.scale = scale;
+    return quant_common(a, stream);
+}
+
+int w8a8_quantize_with_max(const void *x, int dtype, const uint32_t *maxima, int M, int K, int64_t ldx, int8_t *q,
+                           float *scale, void *stream) {
+    REQUIRE(maxima, W8A8_ERR_BAD_ARG);
+    QuantArgs a{};
+    a.mode = QUANT_WITH_MAX; a.dtype = dtype; a.x = x; a.ld = ldx; a.M = M; a.K = K; a.q = q; a.scale = scale;
+    a.maxima_in = maxima;
+    return quant_common(a, stream);
+}
+
+int w8a8_rmsnorm_quantize(const void *x, const void *gamma, int dtype, float eps, int M, int K, int64_t ldx, int8_t *q,
+                          float *scale, void *y_out, uint32_t *maxima_reset, void *stream) {
+    REQUIRE(gamma, W8A8_ERR_BAD_ARG);
+    QuantArgs a{};
+    a.mode = QUANT_RMSNORM; a.dtype = dtype; a.x = x; a.x2 = gamma; a.ld = ldx; a.M = M; a.K = K; a.eps = eps;
+    a.q = q; a.scale = scale; a.y_out = y_out; a.maxima_reset = maxima_reset;
+    return quant_common(a, stream);
+}
+
+int w8a8_swiglu_quantize(const void *gate, const void *up, int dtype, int M, int I, int64_t ld, int8_t *q, float *scale,
+                         void *act_out, void *stream) {
+    REQUIRE(up, W8A8_ERR_BAD_ARG);
+    QuantArgs a{};
+    a.mode = QUANT_SWIGLU; a.dtype = dtype; a.x = gate; a.x2 = up; a.ld = ld; a.M = M; a.K = I;
+    a.q = q; a.scale = scale; a.y_out = act_out;
+    return quant_common(a, stream);
+}
+
+int w8a8_swiglu(const void *gate, const void *up, int dtype, int M, int I, int64_t ld, void *act, uint32_t *maxima,
+                void *stream) {
+    REQUIRE(check_dtype(dtype) && gate && up && act && M > 0 && I > 0 && ld >= I, W8A8_ERR_BAD_ARG);
+    REQUIRE(M <= 65535, W8A8_ERR_UNSUPPORTED);
+    REQUIRE(current_ready_device() >= 0, W8A8_ERR_NOT_INITIALIZED);
+    CUDA_OK(launch_swiglu(gate, up, dtype, M, I, ld, act, maxima, (cudaStream_t)stream), "launch_swiglu");
+    return W8A8_OK;
+}
+
+int w8a8_residual(const void *a, const void *b, int dtype, size_t n, void *out, void *stream) {
+    REQUIRE(check_dtype(dtype) && a && b && out && n > 0, W8A8_ERR_BAD_ARG);
+    REQUIRE(aligned16(a) && aligned16(b) && aligned16(out), W8A8_ERR_ALIGNMENT);
+    REQUIRE(current_ready_device() >= 0, W8A8_ERR_NOT_INITIALIZED);
+    CUDA_OK(launch_residual(a, b, dtype, n, out, (cudaStream_t)stream), "launch_residual");
+    return W8A8_OK;
+}
+
+int w8a8_rounding_probe(const float *x, int8_t *out, size_t n, void *stream) {
+    REQUIRE(x && out && n > 0, W8A8_ERR_BAD_ARG);
+    REQUIRE(current_ready_device() >= 0, W8A8_ERR_NOT_INITIALIZED);
+    CUDA_OK(launch_rounding_probe(x, out, n, (cudaStream_t)stream), "launch_rounding_probe");
+    return W8A8_OK;
+}
+
+// ---- projections -----------------------------------------------------------------------
+
+static int pick_variant(int M, int epilogue) {
+    if (M <= 4) return W8A8_VARIANT_GEMV_DP4A;
+    if (M <= 16 && epilogue != EPI_SWIGLU) return W8A8_VARIANT_GEMV_MMA;
+    return W8A8_VARIANT_GEMM_TCGEN05;
+}
+
+static int run_linear(LinearArgs &l, const w8a8_weight *wt, int variant, void *stream) {
+    REQUIRE(current_ready_device() >= 0, W8A8_ERR_NOT_INITIALIZED);
+    if (variant == W8A8_VARIANT_AUTO) variant = pick_variant(l.M, l.epilogue);
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (variant) {
+        case W8A8_VARIANT_NAIVE: CUDA_OK(launch_linear_naive(l, s), "launch_linear_naive"); return W8A8_OK;
+        case W8A8_VARIANT_GEMV_DP4A:
+            REQUIRE(l.M <= 4 && l.K <= 24576, W8A8_ERR_UNSUPPORTED);
+            CUDA_OK(launch_gemv_dp4a(l, s), "launch_gemv_dp4a");
+            return W8A8_OK;
+        case W8A8_VARIANT_GEMV_MMA:
+            REQUIRE(l.M <= 64 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);
+            CUDA_OK(launch_gemv_mma(l, s), "launch_gemv_mma");
+            return W8A8_OK;
+        case W8A8_VARIANT_GEMM_TCGEN05:
+            REQUIRE(wt && l.count == 1 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);
+            CUDA_OK(launch_gemm_tcgen05(l, wt, s), "launch_gemm_tcgen05");
+            return W8A8_OK;
+        default: return W8A8_ERR_BAD_ARG;
+    }
+}
+
+static bool valid_weight(const w8a8_weight *w) { return w && w->magic == kWeightMagic; }
+
+int w8a8_linear_ex(const int8_t *q, const float *a_scale, w8a8_weight_t weight, int M, const void *residual, void *y,
+                   void *combined, int dtype, int variant, void *stream) {
+    REQUIRE(valid_weight(weight) && q && a_scale && M > 0 && check_dtype(dtype), W8A8_ERR_BAD_ARG);
+    REQUIRE((residual == nullptr) == (combined == nullptr), W8A8_ERR_BAD_ARG);
+    REQUIRE(y || combined, W8A8_ERR_BAD_ARG);
+    REQUIRE(aligned16(q) && (y == nullptr || aligned16(y)) && (combined == nullptr || aligned16(combined)) &&
+                (residual == nullptr || aligned16(residual)), W8A8_ERR_ALIGNMENT);
+    LinearArgs l{};
+    l.q = q; l.a_scale = a_scale; l.M = M; l.K = weight->K; l.count = 1;
+    l.w[0] = weight->w; l.ws[0] = weight->w_scale; l.out[0] = y; l.n[0] = weight->N;
+    l.epilogue = residual ? EPI_RESIDUAL : EPI_PLAIN;
+    l.residual = residual; l.combined = combined; l.dtype = dtype;
+    return run_linear(l, weight, variant, stream);
+}
+
+int w8a8_linear(const int8_t *q, const float *a_scale, w8a8_weight_t weight, int M, const void *residual, void *y,
+                void *combined, int dtype, void *stream) {
+    return w8a8_linear_ex(q, a_scale, weight, M, residual, y, combined, dtype, W8A8_VARIANT_AUTO, stream);
+}
+
+int w8a8_linear_grouped(const int8_t *q, const float *a_scale, const w8a8_weight_t *weights, int count, int M,
+                        void *const *outs, int dtype, void *stream) {
+    REQUIRE(q && a_scale && weights && outs && count >= 1 && count <= kMaxGroup && M > 0 && check_dtype(dtype), W8A8_ERR_BAD_ARG);
+    REQUIRE(M <= 16, W8A8_ERR_UNSUPPORTED);
+    REQUIRE(aligned16(q), W8A8_ERR_ALIGNMENT);
+    LinearArgs l{};
+    l.q = q; l.a_scale = a_scale; l.M = M; l.count = count; l.epilogue = EPI_PLAIN; l.dtype = dtype;
+    for (int g = 0; g < count; ++g) {
+        REQUIRE(valid_weight(weights[g]) && outs[g], W8A8_ERR_BAD_ARG);
+        REQUIRE(weights[g]->K == weights[0]->K, W8A8_ERR_BAD_ARG);
+        REQUIRE(aligned16(outs[g]), W8A8_ERR_ALIGNMENT);
+        l.w[g] = weights[g]->w; l.ws[g] = weights[g]->w_scale; l.out[g] = outs[g]; l.n[g] = weights[g]->N;
+    }
+    l.K = weights[0]->K;
+    return run_linear(l, nullptr, W8A8_VARIANT_AUTO, stream);
+}
+
+int w8a8_linear_gate_up_swiglu(const int8_t *q, const float *a_scale, w8a8_weight_t w_gate, w8a8_weight_t w_up, int M,
+                               void *gate_out, void *up_out, void *act, uint32_t *maxima, int dtype, void *stream) {
+    REQUIRE(q && a_scale && valid_weight(w_gate) && valid_weight(w_up) && act && M > 0 && check_dtype(dtype), W8A8_ERR_BAD_ARG);
+    REQUIRE(w_gate->K == w_up->K && w_gate->N == w_up->N, W8A8_ERR_BAD_ARG);
+    REQUIRE(M <= 16, W8A8_ERR_UNSUPPORTED);
+    REQUIRE(aligned16(q) && aligned16(act), W8A8_ERR_ALIGNMENT);
+    LinearArgs l{};
+    l.q = q; l.a_scale = a_scale; l.M = M; l.K = w_gate->K; l.count = 2; l.dtype = dtype;
+    l.w[0] = w_gate->w; l.ws[0] = w_gate->w_scale; l.n[0] = w_gate->N; l.out[0] = gate_out;
+    l.w[1] = w_up->w; l.ws[1] = w_up->w_scale; l.n[1] = w_up->N; l.out[1] = up_out;
+    l.epilogue = EPI_SWIGLU; l.act = act; l.maxima = maxima;
+    if (M <= 4) return run_linear(l, nullptr, W8A8_VARIANT_GEMV_DP4A, stream);
+    // 5..16 tokens: the two projections in one grouped launch, then the element-wise SwiGLU.
+    // The un-fused pair needs gate/up storage; the caller must supply both.
+    REQUIRE(gate_out && up_out, W8A8_ERR_UNSUPPORTED);
+    l.epilogue = EPI_PLAIN;
+    int st = run_linear(l, nullptr, W8A8_VARIANT_GEMV_MMA, stream);
+    if (st != W8A8_OK) return st;
+    return w8a8_swiglu(gate_out, up_out, dtype, M, w_gate->N, w_gate->N, act, maxima, stream);
+}
+
+int w8a8_linear_acc_i32(const int8_t *q, w8a8_weight_t weight, int M, int32_t *acc, int variant, void *stream) {
+    REQUIRE(valid_weight(weight) && q && acc && M > 0, W8A8_ERR_BAD_ARG);
+    REQUIRE(aligned16(q) && aligned16(acc), W8A8_ERR_ALIGNMENT);
+    LinearArgs l{};
+    l.q = q; l.M = M; l.K = weight->K; l.count = 1; l.dtype = W8A8_BF16;
+    l.w[0] = weight->w; l.ws[0] = weight->w_scale; l.n[0] = weight->N;
+    l.epilogue = EPI_ACC; l.acc = acc;
+    return run_linear(l, weight, variant, stream);
+}
+
+}  // extern "C"

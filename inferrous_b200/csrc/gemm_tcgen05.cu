@@ -1,0 +1,446 @@
+// Prefill-regime W8A8 projection on the 5th-generation tensor cores (sm_100a only):
+// TMA-staged 128-byte-swizzled tiles of the int8 activations [M,K] and weights [N,K],
+// tcgen05.mma kind::i8 (s8 x s8 -> s32) accumulating in tensor memory, and a dequantizing
+// epilogue read back with tcgen05.ld.
+//
+// Replaces, from crates/inferrous-qwen3/: linear_large + tma_copy + tma_word
+// (src/kernels.rs:1145-1289,154-171,316-320), linear_tiled (:1038-1141), the tensor-map builder
+// tensor::map (src/tensor.rs:5-39) and the separate `residual` pass of prefill
+// (src/gpu.rs:419-420).  The reference feeds warp-level mma.sync from a single-buffered TMA
+// stage; here one persistent CTA per SM runs three specialised roles:
+//   warp 0      TMA producer: a 4-deep ring of {A 128x128 B, B 256x128 B} stages
+//   warp 1      MMA issuer: one elected lane issues 4 x tcgen05.mma (M128 N256 K32) per stage
+//               into one of two 256-column accumulators, and owns the TMEM allocation
+//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns, (f32(acc)*a_scale[m])*w_scale[n],
+//               bf16, optional residual add, 16-byte stores -- overlapped with the next tile
+// Every wait on an mbarrier is bounded (about two seconds); on expiry the CTA records a code
+// in the device status word, stops issuing work, and leaves through the common exit that
+// waits for its own TMA copies and frees its tensor memory.
+#include "common.cuh"
+#include "internal.h"
+
+#include <cstdio>
+
+namespace w8a8 {
+namespace {
+
+constexpr int BLOCK_M = 128;   // tokens per tile  (UMMA M)
+constexpr int BLOCK_N = 256;   // output channels per tile (UMMA N)
+constexpr int BLOCK_K = 128;   // bytes of K per stage = one 128-byte swizzle atom
+constexpr int UMMA_K = 32;     // bytes of K per tcgen05.mma kind::i8
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BLOCK_M * BLOCK_K;
+constexpr int B_BYTES = BLOCK_N * BLOCK_K;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 512;  // two accumulators of BLOCK_N columns
+constexpr int kThreads = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+struct GemmDev {
+    const float *a_scale;
+    const float *w_scale;
+    int M, N, K;
+    void *y;
+    const void *residual;
+    void *combined;
+    int32_t *acc;
+    uint32_t *status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded wait.  Returns false when the wait was abandoned (this or another role gave up).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t *status,
+                                          uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 0) {
+            if (*abort_flag) return false;
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                if (status && atomicCAS(status, 0u, code) == 0u) status[1] = blockIdx.x;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem], s8 x s8 -> s32.
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, int (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart.  Fields (in 16-byte units): start address bits [0,14),
+// leading byte offset [16,30) = 1, stride byte offset [32,46) = 64, descriptor version
+// [46,48) = 1, layout type [61,64) = 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor for kind::i8: D = s32 (bits [4,6) = 2), A = B = signed int8
+// (bits [7,10) = [10,13) = 1), both K-major (bits 15, 16 = 0), N>>3 at [17,23), M>>4 at [24,29).
+constexpr uint32_t make_idesc(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <class T, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmDev p) {
+    typedef typename T::storage S;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: the swizzle pattern of TMA and of the UMMA descriptor is a function
+    // of the address bits, and both assume an atom-aligned tile base.
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t tiles = (raw + 1023u) & ~1023u;
+    uint8_t *gen_tiles = smem_raw + (tiles - raw);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(gen_tiles + STAGES * STAGE_BYTES);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) acc_full, [2S+2..2S+4) acc_empty
+    const uint32_t bar_base = tiles + STAGES * STAGE_BYTES;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto accf_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto acce_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (p.M + BLOCK_M - 1) / BLOCK_M;
+    const int n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
+    const int num_tiles = m_tiles * n_tiles;
+    const int num_kb = p.K / BLOCK_K;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(accf_bar(a), 1);
+            mbar_init(acce_bar(a), 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    dependency_wait();
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, WAIT_STAGE_EMPTY))) break;
+                    mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+                    const uint32_t a_dst = tiles + stage * STAGE_BYTES;
+                    tma_load_2d(a_dst, &map_a, kb * BLOCK_K, m_blk * BLOCK_M, full_bar(stage));
+                    tma_load_2d(a_dst + A_BYTES, &map_b, kb * BLOCK_K, n_blk * BLOCK_N, full_bar(stage));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // Abandoned: let the copies already in flight land before the CTA may exit.
+                // A stage that was armed completes its phase when its bytes arrive.
+                for (int s = 0; s < STAGES; ++s) {
+                    const unsigned long long t0 = global_ns();
+                    uint32_t par = (s < stage) ? phase : (phase ^ 1u);
+                    while (!mbar_try_wait(full_bar(s), par) && global_ns() - t0 < kWaitLimitNs / 4) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BLOCK_M, BLOCK_N);
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                if (!(ok = mbar_wait(acce_bar(acc), acc_phase ^ 1u, abort_flag, p.status, WAIT_ACC_EMPTY))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BLOCK_N);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, p.status, WAIT_TMA_FULL))) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = tiles + stage * STAGE_BYTES;
+                    const uint64_t a_desc = smem_desc_sw128(a_addr);
+                    const uint64_t b_desc = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        // advancing K inside the swizzle atom = advancing the start address
+                        const uint64_t koff = (uint64_t)((k * UMMA_K) >> 4);
+                        umma_i8(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) umma_commit(accf_bar(acc));  // accumulator complete
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) belong to this warp
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            const int m_blk = tile % m_tiles, n_blk = tile / m_tiles;
+            const int acc = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            ok = mbar_wait(accf_bar(acc), acc_phase, abort_flag, p.status, WAIT_ACC_FULL);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int m = m_blk * BLOCK_M + quarter * 32 + lane;
+            const bool m_ok = m < p.M;
+            const float as = (EPI != EPI_ACC && m_ok) ? p.a_scale[m] : 0.0f;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N);
+#pragma unroll 1
+            for (int c = 0; c < BLOCK_N / 32; ++c) {
+                const int n0 = n_blk * BLOCK_N + c * 32;
+                if (n0 >= p.N) break;  // warp-uniform
+                int v[32];
+                tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);
+                tmem_ld_wait();
+                if (!m_ok) continue;
+                const int64_t o = (int64_t)m * p.N + n0;
+                const bool full = (n0 + 32 <= p.N);
+                if (EPI == EPI_ACC) {
+                    if (full && (p.N & 3) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            *reinterpret_cast<int4 *>(p.acc + o + i) = make_int4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                    } else {
+                        for (int i = 0; i < 32 && n0 + i < p.N; ++i) p.acc[o + i] = v[i];
+                    }
+                    continue;
+                }
+                if (full && (p.N % T::kVec) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += T::kVec) {
+                        float y[T::kVec];
+#pragma unroll
+                        for (int j = 0; j < T::kVec; j += 4) {
+                            const float4 w4 = __ldg(reinterpret_cast<const float4 *>(p.w_scale + n0 + i + j));
+                            y[j + 0] = dequant(v[i + j + 0], as, w4.x);
+                            y[j + 1] = dequant(v[i + j + 1], as, w4.y);
+                            y[j + 2] = dequant(v[i + j + 2], as, w4.z);
+                            y[j + 3] = dequant(v[i + j + 3], as, w4.w);
+                        }
+                        if (p.y) Vec<T>::store(static_cast<S *>(p.y) + o + i, y);
+                        if (EPI == EPI_RESIDUAL) {
+                            float r[T::kVec];
+                            Vec<T>::load(static_cast<const S *>(p.residual) + o + i, r);
+#pragma unroll
+                            for (int j = 0; j < T::kVec; ++j) r[j] = bf16_rne(__fadd_rn(r[j], y[j]));
+                            Vec<T>::store(static_cast<S *>(p.combined) + o + i, r);
+                        }
+                    }
+                } else {
+                    for (int i = 0; i < 32 && n0 + i < p.N; ++i) {
+                        const float y = dequant(v[i], as, p.w_scale[n0 + i]);
+                        if (p.y) T::store(static_cast<S *>(p.y) + o + i, y);
+                        if (EPI == EPI_RESIDUAL) {
+                            const float r = T::load(static_cast<const S *>(p.residual) + o + i);
+                            T::store(static_cast<S *>(p.combined) + o + i, bf16_rne(__fadd_rn(r, y)));
+                        }
+                    }
+                }
+            }
+            // accumulator drained: hand it back to the MMA issuer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce_bar(acc));
+        }
+    }
+
+    // common exit: every role comes here, whether it finished or gave up
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+cudaError_t load_encode() {
+    if (g_encode) return cudaSuccess;
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess) return e;
+    if (q != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    return cudaSuccess;
+}
+
+// [rows, K] int8 row-major, box = 128 bytes of K x box_rows rows, 128-byte swizzle, zero fill
+// outside the matrix (partial last tiles read zeros, which add nothing to the products).
+cudaError_t encode_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows) {
+    cudaError_t e = load_encode();
+    if (e != cudaSuccess) return e;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K};
+    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+template <class T, int EPI> cudaError_t launch_inst(const CUtensorMap &ma, const CUtensorMap &mb, const GemmDev &d, cudaStream_t s) {
+    const int tiles = ((d.M + BLOCK_M - 1) / BLOCK_M) * ((d.N + BLOCK_N - 1) / BLOCK_N);
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    gemm_tcgen05_kernel<T, EPI><<<grid, kThreads, SMEM_BYTES, s>>>(ma, mb, d);
+    return cudaGetLastError();
+}
+template <class T> cudaError_t launch_epi(int epi, const CUtensorMap &ma, const CUtensorMap &mb, const GemmDev &d, cudaStream_t s) {
+    switch (epi) {
+        case EPI_PLAIN: return launch_inst<T, EPI_PLAIN>(ma, mb, d, s);
+        case EPI_RESIDUAL: return launch_inst<T, EPI_RESIDUAL>(ma, mb, d, s);
+        case EPI_ACC: return launch_inst<T, EPI_ACC>(ma, mb, d, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+template <class T, int EPI> cudaError_t set_attr() {
+    return cudaFuncSetAttribute(gemm_tcgen05_kernel<T, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+}
+
+}  // namespace
+
+cudaError_t init_gemm_tcgen05() {
+    cudaError_t e;
+    if ((e = load_encode()) != cudaSuccess) return e;
+    if ((e = set_attr<Bf16, EPI_PLAIN>()) != cudaSuccess) return e;
+    if ((e = set_attr<Bf16, EPI_RESIDUAL>()) != cudaSuccess) return e;
+    if ((e = set_attr<Bf16, EPI_ACC>()) != cudaSuccess) return e;
+    if ((e = set_attr<F32, EPI_PLAIN>()) != cudaSuccess) return e;
+    if ((e = set_attr<F32, EPI_RESIDUAL>()) != cudaSuccess) return e;
+    if ((e = set_attr<F32, EPI_ACC>()) != cudaSuccess) return e;
+    return cudaSuccess;
+}
+
+cudaError_t make_weight_maps(w8a8_weight *wt) {
+    cudaError_t e = encode_map(&wt->map_rows256, wt->w, wt->N, wt->K, BLOCK_N);
+    if (e != cudaSuccess) return e;
+    e = encode_map(&wt->map_rows128, wt->w, wt->N, wt->K, 128);
+    if (e != cudaSuccess) return e;
+    wt->has_maps = true;
+    return cudaSuccess;
+}
+
+cudaError_t launch_gemm_tcgen05(const LinearArgs &l, const w8a8_weight *wt, cudaStream_t s) {
+    if (!wt || !wt->has_maps || l.count != 1) return cudaErrorInvalidValue;
+    // The activation map is encoded on the host per call (a pure function of pointer and shape:
+    // no device access, no allocation) and travels as a kernel parameter, so a captured graph
+    // keeps its own copy.
+    CUtensorMap map_a;
+    cudaError_t e = encode_map(&map_a, l.q, l.M, l.K, BLOCK_M);
+    if (e != cudaSuccess) return e;
+    GemmDev d{};
+    d.a_scale = l.a_scale; d.w_scale = wt->w_scale; d.M = l.M; d.N = wt->N; d.K = l.K;
+    d.y = l.out[0]; d.residual = l.residual; d.combined = l.combined; d.acc = l.acc;
+    d.status = device_status_ptr();
+    return l.dtype == 0 ? launch_epi<Bf16>(l.epilogue, map_a, wt->map_rows256, d, s)
+                        : launch_epi<F32>(l.epilogue, map_a, wt->map_rows256, d, s);
+}
+
+}  // namespace w8a8

@@ -1,0 +1,414 @@
+// Decode-regime W8A8 projections (few tokens, HBM-bound): stream the int8 weights once with
+// coalesced 16-byte loads and do the integer dot products on the fly (sm_100a).
+//
+// Replaces, from crates/inferrous-qwen3/src/kernels.rs:
+//   linear (:808-845), scaled_dot (:270-291), linear_pair / linear_triple (:698-806),
+//   linear_residual (:579-618), linear_swiglu (:621-695), linear_splitk (:935-1034).
+// The reference gives each output channel to one warp that walks the row 4 bytes per lane.
+// Here:
+//   gemv_dp4a  (M <= 4)   one warp per output channel, 16 bytes per lane per load, up to eight
+//                         loads in flight per lane, dp4a against activations parked in shared
+//                         memory, optional split of K over the warps of a CTA (exact: int32).
+//   gemv_mma   (M <= 64)  one CTA per 16 output channels; the eight warps split K; each lane
+//                         streams 16-byte pieces of two weight rows straight into the A
+//                         fragments of mma.sync.m16n8k32.s8 (K is consumed in a permuted order,
+//                         which integer accumulation allows), tokens are the MMA's N side.
+// Weight loads are issued before griddepcontrol.wait: weights are immutable, only the
+// activations depend on the preceding kernel.
+#include "common.cuh"
+#include "internal.h"
+
+namespace w8a8 {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+
+struct GemvDev {
+    const int8_t *q;
+    const float *a_scale;
+    int M, K, count;
+    const int8_t *w[kMaxGroup];
+    const float *ws[kMaxGroup];
+    void *out[kMaxGroup];
+    int n[kMaxGroup];
+    int ntot;  // rows to iterate: sum of n[], or n[0] for the fused gate/up epilogue
+    int ks;    // warps that share one output channel (dp4a kernel): 1, 2, 4 or 8
+    const void *residual;
+    void *combined;
+    void *act;
+    uint32_t *maxima;
+    int32_t *acc;
+};
+
+__device__ __forceinline__ int dp4a_16(const uint4 &w, const uint4 &a, int acc) {
+    acc = __dp4a((int)w.x, (int)a.x, acc);
+    acc = __dp4a((int)w.y, (int)a.y, acc);
+    acc = __dp4a((int)w.z, (int)a.z, acc);
+    acc = __dp4a((int)w.w, (int)a.w, acc);
+    return acc;
+}
+
+// Which matrix of the group a global row index falls in.
+__device__ __forceinline__ void locate(const GemvDev &a, int row, int &g, int &c) {
+    g = 0;
+    c = row;
+    if (a.count > 1 && c >= a.n[0]) {
+        c -= a.n[0];
+        g = 1;
+        if (a.count > 2 && c >= a.n[1]) {
+            c -= a.n[1];
+            g = 2;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// gemv_dp4a: MT tokens (1..4), R = 1 (plain) or 2 (gate+up) weight rows per warp.
+// ---------------------------------------------------------------------------------------
+template <int MT, class T, int EPI>
+__global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const GemvDev a) {
+    typedef typename T::storage S;
+    constexpr int R = (EPI == EPI_SWIGLU) ? 2 : 1;
+    constexpr int U = (EPI == EPI_SWIGLU) ? 4 : 8;  // 16-byte loads in flight per lane per row
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    int8_t *sq = reinterpret_cast<int8_t *>(smem_raw);                         // [MT][K]
+    int *red = reinterpret_cast<int *>(smem_raw + (size_t)MT * a.K);           // [kWarps][R*MT]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = a.K, KS = a.ks;
+    const int rows_per_cta = kWarps / KS;
+    const int row = blockIdx.x * rows_per_cta + warp / KS;  // global row of this warp
+    const int kslot = warp % KS;
+    const bool live = row < a.ntot;
+
+    int g = 0, c = 0;
+    const int8_t *wr[R];
+    if (live) {
+        if (EPI == EPI_SWIGLU) {
+            c = row;
+            wr[0] = a.w[0] + (int64_t)c * K;
+            wr[R - 1] = a.w[1] + (int64_t)c * K;
+        } else {
+            locate(a, row, g, c);
+            wr[0] = a.w[g] + (int64_t)c * K;
+        }
+    }
+
+    int acc[R][MT];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[r][m] = 0;
+
+    const int step = KS * 512;                // bytes of K between this warp's consecutive chunks
+    const int first = kslot * 512 + lane * 16;
+
+    // First batch of weight loads goes out before anything that depends on the predecessor.
+    uint4 wv[R][U];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int off = first + u * step;
+            wv[r][u] = (live && off < K) ? ld_stream_16(wr[r] + off) : make_uint4(0, 0, 0, 0);
+        }
+
+    dependency_wait();
+    // Park the quantized activations (MT rows of K bytes) in shared memory.
+    for (int i = tid * 16; i < MT * K; i += kThreads * 16)
+        *reinterpret_cast<uint4 *>(sq + i) = *reinterpret_cast<const uint4 *>(a.q + i);
+    __syncthreads();
+
+    for (int base = first; base < K; base += U * step) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int off = base + u * step;
+            if (off < K) {
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    const uint4 av = *reinterpret_cast<const uint4 *>(sq + m * K + off);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) acc[r][m] = dp4a_16(wv[r][u], av, acc[r][m]);
+                }
+            }
+        }
+        const int next = base + U * step;
+        if (next - lane * 16 < K) {  // warp-uniform: does any lane still have bytes to fetch
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int off = next + u * step;
+                    wv[r][u] = (live && off < K) ? ld_stream_16(wr[r] + off) : make_uint4(0, 0, 0, 0);
+                }
+        }
+    }
+
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[r][m] = warp_sum_i32(acc[r][m]);
+
+    if (KS > 1) {  // exact int32 reduction over the warps that split K
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int m = 0; m < MT; ++m) red[warp * (R * MT) + r * MT + m] = acc[r][m];
+        }
+        __syncthreads();
+        if (kslot != 0) return;
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                int s = 0;
+                for (int k = 0; k < KS; ++k) s += red[(warp + k) * (R * MT) + r * MT + m];
+                acc[r][m] = s;
+            }
+    }
+    if (!live || lane >= MT) return;
+
+    // lane m finishes token m
+    int sum[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        sum[r] = acc[r][0];
+#pragma unroll
+        for (int m = 1; m < MT; ++m)
+            if (lane == m) sum[r] = acc[r][m];
+    }
+    const int m = lane;
+    const float as = (EPI == EPI_ACC) ? 0.0f : a.a_scale[m];
+    if (EPI == EPI_ACC) {
+        a.acc[(int64_t)m * a.n[0] + c] = sum[0];
+    } else if (EPI == EPI_SWIGLU) {
+        const float gv = dequant(sum[0], as, a.ws[0][c]);
+        const float uv = dequant(sum[R - 1], as, a.ws[1][c]);
+        const float v = swiglu_value(gv, uv);
+        const int64_t o = (int64_t)m * a.n[0] + c;
+        if (a.out[0]) T::store(static_cast<S *>(a.out[0]) + o, gv);
+        if (a.out[1]) T::store(static_cast<S *>(a.out[1]) + o, uv);
+        T::store(static_cast<S *>(a.act) + o, v);
+        if (a.maxima) atomicMax(a.maxima + m, absmax_key(v));
+    } else {
+        const float y = dequant(sum[0], as, a.ws[g][c]);
+        const int64_t o = (int64_t)m * a.n[g] + c;
+        if (a.out[g]) T::store(static_cast<S *>(a.out[g]) + o, y);
+        if (EPI == EPI_RESIDUAL) {
+            const float res = T::load(static_cast<const S *>(a.residual) + o);
+            T::store(static_cast<S *>(a.combined) + o, bf16_rne(__fadd_rn(res, y)));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// gemv_mma: NT tiles of 8 tokens; one CTA per block of 16 output channels; warps split K.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT, class T, int EPI>
+__global__ void __launch_bounds__(kThreads) gemv_mma_kernel(const GemvDev a) {
+    typedef typename T::storage S;
+    __shared__ int red[kWarps][NT * 4 * 32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gq = lane >> 2, t = lane & 3;
+    const int K = a.K;
+
+    // row block -> matrix of the group (blocks never straddle matrices: each matrix is padded
+    // to whole 16-row blocks by the launcher's block count)
+    int blk = blockIdx.x, g = 0;
+    while (g + 1 < a.count && blk >= (a.n[g] + 15) / 16) { blk -= (a.n[g] + 15) / 16; ++g; }
+    const int n = a.n[g];
+    const int c0 = blk * 16;
+    const int r_lo = min(c0 + gq, n - 1), r_hi = min(c0 + gq + 8, n - 1);  // clamped: extra rows are discarded
+    const int8_t *w_lo = a.w[g] + (int64_t)r_lo * K + t * 16;
+    const int8_t *w_hi = a.w[g] + (int64_t)r_hi * K + t * 16;
+
+    int acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0;
+
+    // This warp owns the 128-byte K steps s with s % kWarps == warp; two steps are in flight,
+    // held in two explicitly named register buffers.
+    const int nsteps = K / 128;
+    uint4 lo0[2], hi0[2], lo1[2], hi1[2];
+    auto load_w = [&](int s, uint4(&lo)[2], uint4(&hi)[2]) {
+        if (s < nsteps) {
+            const int k0 = s * 128;
+            lo[0] = ld_stream_16(w_lo + k0);
+            lo[1] = ld_stream_16(w_lo + k0 + 64);
+            hi[0] = ld_stream_16(w_hi + k0);
+            hi[1] = ld_stream_16(w_hi + k0 + 64);
+        }
+    };
+    load_w(warp, lo0, hi0);
+    load_w(warp + kWarps, lo1, hi1);
+
+    dependency_wait();
+
+    const int8_t *qb = a.q + t * 16;
+    auto compute = [&](int s, const uint4(&lo)[2], const uint4(&hi)[2]) {
+        const int k0 = s * 128;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 r = lo[h], v = hi[h];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int tok = j * 8 + gq;
+                uint4 p = make_uint4(0, 0, 0, 0);
+                if (tok < a.M) p = *reinterpret_cast<const uint4 *>(qb + (int64_t)tok * K + k0 + h * 64);
+                mma_s8(acc[j], r.x, v.x, r.y, v.y, p.x, p.y);
+                mma_s8(acc[j], r.z, v.z, r.w, v.w, p.z, p.w);
+            }
+        }
+    };
+    for (int s = warp; s < nsteps; s += 2 * kWarps) {
+        compute(s, lo0, hi0);
+        load_w(s + 2 * kWarps, lo0, hi0);
+        if (s + kWarps < nsteps) {
+            compute(s + kWarps, lo1, hi1);
+            load_w(s + 3 * kWarps, lo1, hi1);
+        }
+    }
+
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) red[warp][(j * 4 + i) * 32 + lane] = acc[j][i];
+    __syncthreads();
+
+    for (int idx = tid; idx < NT * 128; idx += kThreads) {
+        int sum = 0;
+#pragma unroll
+        for (int k = 0; k < kWarps; ++k) sum += red[k][idx];
+        const int l = idx & 31, reg = (idx >> 5) & 3, j = idx >> 7;
+        const int row = c0 + (l >> 2) + 8 * (reg >> 1);
+        const int tok = j * 8 + 2 * (l & 3) + (reg & 1);
+        if (row >= n || tok >= a.M) continue;
+        const int64_t o = (int64_t)tok * n + row;
+        if (EPI == EPI_ACC) {
+            a.acc[o] = sum;
+            continue;
+        }
+        const float y = dequant(sum, a.a_scale[tok], a.ws[g][row]);
+        if (a.out[g]) T::store(static_cast<S *>(a.out[g]) + o, y);
+        if (EPI == EPI_RESIDUAL) {
+            const float res = T::load(static_cast<const S *>(a.residual) + o);
+            T::store(static_cast<S *>(a.combined) + o, bf16_rne(__fadd_rn(res, y)));
+        }
+    }
+}
+
+GemvDev make_dev(const LinearArgs &l) {
+    GemvDev d{};
+    d.q = l.q; d.a_scale = l.a_scale; d.M = l.M; d.K = l.K; d.count = l.count;
+    int ntot = 0;
+    for (int g = 0; g < kMaxGroup; ++g) {
+        d.w[g] = l.w[g]; d.ws[g] = l.ws[g]; d.out[g] = l.out[g]; d.n[g] = l.n[g];
+        if (g < l.count) ntot += l.n[g];
+    }
+    d.ntot = (l.epilogue == EPI_SWIGLU) ? l.n[0] : ntot;
+    d.ks = 1;
+    d.residual = l.residual; d.combined = l.combined; d.act = l.act; d.maxima = l.maxima; d.acc = l.acc;
+    return d;
+}
+
+constexpr int kMaxDp4aSmem = 4 * 24576 + 1024;
+
+template <int MT, class T, int EPI> cudaError_t launch_dp4a_inst(const GemvDev &d, cudaStream_t s) {
+    const int rows_per_cta = kWarps / d.ks;
+    const unsigned grid = (unsigned)((d.ntot + rows_per_cta - 1) / rows_per_cta);
+    const size_t smem = (size_t)MT * d.K + kWarps * 2 * MT * sizeof(int);
+    gemv_dp4a_kernel<MT, T, EPI><<<grid, kThreads, smem, s>>>(d);
+    return cudaGetLastError();
+}
+template <int MT, class T> cudaError_t launch_dp4a_epi(int epi, const GemvDev &d, cudaStream_t s) {
+    switch (epi) {
+        case EPI_PLAIN: return launch_dp4a_inst<MT, T, EPI_PLAIN>(d, s);
+        case EPI_RESIDUAL: return launch_dp4a_inst<MT, T, EPI_RESIDUAL>(d, s);
+        case EPI_SWIGLU: return launch_dp4a_inst<MT, T, EPI_SWIGLU>(d, s);
+        case EPI_ACC: return launch_dp4a_inst<MT, T, EPI_ACC>(d, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+template <class T> cudaError_t launch_dp4a_m(int M, int epi, const GemvDev &d, cudaStream_t s) {
+    switch (M) {
+        case 1: return launch_dp4a_epi<1, T>(epi, d, s);
+        case 2: return launch_dp4a_epi<2, T>(epi, d, s);
+        case 3: return launch_dp4a_epi<3, T>(epi, d, s);
+        case 4: return launch_dp4a_epi<4, T>(epi, d, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+template <int NT, class T, int EPI> cudaError_t launch_mma_inst(const GemvDev &d, cudaStream_t s) {
+    unsigned grid = 0;
+    for (int g = 0; g < d.count; ++g) grid += (unsigned)((d.n[g] + 15) / 16);
+    gemv_mma_kernel<NT, T, EPI><<<grid, kThreads, 0, s>>>(d);
+    return cudaGetLastError();
+}
+template <int NT, class T> cudaError_t launch_mma_epi(int epi, const GemvDev &d, cudaStream_t s) {
+    switch (epi) {
+        case EPI_PLAIN: return launch_mma_inst<NT, T, EPI_PLAIN>(d, s);
+        case EPI_RESIDUAL: return launch_mma_inst<NT, T, EPI_RESIDUAL>(d, s);
+        case EPI_ACC: return launch_mma_inst<NT, T, EPI_ACC>(d, s);
+        default: return cudaErrorInvalidValue;
+    }
+}
+template <class T> cudaError_t launch_mma_m(int M, int epi, const GemvDev &d, cudaStream_t s) {
+    if (M <= 8) return launch_mma_epi<1, T>(epi, d, s);
+    if (M <= 16) return launch_mma_epi<2, T>(epi, d, s);
+    if (M <= 32) return launch_mma_epi<4, T>(epi, d, s);
+    if (M <= 64) return launch_mma_epi<8, T>(epi, d, s);
+    return cudaErrorInvalidValue;
+}
+
+template <int MT, class T> cudaError_t set_attr_dp4a() {
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<MT, T, EPI_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDp4aSmem))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<MT, T, EPI_RESIDUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDp4aSmem))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<MT, T, EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDp4aSmem))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<MT, T, EPI_ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDp4aSmem))) return e;
+    return cudaSuccess;
+}
+
+}  // namespace
+
+cudaError_t init_gemv() {
+    cudaError_t e;
+#define W8A8_SET(MT)                                               \
+    if ((e = set_attr_dp4a<MT, Bf16>()) != cudaSuccess) return e;  \
+    if ((e = set_attr_dp4a<MT, F32>()) != cudaSuccess) return e;
+    W8A8_SET(1) W8A8_SET(2) W8A8_SET(3) W8A8_SET(4)
+#undef W8A8_SET
+    return cudaSuccess;
+}
+
+cudaError_t launch_gemv_dp4a(const LinearArgs &l, cudaStream_t s) {
+    if (l.M < 1 || l.M > 4 || l.K > 24576) return cudaErrorInvalidValue;
+    GemvDev d = make_dev(l);
+    // Split K over the warps of a CTA while there are too few output channels to fill the GPU.
+    const int want = sm_count() * 16;
+    int ks = 1;
+    while (ks < kWarps && d.ntot * ks < want && l.K / (ks * 2) >= 512) ks *= 2;
+    d.ks = ks;
+    return l.dtype == 0 ? launch_dp4a_m<Bf16>(l.M, l.epilogue, d, s) : launch_dp4a_m<F32>(l.M, l.epilogue, d, s);
+}
+
+cudaError_t launch_gemv_mma(const LinearArgs &l, cudaStream_t s) {
+    if (l.M < 1 || l.M > 64 || l.epilogue == EPI_SWIGLU) return cudaErrorInvalidValue;
+    GemvDev d = make_dev(l);
+    return l.dtype == 0 ? launch_mma_m<Bf16>(l.M, l.epilogue, d, s) : launch_mma_m<F32>(l.M, l.epilogue, d, s);
+}
+
+}  // namespace w8a8

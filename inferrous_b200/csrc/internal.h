@@ -1,0 +1,80 @@
+// Host-side launcher interface between the C ABI (capi.cu) and the kernel files.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+struct w8a8_weight {
+    uint32_t magic;
+    int device;
+    const int8_t *w;
+    const float *w_scale;
+    int N, K;
+    CUtensorMap map_rows256;  // [N,K] uint8, box 128 bytes x 256 rows, SWIZZLE_128B
+    CUtensorMap map_rows128;  // same with a 128-row box
+    bool has_maps;
+};
+
+namespace w8a8 {
+
+constexpr uint32_t kWeightMagic = 0x57384138u;  // "W8A8"
+constexpr int kMaxGroup = 3;
+
+enum QuantMode { QUANT_PLAIN = 0, QUANT_WITH_MAX = 1, QUANT_RMSNORM = 2, QUANT_SWIGLU = 3 };
+
+struct QuantArgs {
+    int mode;
+    int dtype;
+    const void *x;      // plain / with_max / rmsnorm input; swiglu gate
+    const void *x2;     // rmsnorm gamma; swiglu up
+    int64_t ld;         // row stride of x (and x2 for swiglu), elements
+    int M, K;           // K = quantized row width
+    float eps;
+    const uint32_t *maxima_in;  // with_max
+    int8_t *q;
+    float *scale;
+    void *y_out;             // optional pre-quant bf16 row (rmsnorm y / swiglu act), row stride K
+    uint32_t *maxima_reset;  // optional
+};
+cudaError_t launch_quantize(const QuantArgs &a, cudaStream_t s);
+cudaError_t launch_swiglu(const void *gate, const void *up, int dtype, int M, int I, int64_t ld, void *act,
+                          uint32_t *maxima, cudaStream_t s);
+cudaError_t launch_residual(const void *a, const void *b, int dtype, size_t n, void *out, cudaStream_t s);
+cudaError_t launch_rounding_probe(const float *x, int8_t *out, size_t n, cudaStream_t s);
+
+enum Epilogue { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_ACC = 3 };
+
+struct LinearArgs {
+    const int8_t *q;
+    const float *a_scale;
+    int M, K;
+    int count;                    // matrices in the group (1 for a plain projection; 2 for gate/up)
+    const int8_t *w[kMaxGroup];
+    const float *ws[kMaxGroup];
+    void *out[kMaxGroup];         // y per matrix (may be null for EPI_RESIDUAL / EPI_SWIGLU)
+    int n[kMaxGroup];
+    int epilogue;
+    const void *residual;         // EPI_RESIDUAL
+    void *combined;               // EPI_RESIDUAL
+    void *act;                    // EPI_SWIGLU
+    uint32_t *maxima;             // EPI_SWIGLU
+    int32_t *acc;                 // EPI_ACC: raw accumulators [M, n[0]]
+    int dtype;
+};
+cudaError_t launch_linear_naive(const LinearArgs &a, cudaStream_t s);
+cudaError_t launch_gemv_dp4a(const LinearArgs &a, cudaStream_t s);   // M <= 4
+cudaError_t launch_gemv_mma(const LinearArgs &a, cudaStream_t s);    // M <= 64
+// tcgen05 path: one matrix, EPI_PLAIN / EPI_RESIDUAL / EPI_ACC
+cudaError_t launch_gemm_tcgen05(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);
+cudaError_t init_gemm_tcgen05();
+cudaError_t make_weight_maps(w8a8_weight *wt);  // TMA descriptors of the [N,K] matrix
+cudaError_t init_gemv();
+cudaError_t init_quantize();
+
+// Device status word (bounded waits report here instead of trapping).
+uint32_t *device_status_ptr();  // device address of the 2-word status block of the current device
+cudaError_t read_device_status(cudaStream_t s, uint32_t out[2]);
+
+int sm_count();
+
+}  // namespace w8a8

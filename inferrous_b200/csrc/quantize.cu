@@ -1,0 +1,322 @@
+// Dynamic per-token INT8 activation quantizers, standalone and fused with the
+// preceding RMSNorm or SwiGLU (sm_100a).
+//
+// What the reference computes (crates/inferrous-qwen3/):
+//   quantize            src/kernels.rs:415-452   m = max(1e-8, max|x|); s = m/127; q = rne(clamp(x/s))
+//   quantize_with_max   src/kernels.rs:455-475   same with m supplied by the producer
+//   norm_quantize       src/kernels.rs:479-576   y = bf16((x*rsqrt(mean(x^2)+eps))*gain); quantize(y)
+//   swiglu              src/kernels.rs:2172-2190 act = bf16((g/(1+exp(-g)))*u) (+ absmax publish)
+//   residual            src/kernels.rs:2163-2170 bf16(a+b)
+//
+// Design here: one 256-thread CTA per token row, 128-bit global loads, the row parked in
+// shared memory as f32 between the passes (so the row is read from HBM exactly once),
+// warp-level redux for the absmax, one IEEE division per element, 4/8 int8 codes packed per
+// store.  The sum of squares follows the reference's fixed tree (256 strided partials, then
+// distances 128..1) so that the bf16 norm row can match the reference bit for bit wherever
+// rsqrt.approx does.
+#include "common.cuh"
+#include "internal.h"
+
+namespace w8a8 {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct QuantDev {
+    const void *x;
+    const void *x2;
+    int64_t ld;
+    int M, K;
+    float eps;
+    const uint32_t *maxima_in;
+    int8_t *q;
+    float *scale;
+    void *y_out;
+    uint32_t *maxima_reset;
+};
+
+template <int N> __device__ __forceinline__ void store_codes(int8_t *dst, const int (&c)[N]);
+template <> __device__ __forceinline__ void store_codes<8>(int8_t *dst, const int (&c)[8]) {
+    uint2 p;
+    p.x = (c[0] & 0xff) | ((c[1] & 0xff) << 8) | ((c[2] & 0xff) << 16) | ((uint32_t)c[3] << 24);
+    p.y = (c[4] & 0xff) | ((c[5] & 0xff) << 8) | ((c[6] & 0xff) << 16) | ((uint32_t)c[7] << 24);
+    *reinterpret_cast<uint2 *>(dst) = p;
+}
+template <> __device__ __forceinline__ void store_codes<4>(int8_t *dst, const int (&c)[4]) {
+    *reinterpret_cast<uint32_t *>(dst) =
+        (c[0] & 0xff) | ((c[1] & 0xff) << 8) | ((c[2] & 0xff) << 16) | ((uint32_t)c[3] << 24);
+}
+
+// Block-wide maximum of non-negative floats (compared as unsigned bit patterns).
+__device__ __forceinline__ float block_max(float m, uint32_t *slots, int tid) {
+    uint32_t k = warp_max_u32(__float_as_uint(m));
+    if ((tid & 31) == 0) slots[tid >> 5] = k;
+    __syncthreads();
+    uint32_t v = slots[tid & 7];  // 8 warps
+    v = warp_max_u32(v);
+    __syncthreads();  // slots may be reused by the next row
+    return __uint_as_float(v);
+}
+
+template <class T, int MODE>
+__global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const QuantDev a) {
+    typedef typename T::storage S;
+    constexpr int V = T::kVec;
+    extern __shared__ __align__(16) float smem[];
+    float *row = smem;                 // K floats
+    float *red = smem + a.K;           // 256 floats
+    uint32_t *slots = reinterpret_cast<uint32_t *>(red + 256);  // 8 words
+    const int tid = threadIdx.x;
+    const int K = a.K;
+
+    dependency_wait();
+
+    for (int r = blockIdx.x; r < a.M; r += gridDim.x) {
+        const S *xr = static_cast<const S *>(a.x) + (int64_t)r * a.ld;
+        int8_t *qr = a.q + (int64_t)r * K;
+
+        if (MODE == QUANT_WITH_MAX) {
+            const float s = __fdiv_rn(__uint_as_float(a.maxima_in[r]), 127.0f);
+            if (tid == 0) a.scale[r] = s;
+            for (int j = tid * V; j < K; j += kThreads * V) {
+                float v[V];
+                Vec<T>::load(xr + j, v);
+                int c[V];
+#pragma unroll
+                for (int i = 0; i < V; ++i) c[i] = round_i8(__fdiv_rn(v[i], s));
+                store_codes<V>(qr + j, c);
+            }
+            continue;
+        }
+
+        float m = 1e-8f;
+        // pass 1: HBM -> registers -> shared (and the element-wise producer, if fused)
+        for (int j = tid * V; j < K; j += kThreads * V) {
+            float v[V];
+            Vec<T>::load(xr + j, v);
+            if (MODE == QUANT_SWIGLU) {
+                const S *ur = static_cast<const S *>(a.x2) + (int64_t)r * a.ld;
+                float u[V];
+                Vec<T>::load(ur + j, u);
+#pragma unroll
+                for (int i = 0; i < V; ++i) v[i] = swiglu_value(v[i], u[i]);
+                if (a.y_out) Vec<T>::store(static_cast<S *>(a.y_out) + (int64_t)r * K + j, v);
+            }
+            if (MODE != QUANT_RMSNORM) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) m = fmaxf(m, fabsf(v[i]));  // fmaxf drops a NaN operand
+            }
+#pragma unroll
+            for (int i = 0; i < V; i += 4)
+                *reinterpret_cast<float4 *>(row + j + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+
+        if (MODE == QUANT_RMSNORM) {
+            __syncthreads();
+            // 256 strided partial sums, each added in index order (src/kernels.rs:508-519)
+            float s = 0.0f;
+            for (int j = tid; j < K; j += kThreads) s = __fadd_rn(s, __fmul_rn(row[j], row[j]));
+            red[tid] = s;
+            __syncthreads();
+            if (tid < 32) {
+                // distances 128, 64, 32 then the warp distances 16..1 (src/kernels.rs:521-545)
+                float t = __fadd_rn(__fadd_rn(__fadd_rn(red[tid], red[tid + 128]), __fadd_rn(red[tid + 64], red[tid + 192])),
+                                    __fadd_rn(__fadd_rn(red[tid + 32], red[tid + 160]), __fadd_rn(red[tid + 96], red[tid + 224])));
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, d));
+                if (tid == 0) red[0] = t;
+            }
+            __syncthreads();
+            const float inv = rsqrt_approx(__fadd_rn(__fdiv_rn(red[0], (float)K), a.eps));
+            const S *gr = static_cast<const S *>(a.x2);
+            for (int j = tid * V; j < K; j += kThreads * V) {
+                float g[V], y[V];
+                Vec<T>::load(gr + j, g);
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    y[i] = bf16_rne(__fmul_rn(__fmul_rn(row[j + i], inv), g[i]));
+                    m = fmaxf(m, fabsf(y[i]));
+                    row[j + i] = y[i];
+                }
+                if (a.y_out) Vec<T>::store(static_cast<S *>(a.y_out) + (int64_t)r * K + j, y);
+            }
+        }
+
+        const float s = __fdiv_rn(block_max(m, slots, tid), 127.0f);
+        if (tid == 0) {
+            a.scale[r] = s;
+            if (a.maxima_reset) a.maxima_reset[r] = __float_as_uint(1e-8f);
+        }
+        // last pass: each thread re-reads exactly the elements it parked
+        for (int j = tid * V; j < K; j += kThreads * V) {
+            int c[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) c[i] = round_i8(__fdiv_rn(row[j + i], s));
+            store_codes<V>(qr + j, c);
+        }
+        __syncthreads();  // row[] and red[] are reused by the next row of this CTA
+    }
+}
+
+template <class T>
+__global__ void __launch_bounds__(kThreads) swiglu_kernel(const typename T::storage *gate, const typename T::storage *up,
+                                                          int I, int64_t ld, typename T::storage *act, uint32_t *maxima) {
+    constexpr int V = T::kVec;
+    __shared__ uint32_t slots[8];
+    dependency_wait();
+    const int r = blockIdx.y;
+    const int j = (blockIdx.x * kThreads + threadIdx.x) * V;
+    uint32_t key = 0;
+    if (j < I) {
+        float g[V], u[V];
+        Vec<T>::load(gate + (int64_t)r * ld + j, g);
+        Vec<T>::load(up + (int64_t)r * ld + j, u);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            g[i] = swiglu_value(g[i], u[i]);
+            key = max(key, absmax_key(g[i]));
+        }
+        Vec<T>::store(act + (int64_t)r * I + j, g);
+    }
+    if (maxima) {
+        key = warp_max_u32(key);
+        if ((threadIdx.x & 31) == 0) slots[threadIdx.x >> 5] = key;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            key = warp_max_u32(slots[threadIdx.x & 7]);
+            if (threadIdx.x == 0) atomicMax(maxima + r, key);
+        }
+    }
+}
+
+// Any row width and stride (no vector alignment assumed): one element per thread.
+template <class T>
+__global__ void __launch_bounds__(kThreads) swiglu_scalar_kernel(const typename T::storage *gate, const typename T::storage *up,
+                                                                 int I, int64_t ld, typename T::storage *act, uint32_t *maxima) {
+    __shared__ uint32_t slots[8];
+    dependency_wait();
+    const int r = blockIdx.y;
+    const int j = blockIdx.x * kThreads + threadIdx.x;
+    uint32_t key = 0;
+    if (j < I) {
+        const float v = swiglu_value(T::load(gate + (int64_t)r * ld + j), T::load(up + (int64_t)r * ld + j));
+        key = absmax_key(v);
+        T::store(act + (int64_t)r * I + j, v);
+    }
+    if (maxima) {
+        key = warp_max_u32(key);
+        if ((threadIdx.x & 31) == 0) slots[threadIdx.x >> 5] = key;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            key = warp_max_u32(slots[threadIdx.x & 7]);
+            if (threadIdx.x == 0) atomicMax(maxima + r, key);
+        }
+    }
+}
+
+template <class T>
+__global__ void __launch_bounds__(kThreads) residual_kernel(const typename T::storage *a, const typename T::storage *b,
+                                                            size_t n, typename T::storage *out) {
+    constexpr int V = T::kVec;
+    dependency_wait();
+    size_t i = ((size_t)blockIdx.x * kThreads + threadIdx.x) * V;
+    if (i + V <= n) {
+        float x[V], y[V];
+        Vec<T>::load(a + i, x);
+        Vec<T>::load(b + i, y);
+#pragma unroll
+        for (int k = 0; k < V; ++k) x[k] = bf16_rne(__fadd_rn(x[k], y[k]));
+        Vec<T>::store(out + i, x);
+    } else {
+        for (; i < n; ++i) T::store(out + i, bf16_rne(__fadd_rn(T::load(a + i), T::load(b + i))));
+    }
+}
+
+__global__ void rounding_probe_kernel(const float *x, int8_t *out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = (int8_t)round_i8(x[i]);
+}
+
+constexpr int kMaxQuantSmem = 100 * 1024;
+inline size_t quant_smem(int K) { return (size_t)(K + 256 + 8) * sizeof(float); }
+
+template <class T, int MODE> cudaError_t launch_q(const QuantDev &d, cudaStream_t s) {
+    int grid = d.M;
+    quantize_rows_kernel<T, MODE><<<grid, kThreads, quant_smem(d.K), s>>>(d);
+    return cudaGetLastError();
+}
+template <class T, int MODE> cudaError_t set_attr() {
+    return cudaFuncSetAttribute(quantize_rows_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxQuantSmem);
+}
+
+}  // namespace
+
+cudaError_t init_quantize() {
+    cudaError_t e;
+#define W8A8_SET(T)                                                   \
+    if ((e = set_attr<T, QUANT_PLAIN>()) != cudaSuccess) return e;    \
+    if ((e = set_attr<T, QUANT_WITH_MAX>()) != cudaSuccess) return e; \
+    if ((e = set_attr<T, QUANT_RMSNORM>()) != cudaSuccess) return e;  \
+    if ((e = set_attr<T, QUANT_SWIGLU>()) != cudaSuccess) return e;
+    W8A8_SET(Bf16)
+    W8A8_SET(F32)
+#undef W8A8_SET
+    return cudaSuccess;
+}
+
+cudaError_t launch_quantize(const QuantArgs &a, cudaStream_t s) {
+    if (quant_smem(a.K) > (size_t)kMaxQuantSmem) return cudaErrorInvalidValue;
+    QuantDev d{a.x, a.x2, a.ld, a.M, a.K, a.eps, a.maxima_in, a.q, a.scale, a.y_out, a.maxima_reset};
+#define W8A8_DISPATCH(T)                                                           \
+    switch (a.mode) {                                                              \
+        case QUANT_PLAIN: return launch_q<T, QUANT_PLAIN>(d, s);                   \
+        case QUANT_WITH_MAX: return launch_q<T, QUANT_WITH_MAX>(d, s);             \
+        case QUANT_RMSNORM: return launch_q<T, QUANT_RMSNORM>(d, s);               \
+        case QUANT_SWIGLU: return launch_q<T, QUANT_SWIGLU>(d, s);                 \
+        default: return cudaErrorInvalidValue;                                     \
+    }
+    if (a.dtype == 0) { W8A8_DISPATCH(Bf16) }
+    W8A8_DISPATCH(F32)
+#undef W8A8_DISPATCH
+}
+
+cudaError_t launch_swiglu(const void *gate, const void *up, int dtype, int M, int I, int64_t ld, void *act,
+                          uint32_t *maxima, cudaStream_t s) {
+    const int vec = dtype == 0 ? 8 : 4;
+    const bool aligned = (I % vec == 0) && (ld % vec == 0) && ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) |
+                                                                 reinterpret_cast<uintptr_t>(act)) & 15u) == 0;
+    if (!aligned) {
+        dim3 grid((I + kThreads - 1) / kThreads, M);
+        if (dtype == 0)
+            swiglu_scalar_kernel<Bf16><<<grid, kThreads, 0, s>>>((const uint16_t *)gate, (const uint16_t *)up, I, ld, (uint16_t *)act, maxima);
+        else
+            swiglu_scalar_kernel<F32><<<grid, kThreads, 0, s>>>((const float *)gate, (const float *)up, I, ld, (float *)act, maxima);
+        return cudaGetLastError();
+    }
+    if (dtype == 0) {
+        dim3 grid((I + kThreads * 8 - 1) / (kThreads * 8), M);
+        swiglu_kernel<Bf16><<<grid, kThreads, 0, s>>>((const uint16_t *)gate, (const uint16_t *)up, I, ld, (uint16_t *)act, maxima);
+    } else {
+        dim3 grid((I + kThreads * 4 - 1) / (kThreads * 4), M);
+        swiglu_kernel<F32><<<grid, kThreads, 0, s>>>((const float *)gate, (const float *)up, I, ld, (float *)act, maxima);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_residual(const void *a, const void *b, int dtype, size_t n, void *out, cudaStream_t s) {
+    if (dtype == 0) {
+        size_t blocks = (n + kThreads * 8 - 1) / (kThreads * 8);
+        residual_kernel<Bf16><<<(unsigned)blocks, kThreads, 0, s>>>((const uint16_t *)a, (const uint16_t *)b, n, (uint16_t *)out);
+    } else {
+        size_t blocks = (n + kThreads * 4 - 1) / (kThreads * 4);
+        residual_kernel<F32><<<(unsigned)blocks, kThreads, 0, s>>>((const float *)a, (const float *)b, n, (float *)out);
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rounding_probe(const float *x, int8_t *out, size_t n, cudaStream_t s) {
+    rounding_probe_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, out, n);
+    return cudaGetLastError();
+}
+
+}  // namespace w8a8

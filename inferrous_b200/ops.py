@@ -1,0 +1,181 @@
+"""Host-side mirror of the reference host runtime's W8A8 operator methods, over the C ABI.
+
+Names and argument meaning follow `GpuModel` in crates/inferrous-qwen3/src/gpu.rs:
+`norm_quantize` (:340), `linear_residual` (:364), `quantize` (:424), `linear_quantized`
+(:450), `residual` (:510), and the direct launches of `linear_triple` (:571-590),
+`linear_swiglu` (:730-745) and `swiglu` (:770-777); `Matrix` is gpu::Matrix (:43-49).
+Like the reference's methods, every call takes caller-owned OUTPUT buffers and queues work
+on one stream; nothing here allocates, synchronises or falls back to the CPU.
+
+torch supplies device memory and the stream.  Activation tensors are torch.bfloat16
+(2-byte storage) or torch.float32 (the reference's carrier for bf16-valued activations).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import capi
+
+_initialised: set[int] = set()
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return capi.BF16
+    if t.dtype == torch.float32:
+        return capi.F32
+    raise TypeError(f"activation dtype must be bfloat16 or float32, got {t.dtype}")
+
+
+def _ptr(t: torch.Tensor | None):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("w8a8 ops take CUDA tensors only (there is no CPU path)")
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def init(device: int | None = None) -> None:
+    """`device::load(&ctx)` (src/gpu.rs:250): load kernels for a device, once, before capture."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("inferrous_b200 needs a CUDA device (sm_100a); there is no CPU fallback")
+    dev = torch.cuda.current_device() if device is None else device
+    if dev not in _initialised:
+        capi.check(capi.load().w8a8_init(dev), "w8a8_init")
+        _initialised.add(dev)
+
+
+def device_status() -> tuple[int, int]:
+    """(status, detail) of the device-side bounded waits; synchronises the current stream."""
+    detail = C.c_uint32(0)
+    st = capi.load().w8a8_device_status(_stream(), C.byref(detail))
+    return st, detail.value
+
+
+class Matrix:
+    """gpu::Matrix {w, map, scale, k, n} (src/gpu.rs:43-49): an immutable int8 weight [N,K] with
+    one f32 scale per output channel.  The TMA descriptor lives inside the C handle."""
+
+    def __init__(self, w: torch.Tensor, scale: torch.Tensor):
+        assert w.dtype == torch.int8 and w.dim() == 2 and w.is_contiguous() and w.is_cuda
+        assert scale.dtype == torch.float32 and scale.numel() == w.shape[0] and scale.is_contiguous()
+        init(w.device.index)
+        self.w, self.scale = w, scale
+        self.n, self.k = w.shape
+        h = C.c_void_p()
+        capi.check(capi.load().w8a8_weight_create(_ptr(w), _ptr(scale), self.n, self.k, C.byref(h)), "w8a8_weight_create")
+        self.handle = h
+
+    def __del__(self):
+        h = getattr(self, "handle", None)
+        if h:
+            capi.load().w8a8_weight_destroy(h)
+            self.handle = None
+
+
+class Workspace:
+    """The hot path's share of gpu::Workspace (src/gpu.rs:76-143): int8 scratch for the two
+    activation widths, per-row scales and SwiGLU maxima."""
+
+    def __init__(self, rows: int, device, hidden: int = 4096, intermediate: int = 12288):
+        self.quant4 = torch.empty((rows, hidden), dtype=torch.int8, device=device)
+        self.quant12 = torch.empty((rows, intermediate), dtype=torch.int8, device=device)
+        self.scales = torch.empty((rows,), dtype=torch.float32, device=device)
+        self.maxima = torch.full((rows,), 0x322BCC77, dtype=torch.int32, device=device)  # 1e-8f bits
+
+
+def quantize(x: torch.Tensor, q: torch.Tensor, scale: torch.Tensor) -> None:
+    """GpuModel::quantize (src/gpu.rs:424-449) -> kernel `quantize` (src/kernels.rs:415-452)."""
+    M, K = x.shape
+    capi.check(capi.load().w8a8_quantize(_ptr(x), _dtype_code(x), M, K, x.stride(0), _ptr(q), _ptr(scale), _stream()),
+               "w8a8_quantize")
+
+
+def quantize_with_max(x: torch.Tensor, maxima: torch.Tensor, q: torch.Tensor, scale: torch.Tensor) -> None:
+    """Kernel `quantize_with_max` (src/kernels.rs:455-475; src/gpu.rs:377-390)."""
+    M, K = x.shape
+    capi.check(capi.load().w8a8_quantize_with_max(_ptr(x), _dtype_code(x), _ptr(maxima), M, K, x.stride(0), _ptr(q),
+                                                  _ptr(scale), _stream()), "w8a8_quantize_with_max")
+
+
+def norm_quantize(x: torch.Tensor, gain: torch.Tensor, out: torch.Tensor | None, q: torch.Tensor, scale: torch.Tensor,
+                  maxima: torch.Tensor | None, eps: float = 1e-6) -> None:
+    """GpuModel::norm_quantize (src/gpu.rs:340-363) -> kernel `norm_quantize` (src/kernels.rs:479-576).
+    `out` (the bf16 norm row, only ever read by tracing in the reference) may be None."""
+    M, K = x.shape
+    assert gain.dtype == x.dtype
+    capi.check(capi.load().w8a8_rmsnorm_quantize(_ptr(x), _ptr(gain), _dtype_code(x), eps, M, K, x.stride(0), _ptr(q),
+                                                 _ptr(scale), _ptr(out), _ptr(maxima), _stream()), "w8a8_rmsnorm_quantize")
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor, maxima: torch.Tensor | None) -> None:
+    """Kernel `swiglu` (src/kernels.rs:2172-2190; src/gpu.rs:770-777)."""
+    M, I = gate.shape
+    assert gate.stride(0) == up.stride(0)
+    capi.check(capi.load().w8a8_swiglu(_ptr(gate), _ptr(up), _dtype_code(gate), M, I, gate.stride(0), _ptr(out),
+                                       _ptr(maxima), _stream()), "w8a8_swiglu")
+
+
+def swiglu_quantize(gate: torch.Tensor, up: torch.Tensor, q: torch.Tensor, scale: torch.Tensor,
+                    act: torch.Tensor | None = None) -> None:
+    """`swiglu` + `quantize` of the down-projection input in one pass (src/gpu.rs:768-778 + :377-398)."""
+    M, I = gate.shape
+    assert gate.stride(0) == up.stride(0)
+    capi.check(capi.load().w8a8_swiglu_quantize(_ptr(gate), _ptr(up), _dtype_code(gate), M, I, gate.stride(0), _ptr(q),
+                                                _ptr(scale), _ptr(act), _stream()), "w8a8_swiglu_quantize")
+
+
+def residual(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """GpuModel::residual (src/gpu.rs:510-517) -> kernel `residual` (src/kernels.rs:2163-2170)."""
+    capi.check(capi.load().w8a8_residual(_ptr(a), _ptr(b), _dtype_code(a), a.numel(), _ptr(out), _stream()), "w8a8_residual")
+
+
+def linear_quantized(q: torch.Tensor, scale: torch.Tensor, w: Matrix, out: torch.Tensor,
+                     variant: int = capi.VARIANT_AUTO) -> None:
+    """GpuModel::linear_quantized (src/gpu.rs:450-509): regime chosen from the row count."""
+    M = q.shape[0]
+    capi.check(capi.load().w8a8_linear_ex(_ptr(q), _ptr(scale), w.handle, M, None, _ptr(out), None, _dtype_code(out),
+                                          variant, _stream()), "w8a8_linear")
+
+
+def linear_residual(q: torch.Tensor, scale: torch.Tensor, w: Matrix, out: torch.Tensor | None, residual_in: torch.Tensor,
+                    combined: torch.Tensor, variant: int = capi.VARIANT_AUTO) -> None:
+    """The projection half of GpuModel::linear_residual (src/gpu.rs:400-421): kernel `linear_residual`
+    (src/kernels.rs:579-618) in decode, `linear_*` + `residual` in prefill.  `out` may be None."""
+    M = q.shape[0]
+    capi.check(capi.load().w8a8_linear_ex(_ptr(q), _ptr(scale), w.handle, M, _ptr(residual_in), _ptr(out), _ptr(combined),
+                                          _dtype_code(combined), variant, _stream()), "w8a8_linear(residual)")
+
+
+def linear_grouped(q: torch.Tensor, scale: torch.Tensor, ws: list[Matrix], outs: list[torch.Tensor]) -> None:
+    """Kernels `linear_pair` / `linear_triple` (src/kernels.rs:698-806; src/gpu.rs:571-590)."""
+    n = len(ws)
+    handles = (C.c_void_p * n)(*[w.handle for w in ws])
+    optrs = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+    capi.check(capi.load().w8a8_linear_grouped(_ptr(q), _ptr(scale), handles, n, q.shape[0], optrs, _dtype_code(outs[0]),
+                                               _stream()), "w8a8_linear_grouped")
+
+
+def linear_swiglu(q: torch.Tensor, scale: torch.Tensor, w_gate: Matrix, w_up: Matrix, gate: torch.Tensor | None,
+                  up: torch.Tensor | None, act: torch.Tensor, maxima: torch.Tensor | None) -> None:
+    """Kernel `linear_swiglu` (src/kernels.rs:621-695; src/gpu.rs:730-745)."""
+    capi.check(capi.load().w8a8_linear_gate_up_swiglu(_ptr(q), _ptr(scale), w_gate.handle, w_up.handle, q.shape[0],
+                                                      _ptr(gate), _ptr(up), _ptr(act), _ptr(maxima), _dtype_code(act),
+                                                      _stream()), "w8a8_linear_gate_up_swiglu")
+
+
+def linear_acc_i32(q: torch.Tensor, w: Matrix, acc: torch.Tensor, variant: int = capi.VARIANT_NAIVE) -> None:
+    """Raw int32 accumulators (parity checks against the CPU-integer fixtures)."""
+    capi.check(capi.load().w8a8_linear_acc_i32(_ptr(q), w.handle, q.shape[0], _ptr(acc), variant, _stream()),
+               "w8a8_linear_acc_i32")
+
+
+def rounding_probe(x: torch.Tensor, out: torch.Tensor) -> None:
+    """Kernel `rounding_probe` (src/kernels.rs:326-333)."""
+    capi.check(capi.load().w8a8_rounding_probe(_ptr(x), _ptr(out), x.numel(), _stream()), "w8a8_rounding_probe")
