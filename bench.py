@@ -419,8 +419,11 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--shapes", default="", help="comma-separated subset of the five projections (profiling runs)")
     ap.add_argument("--ms", default="", help="comma-separated subset of the token counts (profiling runs)")
+    ap.add_argument("--prefill-ms", default="", help="comma-separated token counts of the prefill table (profiling runs)")
     args = ap.parse_args()
-    global SHAPES, DECODE_M, WORKLOAD
+    global SHAPES, DECODE_M, PREFILL_M, WORKLOAD
+    if args.prefill_ms:
+        PREFILL_M = [int(m) for m in args.prefill_ms.split(",")]
     if args.shapes:
         keep = args.shapes.split(",")
         SHAPES = [s for s in SHAPES if s[0] in keep]
