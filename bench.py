@@ -44,6 +44,22 @@ WORKLOAD = "configs[1]: quantize+linear over 5 Qwen3-8B projections x M in {1,4,
 NCU_TRAFFIC_BYTES_PER_LAUNCH = None
 
 
+def kernel_family(M, weight_bytes, forced=0):
+    """Which kernel w8a8_linear picks (mirrors pick_variant in inferrous_b200/csrc/capi.cu)."""
+    names = {1: "naive_linear", 2: "gemv_dp4a", 3: "gemv_mma", 4: "gemm_tcgen05", 5: "gemm_skinny"}
+    if forced:
+        return names[forced]
+    if M <= 1:
+        return "gemv_dp4a"
+    if M <= 8:
+        return "gemv_mma"
+    if M <= 64:
+        return "gemm_skinny" if weight_bytes >= (48 << 20) else "gemv_mma"
+    if M <= 256 and weight_bytes >= (256 << 20):
+        return "gemm_skinny"
+    return "gemm_tcgen05"
+
+
 def linear_bytes(M, K, N):
     return N * K + 4 * N + M * K + 4 * M + 2 * M * N
 
@@ -200,10 +216,10 @@ def run_ours(args):
                 if record:
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record()
-                ops.linear_quantized(b["q"], b["s"], mats[name], b["y"])
+                ops.linear_quantized(b["q"], b["s"], mats[name], b["y"], args.variant)
                 if record:
                     e1.record()
-                    gemv_events.append(("gemv_dp4a" if M <= 4 else "gemv_mma", linear_bytes(M, k, n), e0, e1))
+                    gemv_events.append((kernel_family(M, k * n, args.variant), linear_bytes(M, k, n), e0, e1))
                 if world > 1 and name in ROW_SPLIT:
                     dist.all_reduce(b["y"])
                 if host_io:
@@ -263,11 +279,12 @@ def run_ours(args):
 
     extra = {}
     if world == 1 and not args.no_extra:
-        extra["per_shape"] = per_shape_table(torch, ops, mats, bufs, hbm_peak)
+        extra["per_shape"] = per_shape_table(torch, ops, mats, bufs, hbm_peak, args.variant)
         extra["prefill"] = prefill_table(torch, ops, mats)
         body = sum(r["us"] for r in extra["per_shape"] if r["M"] == 1 and r["shape"] != "lm_head")
         head = sum(r["us"] for r in extra["per_shape"] if r["M"] == 1 and r["shape"] == "lm_head")
-        extra["decode_linear_only_tok_s_estimate"] = round(1e6 / (36 * body + head), 1)
+        if body > 0 and head > 0:
+            extra["decode_linear_only_tok_s_estimate"] = round(1e6 / (36 * body + head), 1)
 
     out = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
@@ -302,13 +319,13 @@ def time_launch(torch, fn, iters, flush):
     return statistics.median(ts)
 
 
-def per_shape_table(torch, ops, mats, bufs, hbm_peak):
+def per_shape_table(torch, ops, mats, bufs, hbm_peak, variant=0):
     flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
     rows = []
     for M in DECODE_M:
         for name, K, N in SHAPES:
             b = bufs[(M, name)]
-            us = time_launch(torch, lambda: ops.linear_quantized(b["q"], b["s"], mats[name], b["y"]), 20, flush)
+            us = time_launch(torch, lambda: ops.linear_quantized(b["q"], b["s"], mats[name], b["y"], variant), 20, flush)
             gbs = linear_bytes(M, K, N) / us / 1e3
             rows.append({"shape": name, "M": M, "us": round(us, 2), "GB/s": round(gbs, 1), "frac_hbm": round(gbs / hbm_peak, 3)})
     del flush
@@ -419,6 +436,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--shapes", default="", help="comma-separated subset of the five projections (profiling runs)")
     ap.add_argument("--ms", default="", help="comma-separated subset of the token counts (profiling runs)")
+    ap.add_argument("--variant", type=int, default=0, help="force a kernel variant for every linear call (A/B runs)")
     ap.add_argument("--prefill-ms", default="", help="comma-separated token counts of the prefill table (profiling runs)")
     args = ap.parse_args()
     global SHAPES, DECODE_M, PREFILL_M, WORKLOAD

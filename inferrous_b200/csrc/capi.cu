@@ -3,9 +3,11 @@
 // Regime selection mirrors GpuModel::linear_quantized (crates/inferrous-qwen3/src/gpu.rs:450-509),
 // which switches kernels on the token count: 1 -> linear, 2..31 -> linear_splitk,
 // 32..255 -> linear_tiled, >= 256 (and N >= 4096) -> linear_large.  Here:
-//   M <= 4   gemv_dp4a        (weight streaming, dp4a)
-//   M <= 16  gemv_mma         (weight streaming, warp-level int8 MMA)
-//   else     gemm_tcgen05     (TMA + tcgen05.mma kind::i8 + TMEM)
+//   gemv_dp4a      weight streaming with 16-byte loads + dp4a (1 token; fused gate/up up to 4)
+//   gemv_mma       weight streaming + warp-level int8 MMA (2..64 tokens, small and mid matrices)
+//   gemm_skinny    TMA + tcgen05.mma kind::i8, weights on the MMA's M side, stream-K (large matrices, <= 256 tokens)
+//   gemm_tcgen05   TMA + tcgen05.mma kind::i8, 128x256 tiles, persistent (prefill)
+// see pick_variant() for the thresholds.
 #include "../../include/w8a8.h"
 #include "internal.h"
 
@@ -22,6 +24,8 @@ struct DeviceState {
     bool ready = false;
     int sms = 0;
     uint32_t *status = nullptr;  // 2 words: [0] wait code, [1] detail
+    int32_t *sk_scratch = nullptr;   // stream-K partial tiles, zero between launches
+    uint32_t *sk_counters = nullptr; // stream-K arrival counters, zero between launches
 };
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;
@@ -47,6 +51,14 @@ int sm_count() {
 uint32_t *device_status_ptr() {
     int dev = current_ready_device();
     return dev < 0 ? nullptr : g_dev[dev].status;
+}
+int32_t *skinny_scratch() {
+    int dev = current_ready_device();
+    return dev < 0 ? nullptr : g_dev[dev].sk_scratch;
+}
+uint32_t *skinny_counters() {
+    int dev = current_ready_device();
+    return dev < 0 ? nullptr : g_dev[dev].sk_counters;
 }
 cudaError_t read_device_status(cudaStream_t s, uint32_t out[2]) {
     uint32_t *p = device_status_ptr();
@@ -105,9 +117,16 @@ int w8a8_init(int device) {
     d.sms = prop.multiProcessorCount;
     CUDA_OK(cudaMalloc(&d.status, 8), "cudaMalloc(status)");
     CUDA_OK(cudaMemset(d.status, 0, 8), "cudaMemset(status)");
+    // Scratch of the stream-K fix-up (gemm_skinny.cu): allocated once here, never in a launch call.
+    const size_t sk_bytes = (size_t)d.sms * kSkinnySlotInts * sizeof(int32_t);
+    CUDA_OK(cudaMalloc(&d.sk_scratch, sk_bytes), "cudaMalloc(stream-K scratch)");
+    CUDA_OK(cudaMemset(d.sk_scratch, 0, sk_bytes), "cudaMemset(stream-K scratch)");
+    CUDA_OK(cudaMalloc(&d.sk_counters, (size_t)d.sms * 4 * sizeof(uint32_t)), "cudaMalloc(stream-K counters)");
+    CUDA_OK(cudaMemset(d.sk_counters, 0, (size_t)d.sms * 4 * sizeof(uint32_t)), "cudaMemset(stream-K counters)");
     CUDA_OK(init_quantize(), "init_quantize");
     CUDA_OK(init_gemv(), "init_gemv");
     CUDA_OK(init_gemm_tcgen05(), "init_gemm_tcgen05");
+    CUDA_OK(init_gemm_skinny(), "init_gemm_skinny");
     d.ready = true;
     return W8A8_OK;
 }
@@ -236,15 +255,26 @@ int w8a8_rounding_probe(const float *x, int8_t *out, size_t n, void *stream) {
 
 // ---- projections -----------------------------------------------------------------------
 
-static int pick_variant(int M, int epilogue) {
-    if (M <= 4) return W8A8_VARIANT_GEMV_DP4A;
-    if (M <= 16 && epilogue != EPI_SWIGLU) return W8A8_VARIANT_GEMV_MMA;
+// Regime selection, from measurements on B200 (CUDA events, cold weights):
+//   1 token            gemv_dp4a: whole weight rows per warp, 6.5 TB/s on the large projections
+//   2..8 tokens        gemv_mma
+//   9..64 tokens       gemm_skinny for the large matrices (>= 48 MB of weights), gemv_mma otherwise
+//   65..256 tokens     gemm_skinny for the very large ones (>= 256 MB), gemm_tcgen05 otherwise
+//   more               gemm_tcgen05
+static int pick_variant(int M, int epilogue, bool single_matrix, long long weight_bytes) {
+    if (M <= 1) return W8A8_VARIANT_GEMV_DP4A;
+    if (epilogue == EPI_SWIGLU) return W8A8_VARIANT_GEMV_DP4A;  // fused gate/up exists only there (M <= 4)
+    if (!single_matrix) return W8A8_VARIANT_GEMV_MMA;  // grouped siblings, 2..16 tokens
+    if (M <= 8) return W8A8_VARIANT_GEMV_MMA;
+    if (M <= 64) return weight_bytes >= (48ll << 20) ? W8A8_VARIANT_GEMM_SKINNY : W8A8_VARIANT_GEMV_MMA;
+    if (M <= kSkinnyMaxTokens && weight_bytes >= (256ll << 20)) return W8A8_VARIANT_GEMM_SKINNY;
     return W8A8_VARIANT_GEMM_TCGEN05;
 }
 
 static int run_linear(LinearArgs &l, const w8a8_weight *wt, int variant, void *stream) {
     REQUIRE(current_ready_device() >= 0, W8A8_ERR_NOT_INITIALIZED);
-    if (variant == W8A8_VARIANT_AUTO) variant = pick_variant(l.M, l.epilogue);
+    if (variant == W8A8_VARIANT_AUTO)
+        variant = pick_variant(l.M, l.epilogue, wt != nullptr && l.count == 1, (long long)l.n[0] * l.K);
     cudaStream_t s = (cudaStream_t)stream;
     switch (variant) {
         case W8A8_VARIANT_NAIVE: CUDA_OK(launch_linear_naive(l, s), "launch_linear_naive"); return W8A8_OK;
@@ -259,6 +289,10 @@ static int run_linear(LinearArgs &l, const w8a8_weight *wt, int variant, void *s
         case W8A8_VARIANT_GEMM_TCGEN05:
             REQUIRE(wt && l.count == 1 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);
             CUDA_OK(launch_gemm_tcgen05(l, wt, s), "launch_gemm_tcgen05");
+            return W8A8_OK;
+        case W8A8_VARIANT_GEMM_SKINNY:
+            REQUIRE(wt && l.count == 1 && l.epilogue != EPI_SWIGLU && l.M <= kSkinnyMaxTokens, W8A8_ERR_UNSUPPORTED);
+            CUDA_OK(launch_gemm_skinny(l, wt, s), "launch_gemm_skinny");
             return W8A8_OK;
         default: return W8A8_ERR_BAD_ARG;
     }

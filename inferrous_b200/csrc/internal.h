@@ -68,6 +68,16 @@ cudaError_t launch_gemv_mma(const LinearArgs &a, cudaStream_t s);    // M <= 64
 cudaError_t launch_gemm_tcgen05(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);
 cudaError_t init_gemm_tcgen05();
 cudaError_t make_weight_maps(w8a8_weight *wt);  // TMA descriptors of the [N,K] matrix
+// [rows,K] int8 row-major -> tiled map with a box of 128 bytes of K x box_rows rows, 128-byte swizzle, zero fill.
+cudaError_t encode_tile_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows);
+// few-token tensor-core path (weights on the MMA's M side, stream-K over output tiles x K blocks)
+cudaError_t launch_gemm_skinny(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);
+cudaError_t init_gemm_skinny();
+// Per-device scratch of the stream-K fix-up: int32 partial tiles and arrival counters (all zero between launches).
+int32_t *skinny_scratch();
+uint32_t *skinny_counters();
+constexpr int kSkinnyMaxTokens = 256;
+constexpr size_t kSkinnySlotInts = 4 * (size_t)kSkinnyMaxTokens * 32;  // one 128-channel tile: [quarter][token][32]
 cudaError_t init_gemv();
 cudaError_t init_quantize();
 

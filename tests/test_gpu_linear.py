@@ -12,7 +12,7 @@ from tests.util import bits, empty_act, synth_activations, synth_weights, to_dev
 
 pytestmark = pytest.mark.gpu
 
-NAIVE, DP4A, MMA, TC = 1, 2, 3, 4
+NAIVE, DP4A, MMA, TC, SKINNY = 1, 2, 3, 4, 5
 CARRIERS = ["bf16", "f32"]
 
 
@@ -28,6 +28,8 @@ def ops():
 
 def variants_for(M):
     v = [NAIVE, TC]
+    if M <= 256:
+        v.append(SKINNY)
     if os.environ.get("W8A8_TEST_SKIP_TCGEN05"):  # bring-up aid: check the SIMT variants alone
         v = [NAIVE]
     if M <= 4:
@@ -220,7 +222,7 @@ def test_fused_gate_up_matches_separate(ops, K, N, M):
 
 
 @pytest.mark.parametrize("M,K,N", [(129, 4096, 4096), (512, 4096, 6144), (257, 12288, 4096), (130, 4096, 33), (64, 4096, 256),
-                                   (1000, 4096, 1000)])
+                                   (1000, 4096, 1000), (17, 12288, 4096), (48, 4096, 24576), (256, 4096, 1024), (200, 128, 136)])
 def test_prefill_shapes_exact(ops, M, K, N):
     """Tensor-core path against the CPU oracle at sizes the oracle finishes in seconds, with ragged M and N tails."""
     rng = np.random.default_rng(M + N)
@@ -230,13 +232,17 @@ def test_prefill_shapes_exact(ops, M, K, N):
     mat = make_matrix(ops, w, ws)
     acc_ref = oracle.linear_acc(q, w)
     y_ref = oracle.epilogue(acc_ref, s, ws)
-    assert np.array_equal(run_acc(ops, mat, q, TC), acc_ref)
+    for v in variants_for(M)[1:]:
+        assert np.array_equal(run_acc(ops, mat, q, v), acc_ref), v
+        yv, _ = run_linear(ops, mat, q, s, "f32", v)
+        assert np.array_equal(bits(yv), bits(y_ref)), v
     y, _ = run_linear(ops, mat, q, s, "bf16", 0)
     assert np.array_equal(bits(y), bits(y_ref))
     res = oracle.bf16(rng.standard_normal((M, N), dtype=np.float32))
-    y2, comb = run_linear(ops, mat, q, s, "bf16", TC, residual=res)
-    assert np.array_equal(bits(y2), bits(y_ref))
-    assert np.array_equal(bits(comb), bits(oracle.residual(res, y_ref)))
+    for v in variants_for(M)[1:]:
+        y2, comb = run_linear(ops, mat, q, s, "bf16", v, residual=res)
+        assert np.array_equal(bits(y2), bits(y_ref)), v
+        assert np.array_equal(bits(comb), bits(oracle.residual(res, y_ref))), v
     check_status(ops)
 
 
