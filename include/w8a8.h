@@ -147,6 +147,22 @@ int w8a8_linear_gate_up_swiglu(const int8_t *q, const float *a_scale, w8a8_weigh
                                int M, void *gate_out, void *up_out, void *act, uint32_t *maxima, int dtype,
                                void *stream);
 
+/* The same projection, y = bf16((f32(acc) * a_scale[m]) * w_scale[n]), for callers that must not
+ * allocate device memory: code running where cudaMalloc is forbidden or unavailable -- inside a
+ * stream capture that the host application owns, in a process whose memory pool is closed after
+ * start-up, or in a plug-in that is handed buffers and a stream and nothing else.  It needs neither
+ * w8a8_init nor a weight handle (both allocate): weights are passed as raw pointers, and the
+ * partial-sum tiles that the stream-K kernel exchanges between CTAs live in a fixed 1.25 MiB device
+ * array inside the library (held by every GPU that loads the library until the process exits).
+ * There is no counterpart in the reference; it is an addition of this library.
+ * Limits: M <= 16 tokens (W8A8_ERR_UNSUPPORTED beyond, with the reason in w8a8_last_cuda_error()),
+ * plain epilogue only.  The first call on a device resolves the array's address and raises the
+ * kernel's shared-memory limit; make that first call before any stream capture.  Every call clears
+ * the array in stream order and then uses it, so two calls that overlap on the GPU (different
+ * streams, or a captured graph replayed concurrently with itself) race on it: keep them in order. */
+int w8a8_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w, const float *w_scale, int M, int N,
+                         int K, void *y, int dtype, void *stream);
+
 /* Raw int32 accumulators acc[M,N] of the product (debug / parity: the reference's tests
  * hold these bit-exact through its CPU-integer fixtures, tools/operator_fixtures.py:54). */
 int w8a8_linear_acc_i32(const int8_t *q, w8a8_weight_t weight, int M, int32_t *acc, int variant, void *stream);

@@ -358,6 +358,20 @@ int w8a8_linear_gate_up_swiglu(const int8_t *q, const float *a_scale, w8a8_weigh
     return w8a8_swiglu(gate_out, up_out, dtype, M, w_gate->N, w_gate->N, act, maxima, stream);
 }
 
+int w8a8_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w, const float *w_scale, int M, int N, int K,
+                         void *y, int dtype, void *stream) {
+    REQUIRE(q && a_scale && w && w_scale && y && M > 0 && N > 0 && K > 0 && check_dtype(dtype), W8A8_ERR_BAD_ARG);
+    REQUIRE(K % 128 == 0 && aligned16(q) && aligned16(y) && (reinterpret_cast<uintptr_t>(w) & 127u) == 0 && aligned16(w_scale),
+            W8A8_ERR_ALIGNMENT);
+    if (M > kNoAllocMaxTokens) {
+        snprintf(g_err, sizeof g_err, "w8a8_linear_no_alloc: M=%d exceeds the %d tokens its fixed scratch array holds", M,
+                 kNoAllocMaxTokens);
+        return W8A8_ERR_UNSUPPORTED;
+    }
+    CUDA_OK(launch_linear_no_alloc(q, a_scale, w, w_scale, M, N, K, y, dtype, (cudaStream_t)stream), "launch_linear_no_alloc");
+    return W8A8_OK;
+}
+
 int w8a8_linear_acc_i32(const int8_t *q, w8a8_weight_t weight, int M, int32_t *acc, int variant, void *stream) {
     REQUIRE(valid_weight(weight) && q && acc && M > 0, W8A8_ERR_BAD_ARG);
     REQUIRE(aligned16(q) && aligned16(acc), W8A8_ERR_ALIGNMENT);

@@ -78,7 +78,7 @@ __device__ __forceinline__ void finish_value(const SkinnyDev &p, int m, int n, i
     }
 }
 
-template <class T, int EPI>
+template <class T, int EPI, int TOK_STRIDE = kSkinnyMaxTokens>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_q, const SkinnyDev p) {
     extern __shared__ uint8_t smem_raw[];
@@ -225,7 +225,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 while (span_begin(c + 1, units, gridDim.x) <= first) ++c;
                 slot = (int)c;
             }
-            int32_t *sc = p.scratch + ((size_t)slot * 4 + quarter) * ((size_t)kSkinnyMaxTokens * 32);
+            int32_t *sc = p.scratch + ((size_t)slot * 4 + quarter) * ((size_t)TOK_STRIDE * 32);
 
             for (int c0 = 0; c0 < p.ntok; c0 += 16) {
                 int v[16];
@@ -339,6 +339,95 @@ cudaError_t launch_gemm_skinny(const LinearArgs &l, const w8a8_weight *wt, cudaS
     const size_t smem = (size_t)stages * stage_bytes + 1024 + 8 * (2 * (size_t)stages + 4) + 64;
     return l.dtype == 0 ? launch_epi<Bf16>(l.epilogue, wt->map_rows128, map_q, d, grid, smem, s)
                         : launch_epi<F32>(l.epilogue, wt->map_rows128, map_q, d, grid, smem, s);
+}
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant: the stream-K scratch lives in a fixed device array of this module.
+// ---------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kStaticMaxTokens = 16;   // token limit of the allocation-free entry point
+constexpr int kStaticSlots = 160;      // CTAs (one scratch tile each); the grid is capped to this
+constexpr size_t kStaticTileInts = (size_t)kStaticSlots * 4 * kStaticMaxTokens * 32;
+constexpr size_t kStaticCounterInts = (size_t)kStaticSlots * 4;
+constexpr size_t kStaticInts = kStaticTileInts + kStaticCounterInts + 2 /* status words */ + 62 /* pad */;
+
+// 1.25 MiB, resident on every GPU that loads the library until the process exits.
+// In host code this name is only a stand-in for the symbol: the device address comes from
+// cudaGetSymbolAddress (static_scratch_address below) and that pointer is what kernels receive.
+static __device__ __align__(256) int32_t g_static_scratch[kStaticInts];
+
+struct StaticState {
+    bool ready = false;
+    int32_t *base = nullptr;
+    int sms = 0;
+};
+StaticState g_static[64];
+
+// Once per device, with that device current: resolve the array's device address and raise the
+// kernels' shared-memory limit.  Neither call allocates.
+cudaError_t static_setup(int dev) {
+    StaticState &st = g_static[dev];
+    if (st.ready) return cudaSuccess;
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return e;
+    if ((e = cudaDeviceGetAttribute(&st.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(gemm_skinny_kernel<Bf16, EPI_PLAIN, kStaticMaxTokens>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kSmemBudget + 2048)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(gemm_skinny_kernel<F32, EPI_PLAIN, kStaticMaxTokens>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kSmemBudget + 2048)) != cudaSuccess) return e;
+    st.base = static_cast<int32_t *>(ptr);
+    st.ready = true;
+    return cudaSuccess;
+}
+
+}  // namespace
+
+// See w8a8_linear_no_alloc in include/w8a8.h.  Returns cudaErrorInvalidValue for shapes beyond the
+// fixed scratch (the C ABI turns that into W8A8_ERR_UNSUPPORTED before coming here).
+cudaError_t launch_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w, const float *w_scale, int M, int N,
+                                   int K, void *y, int dtype, cudaStream_t s) {
+    if (M < 1 || M > kStaticMaxTokens || N < 1 || K < BLOCK_K || K % BLOCK_K != 0) return cudaErrorInvalidValue;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if ((e = static_setup(dev)) != cudaSuccess) return e;
+    const StaticState &st = g_static[dev];
+
+    // Tensor maps are encoded on the host (no device work, no allocation) and passed by value.
+    CUtensorMap map_w, map_q;
+    const int ntok = kStaticMaxTokens;
+    if ((e = encode_tile_map(&map_w, w, N, K, TILE_N)) != cudaSuccess) return e;
+    if ((e = encode_tile_map(&map_q, q, M, K, ntok)) != cudaSuccess) return e;
+
+    SkinnyDev d{};
+    d.a_scale = a_scale; d.w_scale = w_scale; d.M = M; d.N = N; d.K = K; d.ntok = ntok;
+    int kps = 4;
+    while (kps > 1 && (K / BLOCK_K) % kps != 0) kps /= 2;
+    d.kps = kps;
+    const int stage_bytes = kps * (A_BYTES + ntok * BLOCK_K);
+    int stages = (kSmemBudget - 1024) / stage_bytes;
+    if (stages > 16) stages = 16;
+    d.stages = stages;
+    d.y = y;
+    d.scratch = st.base;
+    d.counters = reinterpret_cast<uint32_t *>(st.base + kStaticTileInts);
+    d.status = reinterpret_cast<uint32_t *>(st.base + kStaticTileInts + kStaticCounterInts);
+    // The array keeps whatever the previous call left (normally zeros, but not after an abandoned
+    // launch): partial tiles, counters and status must start at zero, so clear them in stream order.
+    if ((e = cudaMemsetAsync(st.base, 0, kStaticInts * sizeof(int32_t), s)) != cudaSuccess) return e;
+
+    const long long units = (long long)((N + TILE_N - 1) / TILE_N) * (K / (BLOCK_K * kps));
+    int grid = st.sms < kStaticSlots ? st.sms : kStaticSlots;
+    if (units < grid) grid = (int)units;
+    const size_t smem = (size_t)stages * stage_bytes + 1024 + 8 * (2 * (size_t)stages + 4) + 64;
+    if (dtype == 0)
+        gemm_skinny_kernel<Bf16, EPI_PLAIN, kStaticMaxTokens><<<grid, kThreads, smem, s>>>(map_w, map_q, d);
+    else
+        gemm_skinny_kernel<F32, EPI_PLAIN, kStaticMaxTokens><<<grid, kThreads, smem, s>>>(map_w, map_q, d);
+    return cudaGetLastError();
 }
 
 }  // namespace w8a8

@@ -77,6 +77,10 @@ cudaError_t init_gemm_skinny();
 int32_t *skinny_scratch();
 uint32_t *skinny_counters();
 constexpr int kSkinnyMaxTokens = 256;
+constexpr int kNoAllocMaxTokens = 16;
+// Allocation-free projection: stream-K scratch in a fixed device array of the library (gemm_skinny.cu).
+cudaError_t launch_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w, const float *w_scale, int M, int N,
+                                   int K, void *y, int dtype, cudaStream_t s);
 constexpr size_t kSkinnySlotInts = 4 * (size_t)kSkinnyMaxTokens * 32;  // one 128-channel tile: [quarter][token][32]
 cudaError_t init_gemv();
 cudaError_t init_quantize();

@@ -170,6 +170,15 @@ def linear_swiglu(q: torch.Tensor, scale: torch.Tensor, w_gate: Matrix, w_up: Ma
                                                       _stream()), "w8a8_linear_gate_up_swiglu")
 
 
+def linear_no_alloc(q: torch.Tensor, scale: torch.Tensor, w: torch.Tensor, w_scale: torch.Tensor, out: torch.Tensor) -> None:
+    """The projection for callers that cannot allocate device memory (w8a8_linear_no_alloc): raw weight
+    tensors instead of a Matrix handle, at most 16 tokens, scratch in a fixed array inside the library.
+    Needs no init(); calls on different streams must not overlap."""
+    N, K = w.shape
+    capi.check(capi.load().w8a8_linear_no_alloc(_ptr(q), _ptr(scale), _ptr(w), _ptr(w_scale), q.shape[0], N, K, _ptr(out),
+                                                _dtype_code(out), _stream()), "w8a8_linear_no_alloc")
+
+
 def linear_acc_i32(q: torch.Tensor, w: Matrix, acc: torch.Tensor, variant: int = capi.VARIANT_NAIVE) -> None:
     """Raw int32 accumulators (parity checks against the CPU-integer fixtures)."""
     capi.check(capi.load().w8a8_linear_acc_i32(_ptr(q), w.handle, q.shape[0], _ptr(acc), variant, _stream()),
