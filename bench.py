@@ -69,9 +69,8 @@ def quant_bytes(M, K):
 
 
 def shard(name, K, N, tp):
-    if tp == 1:
-        return K, N
-    return (K // tp, N) if name in ROW_SPLIT else (K, N // tp)
+    from inferrous_b200.tp import shard_shape
+    return shard_shape(name, K, N, tp)
 
 
 def measured_peaks():
@@ -165,6 +164,7 @@ def run_ours(args):
     import torch.distributed as dist
 
     from inferrous_b200 import ops
+    from inferrous_b200.tp import all_reduce_sum
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -221,7 +221,7 @@ def run_ours(args):
                     e1.record()
                     gemv_events.append((kernel_family(M, k * n, args.variant), linear_bytes(M, k, n), e0, e1))
                 if world > 1 and name in ROW_SPLIT:
-                    dist.all_reduce(b["y"])
+                    all_reduce_sum(b["y"])  # bf16 NCCL all-reduce of the partial outputs [M,4096]
                 if host_io:
                     b["hy"].copy_(b["y"], non_blocking=True)
 

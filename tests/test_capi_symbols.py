@@ -1,0 +1,68 @@
+"""CPU-only checks of the C-ABI boundary: the built library loads without a GPU and exports exactly the
+functions include/w8a8.h declares; the ctypes binding covers each of them.  No compute call is made."""
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def declared():
+    text = (ROOT / "include" / "w8a8.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"\b(w8a8_[a-z0-9_]+)\s*\(", text)
+    return sorted(set(names))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from inferrous_b200.build import build_library
+    from inferrous_b200 import capi
+
+    build_library()  # nvcc cross-compiles for sm_100a without a GPU
+    return capi.load()
+
+
+def test_header_declares_the_expected_surface(declared):
+    for name in ("w8a8_init", "w8a8_weight_create", "w8a8_quantize", "w8a8_rmsnorm_quantize", "w8a8_swiglu_quantize",
+                 "w8a8_linear", "w8a8_linear_grouped", "w8a8_linear_gate_up_swiglu", "w8a8_residual", "w8a8_device_status"):
+        assert name in declared
+
+
+def test_library_exports_every_declared_symbol(lib, declared):
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/w8a8.h but not exported by libw8a8.so"
+
+
+def test_binding_covers_every_declared_symbol(declared):
+    from inferrous_b200 import capi
+
+    assert sorted(capi.SIGNATURES) == declared
+
+
+def test_status_strings_and_version_need_no_gpu(lib):
+    assert lib.w8a8_version().decode().count(".") == 2
+    assert lib.w8a8_status_string(0) == b"ok"
+    for code in range(1, 7):
+        assert lib.w8a8_status_string(code) not in (b"ok", b"unknown status")
+    assert lib.w8a8_status_string(99) == b"unknown status"
+
+
+def test_argument_validation_needs_no_gpu(lib):
+    # rejected before any CUDA call is made
+    assert lib.w8a8_quantize(None, 0, 1, 128, 128, None, None, None) == 1
+    assert lib.w8a8_linear(None, None, None, 1, None, None, None, 0, None) == 1
+    assert lib.w8a8_weight_destroy(None) == 1
+    assert lib.w8a8_init(-1) == 1
+
+
+def test_product_does_not_import_the_oracle():
+    """The oracle is test infrastructure: nothing under inferrous_b200/ may import, load or link it."""
+    needles = ("import oracle", "from oracle", "w8a8_oracle", "oracle/", "oracle.py")
+    for path in (ROOT / "inferrous_b200").rglob("*"):
+        if path.suffix in {".py", ".cu", ".cuh", ".h"}:
+            text = path.read_text()
+            for n in needles:
+                assert n not in text, f"{path} mentions {n!r}"
