@@ -171,6 +171,8 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", 0))
     tp = world
     torch.cuda.set_device(local)
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"  # NCCL would print its version on stdout, which carries the one JSON line
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -183,17 +185,30 @@ def run_ours(args):
         k, n = shard(name, K, N, tp)
         wq, ws = make_weights_device(torch, k, n, seed=1000 + 10 * i + rank)
         mats[name] = ops.Matrix(wq, ws)
-    for M in DECODE_M:
-        for i, (name, K, N) in enumerate(SHAPES):
-            k, n = shard(name, K, N, tp)
-            bufs[(M, name)] = dict(
-                x=make_activations_device(torch, M, k, seed=7 * M + i + 100 * rank),
-                q=torch.empty((M, k), dtype=torch.int8, device="cuda"),
-                s=torch.empty((M,), dtype=torch.float32, device="cuda"),
-                y=torch.empty((M, n), dtype=torch.bfloat16, device="cuda"),
-                hx=torch.empty((M, k), dtype=torch.bfloat16).pin_memory(),
-                hy=torch.empty((M, n), dtype=torch.bfloat16).pin_memory())
-            bufs[(M, name)]["hx"].copy_(bufs[(M, name)]["x"])
+    # Activations and outputs of one step live in two device arenas mirrored by two pinned host arenas, so the
+    # end-to-end step moves them with one host->device and one device->host copy.
+    def carve(sizes):
+        offs, total = [], 0
+        for n_el in sizes:
+            offs.append(total)
+            total += (n_el + 127) // 128 * 128  # 256-byte aligned bf16 slices
+        return offs, total
+    keys = [(M, name, *shard(name, K, N, tp)) for M in DECODE_M for name, K, N in SHAPES]
+    x_off, x_tot = carve([M * k for M, _, k, _ in keys])
+    y_off, y_tot = carve([M * n for M, _, _, n in keys])
+    x_all = torch.empty(x_tot, dtype=torch.bfloat16, device="cuda")
+    y_all = torch.empty(y_tot, dtype=torch.bfloat16, device="cuda")
+    hx_all = torch.empty(x_tot, dtype=torch.bfloat16).pin_memory()
+    hy_all = torch.empty(y_tot, dtype=torch.bfloat16).pin_memory()
+    for i, (M, name, k, n) in enumerate(keys):
+        x = x_all[x_off[i]:x_off[i] + M * k].view(M, k)
+        x.copy_(make_activations_device(torch, M, k, seed=7 * M + i + 100 * rank))
+        bufs[(M, name)] = dict(
+            x=x,
+            q=torch.empty((M, k), dtype=torch.int8, device="cuda"),
+            s=torch.empty((M,), dtype=torch.float32, device="cuda"),
+            y=y_all[y_off[i]:y_off[i] + M * n].view(M, n))
+    hx_all.copy_(x_all)
     torch.cuda.synchronize()
 
     step_bytes = 0
@@ -206,12 +221,12 @@ def run_ours(args):
     gemv_events = []  # (kernel family, bytes, start, end) per linear launch of the timed region
 
     def step(record=False, host_io=False):
+        if host_io:
+            x_all.copy_(hx_all, non_blocking=True)
         for M in DECODE_M:
             for name, K, N in SHAPES:
                 b = bufs[(M, name)]
                 k, n = shard(name, K, N, tp)
-                if host_io:
-                    b["x"].copy_(b["hx"], non_blocking=True)
                 ops.quantize(b["x"], b["q"], b["s"])
                 if record:
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -222,8 +237,10 @@ def run_ours(args):
                     gemv_events.append((kernel_family(M, k * n, args.variant), linear_bytes(M, k, n), e0, e1))
                 if world > 1 and name in ROW_SPLIT:
                     all_reduce_sum(b["y"])  # bf16 NCCL all-reduce of the partial outputs [M,4096]
-                if host_io:
-                    b["hy"].copy_(b["y"], non_blocking=True)
+
+    def step_e2e():
+        step(host_io=True)
+        hy_all.copy_(y_all, non_blocking=True)
 
     def timed(fn, steps):
         if world > 1:
@@ -241,14 +258,45 @@ def run_ours(args):
             dist.barrier()
         return float(ms.item())
 
+    def capture(fn):
+        """One step as a CUDA graph (the reference replays captured decode graphs, src/gpu.rs:318-328,890).
+        Every launch call of the library is capture-safe; under TP the NCCL all-reduce is captured with it."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            fn()
+        return g
+
     for _ in range(args.warmup):
         step()
+    launch_mode = "eager"
+    run_step = step
+    graph = e2e_graph = None
+    if not args.eager:
+        try:
+            graph = capture(step)
+            run_step = graph.replay
+            launch_mode = "cuda_graph"
+            for _ in range(args.warmup):
+                run_step()
+        except Exception as exc:  # keep measuring, say why
+            print(f"bench: CUDA graph capture failed ({exc}); timing eager launches", file=sys.stderr)
+            torch.cuda.synchronize()
     sampler = ClockSampler(local)
     sampler.start()
-    ms = timed(lambda: step(record=True), args.steps)
+    ms = timed(run_step, args.steps)
     clocks = sampler.stop()
     ms_per_step = ms / args.steps
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # per-launch CUDA events need eager launches: the same steps again, instrumented
+    eager_ms = timed(lambda: step(record=True), args.steps) / args.steps
 
     # ---- roofline of the dominant kernel family, from the per-launch events of the timed region ----
     fam = {}
@@ -264,15 +312,27 @@ def run_ours(args):
                 "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
                 "algorithmic_bytes_per_launch": dom_bytes // dom_n, "avg_launch_us": round(dom_s / dom_n * 1e6, 2),
                 "launches": dom_n,
+                "timing": "per-launch CUDA events over the same K steps launched eagerly right after the timed region "
+                          f"({eager_ms:.4f} ms/step eager)",
                 "other_kernels": {k: {"achieved": round(v[0] / v[1] / 1e9, 1), "frac": round(v[0] / v[1] / 1e9 / hbm_peak, 4),
                                       "launches": v[2]} for k, v in fam.items() if k != dominant}}
 
     # ---- end to end: host buffers in, host buffers out, through the same calls ----
+    e2e_step = step_e2e
     for _ in range(3):
-        step(host_io=True)
-    e2e_ms = timed(lambda: step(host_io=True), args.steps) / args.steps
-    h2d = sum(2 * M * shard(n_, K, N, tp)[0] for M in DECODE_M for n_, K, N in SHAPES)
-    d2h = sum(2 * M * shard(n_, K, N, tp)[1] for M in DECODE_M for n_, K, N in SHAPES)
+        e2e_step()
+    if launch_mode == "cuda_graph":
+        try:
+            e2e_graph = capture(e2e_step)
+            e2e_step = e2e_graph.replay
+            for _ in range(3):
+                e2e_step()
+        except Exception as exc:
+            print(f"bench: e2e graph capture failed ({exc}); timing eager launches", file=sys.stderr)
+            torch.cuda.synchronize()
+    e2e_ms = timed(e2e_step, args.steps) / args.steps
+    h2d = x_all.numel() * 2
+    d2h = y_all.numel() * 2
     e2e = {"value": round(total_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4),
            "note": "activations from pinned host memory and outputs back to it every step; weights resident (model state)"}
@@ -291,7 +351,7 @@ def run_ours(args):
            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8xint8->int32 (bf16 in/out)",
            "data": "synthetic", "impl": "ours",
            "config": {"workload": WORKLOAD, "shapes": {n: [K, N] for n, K, N in SHAPES}, "M": DECODE_M,
-                      "parallelism": f"tp{world}" if world > 1 else "single",
+                      "parallelism": f"tp{world}" if world > 1 else "single", "launch": launch_mode,
                       "l2": f"weights ({sum(shard(n, K, N, tp)[0] * shard(n, K, N, tp)[1] for n, K, N in SHAPES) >> 20} MiB streamed per "
                             "pass, each matrix revisited only after all the others) exceed the 126 MB L2; no flush",
                       "bytes_per_step": step_bytes},
@@ -300,9 +360,16 @@ def run_ours(args):
         out["cpu_baseline"] = cpu_baseline(torch, mats, bufs, reps=3)
     out.update(extra)
     if rank == 0:
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Captured graphs hold NCCL work of this process group: release them before the group, and do not let
+        # a slow communicator teardown keep the job alive after the result is out.
+        graph = e2e_graph = run_step = e2e_step = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def time_launch(torch, fn, iters, flush):
@@ -364,7 +431,7 @@ def host_copies(torch, mats, bufs):
     host = {}
     wh = {name: (m.w.cpu().numpy(), m.scale.cpu().numpy()) for name, m in mats.items()}
     for (M, name), b in bufs.items():
-        host[(M, name)] = (b["x"].float().cpu().numpy(), *wh[name])
+        host[(M, name)] = (b["x"].float().cpu().numpy().copy(), *wh[name])
     return host
 
 
@@ -432,6 +499,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--no-extra", action="store_true", help="skip the per-shape and prefill tables")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--shapes", default="", help="comma-separated subset of the five projections (profiling runs)")
