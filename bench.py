@@ -177,6 +177,7 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ops.init(local)
+    ops.set_programmatic_launch(not args.no_pdl)
     hbm_peak, _, peak_kind = measured_peaks()
 
     # ---- resident weights (model state) and per-(M,shape) activation/output buffers ----
@@ -351,7 +352,8 @@ def run_ours(args):
            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8xint8->int32 (bf16 in/out)",
            "data": "synthetic", "impl": "ours",
            "config": {"workload": WORKLOAD, "shapes": {n: [K, N] for n, K, N in SHAPES}, "M": DECODE_M,
-                      "parallelism": f"tp{world}" if world > 1 else "single", "launch": launch_mode,
+                      "parallelism": f"tp{world}" if world > 1 else "single",
+                      "launch": launch_mode + ("" if args.no_pdl else "+programmatic_dependent_launch"),
                       "l2": f"weights ({sum(shard(n, K, N, tp)[0] * shard(n, K, N, tp)[1] for n, K, N in SHAPES) >> 20} MiB streamed per "
                             "pass, each matrix revisited only after all the others) exceed the 126 MB L2; no flush",
                       "bytes_per_step": step_bytes},
@@ -499,6 +501,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-pdl", action="store_true", help="ordinary launches instead of programmatic dependent launches")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--no-extra", action="store_true", help="skip the per-shape and prefill tables")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")

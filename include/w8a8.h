@@ -71,6 +71,12 @@ const char *w8a8_version(void);
 const char *w8a8_status_string(int status);
 /* Text of the last failing CUDA call on this host thread ("" if none). */
 const char *w8a8_last_cuda_error(void);
+/* Programmatic dependent launch, the reference's CLEAN_PDL switch (src/gpu.rs:317; the graph rewrite of
+ * src/graph.rs:63-127).  When enabled (default off; env W8A8_PDL=1 at init), every hot-path kernel is
+ * launched with the programmatic-stream-serialization attribute: it may begin while its predecessor on
+ * the stream drains, and its own griddepcontrol.wait orders the data.  Captured into a CUDA graph the
+ * launches become programmatic edges.  Process-wide switch; set it before capturing. */
+int w8a8_set_programmatic_launch(int enabled);
 /* Reads (and clears) the device-side status word of the current device: 0, or
  * W8A8_ERR_DEVICE_TIMEOUT with *detail = code of the wait that gave up.  Synchronises `stream`. */
 int w8a8_device_status(void *stream, uint32_t *detail);

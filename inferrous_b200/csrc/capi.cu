@@ -29,6 +29,7 @@ struct DeviceState {
 };
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;
+bool g_pdl = false;
 thread_local char g_err[256] = "";
 
 int fail_cuda(cudaError_t e, const char *what) {
@@ -43,6 +44,8 @@ int current_ready_device() {
     return g_dev[dev].ready ? dev : -1;
 }
 }  // namespace
+
+bool programmatic_launch_enabled() { return g_pdl; }
 
 int sm_count() {
     int dev = current_ready_device();
@@ -102,6 +105,11 @@ const char *w8a8_status_string(int status) {
 
 const char *w8a8_last_cuda_error(void) { return g_err; }
 
+int w8a8_set_programmatic_launch(int enabled) {
+    g_pdl = enabled != 0;
+    return W8A8_OK;
+}
+
 int w8a8_init(int device) {
     REQUIRE(device >= 0 && device < kMaxDevices, W8A8_ERR_BAD_ARG);
     std::lock_guard<std::mutex> lock(g_mu);
@@ -115,6 +123,7 @@ int w8a8_init(int device) {
         return W8A8_ERR_CUDA;
     }
     d.sms = prop.multiProcessorCount;
+    if (const char *e = getenv("W8A8_PDL")) g_pdl = atoi(e) != 0;
     CUDA_OK(cudaMalloc(&d.status, 8), "cudaMalloc(status)");
     CUDA_OK(cudaMemset(d.status, 0, 8), "cudaMemset(status)");
     // Scratch of the stream-K fix-up (gemm_skinny.cu): allocated once here, never in a launch call.

@@ -285,8 +285,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 template <class T, int EPI> cudaError_t launch_inst(const CUtensorMap &mw, const CUtensorMap &mq, const SkinnyDev &d, int grid,
                                                     size_t smem, cudaStream_t s) {
-    gemm_skinny_kernel<T, EPI><<<grid, kThreads, smem, s>>>(mw, mq, d);
-    return cudaGetLastError();
+    return launch_kernel(gemm_skinny_kernel<T, EPI>, dim3(grid), dim3(kThreads), smem, s, mw, mq, d);
 }
 template <class T> cudaError_t launch_epi(int epi, const CUtensorMap &mw, const CUtensorMap &mq, const SkinnyDev &d, int grid,
                                           size_t smem, cudaStream_t s) {

@@ -275,8 +275,7 @@ cudaError_t encode_map_impl(CUtensorMap *map, const void *base, int rows, int K,
 template <class T, int EPI> cudaError_t launch_inst(const CUtensorMap &ma, const CUtensorMap &mb, const GemmDev &d, cudaStream_t s) {
     const int tiles = ((d.M + BLOCK_M - 1) / BLOCK_M) * ((d.N + BLOCK_N - 1) / BLOCK_N);
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    gemm_tcgen05_kernel<T, EPI><<<grid, kThreads, SMEM_BYTES, s>>>(ma, mb, d);
-    return cudaGetLastError();
+    return launch_kernel(gemm_tcgen05_kernel<T, EPI>, dim3(grid), dim3(kThreads), (size_t)SMEM_BYTES, s, ma, mb, d);
 }
 template <class T> cudaError_t launch_epi(int epi, const CUtensorMap &ma, const CUtensorMap &mb, const GemmDev &d, cudaStream_t s) {
     switch (epi) {

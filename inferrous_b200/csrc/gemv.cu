@@ -329,8 +329,7 @@ template <int MT, class T, int EPI> cudaError_t launch_dp4a_inst(const GemvDev &
     const int rows_per_cta = kWarps / d.ks;
     const unsigned grid = (unsigned)((d.ntot + rows_per_cta - 1) / rows_per_cta);
     const size_t smem = (size_t)MT * d.K + kWarps * 2 * MT * sizeof(int);
-    gemv_dp4a_kernel<MT, T, EPI><<<grid, kThreads, smem, s>>>(d);
-    return cudaGetLastError();
+    return launch_kernel(gemv_dp4a_kernel<MT, T, EPI>, dim3(grid), dim3(kThreads), smem, s, d);
 }
 template <int MT, class T> cudaError_t launch_dp4a_epi(int epi, const GemvDev &d, cudaStream_t s) {
     switch (epi) {
@@ -354,8 +353,7 @@ template <class T> cudaError_t launch_dp4a_m(int M, int epi, const GemvDev &d, c
 template <int NT, class T, int EPI> cudaError_t launch_mma_inst(const GemvDev &d, cudaStream_t s) {
     unsigned grid = 0;
     for (int g = 0; g < d.count; ++g) grid += (unsigned)((d.n[g] + 15) / 16);
-    gemv_mma_kernel<NT, T, EPI><<<grid, kThreads, 0, s>>>(d);
-    return cudaGetLastError();
+    return launch_kernel(gemv_mma_kernel<NT, T, EPI>, dim3(grid), dim3(kThreads), (size_t)0, s, d);
 }
 template <int NT, class T> cudaError_t launch_mma_epi(int epi, const GemvDev &d, cudaStream_t s) {
     switch (epi) {

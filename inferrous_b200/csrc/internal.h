@@ -91,4 +91,26 @@ cudaError_t read_device_status(cudaStream_t s, uint32_t out[2]);
 
 int sm_count();
 
+// Programmatic dependent launch (the reference's CLEAN_PDL switch, src/gpu.rs:317; src/graph.rs:63-127):
+// when enabled, every hot-path kernel is launched with the programmatic-stream-serialization attribute,
+// so it may start while its predecessor drains; each kernel's griddepcontrol.wait keeps the data order.
+bool programmatic_launch_enabled();
+
+template <class Kernel, class... Args>
+cudaError_t launch_kernel(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    if (programmatic_launch_enabled()) {
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 }  // namespace w8a8

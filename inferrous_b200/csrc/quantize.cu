@@ -242,8 +242,7 @@ inline size_t quant_smem(int K) { return (size_t)(K + 256 + 8) * sizeof(float); 
 
 template <class T, int MODE> cudaError_t launch_q(const QuantDev &d, cudaStream_t s) {
     int grid = d.M;
-    quantize_rows_kernel<T, MODE><<<grid, kThreads, quant_smem(d.K), s>>>(d);
-    return cudaGetLastError();
+    return launch_kernel(quantize_rows_kernel<T, MODE>, dim3(grid), dim3(kThreads), quant_smem(d.K), s, d);
 }
 template <class T, int MODE> cudaError_t set_attr() {
     return cudaFuncSetAttribute(quantize_rows_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxQuantSmem);
@@ -295,10 +294,10 @@ cudaError_t launch_swiglu(const void *gate, const void *up, int dtype, int M, in
     }
     if (dtype == 0) {
         dim3 grid((I + kThreads * 8 - 1) / (kThreads * 8), M);
-        swiglu_kernel<Bf16><<<grid, kThreads, 0, s>>>((const uint16_t *)gate, (const uint16_t *)up, I, ld, (uint16_t *)act, maxima);
+        return launch_kernel(swiglu_kernel<Bf16>, grid, dim3(kThreads), (size_t)0, s, (const uint16_t *)gate, (const uint16_t *)up, I, ld, (uint16_t *)act, maxima);
     } else {
         dim3 grid((I + kThreads * 4 - 1) / (kThreads * 4), M);
-        swiglu_kernel<F32><<<grid, kThreads, 0, s>>>((const float *)gate, (const float *)up, I, ld, (float *)act, maxima);
+        return launch_kernel(swiglu_kernel<F32>, grid, dim3(kThreads), (size_t)0, s, (const float *)gate, (const float *)up, I, ld, (float *)act, maxima);
     }
     return cudaGetLastError();
 }
@@ -306,10 +305,10 @@ cudaError_t launch_swiglu(const void *gate, const void *up, int dtype, int M, in
 cudaError_t launch_residual(const void *a, const void *b, int dtype, size_t n, void *out, cudaStream_t s) {
     if (dtype == 0) {
         size_t blocks = (n + kThreads * 8 - 1) / (kThreads * 8);
-        residual_kernel<Bf16><<<(unsigned)blocks, kThreads, 0, s>>>((const uint16_t *)a, (const uint16_t *)b, n, (uint16_t *)out);
+        return launch_kernel(residual_kernel<Bf16>, dim3((unsigned)blocks), dim3(kThreads), (size_t)0, s, (const uint16_t *)a, (const uint16_t *)b, n, (uint16_t *)out);
     } else {
         size_t blocks = (n + kThreads * 4 - 1) / (kThreads * 4);
-        residual_kernel<F32><<<(unsigned)blocks, kThreads, 0, s>>>((const float *)a, (const float *)b, n, (float *)out);
+        return launch_kernel(residual_kernel<F32>, dim3((unsigned)blocks), dim3(kThreads), (size_t)0, s, (const float *)a, (const float *)b, n, (float *)out);
     }
     return cudaGetLastError();
 }

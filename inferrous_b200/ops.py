@@ -51,6 +51,11 @@ def init(device: int | None = None) -> None:
         _initialised.add(dev)
 
 
+def set_programmatic_launch(enabled: bool) -> None:
+    """The reference's CLEAN_PDL switch (src/gpu.rs:317): launch every hot-path kernel with a programmatic edge."""
+    capi.check(capi.load().w8a8_set_programmatic_launch(1 if enabled else 0), "w8a8_set_programmatic_launch")
+
+
 def device_status() -> tuple[int, int]:
     """(status, detail) of the device-side bounded waits; synchronises the current stream."""
     detail = C.c_uint32(0)
