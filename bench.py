@@ -44,15 +44,17 @@ WORKLOAD = "configs[1]: quantize+linear over 5 Qwen3-8B projections x M in {1,4,
 NCU_TRAFFIC_BYTES_PER_LAUNCH = None
 
 
-def kernel_family(M, weight_bytes, forced=0):
+def kernel_family(M, weight_bytes, K, forced=0):
     """Which kernel w8a8_linear picks (mirrors pick_variant in inferrous_b200/csrc/capi.cu)."""
-    names = {1: "naive_linear", 2: "gemv_dp4a", 3: "gemv_mma", 4: "gemm_tcgen05", 5: "gemm_skinny"}
+    names = {1: "naive_linear", 2: "gemv_dp4a", 3: "gemv_mma", 4: "gemm_tcgen05", 5: "gemm_skinny", 6: "gemv_rows"}
     if forced:
         return names[forced]
     if M <= 1:
         return "gemv_dp4a"
     if M <= 8:
         return "gemv_mma"
+    if M <= 16 and K <= 4096 and weight_bytes < (256 << 20):
+        return "gemv_rows"
     if M <= 64:
         return "gemm_skinny" if weight_bytes >= (48 << 20) else "gemv_mma"
     if M <= 256 and weight_bytes >= (256 << 20):
@@ -235,7 +237,7 @@ def run_ours(args):
                 ops.linear_quantized(b["q"], b["s"], mats[name], b["y"], args.variant)
                 if record:
                     e1.record()
-                    gemv_events.append((kernel_family(M, k * n, args.variant), linear_bytes(M, k, n), e0, e1))
+                    gemv_events.append((kernel_family(M, k * n, k, args.variant), linear_bytes(M, k, n), e0, e1))
                 if world > 1 and name in ROW_SPLIT:
                     all_reduce_sum(b["y"])  # bf16 NCCL all-reduce of the partial outputs [M,4096]
 

@@ -5,6 +5,7 @@
 // 32..255 -> linear_tiled, >= 256 (and N >= 4096) -> linear_large.  Here:
 //   gemv_dp4a      weight streaming with 16-byte loads + dp4a (1 token; fused gate/up up to 4)
 //   gemv_mma       weight streaming + warp-level int8 MMA (2..64 tokens, small and mid matrices)
+//   gemv_rows      bulk-copied weight rows in a shared-memory ring + warp-level int8 MMA (9..16 tokens, K <= 4096)
 //   gemm_skinny    TMA + tcgen05.mma kind::i8, weights on the MMA's M side, stream-K (large matrices, <= 256 tokens)
 //   gemm_tcgen05   TMA + tcgen05.mma kind::i8, 128x256 tiles, persistent (prefill)
 // see pick_variant() for the thresholds.
@@ -136,6 +137,7 @@ int w8a8_init(int device) {
     CUDA_OK(init_gemv(), "init_gemv");
     CUDA_OK(init_gemm_tcgen05(), "init_gemm_tcgen05");
     CUDA_OK(init_gemm_skinny(), "init_gemm_skinny");
+    CUDA_OK(init_gemv_rows(), "init_gemv_rows");
     d.ready = true;
     return W8A8_OK;
 }
@@ -267,14 +269,16 @@ int w8a8_rounding_probe(const float *x, int8_t *out, size_t n, void *stream) {
 // Regime selection, from measurements on B200 (CUDA events, cold weights):
 //   1 token            gemv_dp4a: whole weight rows per warp, 6.5 TB/s on the large projections
 //   2..8 tokens        gemv_mma
+//   9..16 tokens       gemv_rows when K <= 4096 and the matrix is under 256 MB, else as below
 //   9..64 tokens       gemm_skinny for the large matrices (>= 48 MB of weights), gemv_mma otherwise
 //   65..256 tokens     gemm_skinny for the very large ones (>= 256 MB), gemm_tcgen05 otherwise
 //   more               gemm_tcgen05
-static int pick_variant(int M, int epilogue, bool single_matrix, long long weight_bytes) {
+static int pick_variant(int M, int epilogue, bool single_matrix, long long weight_bytes, int K) {
     if (M <= 1) return W8A8_VARIANT_GEMV_DP4A;
     if (epilogue == EPI_SWIGLU) return W8A8_VARIANT_GEMV_DP4A;  // fused gate/up exists only there (M <= 4)
     if (!single_matrix) return W8A8_VARIANT_GEMV_MMA;  // grouped siblings, 2..16 tokens
     if (M <= 8) return W8A8_VARIANT_GEMV_MMA;
+    if (M <= 16 && K <= 4096 && weight_bytes < (256ll << 20)) return W8A8_VARIANT_GEMV_ROWS;
     if (M <= 64) return weight_bytes >= (48ll << 20) ? W8A8_VARIANT_GEMM_SKINNY : W8A8_VARIANT_GEMV_MMA;
     if (M <= kSkinnyMaxTokens && weight_bytes >= (256ll << 20)) return W8A8_VARIANT_GEMM_SKINNY;
     return W8A8_VARIANT_GEMM_TCGEN05;
@@ -283,7 +287,7 @@ static int pick_variant(int M, int epilogue, bool single_matrix, long long weigh
 static int run_linear(LinearArgs &l, const w8a8_weight *wt, int variant, void *stream) {
     REQUIRE(current_ready_device() >= 0, W8A8_ERR_NOT_INITIALIZED);
     if (variant == W8A8_VARIANT_AUTO)
-        variant = pick_variant(l.M, l.epilogue, wt != nullptr && l.count == 1, (long long)l.n[0] * l.K);
+        variant = pick_variant(l.M, l.epilogue, wt != nullptr && l.count == 1, (long long)l.n[0] * l.K, l.K);
     cudaStream_t s = (cudaStream_t)stream;
     switch (variant) {
         case W8A8_VARIANT_NAIVE: CUDA_OK(launch_linear_naive(l, s), "launch_linear_naive"); return W8A8_OK;
@@ -294,6 +298,10 @@ static int run_linear(LinearArgs &l, const w8a8_weight *wt, int variant, void *s
         case W8A8_VARIANT_GEMV_MMA:
             REQUIRE(l.M <= 64 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);
             CUDA_OK(launch_gemv_mma(l, s), "launch_gemv_mma");
+            return W8A8_OK;
+        case W8A8_VARIANT_GEMV_ROWS:
+            REQUIRE(l.M <= 16 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);
+            CUDA_OK(launch_gemv_rows(l, s), "launch_gemv_rows");
             return W8A8_OK;
         case W8A8_VARIANT_GEMM_TCGEN05:
             REQUIRE(wt && l.count == 1 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);

@@ -64,6 +64,8 @@ struct LinearArgs {
 cudaError_t launch_linear_naive(const LinearArgs &a, cudaStream_t s);
 cudaError_t launch_gemv_dp4a(const LinearArgs &a, cudaStream_t s);   // M <= 4
 cudaError_t launch_gemv_mma(const LinearArgs &a, cudaStream_t s);    // M <= 64
+cudaError_t launch_gemv_rows(const LinearArgs &a, cudaStream_t s);   // M <= 16
+cudaError_t init_gemv_rows();
 // tcgen05 path: one matrix, EPI_PLAIN / EPI_RESIDUAL / EPI_ACC
 cudaError_t launch_gemm_tcgen05(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);
 cudaError_t init_gemm_tcgen05();
