@@ -47,27 +47,31 @@ template <> __device__ __forceinline__ void store_codes<4>(int8_t *dst, const in
         (c[0] & 0xff) | ((c[1] & 0xff) << 8) | ((c[2] & 0xff) << 16) | ((uint32_t)c[3] << 24);
 }
 
-// Block-wide maximum of non-negative floats (compared as unsigned bit patterns).
+// Block-wide maximum of non-negative floats (compared as unsigned bit patterns); up to 32 warps.
 __device__ __forceinline__ float block_max(float m, uint32_t *slots, int tid) {
+    const int nwarps = blockDim.x >> 5;
     uint32_t k = warp_max_u32(__float_as_uint(m));
     if ((tid & 31) == 0) slots[tid >> 5] = k;
     __syncthreads();
-    uint32_t v = slots[tid & 7];  // 8 warps
+    uint32_t v = (tid & 31) < nwarps ? slots[tid & 31] : 0u;
     v = warp_max_u32(v);
     __syncthreads();  // slots may be reused by the next row
     return __uint_as_float(v);
 }
 
+// Launched with 256 threads per row, or 1024 when there are only a few rows (decode): the work per
+// thread then shrinks to one or two 16-byte vectors and the kernel is one memory round trip long.
 template <class T, int MODE>
-__global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const QuantDev a) {
+__global__ void __launch_bounds__(1024) quantize_rows_kernel(const QuantDev a) {
     typedef typename T::storage S;
     constexpr int V = T::kVec;
     extern __shared__ __align__(16) float smem[];
     float *row = smem;                 // K floats
     float *red = smem + a.K;           // 256 floats
-    uint32_t *slots = reinterpret_cast<uint32_t *>(red + 256);  // 8 words
+    uint32_t *slots = reinterpret_cast<uint32_t *>(red + 256);  // 32 words
     const int tid = threadIdx.x;
     const int K = a.K;
+    const int nthreads = blockDim.x;
 
     dependency_wait();
 
@@ -78,7 +82,7 @@ __global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const QuantDev 
         if (MODE == QUANT_WITH_MAX) {
             const float s = __fdiv_rn(__uint_as_float(a.maxima_in[r]), 127.0f);
             if (tid == 0) a.scale[r] = s;
-            for (int j = tid * V; j < K; j += kThreads * V) {
+            for (int j = tid * V; j < K; j += nthreads * V) {
                 float v[V];
                 Vec<T>::load(xr + j, v);
                 int c[V];
@@ -91,7 +95,7 @@ __global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const QuantDev 
 
         float m = 1e-8f;
         // pass 1: HBM -> registers -> shared (and the element-wise producer, if fused)
-        for (int j = tid * V; j < K; j += kThreads * V) {
+        for (int j = tid * V; j < K; j += nthreads * V) {
             float v[V];
             Vec<T>::load(xr + j, v);
             if (MODE == QUANT_SWIGLU) {
@@ -114,9 +118,11 @@ __global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const QuantDev 
         if (MODE == QUANT_RMSNORM) {
             __syncthreads();
             // 256 strided partial sums, each added in index order (src/kernels.rs:508-519)
-            float s = 0.0f;
-            for (int j = tid; j < K; j += kThreads) s = __fadd_rn(s, __fmul_rn(row[j], row[j]));
-            red[tid] = s;
+            if (tid < 256) {
+                float s = 0.0f;
+                for (int j = tid; j < K; j += 256) s = __fadd_rn(s, __fmul_rn(row[j], row[j]));
+                red[tid] = s;
+            }
             __syncthreads();
             if (tid < 32) {
                 // distances 128, 64, 32 then the warp distances 16..1 (src/kernels.rs:521-545)
@@ -129,7 +135,7 @@ __global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const QuantDev 
             __syncthreads();
             const float inv = rsqrt_approx(__fadd_rn(__fdiv_rn(red[0], (float)K), a.eps));
             const S *gr = static_cast<const S *>(a.x2);
-            for (int j = tid * V; j < K; j += kThreads * V) {
+            for (int j = tid * V; j < K; j += nthreads * V) {
                 float g[V], y[V];
                 Vec<T>::load(gr + j, g);
 #pragma unroll
@@ -148,7 +154,7 @@ __global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const QuantDev 
             if (a.maxima_reset) a.maxima_reset[r] = __float_as_uint(1e-8f);
         }
         // last pass: each thread re-reads exactly the elements it parked
-        for (int j = tid * V; j < K; j += kThreads * V) {
+        for (int j = tid * V; j < K; j += nthreads * V) {
             int c[V];
 #pragma unroll
             for (int i = 0; i < V; ++i) c[i] = round_i8(__fdiv_rn(row[j + i], s));
@@ -238,11 +244,12 @@ __global__ void rounding_probe_kernel(const float *x, int8_t *out, size_t n) {
 }
 
 constexpr int kMaxQuantSmem = 100 * 1024;
-inline size_t quant_smem(int K) { return (size_t)(K + 256 + 8) * sizeof(float); }
+inline size_t quant_smem(int K) { return (size_t)(K + 256 + 32) * sizeof(float); }
 
 template <class T, int MODE> cudaError_t launch_q(const QuantDev &d, cudaStream_t s) {
-    int grid = d.M;
-    return launch_kernel(quantize_rows_kernel<T, MODE>, dim3(grid), dim3(kThreads), quant_smem(d.K), s, d);
+    const int grid = d.M;
+    const int threads = (d.M <= 64 && MODE != QUANT_WITH_MAX) ? 1024 : kThreads;
+    return launch_kernel(quantize_rows_kernel<T, MODE>, dim3(grid), dim3(threads), quant_smem(d.K), s, d);
 }
 template <class T, int MODE> cudaError_t set_attr() {
     return cudaFuncSetAttribute(quantize_rows_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxQuantSmem);
