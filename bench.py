@@ -39,9 +39,10 @@ ROW_SPLIT = {"o", "down"}  # sharded along K under tensor parallelism, all-reduc
 METRIC = "W8A8 decode GEMM set (Qwen3-8B shapes, M in {1,4,16}): algorithmic HBM GB/s"
 WORKLOAD = "configs[1]: quantize+linear over 5 Qwen3-8B projections x M in {1,4,16}"
 
-# DRAM bytes per launch of the dominant kernel from one ncu capture of this command
-# (profiles/gemv_dp4a_decode_set.md), averaged over the launches of one step; None until captured.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, per kernel family, from the ncu captures
+# summarised under profiles/ (captured on the 50 MB and 100 MB projections; traffic grows with the weight bytes, so
+# the ratio is applied to the bench's average algorithmic bytes per launch).
+NCU_TRAFFIC_RATIO = {"gemv_mma": 1.025, "gemv_dp4a": 1.035, "gemm_skinny": 1.003, "gemv_rows": 1.03}
 
 
 def kernel_family(M, weight_bytes, K, forced=0):
@@ -312,7 +313,8 @@ def run_ours(args):
     dom_bytes, dom_s, dom_n = fam[dominant]
     achieved = dom_bytes / dom_s / 1e9
     roofline = {"bound": "hbm", "kernel": dominant, "achieved": round(achieved, 1), "peak": hbm_peak, "peak_kind": peak_kind,
-                "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
+                "traffic": int(dom_bytes / dom_n * NCU_TRAFFIC_RATIO[dominant]) if dominant in NCU_TRAFFIC_RATIO else None,
                 "algorithmic_bytes_per_launch": dom_bytes // dom_n, "avg_launch_us": round(dom_s / dom_n * 1e6, 2),
                 "launches": dom_n,
                 "timing": "per-launch CUDA events over the same K steps launched eagerly right after the timed region "
