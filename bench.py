@@ -346,6 +346,9 @@ def run_ours(args):
     if world == 1 and not args.no_extra:
         extra["per_shape"] = per_shape_table(torch, ops, mats, bufs, hbm_peak, args.variant)
         extra["prefill"] = prefill_table(torch, ops, mats)
+        if not args.shapes:
+            extra["quantizers"] = quantizer_table(torch, ops, hbm_peak)
+            extra["decode_fused_kernels"] = decode_fused_table(torch, ops, hbm_peak)
         body = sum(r["us"] for r in extra["per_shape"] if r["M"] == 1 and r["shape"] != "lm_head")
         head = sum(r["us"] for r in extra["per_shape"] if r["M"] == 1 and r["shape"] == "lm_head")
         if body > 0 and head > 0:
@@ -379,10 +382,12 @@ def run_ours(args):
 
 
 def time_launch(torch, fn, iters, flush):
-    """Median device time of fn() with an L2 flush before every timed launch."""
+    """Median device time of fn() with the L2 displaced before every timed launch.  The displacement is a READ of a
+    buffer twice the size of L2: it leaves clean lines behind, so the timed kernel does not pay for writing back
+    somebody else's dirty data."""
     ts = []
     for _ in range(iters):
-        flush.add_(1)
+        flush.sum()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         fn()
@@ -393,7 +398,7 @@ def time_launch(torch, fn, iters, flush):
 
 
 def per_shape_table(torch, ops, mats, bufs, hbm_peak, variant=0):
-    flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+    flush = torch.zeros(64 << 20, dtype=torch.int32, device="cuda")
     rows = []
     for M in DECODE_M:
         for name, K, N in SHAPES:
@@ -407,7 +412,7 @@ def per_shape_table(torch, ops, mats, bufs, hbm_peak, variant=0):
 
 def prefill_table(torch, ops, mats):
     """Tensor-core regime, reported beside the headline: quantize + GEMM at M in {129,512,4096}."""
-    flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+    flush = torch.zeros(64 << 20, dtype=torch.int32, device="cuda")
     rows = []
     for M in PREFILL_M:
         for name, K, N in SHAPES:
@@ -422,6 +427,70 @@ def prefill_table(torch, ops, mats):
                          "GB/s": round(linear_bytes(M, K, N) / us / 1e3, 1)})
             del x, q, s, y
     del flush
+    return rows
+
+
+def quantizer_table(torch, ops, hbm_peak):
+    """The activation quantizers of configs[2]: fused with RMSNorm (QKV / gate_up input, K=4096) and with SwiGLU
+    (down input, [M,24576] -> [M,12288]); HBM-bound.  Bytes: 2MK in + MK out + 4M (+2K gamma); SwiGLU reads 4MI.
+    Timed as 8 back-to-back launches over rotating buffer sets that together exceed the L2 (single launches of a
+    few microseconds are below what a CUDA-event pair resolves)."""
+    rows = []
+    K, I = 4096, 12288
+    for M in DECODE_M + PREFILL_M:
+        sets = max(2, min(8, (300 << 20) // max(1, 5 * M * I)))  # enough copies to push the working set past the L2
+        xs = [make_activations_device(torch, M, K, seed=M + i) for i in range(sets)]
+        gus = [make_activations_device(torch, M, 2 * I, seed=M + 50 + i) for i in range(sets)]
+        gamma = (1.0 + 0.1 * torch.randn(K, device="cuda")).to(torch.bfloat16)
+        q4 = [torch.empty((M, K), dtype=torch.int8, device="cuda") for _ in range(sets)]
+        q12 = [torch.empty((M, I), dtype=torch.int8, device="cuda") for _ in range(sets)]
+        s = torch.empty((M,), dtype=torch.float32, device="cuda")
+        cases = [("quantize", lambda i: ops.quantize(xs[i], q4[i], s), 3 * M * K + 4 * M),
+                 ("rmsnorm_quantize", lambda i: ops.norm_quantize(xs[i], gamma, None, q4[i], s, None), 3 * M * K + 4 * M + 2 * K),
+                 ("swiglu_quantize", lambda i: ops.swiglu_quantize(gus[i][:, :I], gus[i][:, I:], q12[i], s), 5 * M * I + 4 * M)]
+        for name, fn, nbytes in cases:
+            reps = 8
+            for i in range(sets):
+                fn(i)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for r in range(reps):
+                fn(r % sets)
+            e1.record()
+            e1.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps
+            rows.append({"kernel": name, "M": M, "us": round(us, 2), "GB/s": round(nbytes / us / 1e3, 1),
+                         "frac_hbm": round(nbytes / us / 1e3 / hbm_peak, 3), "buffer_sets": sets})
+        del xs, gus, q4, q12
+    return rows
+
+
+def decode_fused_table(torch, ops, hbm_peak):
+    """The fused decode kernels the reference publishes per-kernel numbers for (docs/qwen3-8b-w8a8/optimization/
+    round-6.md:11-13, on an RTX PRO 6000): gate+up+SwiGLU, O and down with residual, grouped Q/K/V; 1 token."""
+    flush = torch.zeros(64 << 20, dtype=torch.int32, device="cuda")
+    mk = lambda K, N, seed: ops.Matrix(*make_weights_device(torch, K, N, seed))
+    act = lambda n: torch.empty((1, n), dtype=torch.bfloat16, device="cuda")
+    q4 = torch.randint(-127, 128, (1, 4096), dtype=torch.int8, device="cuda")
+    q12 = torch.randint(-127, 128, (1, 12288), dtype=torch.int8, device="cuda")
+    s = torch.full((1,), 0.01, dtype=torch.float32, device="cuda")
+    wg, wu, wo, wd = mk(4096, 12288, 1), mk(4096, 12288, 2), mk(4096, 4096, 3), mk(12288, 4096, 4)
+    wq, wk, wv = mk(4096, 4096, 5), mk(4096, 1024, 6), mk(4096, 1024, 7)
+    g, u, a = act(12288), act(12288), act(12288)
+    mx = torch.zeros(1, dtype=torch.int32, device="cuda")
+    res, y, comb = act(4096), act(4096), act(4096)
+    oq, ok_, ov = act(4096), act(1024), act(1024)
+    cases = [("linear_swiglu (gate+up, 100.7 MB)", lambda: ops.linear_swiglu(q4, s, wg, wu, g, u, a, mx), 2 * 12288 * 4096, 63.22),
+             ("linear_residual O (16.8 MB)", lambda: ops.linear_residual(q4, s, wo, y, res, comb), 4096 * 4096, 11.94),
+             ("linear_residual down (50.3 MB)", lambda: ops.linear_residual(q12, s, wd, y, res, comb), 4096 * 12288, 33.94),
+             ("linear_triple QKV (25.2 MB)", lambda: ops.linear_grouped(q4, s, [wq, wk, wv], [oq, ok_, ov]), 6144 * 4096, 16.91)]
+    rows = []
+    for name, fn, wbytes, ref_us in cases:
+        fn()
+        us = time_launch(torch, fn, 20, flush)
+        rows.append({"kernel": name, "us": round(us, 2), "GB/s": round(wbytes / us / 1e3, 1),
+                     "frac_hbm": round(wbytes / us / 1e3 / hbm_peak, 3), "reference_us_rtx_pro_6000": ref_us})
     return rows
 
 

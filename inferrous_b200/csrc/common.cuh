@@ -11,7 +11,7 @@
 
 namespace w8a8 {
 
-// Code of a device-side wait that expired; written to g_device_status (see status.cu).
+// Code of a device-side wait that expired; written to the per-device status word (w8a8_device_status).
 enum DeviceWait : uint32_t {
     WAIT_NONE = 0,
     WAIT_TMA_FULL = 1,    // consumer waited for a TMA stage to land
@@ -35,6 +35,23 @@ __device__ __forceinline__ int round_i8(float x) {
     int r;
     asm("cvt.rni.s32.f32 %0, %1;" : "=r"(r) : "f"(x));  // NaN converts to 0
     return r;
+}
+
+// q = round_i8(x / s) with one multiply instead of one IEEE division per element, bit-identical to the
+// division the reference performs (src/kernels.rs:448: round(div(x, s))).
+// inv = rcp.rn(s) is computed once per row.  t = x * inv differs from the true quotient by at most
+// (1 + 2^-24)^2 - 1 < 1.2e-7 relative, i.e. by less than 1.6e-5 for |t| <= 127, and the correctly rounded
+// quotient differs from the true one by at most half an ulp (3.8e-6 below 128).  Two numbers that close
+// round to different integers only if a rounding boundary k + 0.5 lies between or on them, so whenever t is
+// farther than 4e-5 from every k + 0.5 both round alike; otherwise (about one element in 12 000, and for
+// NaN / infinity, whose distance test is false) the exact division decides.  Values beyond +-127 clamp to
+// the same code either way.
+__device__ __forceinline__ int quant_code(float x, float s, float inv) {
+    const float t = __fmul_rn(x, inv);
+    const float a = fabsf(t);
+    const float fr = a - floorf(a);
+    if (fabsf(fr - 0.5f) > 4e-5f) return round_i8(t);
+    return round_i8(__fdiv_rn(x, s));
 }
 
 // exp(x) as the reference writes it: ex2.approx(x * log2(e)) (src/kernels.rs:21-23).

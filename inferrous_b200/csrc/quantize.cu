@@ -10,8 +10,8 @@
 //
 // Design here: one 256-thread CTA per token row, 128-bit global loads, the row parked in
 // shared memory as f32 between the passes (so the row is read from HBM exactly once),
-// warp-level redux for the absmax, one IEEE division per element, 4/8 int8 codes packed per
-// store.  The sum of squares follows the reference's fixed tree (256 strided partials, then
+// warp-level redux for the absmax, a multiply with an exact-division fallback near rounding ties
+// (quant_code, bit-identical to the reference's per-element division), 4/8 int8 codes packed per store.  The sum of squares follows the reference's fixed tree (256 strided partials, then
 // distances 128..1) so that the bf16 norm row can match the reference bit for bit wherever
 // rsqrt.approx does.
 #include "common.cuh"
@@ -59,6 +59,110 @@ __device__ __forceinline__ float block_max(float m, uint32_t *slots, int tid) {
     return __uint_as_float(v);
 }
 
+// Register-resident fast path: each thread keeps its RV 16-byte vectors of the row in registers between the
+// absmax pass and the coding pass, so shared memory carries only the reductions (plain / SwiGLU) or the one
+// copy of x that the reference's summation tree walks with stride 256 (RMSNorm; stored with a 16-byte XOR
+// swizzle so that both the vector stores and the strided reads are bank-conflict free).
+// Used whenever K <= RV * blockDim.x * kVec; the generic kernel below covers the rest.
+template <class T, int MODE, int RV, int THREADS>
+__global__ void __launch_bounds__(THREADS) quantize_rows_reg_kernel(const QuantDev a) {
+    typedef typename T::storage S;
+    constexpr int V = T::kVec;
+    extern __shared__ __align__(16) float smem[];
+    float *red = smem;                                           // 256 floats
+    uint32_t *slots = reinterpret_cast<uint32_t *>(red + 256);  // 32 words
+    float *row = smem + 256 + 32;                                // K floats, RMSNorm only
+    const int tid = threadIdx.x;
+    const int K = a.K;
+    // float index swizzle: 16-byte group ^= bit 5 of the element index
+    auto swz = [](int e) { return e ^ (((e >> 5) & 1) << 2); };
+
+    dependency_wait();
+
+    for (int r = blockIdx.x; r < a.M; r += gridDim.x) {
+        const S *xr = static_cast<const S *>(a.x) + (int64_t)r * a.ld;
+        int8_t *qr = a.q + (int64_t)r * K;
+        float v[RV][V];
+        float m = 1e-8f;
+#pragma unroll
+        for (int c = 0; c < RV; ++c) {
+            const int j = (c * THREADS + tid) * V;
+            if (j < K) {
+                Vec<T>::load(xr + j, v[c]);
+                if (MODE == QUANT_SWIGLU) {
+                    const S *ur = static_cast<const S *>(a.x2) + (int64_t)r * a.ld;
+                    float u[V];
+                    Vec<T>::load(ur + j, u);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) v[c][i] = swiglu_value(v[c][i], u[i]);
+                    if (a.y_out) Vec<T>::store(static_cast<S *>(a.y_out) + (int64_t)r * K + j, v[c]);
+                }
+                if (MODE == QUANT_RMSNORM) {
+#pragma unroll
+                    for (int i = 0; i < V; i += 4)
+                        *reinterpret_cast<float4 *>(row + swz(j + i)) = make_float4(v[c][i], v[c][i + 1], v[c][i + 2], v[c][i + 3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) m = fmaxf(m, fabsf(v[c][i]));  // fmaxf drops a NaN operand
+                }
+            }
+        }
+        if (MODE == QUANT_RMSNORM) {
+            __syncthreads();
+            if (tid < 256) {  // 256 strided partial sums, each added in index order (src/kernels.rs:508-519)
+                float s = 0.0f;
+                for (int j = tid; j < K; j += 256) {
+                    const float x = row[swz(j)];
+                    s = __fadd_rn(s, __fmul_rn(x, x));
+                }
+                red[tid] = s;
+            }
+            __syncthreads();
+            if (tid < 32) {  // distances 128, 64, 32 then the warp distances 16..1 (src/kernels.rs:521-545)
+                float t = __fadd_rn(__fadd_rn(__fadd_rn(red[tid], red[tid + 128]), __fadd_rn(red[tid + 64], red[tid + 192])),
+                                    __fadd_rn(__fadd_rn(red[tid + 32], red[tid + 160]), __fadd_rn(red[tid + 96], red[tid + 224])));
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, d));
+                if (tid == 0) red[0] = t;
+            }
+            __syncthreads();
+            const float inv = rsqrt_approx(__fadd_rn(__fdiv_rn(red[0], (float)K), a.eps));
+            const S *gr = static_cast<const S *>(a.x2);
+#pragma unroll
+            for (int c = 0; c < RV; ++c) {
+                const int j = (c * THREADS + tid) * V;
+                if (j < K) {
+                    float g[V];
+                    Vec<T>::load(gr + j, g);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) {
+                        v[c][i] = bf16_rne(__fmul_rn(__fmul_rn(v[c][i], inv), g[i]));
+                        m = fmaxf(m, fabsf(v[c][i]));
+                    }
+                    if (a.y_out) Vec<T>::store(static_cast<S *>(a.y_out) + (int64_t)r * K + j, v[c]);
+                }
+            }
+        }
+        const float s = __fdiv_rn(block_max(m, slots, tid), 127.0f);
+        const float inv_s = __frcp_rn(s);
+        if (tid == 0) {
+            a.scale[r] = s;
+            if (a.maxima_reset) a.maxima_reset[r] = __float_as_uint(1e-8f);
+        }
+#pragma unroll
+        for (int c = 0; c < RV; ++c) {
+            const int j = (c * THREADS + tid) * V;
+            if (j < K) {
+                int code[V];
+#pragma unroll
+                for (int i = 0; i < V; ++i) code[i] = quant_code(v[c][i], s, inv_s);
+                store_codes<V>(qr + j, code);
+            }
+        }
+        // block_max ends with a barrier, so red[] / slots[] / row[] are free for the next row
+    }
+}
+
 // Launched with 256 threads per row, or 1024 when there are only a few rows (decode): the work per
 // thread then shrinks to one or two 16-byte vectors and the kernel is one memory round trip long.
 template <class T, int MODE>
@@ -81,13 +185,14 @@ __global__ void __launch_bounds__(1024) quantize_rows_kernel(const QuantDev a) {
 
         if (MODE == QUANT_WITH_MAX) {
             const float s = __fdiv_rn(__uint_as_float(a.maxima_in[r]), 127.0f);
+            const float inv = __frcp_rn(s);
             if (tid == 0) a.scale[r] = s;
             for (int j = tid * V; j < K; j += nthreads * V) {
                 float v[V];
                 Vec<T>::load(xr + j, v);
                 int c[V];
 #pragma unroll
-                for (int i = 0; i < V; ++i) c[i] = round_i8(__fdiv_rn(v[i], s));
+                for (int i = 0; i < V; ++i) c[i] = quant_code(v[i], s, inv);
                 store_codes<V>(qr + j, c);
             }
             continue;
@@ -149,6 +254,7 @@ __global__ void __launch_bounds__(1024) quantize_rows_kernel(const QuantDev a) {
         }
 
         const float s = __fdiv_rn(block_max(m, slots, tid), 127.0f);
+        const float inv = __frcp_rn(s);
         if (tid == 0) {
             a.scale[r] = s;
             if (a.maxima_reset) a.maxima_reset[r] = __float_as_uint(1e-8f);
@@ -157,7 +263,7 @@ __global__ void __launch_bounds__(1024) quantize_rows_kernel(const QuantDev a) {
         for (int j = tid * V; j < K; j += nthreads * V) {
             int c[V];
 #pragma unroll
-            for (int i = 0; i < V; ++i) c[i] = round_i8(__fdiv_rn(row[j + i], s));
+            for (int i = 0; i < V; ++i) c[i] = quant_code(row[j + i], s, inv);
             store_codes<V>(qr + j, c);
         }
         __syncthreads();  // row[] and red[] are reused by the next row of this CTA
@@ -248,11 +354,31 @@ inline size_t quant_smem(int K) { return (size_t)(K + 256 + 32) * sizeof(float);
 
 template <class T, int MODE> cudaError_t launch_q(const QuantDev &d, cudaStream_t s) {
     const int grid = d.M;
+    if (MODE != QUANT_WITH_MAX) {
+        // Register-resident kernels.  Few rows: 1024 threads so that the kernel is one memory round trip long.
+        // Many rows: the smallest CTA that holds the row in <= 3 vectors per thread, which keeps the register
+        // count low enough for 32-64 resident warps per SM (the bytes in flight that HBM needs).
+        const size_t smem = (256 + 32 + (MODE == QUANT_RMSNORM ? (size_t)d.K : 0)) * sizeof(float);
+        const int V = T::kVec;
+        if (d.M > 64 && d.K <= 2 * 256 * V)
+            return launch_kernel(quantize_rows_reg_kernel<T, MODE, 2, 256>, dim3(grid), dim3(256), smem, s, d);
+        if (d.M > 64 && d.K <= 3 * 512 * V)
+            return launch_kernel(quantize_rows_reg_kernel<T, MODE, 3, 512>, dim3(grid), dim3(512), smem, s, d);
+        if (d.K <= 3 * 1024 * V)
+            return launch_kernel(quantize_rows_reg_kernel<T, MODE, 3, 1024>, dim3(grid), dim3(1024), smem, s, d);
+    }
     const int threads = (d.M <= 64 && MODE != QUANT_WITH_MAX) ? 1024 : kThreads;
     return launch_kernel(quantize_rows_kernel<T, MODE>, dim3(grid), dim3(threads), quant_smem(d.K), s, d);
 }
 template <class T, int MODE> cudaError_t set_attr() {
-    return cudaFuncSetAttribute(quantize_rows_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxQuantSmem);
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(quantize_rows_kernel<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxQuantSmem))) return e;
+    if (MODE != QUANT_WITH_MAX) {
+        if ((e = cudaFuncSetAttribute(quantize_rows_reg_kernel<T, MODE, 3, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxQuantSmem))) return e;
+        if ((e = cudaFuncSetAttribute(quantize_rows_reg_kernel<T, MODE, 2, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxQuantSmem))) return e;
+        if ((e = cudaFuncSetAttribute(quantize_rows_reg_kernel<T, MODE, 3, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxQuantSmem))) return e;
+    }
+    return cudaSuccess;
 }
 
 }  // namespace

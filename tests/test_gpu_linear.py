@@ -270,3 +270,56 @@ def test_bad_arguments_are_rejected(ops):
     assert lib.w8a8_linear_ex(q.data_ptr(), a.data_ptr(), mat.handle, 5, None, y.data_ptr(), None, 0, DP4A, None) == 3
     # residual without combined
     assert lib.w8a8_linear(q.data_ptr(), a.data_ptr(), mat.handle, 5, y.data_ptr(), y.data_ptr(), None, 0, None) == 1
+
+
+def test_graph_replay_matches_eager(ops):
+    """Every launch call is legal inside stream capture and a replayed graph reproduces the eager results bit for bit
+    (operator-level counterpart of reused_graphs_match_eager, src/gpu.rs:945-982), with programmatic launches on."""
+    import torch
+
+    rng = np.random.default_rng(99)
+    K, N, I = 4096, 4096, 12288
+    w, ws = synth_weights(rng, N, K)
+    mat = make_matrix(ops, w, ws)
+    wg, wgs = synth_weights(rng, 256, K)
+    wu, wus = synth_weights(rng, 256, K)
+    mg, mu = make_matrix(ops, wg, wgs), make_matrix(ops, wu, wus)
+    gamma = to_dev(oracle.bf16((1 + 0.1 * rng.standard_normal(K)).astype(np.float32)), "bf16")
+    ops.set_programmatic_launch(True)
+    try:
+        for M in (1, 16, 129, 300):
+            x = to_dev(synth_activations(rng, M, K), "bf16")
+            res = to_dev(oracle.bf16(rng.standard_normal((M, N), dtype=np.float32)), "bf16")
+            q = torch.zeros((M, K), dtype=torch.int8, device="cuda")
+            s = torch.zeros((M,), dtype=torch.float32, device="cuda")
+            y, comb = empty_act((M, N), "bf16"), empty_act((M, N), "bf16")
+            act = empty_act((M, 256), "bf16")
+            g, u = empty_act((M, 256), "bf16"), empty_act((M, 256), "bf16")
+            mx = torch.zeros((M,), dtype=torch.int32, device="cuda")
+
+            def chain():
+                ops.norm_quantize(x, gamma, None, q, s, mx)
+                ops.linear_residual(q, s, mat, y, res, comb)
+                if M <= 16:
+                    ops.linear_swiglu(q, s, mg, mu, g, u, act, mx)
+
+            chain()
+            torch.cuda.synchronize()
+            outs = (q, s, y, comb, act, mx) if M <= 16 else (q, s, y, comb)
+            eager = [t.clone() for t in outs]
+            for t in outs:
+                t.zero_()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                chain()
+            for _ in range(2):
+                mx.zero_()
+                graph.replay()
+            torch.cuda.synchronize()
+            for a, b in zip(eager, outs):
+                assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), M
+    finally:
+        ops.set_programmatic_launch(False)
+    check_status(ops)

@@ -225,3 +225,33 @@ def test_bad_arguments_are_rejected(ops):
     lib = capi.load()
     assert lib.w8a8_quantize(None, 0, 1, 128, 128, None, None, None) == 1
     assert lib.w8a8_quantize(x.data_ptr(), 7, 2, 128, 128, q.data_ptr(), s.data_ptr(), None) == 1
+
+
+@pytest.mark.parametrize("carrier", CARRIERS)
+def test_quantize_near_rounding_ties_exact(ops, carrier):
+    """Rows whose quotients x/scale sit on, or a few ulps beside, every half-integer k+0.5: the kernel's multiply
+    with exact-division fallback must give the codes of a true IEEE division (src/kernels.rs:448)."""
+    rng = np.random.default_rng(5)
+    rows = []
+    for amax in (127.0, 100.25, 3.0, 0.0123, 77.7, 1e-3, 250.0):
+        amax = oracle.bf16(np.float32([amax]))[0]
+        s = np.float32(amax) / np.float32(127)
+        k = np.arange(0, 127, dtype=np.float32) + np.float32(0.5)
+        base = (k * s).astype(np.float32)
+        cand = []
+        for d in range(-6, 7):
+            cand.append((base.view(np.int32) + d).view(np.float32))
+        v = np.concatenate(cand + [-c for c in cand])
+        v = v[np.abs(v) <= amax]
+        if carrier == "bf16":
+            v = np.unique(oracle.bf16(v))
+        row = np.zeros(4096, np.float32)
+        take = min(v.size, 4000)
+        row[:take] = rng.permutation(v)[:take]
+        row[4095] = amax
+        rows.append(row)
+    x = np.stack(rows)
+    q, s = run_quantize(ops, x, carrier)
+    eq, es = oracle.quantize(x)
+    assert np.array_equal(bits(s), bits(es))
+    assert np.array_equal(q, eq), int((q != eq).sum())
