@@ -47,7 +47,7 @@ NCU_TRAFFIC_RATIO = {"gemv_mma": 1.025, "gemv_dp4a": 1.035, "gemm_skinny": 1.003
 
 def kernel_family(M, weight_bytes, K, forced=0):
     """Which kernel w8a8_linear picks (mirrors pick_variant in inferrous_b200/csrc/capi.cu)."""
-    names = {1: "naive_linear", 2: "gemv_dp4a", 3: "gemv_mma", 4: "gemm_tcgen05", 5: "gemm_skinny", 6: "gemv_rows"}
+    names = {1: "naive_linear", 2: "gemv_dp4a", 3: "gemv_mma", 4: "gemm_tcgen05", 5: "gemm_skinny", 6: "gemv_rows", 7: "gemm_tcgen05_wide"}
     if forced:
         return names[forced]
     if M <= 1:
@@ -345,7 +345,7 @@ def run_ours(args):
     extra = {}
     if world == 1 and not args.no_extra:
         extra["per_shape"] = per_shape_table(torch, ops, mats, bufs, hbm_peak, args.variant)
-        extra["prefill"] = prefill_table(torch, ops, mats)
+        extra["prefill"] = prefill_table(torch, ops, mats, args.prefill_variant)
         if not args.shapes:
             extra["quantizers"] = quantizer_table(torch, ops, hbm_peak)
             extra["decode_fused_kernels"] = decode_fused_table(torch, ops, hbm_peak)
@@ -410,7 +410,7 @@ def per_shape_table(torch, ops, mats, bufs, hbm_peak, variant=0):
     return rows
 
 
-def prefill_table(torch, ops, mats):
+def prefill_table(torch, ops, mats, variant=0):
     """Tensor-core regime, reported beside the headline: quantize + GEMM at M in {129,512,4096}."""
     flush = torch.zeros(64 << 20, dtype=torch.int32, device="cuda")
     rows = []
@@ -421,8 +421,8 @@ def prefill_table(torch, ops, mats):
             s = torch.empty((M,), dtype=torch.float32, device="cuda")
             y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
             ops.quantize(x, q, s)
-            ops.linear_quantized(q, s, mats[name], y)
-            us = time_launch(torch, lambda: ops.linear_quantized(q, s, mats[name], y), 5, flush)
+            ops.linear_quantized(q, s, mats[name], y, variant)
+            us = time_launch(torch, lambda: ops.linear_quantized(q, s, mats[name], y, variant), 5, flush)
             rows.append({"shape": name, "M": M, "us": round(us, 1), "TOPS": round(2.0 * M * N * K / us / 1e6, 1),
                          "GB/s": round(linear_bytes(M, K, N) / us / 1e3, 1)})
             del x, q, s, y
@@ -581,6 +581,7 @@ def main():
     ap.add_argument("--shapes", default="", help="comma-separated subset of the five projections (profiling runs)")
     ap.add_argument("--ms", default="", help="comma-separated subset of the token counts (profiling runs)")
     ap.add_argument("--variant", type=int, default=0, help="force a kernel variant for every linear call (A/B runs)")
+    ap.add_argument("--prefill-variant", type=int, default=0, help="force a kernel variant in the prefill table (A/B runs)")
     ap.add_argument("--prefill-ms", default="", help="comma-separated token counts of the prefill table (profiling runs)")
     args = ap.parse_args()
     global SHAPES, DECODE_M, PREFILL_M, WORKLOAD

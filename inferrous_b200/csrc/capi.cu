@@ -136,6 +136,7 @@ int w8a8_init(int device) {
     CUDA_OK(init_quantize(), "init_quantize");
     CUDA_OK(init_gemv(), "init_gemv");
     CUDA_OK(init_gemm_tcgen05(), "init_gemm_tcgen05");
+    CUDA_OK(init_gemm_tcgen05_wide(), "init_gemm_tcgen05_wide");
     CUDA_OK(init_gemm_skinny(), "init_gemm_skinny");
     CUDA_OK(init_gemv_rows(), "init_gemv_rows");
     d.ready = true;
@@ -272,7 +273,7 @@ int w8a8_rounding_probe(const float *x, int8_t *out, size_t n, void *stream) {
 //   9..16 tokens       gemv_rows when K <= 4096 and the matrix is under 256 MB, else as below
 //   9..64 tokens       gemm_skinny for the large matrices (>= 48 MB of weights), gemv_mma otherwise
 //   65..256 tokens     gemm_skinny for the very large ones (>= 256 MB), gemm_tcgen05 otherwise
-//   more               gemm_tcgen05
+//   more               gemm_tcgen05 (256x256-tile variant from 2048 tokens when K >= 8192)
 static int pick_variant(int M, int epilogue, bool single_matrix, long long weight_bytes, int K) {
     if (M <= 1) return W8A8_VARIANT_GEMV_DP4A;
     if (epilogue == EPI_SWIGLU) return W8A8_VARIANT_GEMV_DP4A;  // fused gate/up exists only there (M <= 4)
@@ -281,6 +282,8 @@ static int pick_variant(int M, int epilogue, bool single_matrix, long long weigh
     if (M <= 16 && K <= 4096 && weight_bytes < (256ll << 20)) return W8A8_VARIANT_GEMV_ROWS;
     if (M <= 64) return weight_bytes >= (48ll << 20) ? W8A8_VARIANT_GEMM_SKINNY : W8A8_VARIANT_GEMV_MMA;
     if (M <= kSkinnyMaxTokens && weight_bytes >= (256ll << 20)) return W8A8_VARIANT_GEMM_SKINNY;
+    // 256x256 tiles pay off once the K loop is long enough to hide their un-overlapped epilogue
+    if (M >= 2048 && K >= 8192) return W8A8_VARIANT_GEMM_TCGEN05_WIDE;
     return W8A8_VARIANT_GEMM_TCGEN05;
 }
 
@@ -306,6 +309,10 @@ static int run_linear(LinearArgs &l, const w8a8_weight *wt, int variant, void *s
         case W8A8_VARIANT_GEMM_TCGEN05:
             REQUIRE(wt && l.count == 1 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);
             CUDA_OK(launch_gemm_tcgen05(l, wt, s), "launch_gemm_tcgen05");
+            return W8A8_OK;
+        case W8A8_VARIANT_GEMM_TCGEN05_WIDE:
+            REQUIRE(wt && l.count == 1 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);
+            CUDA_OK(launch_gemm_tcgen05_wide(l, wt, s), "launch_gemm_tcgen05_wide");
             return W8A8_OK;
         case W8A8_VARIANT_GEMM_SKINNY:
             REQUIRE(wt && l.count == 1 && l.epilogue != EPI_SWIGLU && l.M <= kSkinnyMaxTokens, W8A8_ERR_UNSUPPORTED);

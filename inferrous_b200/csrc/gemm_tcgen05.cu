@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "internal.h"
 #include "ptx.cuh"
+#include "gemm_common.cuh"
 
 #include <cstdio>
 
@@ -37,16 +38,6 @@ constexpr int TMEM_COLS = 512;  // two accumulators of BLOCK_N columns
 constexpr int kThreads = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
-struct GemmDev {
-    const float *a_scale;
-    const float *w_scale;
-    int M, N, K;
-    void *y;
-    const void *residual;
-    void *combined;
-    int32_t *acc;
-    uint32_t *status;
-};
 
 template <class T, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -173,58 +164,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const bool m_ok = m < p.M;
             const float as = (EPI != EPI_ACC && m_ok) ? p.a_scale[m] : 0.0f;
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N);
-#pragma unroll 1
-            for (int c = 0; c < BLOCK_N / 32; ++c) {
-                const int n0 = n_blk * BLOCK_N + c * 32;
-                if (n0 >= p.N) break;  // warp-uniform
-                int v[32];
-                tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);
-                tmem_ld_wait();
-                if (!m_ok) continue;
-                const int64_t o = (int64_t)m * p.N + n0;
-                const bool full = (n0 + 32 <= p.N);
-                if (EPI == EPI_ACC) {
-                    if (full && (p.N & 3) == 0) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4)
-                            *reinterpret_cast<int4 *>(p.acc + o + i) = make_int4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                    } else {
-                        for (int i = 0; i < 32 && n0 + i < p.N; ++i) p.acc[o + i] = v[i];
-                    }
-                    continue;
-                }
-                if (full && (p.N % T::kVec) == 0) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += T::kVec) {
-                        float y[T::kVec];
-#pragma unroll
-                        for (int j = 0; j < T::kVec; j += 4) {
-                            const float4 w4 = __ldg(reinterpret_cast<const float4 *>(p.w_scale + n0 + i + j));
-                            y[j + 0] = dequant(v[i + j + 0], as, w4.x);
-                            y[j + 1] = dequant(v[i + j + 1], as, w4.y);
-                            y[j + 2] = dequant(v[i + j + 2], as, w4.z);
-                            y[j + 3] = dequant(v[i + j + 3], as, w4.w);
-                        }
-                        if (p.y) Vec<T>::store(static_cast<S *>(p.y) + o + i, y);
-                        if (EPI == EPI_RESIDUAL) {
-                            float r[T::kVec];
-                            Vec<T>::load(static_cast<const S *>(p.residual) + o + i, r);
-#pragma unroll
-                            for (int j = 0; j < T::kVec; ++j) r[j] = bf16_rne(__fadd_rn(r[j], y[j]));
-                            Vec<T>::store(static_cast<S *>(p.combined) + o + i, r);
-                        }
-                    }
-                } else {
-                    for (int i = 0; i < 32 && n0 + i < p.N; ++i) {
-                        const float y = dequant(v[i], as, p.w_scale[n0 + i]);
-                        if (p.y) T::store(static_cast<S *>(p.y) + o + i, y);
-                        if (EPI == EPI_RESIDUAL) {
-                            const float r = T::load(static_cast<const S *>(p.residual) + o + i);
-                            T::store(static_cast<S *>(p.combined) + o + i, bf16_rne(__fadd_rn(r, y)));
-                        }
-                    }
-                }
-            }
+            drain_accumulator<T, EPI>(p, t_row, m, m_ok, as, n_blk * BLOCK_N, BLOCK_N);
             // accumulator drained: hand it back to the MMA issuer
             tc_fence_before();
             __syncwarp();
