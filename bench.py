@@ -47,7 +47,7 @@ NCU_TRAFFIC_RATIO = {"gemv_mma": 1.025, "gemv_dp4a": 1.035, "gemm_skinny": 1.003
 
 def kernel_family(M, weight_bytes, K, forced=0):
     """Which kernel w8a8_linear picks (mirrors pick_variant in inferrous_b200/csrc/capi.cu)."""
-    names = {1: "naive_linear", 2: "gemv_dp4a", 3: "gemv_mma", 4: "gemm_tcgen05", 5: "gemm_skinny", 6: "gemv_rows", 7: "gemm_tcgen05_wide"}
+    names = {1: "naive_linear", 2: "gemv_dp4a", 3: "gemv_mma", 4: "gemm_tcgen05", 5: "gemm_skinny", 6: "gemv_rows", 7: "gemm_tcgen05_wide", 8: "gemm_tcgen05_pair"}
     if forced:
         return names[forced]
     if M <= 1:
@@ -58,9 +58,9 @@ def kernel_family(M, weight_bytes, K, forced=0):
         return "gemv_rows"
     if M <= 64:
         return "gemm_skinny" if weight_bytes >= (48 << 20) else "gemv_mma"
-    if M <= 256 and weight_bytes >= (256 << 20):
-        return "gemm_skinny"
-    return "gemm_tcgen05"
+    if M <= 128:
+        return "gemm_skinny" if weight_bytes >= (256 << 20) else "gemm_tcgen05"
+    return "gemm_tcgen05_pair"
 
 
 def linear_bytes(M, K, N):

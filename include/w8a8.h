@@ -55,7 +55,8 @@ typedef enum {
     W8A8_VARIANT_GEMM_TCGEN05 = 4, /* any M: TMA-staged 128x256 tiles + tcgen05.mma kind::i8 into TMEM */
     W8A8_VARIANT_GEMM_SKINNY = 5,  /* M <= 256: tcgen05 with the weights on the MMA's M side, stream-K split */
     W8A8_VARIANT_GEMV_ROWS = 6,    /* M <= 16: whole weight rows through a bulk-copy ring + warp-level int8 MMA */
-    W8A8_VARIANT_GEMM_TCGEN05_WIDE = 7 /* any M: as GEMM_TCGEN05 with 256x256 tiles (less operand traffic per MMA) */
+    W8A8_VARIANT_GEMM_TCGEN05_WIDE = 7, /* any M: as GEMM_TCGEN05 with 256x256 tiles (less operand traffic per MMA) */
+    W8A8_VARIANT_GEMM_TCGEN05_PAIR = 8  /* any M: 256x256 tiles over CTA pairs (tcgen05.mma.cta_group::2) */
 } w8a8_variant_t;
 
 /* Immutable weight matrix handle: device pointers, shape and the TMA descriptor of the

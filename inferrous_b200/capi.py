@@ -8,7 +8,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libw8a8.so"
 
 OK = 0
 BF16, F32 = 0, 1
-VARIANT_AUTO, VARIANT_NAIVE, VARIANT_GEMV_DP4A, VARIANT_GEMV_MMA, VARIANT_GEMM_TCGEN05, VARIANT_GEMM_SKINNY, VARIANT_GEMV_ROWS, VARIANT_GEMM_TCGEN05_WIDE = range(8)
+VARIANT_AUTO, VARIANT_NAIVE, VARIANT_GEMV_DP4A, VARIANT_GEMV_MMA, VARIANT_GEMM_TCGEN05, VARIANT_GEMM_SKINNY, VARIANT_GEMV_ROWS, VARIANT_GEMM_TCGEN05_WIDE, VARIANT_GEMM_TCGEN05_PAIR = range(9)
 
 _vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 

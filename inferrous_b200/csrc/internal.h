@@ -71,6 +71,8 @@ cudaError_t launch_gemm_tcgen05(const LinearArgs &a, const w8a8_weight *wt, cuda
 cudaError_t init_gemm_tcgen05();
 cudaError_t launch_gemm_tcgen05_wide(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);  // 256x256 tiles
 cudaError_t init_gemm_tcgen05_wide();
+cudaError_t launch_gemm_tcgen05_pair(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);  // CTA pairs
+cudaError_t init_gemm_tcgen05_pair();
 cudaError_t make_weight_maps(w8a8_weight *wt);  // TMA descriptors of the [N,K] matrix
 // [rows,K] int8 row-major -> tiled map with a box of 128 bytes of K x box_rows rows, 128-byte swizzle, zero fill.
 cudaError_t encode_tile_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows);

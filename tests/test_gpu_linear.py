@@ -12,7 +12,7 @@ from tests.util import bits, empty_act, synth_activations, synth_weights, to_dev
 
 pytestmark = pytest.mark.gpu
 
-NAIVE, DP4A, MMA, TC, SKINNY, ROWS, WIDE = 1, 2, 3, 4, 5, 6, 7
+NAIVE, DP4A, MMA, TC, SKINNY, ROWS, WIDE, PAIR = 1, 2, 3, 4, 5, 6, 7, 8
 CARRIERS = ["bf16", "f32"]
 
 
@@ -27,7 +27,7 @@ def ops():
 
 
 def variants_for(M):
-    v = [NAIVE, TC, WIDE]
+    v = [NAIVE, TC, WIDE, PAIR]
     if M <= 256:
         v.append(SKINNY)
     if M <= 16:
