@@ -181,6 +181,29 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     ops.init(local)
     ops.set_programmatic_launch(not args.no_pdl)
+    # Sum of the row-split partial outputs: NCCL, or (--peer-allreduce) the library's one-shot peer-memory kernel.
+    reducer, reduce_kind, reduce_check = None, "none", None
+    if world > 1:
+        reduce_kind = "nccl"
+        if args.peer_allreduce:
+            try:
+                from inferrous_b200.tp import PeerAllReduce
+                reducer = PeerAllReduce(dist.group.WORLD, slot_elems=max(DECODE_M) * 4096)
+                # self-check against NCCL on seeded data before anything is timed
+                t = (torch.randn(16 * 4096, device="cuda", generator=torch.Generator(device="cuda").manual_seed(rank)) * 3).to(torch.bfloat16)
+                ref = t.float().clone()
+                dist.all_reduce(ref)
+                got = reducer.all_reduce(t.clone())
+                torch.cuda.synchronize()
+                err = (got.float() - ref).abs().max().item() / max(1e-6, ref.abs().max().item())
+                same = torch.tensor([1.0 if err < 2e-2 else 0.0], device="cuda")
+                dist.all_reduce(same, op=dist.ReduceOp.MIN)
+                if same.item() < 1.0:
+                    raise RuntimeError(f"peer all-reduce differs from NCCL (rel err {err:.3g})")
+                reduce_kind, reduce_check = "peer_memory_one_shot", f"max rel err vs f32 NCCL sum {err:.2e}"
+            except Exception as exc:
+                print(f"bench: peer-memory all-reduce unavailable ({exc}); using NCCL", file=sys.stderr)
+                reducer = None
     hbm_peak, _, peak_kind = measured_peaks()
 
     # ---- resident weights (model state) and per-(M,shape) activation/output buffers ----
@@ -240,7 +263,10 @@ def run_ours(args):
                     e1.record()
                     gemv_events.append((kernel_family(M, k * n, k, args.variant), linear_bytes(M, k, n), e0, e1))
                 if world > 1 and name in ROW_SPLIT:
-                    all_reduce_sum(b["y"])  # bf16 NCCL all-reduce of the partial outputs [M,4096]
+                    if reducer is not None:
+                        reducer.all_reduce(b["y"])  # one kernel: push to peers, wait, sum in rank order
+                    else:
+                        all_reduce_sum(b["y"])  # bf16 NCCL all-reduce of the partial outputs [M,4096]
 
     def step_e2e():
         step(host_io=True)
@@ -361,6 +387,7 @@ def run_ours(args):
            "config": {"workload": WORKLOAD, "shapes": {n: [K, N] for n, K, N in SHAPES}, "M": DECODE_M,
                       "parallelism": f"tp{world}" if world > 1 else "single",
                       "launch": launch_mode + ("" if args.no_pdl else "+programmatic_dependent_launch"),
+                      "all_reduce": reduce_kind, "all_reduce_check": reduce_check,
                       "l2": f"weights ({sum(shard(n, K, N, tp)[0] * shard(n, K, N, tp)[1] for n, K, N in SHAPES) >> 20} MiB streamed per "
                             "pass, each matrix revisited only after all the others) exceed the 126 MB L2; no flush",
                       "bytes_per_step": step_bytes},
@@ -575,6 +602,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-pdl", action="store_true", help="ordinary launches instead of programmatic dependent launches")
+    ap.add_argument("--peer-allreduce", action="store_true",
+                    help="tensor parallel: the library's one-shot peer-memory all-reduce instead of NCCL (measured 3 us per "
+                         "call slower than NCCL at 2 and 4 GPUs, so NCCL is the default)")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--no-extra", action="store_true", help="skip the per-shape and prefill tables")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")

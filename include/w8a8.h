@@ -172,6 +172,18 @@ int w8a8_linear_gate_up_swiglu(const int8_t *q, const float *a_scale, w8a8_weigh
 int w8a8_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w, const float *w_scale, int M, int N,
                          int K, void *y, int dtype, void *stream);
 
+/* Tensor-parallel sum of the row-split projections' partial outputs (O, down) over peer memory; no counterpart in
+ * the reference, which is single-GPU.  One kernel per rank pushes the local partial into every rank's staging buffer
+ * with plain peer stores, waits (bounded) for the other ranks' pushes and writes out = bf16(sum over ranks, in rank
+ * order, accumulated in f32) -- identical on every rank.
+ *   peer_bufs[p]   staging buffer of rank p, visible from this GPU: 2 * tp * slot_el elements
+ *   peer_flags[p]  flag pad of rank p: tp uint32 counters, zero before the first call
+ *   seq            4 uint32 in local memory, zero before the first call (call number and CTA counts, kept by the kernel)
+ * Every rank must issue the same sequence of calls with the same n_el.  An expired wait is reported by
+ * w8a8_device_status.  Meant for decode-sized messages (n_el <= slot_el). */
+int w8a8_tp_allreduce(const void *partial, void *out, size_t n_el, int dtype, void *const *peer_bufs,
+                      uint32_t *const *peer_flags, uint32_t *seq, int rank, int tp, size_t slot_el, void *stream);
+
 /* Raw int32 accumulators acc[M,N] of the product (debug / parity: the reference's tests
  * hold these bit-exact through its CPU-integer fixtures, tools/operator_fixtures.py:54). */
 int w8a8_linear_acc_i32(const int8_t *q, w8a8_weight_t weight, int M, int32_t *acc, int variant, void *stream);

@@ -401,6 +401,18 @@ int w8a8_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w,
     return W8A8_OK;
 }
 
+int w8a8_tp_allreduce(const void *partial, void *out, size_t n_el, int dtype, void *const *peer_bufs, uint32_t *const *peer_flags,
+                      uint32_t *seq, int rank, int tp, size_t slot_el, void *stream) {
+    REQUIRE(partial && out && peer_bufs && peer_flags && seq && check_dtype(dtype), W8A8_ERR_BAD_ARG);
+    REQUIRE(tp >= 1 && tp <= 8 && rank >= 0 && rank < tp && n_el > 0 && n_el <= slot_el, W8A8_ERR_BAD_ARG);
+    REQUIRE(n_el % elem_vec(dtype) == 0 && slot_el % elem_vec(dtype) == 0 && aligned16(partial) && aligned16(out), W8A8_ERR_ALIGNMENT);
+    for (int p = 0; p < tp; ++p) REQUIRE(peer_bufs[p] && peer_flags[p] && aligned16(peer_bufs[p]), W8A8_ERR_BAD_ARG);
+    REQUIRE(current_ready_device() >= 0, W8A8_ERR_NOT_INITIALIZED);
+    CUDA_OK(launch_tp_allreduce(partial, out, n_el, dtype, peer_bufs, peer_flags, seq, rank, tp, slot_el, (cudaStream_t)stream),
+            "launch_tp_allreduce");
+    return W8A8_OK;
+}
+
 int w8a8_linear_acc_i32(const int8_t *q, w8a8_weight_t weight, int M, int32_t *acc, int variant, void *stream) {
     REQUIRE(valid_weight(weight) && q && acc && M > 0, W8A8_ERR_BAD_ARG);
     REQUIRE(aligned16(q) && aligned16(acc), W8A8_ERR_ALIGNMENT);

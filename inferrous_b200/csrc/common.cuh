@@ -18,6 +18,7 @@ enum DeviceWait : uint32_t {
     WAIT_STAGE_EMPTY = 2, // producer waited for the MMA to release a stage
     WAIT_ACC_FULL = 3,    // epilogue waited for an accumulator
     WAIT_ACC_EMPTY = 4,   // MMA waited for the epilogue to drain an accumulator
+    WAIT_PEER = 5,        // tensor-parallel all-reduce waited for another rank's partial outputs
 };
 
 __device__ __forceinline__ float bf16_rne(float x) {

@@ -95,6 +95,10 @@ cudaError_t init_quantize();
 uint32_t *device_status_ptr();  // device address of the 2-word status block of the current device
 cudaError_t read_device_status(cudaStream_t s, uint32_t out[2]);
 
+// one-shot all-reduce over peer memory (tp_allreduce.cu)
+cudaError_t launch_tp_allreduce(const void *partial, void *out, size_t n_el, int dtype, void *const *bufs, uint32_t *const *flags,
+                                uint32_t *seq, int rank, int tp, size_t slot_el, cudaStream_t s);
+
 int sm_count();
 
 // Programmatic dependent launch (the reference's CLEAN_PDL switch, src/gpu.rs:317; src/graph.rs:63-127):

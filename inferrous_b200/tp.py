@@ -57,3 +57,54 @@ def all_reduce_sum(y, group=None):
 
     dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
     return y
+
+
+class PeerAllReduce:
+    """One-shot all-reduce of decode-sized partial outputs over peer memory (w8a8_tp_allreduce).
+
+    Each rank owns a staging buffer in symmetric memory ([2 halves][tp slots][slot_elems]) and a flag pad; every
+    rank sees every other rank's buffer and pad through NVLink.  `all_reduce(partial, out)` queues ONE kernel on the
+    current stream: push to all ranks, bounded wait, sum in rank order (f32) -> bf16.  Capturable in a CUDA graph.
+    Falls back to nothing: if symmetric memory cannot be set up, construction raises and the caller uses NCCL."""
+
+    def __init__(self, group, slot_elems: int, dtype=None):
+        import ctypes as C
+
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from . import capi
+
+        self.tp = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.dtype = dtype or torch.bfloat16
+        self.slot_elems = (slot_elems + 127) // 128 * 128
+        dev = torch.device("cuda", torch.cuda.current_device())
+        # one symmetric allocation: 256 bytes of arrival counters (the library's own, not torch's signal pad),
+        # then the two halves of the staging area
+        flag_elems = 256 // torch.empty((), dtype=self.dtype).element_size()
+        self.buf = symm.empty(flag_elems + 2 * self.tp * self.slot_elems, dtype=self.dtype, device=dev)
+        self.handle = symm.rendezvous(self.buf, group.group_name if hasattr(group, "group_name") else group)
+        self.buf.zero_()
+        self.seq = torch.zeros(4, dtype=torch.int32, device=dev)
+        self._flags = (C.c_void_p * self.tp)(*[int(p) for p in self.handle.buffer_ptrs])
+        self._bufs = (C.c_void_p * self.tp)(*[int(p) + 256 for p in self.handle.buffer_ptrs])
+        self._lib = capi.load()
+        self._capi = capi
+        torch.cuda.synchronize()
+        dist.barrier(group)
+
+    def all_reduce(self, partial, out=None):
+        import ctypes as C
+
+        import torch
+
+        out = partial if out is None else out
+        n = partial.numel()
+        code = 0 if partial.dtype == torch.bfloat16 else 1
+        st = self._lib.w8a8_tp_allreduce(C.c_void_p(partial.data_ptr()), C.c_void_p(out.data_ptr()), n, code, self._bufs,
+                                         self._flags, C.c_void_p(self.seq.data_ptr()), self.rank, self.tp, self.slot_elems,
+                                         C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        self._capi.check(st, "w8a8_tp_allreduce")
+        return out

@@ -323,3 +323,32 @@ def test_graph_replay_matches_eager(ops):
     finally:
         ops.set_programmatic_launch(False)
     check_status(ops)
+
+
+def test_tp_allreduce_single_rank_degenerate(ops):
+    """w8a8_tp_allreduce with tp=1 (the only form one GPU can run): push to self, wait on self, out = bf16(partial),
+    repeated so that both halves of the staging buffer and the device-side call counter are exercised."""
+    import ctypes as C
+    import torch
+    from inferrous_b200 import capi
+
+    lib = capi.load()
+    slot = 16 * 4096
+    buf = torch.zeros(2 * slot, dtype=torch.bfloat16, device="cuda")
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    seq = torch.zeros(4, dtype=torch.int32, device="cuda")
+    bufs = (C.c_void_p * 1)(buf.data_ptr())
+    fl = (C.c_void_p * 1)(flags.data_ptr())
+    for call in range(5):
+        n = (4096, 16 * 4096, 4 * 4096, 16 * 4096, 4096)[call]  # different sizes are cut into different CTA counts
+        x = (torch.randn(n, device="cuda") * (call + 1)).to(torch.bfloat16)
+        out = torch.zeros_like(x)
+        st = lib.w8a8_tp_allreduce(x.data_ptr(), out.data_ptr(), n, 0, bufs, fl, seq.data_ptr(), 0, 1, slot, None)
+        assert st == 0
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), x.view(torch.int16))
+    assert seq.tolist() == [5, 0, 0, 0] and flags[0].item() == 5
+    check_status(ops)
+    # bad arguments
+    assert lib.w8a8_tp_allreduce(x.data_ptr(), out.data_ptr(), n, 0, bufs, fl, seq.data_ptr(), 1, 1, slot, None) == 1
+    assert lib.w8a8_tp_allreduce(x.data_ptr(), out.data_ptr(), n + 3, 0, bufs, fl, seq.data_ptr(), 0, 1, 2 * slot, None) == 2
