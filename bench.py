@@ -54,8 +54,8 @@ def kernel_family(M, weight_bytes, K, forced=0):
         return "gemv_dp4a"
     if M <= 8:
         return "gemv_mma"
-    if M <= 16 and K <= 4096 and weight_bytes < (256 << 20):
-        return "gemv_rows"
+    if M <= 16:
+        return "gemm_skinny" if weight_bytes >= (256 << 20) else "gemv_mma"
     if M <= 64:
         return "gemm_skinny" if weight_bytes >= (48 << 20) else "gemv_mma"
     if M <= 128:

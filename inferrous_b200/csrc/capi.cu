@@ -5,7 +5,7 @@
 // 32..255 -> linear_tiled, >= 256 (and N >= 4096) -> linear_large.  Here:
 //   gemv_dp4a      weight streaming with 16-byte loads + dp4a (1 token; fused gate/up up to 4)
 //   gemv_mma       weight streaming + warp-level int8 MMA (2..64 tokens, small and mid matrices)
-//   gemv_rows      bulk-copied weight rows in a shared-memory ring + warp-level int8 MMA (9..16 tokens, K <= 4096)
+//   gemv_rows      bulk-copied weight rows in a shared-memory ring + warp-level int8 MMA (selectable variant)
 //   gemm_skinny    TMA + tcgen05.mma kind::i8, weights on the MMA's M side, stream-K (large matrices, <= 256 tokens)
 //   gemm_tcgen05   TMA + tcgen05.mma kind::i8, 128x256 tiles, persistent (65..128 tokens)
 //   gemm_tcgen05_pair  the same over CTA pairs (cta_group::2), 256x256 tiles (prefill, >= 129 tokens)
@@ -273,8 +273,8 @@ int w8a8_rounding_probe(const float *x, int8_t *out, size_t n, void *stream) {
 // Regime selection, from measurements on B200 (CUDA events, cold weights):
 //   1 token            gemv_dp4a: whole weight rows per warp, 6.5 TB/s on the large projections
 //   2..8 tokens        gemv_mma
-//   9..16 tokens       gemv_rows when K <= 4096 and the matrix is under 256 MB, else as below
-//   9..64 tokens       gemm_skinny for the large matrices (>= 48 MB of weights), gemv_mma otherwise
+//   9..16 tokens       gemm_skinny for the very large matrices (>= 256 MB), gemv_mma otherwise
+//   17..64 tokens      gemm_skinny for the large matrices (>= 48 MB of weights), gemv_mma otherwise
 //   65..128 tokens     gemm_skinny for the very large ones (>= 256 MB), gemm_tcgen05 otherwise
 //   more               gemm_tcgen05_pair (256x256 tiles over CTA pairs)
 static int pick_variant(int M, int epilogue, bool single_matrix, long long weight_bytes, int K) {
@@ -282,7 +282,7 @@ static int pick_variant(int M, int epilogue, bool single_matrix, long long weigh
     if (epilogue == EPI_SWIGLU) return W8A8_VARIANT_GEMV_DP4A;  // fused gate/up exists only there (M <= 4)
     if (!single_matrix) return W8A8_VARIANT_GEMV_MMA;  // grouped siblings, 2..16 tokens
     if (M <= 8) return W8A8_VARIANT_GEMV_MMA;
-    if (M <= 16 && K <= 4096 && weight_bytes < (256ll << 20)) return W8A8_VARIANT_GEMV_ROWS;
+    if (M <= 16) return weight_bytes >= (256ll << 20) ? W8A8_VARIANT_GEMM_SKINNY : W8A8_VARIANT_GEMV_MMA;
     if (M <= 64) return weight_bytes >= (48ll << 20) ? W8A8_VARIANT_GEMM_SKINNY : W8A8_VARIANT_GEMV_MMA;
     if (M <= 128) return weight_bytes >= (256ll << 20) ? W8A8_VARIANT_GEMM_SKINNY : W8A8_VARIANT_GEMM_TCGEN05;
     return W8A8_VARIANT_GEMM_TCGEN05_PAIR;  // 256x256 tiles over CTA pairs: 5-16 % faster than 128x256 tiles from 129 tokens up

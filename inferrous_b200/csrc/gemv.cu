@@ -256,28 +256,44 @@ __global__ void __launch_bounds__(kThreads) gemv_mma_kernel(const GemvDev a) {
 
     dependency_wait();
 
+    // Token fragments travel with the weights: they are fetched one step ahead of their use, so the MMAs of a
+    // step wait on nothing but registers.
     const int8_t *qb = a.q + t * 16;
-    auto compute = [&](int s, const uint4(&lo)[2], const uint4(&hi)[2]) {
-        const int k0 = s * 128;
+    uint4 b0[2][NT], b1[2][NT];
+    auto load_b = [&](int s, uint4(&b)[2][NT]) {
+        if (s < nsteps) {
+            const int k0 = s * 128;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const int tok = j * 8 + gq;
+                    b[h][j] = tok < a.M ? *reinterpret_cast<const uint4 *>(qb + (int64_t)tok * K + k0 + h * 64) : make_uint4(0, 0, 0, 0);
+                }
+        }
+    };
+    auto compute = [&](const uint4(&lo)[2], const uint4(&hi)[2], const uint4(&b)[2][NT]) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const uint4 r = lo[h], v = hi[h];
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                const int tok = j * 8 + gq;
-                uint4 p = make_uint4(0, 0, 0, 0);
-                if (tok < a.M) p = *reinterpret_cast<const uint4 *>(qb + (int64_t)tok * K + k0 + h * 64);
+                const uint4 p = b[h][j];
                 mma_s8(acc[j], r.x, v.x, r.y, v.y, p.x, p.y);
                 mma_s8(acc[j], r.z, v.z, r.w, v.w, p.z, p.w);
             }
         }
     };
+    load_b(warp, b0);
+    load_b(warp + kWarps, b1);
     for (int s = warp; s < nsteps; s += 2 * kWarps) {
-        compute(s, lo0, hi0);
+        compute(lo0, hi0, b0);
         load_w(s + 2 * kWarps, lo0, hi0);
+        load_b(s + 2 * kWarps, b0);
         if (s + kWarps < nsteps) {
-            compute(s + kWarps, lo1, hi1);
+            compute(lo1, hi1, b1);
             load_w(s + 3 * kWarps, lo1, hi1);
+            load_b(s + 3 * kWarps, b1);
         }
     }
 
