@@ -172,6 +172,16 @@ int w8a8_linear_gate_up_swiglu(const int8_t *q, const float *a_scale, w8a8_weigh
 int w8a8_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w, const float *w_scale, int M, int N,
                          int K, void *y, int dtype, void *stream);
 
+/* Head projection with greedy token selection fused into its epilogue: token[m] = argmax_n of
+ * y[m,n] = bf16((f32(acc) * a_scale[m]) * w_scale[n]) without ever storing the logits.  Selection follows
+ * `select_token` (src/kernels.rs:2191-2231; host check model::argmax, src/model.rs:206-218): the largest value wins,
+ * equal values (0.0 and -0.0 included) go to the lowest index, and a row with any non-finite logit yields 0xffffffff.
+ * value (optional) receives the winning logit.  Replaces the pair `head` + `select_token` (src/gpu.rs:801-811) for a
+ * W8A8 head; the reference's own head is bf16 weights (src/kernels.rs:2233-2373).  M <= 16, N <= 262144.
+ * Calls on different streams share one per-device candidate buffer: keep them in order. */
+int w8a8_linear_argmax(const int8_t *q, const float *a_scale, w8a8_weight_t weight, int M, uint32_t *token, float *value,
+                       void *stream);
+
 /* Tensor-parallel sum of the row-split projections' partial outputs (O, down) over peer memory; no counterpart in
  * the reference, which is single-GPU.  One kernel per rank pushes the local partial into every rank's staging buffer
  * with plain peer stores, waits (bounded) for the other ranks' pushes and writes out = bf16(sum over ranks, in rank

@@ -29,6 +29,7 @@ struct DeviceState {
     uint32_t *status = nullptr;  // 2 words: [0] wait code, [1] detail
     int32_t *sk_scratch = nullptr;   // stream-K partial tiles, zero between launches
     uint32_t *sk_counters = nullptr; // stream-K arrival counters, zero between launches
+    unsigned long long *argmax = nullptr;  // per-block candidates of the fused head projection
 };
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;
@@ -61,6 +62,10 @@ uint32_t *device_status_ptr() {
 int32_t *skinny_scratch() {
     int dev = current_ready_device();
     return dev < 0 ? nullptr : g_dev[dev].sk_scratch;
+}
+unsigned long long *argmax_scratch() {
+    int dev = current_ready_device();
+    return dev < 0 ? nullptr : g_dev[dev].argmax;
 }
 uint32_t *skinny_counters() {
     int dev = current_ready_device();
@@ -135,6 +140,7 @@ int w8a8_init(int device) {
     CUDA_OK(cudaMemset(d.sk_scratch, 0, sk_bytes), "cudaMemset(stream-K scratch)");
     CUDA_OK(cudaMalloc(&d.sk_counters, (size_t)d.sms * 4 * sizeof(uint32_t)), "cudaMalloc(stream-K counters)");
     CUDA_OK(cudaMemset(d.sk_counters, 0, (size_t)d.sms * 4 * sizeof(uint32_t)), "cudaMemset(stream-K counters)");
+    CUDA_OK(cudaMalloc(&d.argmax, (size_t)kArgmaxMaxBlocks * 16 * sizeof(unsigned long long)), "cudaMalloc(argmax candidates)");
     CUDA_OK(init_quantize(), "init_quantize");
     CUDA_OK(init_gemv(), "init_gemv");
     CUDA_OK(init_gemm_tcgen05(), "init_gemm_tcgen05");
@@ -398,6 +404,22 @@ int w8a8_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w,
         return W8A8_ERR_UNSUPPORTED;
     }
     CUDA_OK(launch_linear_no_alloc(q, a_scale, w, w_scale, M, N, K, y, dtype, (cudaStream_t)stream), "launch_linear_no_alloc");
+    return W8A8_OK;
+}
+
+int w8a8_linear_argmax(const int8_t *q, const float *a_scale, w8a8_weight_t weight, int M, uint32_t *token, float *value,
+                       void *stream) {
+    REQUIRE(valid_weight(weight) && q && a_scale && token && M > 0, W8A8_ERR_BAD_ARG);
+    REQUIRE(aligned16(q), W8A8_ERR_ALIGNMENT);
+    REQUIRE(M <= 16 && (weight->N + 15) / 16 <= kArgmaxMaxBlocks, W8A8_ERR_UNSUPPORTED);
+    REQUIRE(current_ready_device() >= 0, W8A8_ERR_NOT_INITIALIZED);
+    LinearArgs l{};
+    l.q = q; l.a_scale = a_scale; l.M = M; l.K = weight->K; l.count = 1; l.dtype = W8A8_BF16;
+    l.w[0] = weight->w; l.ws[0] = weight->w_scale; l.n[0] = weight->N;
+    l.epilogue = EPI_ARGMAX; l.partial_best = argmax_scratch();
+    cudaStream_t s = (cudaStream_t)stream;
+    CUDA_OK(launch_gemv_mma(l, s), "launch_gemv_mma(argmax)");
+    CUDA_OK(launch_argmax_finish(l.partial_best, (weight->N + 15) / 16, M, token, value, s), "launch_argmax_finish");
     return W8A8_OK;
 }
 

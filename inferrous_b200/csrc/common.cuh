@@ -78,6 +78,16 @@ __device__ __forceinline__ uint32_t absmax_key(float v) {
     return bits > 0x7f800000u ? 0u : bits;
 }
 
+// Greedy selection key: larger value wins, equal values (0.0 == -0.0 included) go to the LOWER index, as the
+// reference's select_token does (src/kernels.rs:2191-2231).  A non-finite value poisons the row (index ~0).
+__device__ __forceinline__ unsigned long long argmax_key(float v, uint32_t index) {
+    if (!(fabsf(v) <= 3.402823466e38f)) return ~0ull;  // NaN or infinity: wins every max, flags the row as bad
+    v = v + 0.0f;                                       // -0.0 -> +0.0
+    const uint32_t b = __float_as_uint(v);
+    const uint32_t ordered = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((unsigned long long)ordered << 32) | (unsigned long long)(0xffffffffu - index);
+}
+
 // The epilogue of every projection (src/kernels.rs:290): two separately rounded multiplies, then bf16.
 __device__ __forceinline__ float dequant(int acc, float a_scale, float w_scale) {
     return bf16_rne(__fmul_rn(__fmul_rn(__int2float_rn(acc), a_scale), w_scale));

@@ -39,6 +39,7 @@ struct GemvDev {
     void *act;
     uint32_t *maxima;
     int32_t *acc;
+    unsigned long long *partial_best;
 };
 
 __device__ __forceinline__ int dp4a_16(const uint4 &w, const uint4 &a, int acc) {
@@ -303,6 +304,7 @@ __global__ void __launch_bounds__(kThreads) gemv_mma_kernel(const GemvDev a) {
         for (int i = 0; i < 4; ++i) red[warp][(j * 4 + i) * 32 + lane] = acc[j][i];
     __syncthreads();
 
+    __shared__ unsigned long long cand[(EPI == EPI_ARGMAX) ? NT * 8 * 16 : 1];  // [token][row of the block]
     for (int idx = tid; idx < NT * 128; idx += kThreads) {
         int sum = 0;
 #pragma unroll
@@ -310,6 +312,13 @@ __global__ void __launch_bounds__(kThreads) gemv_mma_kernel(const GemvDev a) {
         const int l = idx & 31, reg = (idx >> 5) & 3, j = idx >> 7;
         const int row = c0 + (l >> 2) + 8 * (reg >> 1);
         const int tok = j * 8 + 2 * (l & 3) + (reg & 1);
+        if (EPI == EPI_ARGMAX) {
+            // the logit itself is never stored: only this block's best (value, index) per token survives
+            unsigned long long key = 0;
+            if (row < n && tok < a.M) key = argmax_key(dequant(sum, a.a_scale[tok], a.ws[g][row]), (uint32_t)row);
+            cand[tok * 16 + (row - c0)] = key;
+            continue;
+        }
         if (row >= n || tok >= a.M) continue;
         const int64_t o = (int64_t)tok * n + row;
         if (EPI == EPI_ACC) {
@@ -321,6 +330,46 @@ __global__ void __launch_bounds__(kThreads) gemv_mma_kernel(const GemvDev a) {
         if (EPI == EPI_RESIDUAL) {
             const float res = T::load(static_cast<const S *>(a.residual) + o);
             T::store(static_cast<S *>(a.combined) + o, bf16_rne(__fadd_rn(res, y)));
+        }
+    }
+    if (EPI == EPI_ARGMAX) {
+        __syncthreads();
+        if (tid < 16) {  // thread = token: best of the block's 16 channels (16 candidates per block, absent tokens 0)
+            unsigned long long best = 0;
+            if (tid < NT * 8) {
+#pragma unroll
+                for (int r = 0; r < 16; ++r) best = max(best, cand[tid * 16 + r]);
+            }
+            a.partial_best[(size_t)blockIdx.x * 16 + tid] = best;
+        }
+    }
+}
+
+// Reduces the per-block candidates of the fused head projection to one token per row of activations:
+// the largest finite logit, the lowest index among equals, ~0 when any logit of the row was not finite.
+__global__ void __launch_bounds__(1024) argmax_finish_kernel(const unsigned long long *partial, int blocks, uint32_t *token,
+                                                             float *value) {
+    __shared__ unsigned long long slots[32];
+    dependency_wait();
+    const int m = blockIdx.x, t = threadIdx.x;
+    unsigned long long best = 0;
+    for (int b = t; b < blocks; b += 1024) best = max(best, partial[(size_t)b * 16 + m]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) best = max(best, __shfl_down_sync(0xffffffffu, best, d));
+    if ((t & 31) == 0) slots[t >> 5] = best;
+    __syncthreads();
+    if (t < 32) {
+        best = slots[t];
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) best = max(best, __shfl_down_sync(0xffffffffu, best, d));
+        if (t == 0) {
+            const bool bad = best == ~0ull || best == 0ull;
+            token[m] = bad ? 0xffffffffu : 0xffffffffu - (uint32_t)(best & 0xffffffffull);
+            if (value) {
+                const uint32_t o = (uint32_t)(best >> 32);
+                const uint32_t bits = (o & 0x80000000u) ? (o & 0x7fffffffu) : ~o;
+                value[m] = bad ? __uint_as_float(0x7fc00000u) : __uint_as_float(bits);
+            }
         }
     }
 }
@@ -336,6 +385,7 @@ GemvDev make_dev(const LinearArgs &l) {
     d.ntot = (l.epilogue == EPI_SWIGLU) ? l.n[0] : ntot;
     d.ks = 1;
     d.residual = l.residual; d.combined = l.combined; d.act = l.act; d.maxima = l.maxima; d.acc = l.acc;
+    d.partial_best = l.partial_best;
     return d;
 }
 
@@ -376,6 +426,7 @@ template <int NT, class T> cudaError_t launch_mma_epi(int epi, const GemvDev &d,
         case EPI_PLAIN: return launch_mma_inst<NT, T, EPI_PLAIN>(d, s);
         case EPI_RESIDUAL: return launch_mma_inst<NT, T, EPI_RESIDUAL>(d, s);
         case EPI_ACC: return launch_mma_inst<NT, T, EPI_ACC>(d, s);
+        case EPI_ARGMAX: return launch_mma_inst<NT, T, EPI_ARGMAX>(d, s);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -417,6 +468,10 @@ cudaError_t launch_gemv_dp4a(const LinearArgs &l, cudaStream_t s) {
     while (ks < kWarps && d.ntot * ks < want && l.K / (ks * 2) >= 512) ks *= 2;
     d.ks = ks;
     return l.dtype == 0 ? launch_dp4a_m<Bf16>(l.M, l.epilogue, d, s) : launch_dp4a_m<F32>(l.M, l.epilogue, d, s);
+}
+
+cudaError_t launch_argmax_finish(const unsigned long long *partial, int blocks, int M, uint32_t *token, float *value, cudaStream_t s) {
+    return launch_kernel(argmax_finish_kernel, dim3(M), dim3(1024), (size_t)0, s, partial, blocks, token, value);
 }
 
 cudaError_t launch_gemv_mma(const LinearArgs &l, cudaStream_t s) {

@@ -42,7 +42,7 @@ cudaError_t launch_swiglu(const void *gate, const void *up, int dtype, int M, in
 cudaError_t launch_residual(const void *a, const void *b, int dtype, size_t n, void *out, cudaStream_t s);
 cudaError_t launch_rounding_probe(const float *x, int8_t *out, size_t n, cudaStream_t s);
 
-enum Epilogue { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_ACC = 3 };
+enum Epilogue { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_ACC = 3, EPI_ARGMAX = 4 };
 
 struct LinearArgs {
     const int8_t *q;
@@ -59,6 +59,7 @@ struct LinearArgs {
     void *act;                    // EPI_SWIGLU
     uint32_t *maxima;             // EPI_SWIGLU
     int32_t *acc;                 // EPI_ACC: raw accumulators [M, n[0]]
+    unsigned long long *partial_best;  // EPI_ARGMAX: [row blocks][16] packed (ordered value, ~index) per token
     int dtype;
 };
 cudaError_t launch_linear_naive(const LinearArgs &a, cudaStream_t s);
@@ -94,6 +95,11 @@ cudaError_t init_quantize();
 // Device status word (bounded waits report here instead of trapping).
 uint32_t *device_status_ptr();  // device address of the 2-word status block of the current device
 cudaError_t read_device_status(cudaStream_t s, uint32_t out[2]);
+
+// greedy token selection fused into the head projection (gemv.cu): finish = reduce the per-block candidates
+cudaError_t launch_argmax_finish(const unsigned long long *partial, int blocks, int M, uint32_t *token, float *value, cudaStream_t s);
+unsigned long long *argmax_scratch();  // per device: kArgmaxMaxBlocks x 16 candidates
+constexpr int kArgmaxMaxBlocks = 16384;  // head matrices up to 262144 output channels
 
 // one-shot all-reduce over peer memory (tp_allreduce.cu)
 cudaError_t launch_tp_allreduce(const void *partial, void *out, size_t n_el, int dtype, void *const *bufs, uint32_t *const *flags,

@@ -184,6 +184,13 @@ def linear_no_alloc(q: torch.Tensor, scale: torch.Tensor, w: torch.Tensor, w_sca
                                                 _dtype_code(out), _stream()), "w8a8_linear_no_alloc")
 
 
+def linear_argmax(q: torch.Tensor, scale: torch.Tensor, w: Matrix, token: torch.Tensor, value: torch.Tensor | None = None) -> None:
+    """Head projection + `select_token` (src/kernels.rs:2191-2231) in one pass: token[m] = index of the largest logit
+    (lowest index among equals, 0xffffffff if any logit is not finite); the logits are never written."""
+    capi.check(capi.load().w8a8_linear_argmax(_ptr(q), _ptr(scale), w.handle, q.shape[0], _ptr(token), _ptr(value), _stream()),
+               "w8a8_linear_argmax")
+
+
 def linear_acc_i32(q: torch.Tensor, w: Matrix, acc: torch.Tensor, variant: int = capi.VARIANT_NAIVE) -> None:
     """Raw int32 accumulators (parity checks against the CPU-integer fixtures)."""
     capi.check(capi.load().w8a8_linear_acc_i32(_ptr(q), w.handle, q.shape[0], _ptr(acc), variant, _stream()),

@@ -352,3 +352,60 @@ def test_tp_allreduce_single_rank_degenerate(ops):
     # bad arguments
     assert lib.w8a8_tp_allreduce(x.data_ptr(), out.data_ptr(), n, 0, bufs, fl, seq.data_ptr(), 1, 1, slot, None) == 1
     assert lib.w8a8_tp_allreduce(x.data_ptr(), out.data_ptr(), n + 3, 0, bufs, fl, seq.data_ptr(), 0, 1, 2 * slot, None) == 2
+
+
+def host_argmax(y):
+    """model::argmax (src/model.rs:206-218): first index of the maximum; rows with a non-finite value are rejected."""
+    out = []
+    for row in y:
+        out.append(0xFFFFFFFF if not np.all(np.isfinite(row)) else int(np.argmax(row)))  # np.argmax returns the first maximum
+    return np.array(out, dtype=np.uint32)
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 151936), (4, 4096, 4096), (16, 128, 33), (9, 4096, 1000)])
+def test_linear_argmax_matches_linear_then_select(ops, M, K, N):
+    """Fused head + greedy selection == projection followed by the reference's selection rule, including ties
+    (duplicated weight rows give equal logits: the lowest index must win) and the winning value."""
+    import torch
+
+    rng = np.random.default_rng(N + M)
+    q = rng.integers(-127, 128, (M, K), dtype=np.int8)
+    w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    ws = np.full(N, 1.0 / 4096, dtype=np.float32)
+    # make the maximum appear several times: copy the best channel of token 0 to other places
+    acc0 = (q[:1].astype(np.int64) @ w.astype(np.int64).T)[0]
+    best = int(np.argmax(acc0))
+    for dup in (N - 1, N // 2, max(0, best - 1)):
+        w[dup] = w[best]
+    asc = (rng.random(M, dtype=np.float32) / 64 + 1e-3).astype(np.float32)
+    mat = make_matrix(ops, w, ws)
+    y = empty_act((M, N), "f32")
+    ops.linear_quantized(to_dev(q), to_dev(asc, "f32"), mat, y, NAIVE)
+    expect = host_argmax(to_host(y))
+    tok = torch.zeros(M, dtype=torch.int32, device="cuda")
+    val = torch.zeros(M, dtype=torch.float32, device="cuda")
+    for _ in range(2):  # the candidate buffer is reused
+        ops.linear_argmax(to_dev(q), to_dev(asc, "f32"), mat, tok, val)
+    got = to_host(tok).view(np.uint32)
+    assert np.array_equal(got, expect)
+    yh = to_host(y)
+    assert np.array_equal(bits(to_host(val)), bits(yh[np.arange(M), expect.astype(np.int64)]))
+    assert expect[0] == min(best, N - 1, N // 2, max(0, best - 1))  # the lowest of the equal maxima wins the tie
+
+
+def test_linear_argmax_rejects_non_finite_rows(ops):
+    import torch
+
+    rng = np.random.default_rng(3)
+    M, K, N = 3, 256, 64
+    q = rng.integers(1, 128, (M, K), dtype=np.int8)
+    w = rng.integers(1, 128, (N, K), dtype=np.int8)
+    ws = np.full(N, 1e-3, dtype=np.float32)
+    asc = np.array([1e-3, np.inf, 1e-3], dtype=np.float32)  # token 1 overflows to infinity everywhere
+    mat = make_matrix(ops, w, ws)
+    tok = torch.zeros(M, dtype=torch.int32, device="cuda")
+    ops.linear_argmax(to_dev(q), to_dev(asc, "f32"), mat, tok, None)
+    got = to_host(tok).view(np.uint32)
+    y = oracle.linear(q, asc, w, ws)
+    assert got[1] == 0xFFFFFFFF
+    assert got[0] == np.argmax(y[0]) and got[2] == np.argmax(y[2])
