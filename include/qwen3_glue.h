@@ -1,0 +1,57 @@
+/* C ABI of the three operators that surround the W8A8 linear layers inside one Qwen3 decoder layer, so that a
+ * host can run a whole forward pass through libw8a8.so: token embedding, per-head RMSNorm + rotary embedding +
+ * KV-cache append, and causal grouped-query attention.  They are the callers on either side of the linear-layer
+ * path declared in w8a8.h, not part of it: plain kernels that restate the reference's arithmetic.  Embedding, head
+ * norm and rotary embedding keep the reference's summation order (bit-identical but for rsqrt.approx); attention
+ * reassociates its float32 sums for parallelism and stays within the reference's own tolerance for that operator.
+ *
+ * Reference interfaces replaced (paths under crates/inferrous-qwen3/):
+ *   qwen3_embedding    kernel `embedding`   src/kernels.rs:335-345   launched at src/gpu.rs:543-551
+ *   qwen3_prepare_qk   kernel `prepare_qk`  src/kernels.rs:1350-1443 launched at src/gpu.rs:626-641
+ *   qwen3_attention    kernel `attention`   src/kernels.rs:1490-1658 launched at src/gpu.rs:659-671
+ *                      (`attention_prefill` :1664 and the three-kernel long-context form :1832-2160 compute the
+ *                      same function with other launch shapes; one kernel serves every length here)
+ *
+ * Conventions are those of w8a8.h: device pointers, work queued on `stream`, nothing synchronises or allocates,
+ * int status return (W8A8_OK = 0), w8a8_init() first.  `dtype` is the activation carrier (W8A8_BF16 / W8A8_F32).
+ * Head width is 128, the context at most 4096 positions (src/lib.rs:16-18).
+ *
+ * `control` is the reference's two-word device buffer {token id, absolute position of the first row}
+ * (src/gpu.rs:189); the position is read on the device so that a captured graph can be replayed for every step.
+ * A position or token id beyond its limit is not an error the host can see at launch time: the kernel skips the
+ * access and records code 6 in the device status word (w8a8_device_status).
+ *
+ * KV caches: `k_cache` and `v_cache` are [capacity][kv_heads][128] bf16, token-major, owned by the caller.  The
+ * layout is private to qwen3_prepare_qk and qwen3_attention (the reference stores its keys channel-major).
+ */
+#ifndef QWEN3_GLUE_H
+#define QWEN3_GLUE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* out[r, :] = table[ids[r], :], widened to the carrier.  `table` is [vocab, hidden] bf16, hidden % 8 == 0. */
+int qwen3_embedding(const uint32_t *ids, const uint16_t *table, int rows, int hidden, int vocab, void *out, int dtype,
+                    void *stream);
+
+/* `qkv` holds, per row, q_heads query heads, then kv_heads key heads, then kv_heads value heads (128 wide each; row
+ * stride `ld` elements) — the output of one projection against the concatenated Q|K|V matrix.  In place: every
+ * query and key head becomes bf16(rope(bf16(rmsnorm(head, eps 1e-6) * gain))) with the rotary row of position
+ * control[1] + row taken from `rope_table` ([capacity or more][128] f32: 64 cosines then 64 sines per position,
+ * tools/prepare.py:90-92).  The rotated keys and the untouched values are appended to the caches at that position. */
+int qwen3_prepare_qk(void *qkv, int dtype, int64_t ld, int rows, int q_heads, int kv_heads, const float *q_gain,
+                     const float *k_gain, const float *rope_table, const uint32_t *control, uint16_t *k_cache, uint16_t *v_cache,
+                     int capacity, void *stream);
+
+/* out[r, h, :] = bf16(softmax(q[r, h, :] . K[0 .. control[1] + r, h / (q_heads / kv_heads), :] * 128^-0.5) . V[...]).
+ * `q` may point into the qkv buffer (row stride `ldq`); `out` is [rows][q_heads * 128] with row stride `ldo`. */
+int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
+                    const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

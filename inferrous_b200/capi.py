@@ -1,4 +1,4 @@
-"""ctypes binding of include/w8a8.h.  Every symbol the header declares is bound here."""
+"""ctypes binding of include/w8a8.h and include/qwen3_glue.h.  Every symbol the headers declare is bound here."""
 from __future__ import annotations
 
 import ctypes as C
@@ -38,6 +38,10 @@ SIGNATURES = {
     "w8a8_tp_allreduce": (_i, [_vp, _vp, _sz, _i, C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _i, _sz, _vp]),
     "w8a8_linear_acc_i32": (_i, [_vp, _vp, _i, _vp, _i, _vp]),
     "w8a8_rounding_probe": (_i, [_vp, _vp, _sz, _vp]),
+    # include/qwen3_glue.h
+    "qwen3_embedding": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp]),
+    "qwen3_prepare_qk": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "qwen3_attention": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _i, _vp]),
 }
 
 

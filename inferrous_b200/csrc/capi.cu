@@ -36,10 +36,6 @@ std::mutex g_mu;
 bool g_pdl = false;
 thread_local char g_err[256] = "";
 
-int fail_cuda(cudaError_t e, const char *what) {
-    snprintf(g_err, sizeof g_err, "%s: %s", what, cudaGetErrorString(e));
-    return W8A8_ERR_CUDA;
-}
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int current_ready_device() {
@@ -50,6 +46,11 @@ int current_ready_device() {
 }  // namespace
 
 bool programmatic_launch_enabled() { return g_pdl; }
+
+int fail_cuda(cudaError_t e, const char *what) {
+    snprintf(g_err, sizeof g_err, "%s: %s", what, cudaGetErrorString(e));
+    return W8A8_ERR_CUDA;
+}
 
 int sm_count() {
     int dev = current_ready_device();

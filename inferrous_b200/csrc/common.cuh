@@ -19,6 +19,7 @@ enum DeviceWait : uint32_t {
     WAIT_ACC_FULL = 3,    // epilogue waited for an accumulator
     WAIT_ACC_EMPTY = 4,   // MMA waited for the epilogue to drain an accumulator
     WAIT_PEER = 5,        // tensor-parallel all-reduce waited for another rank's partial outputs
+    FAULT_CACHE_RANGE = 6,  // not a wait: a token id or cache position read from device memory was out of range; the access was skipped
 };
 
 __device__ __forceinline__ float bf16_rne(float x) {

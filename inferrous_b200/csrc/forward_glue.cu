@@ -1,0 +1,312 @@
+// The operators on either side of the W8A8 linear layers in one Qwen3 decoder layer: token embedding,
+// per-head RMSNorm + rotary embedding + KV-cache append, and causal grouped-query attention.
+//
+// They exist so that the linear-layer kernels can be driven through a whole forward pass (the callers of
+// the hot path); they are plain CUDA kernels restating the reference's arithmetic (paths under
+// crates/inferrous-qwen3/):
+//   embedding    src/kernels.rs:335-345
+//   prepare_qk   src/kernels.rs:1350-1443  (= norm :347-413 at width 128, rope :1444-1468, cache :1470-1488)
+//   attention    src/kernels.rs:1490-1658  (scores, maximum, exp / total, RN division per key, P.V; the float32
+//                sums are reassociated here for parallelism, see the kernel)
+// The caches are stored token-major, [position][kv head][128] bf16, for keys and values alike (the reference
+// keeps its keys channel-major; the layout is private to these two kernels).
+#include "../../include/qwen3_glue.h"
+#include "../../include/w8a8.h"
+#include "common.cuh"
+#include "internal.h"
+
+namespace w8a8 {
+namespace {
+
+constexpr int kHeadDim = 128;
+constexpr int kMaxContext = 4096;  // src/lib.rs:18
+
+__device__ __forceinline__ void record_range_fault(uint32_t *status, uint32_t detail) {
+    if (status && atomicCAS(status, 0u, (uint32_t)FAULT_CACHE_RANGE) == 0u) status[1] = detail;
+}
+
+// ---- embedding ---------------------------------------------------------------------------------------------
+template <class T>
+__global__ void __launch_bounds__(256) embedding_kernel(const uint32_t *__restrict__ ids, const uint16_t *__restrict__ table,
+                                                        int hidden, uint32_t vocab, typename T::storage *__restrict__ out,
+                                                        uint32_t *status) {
+    dependency_wait();
+    const int row = blockIdx.y;
+    const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
+    if (c >= hidden) return;
+    const uint32_t id = ids[row];
+    if (id >= vocab) {
+        if (c == 0) record_range_fault(status, id);
+        return;
+    }
+    float v[8];
+    Vec<Bf16>::load(table + (size_t)id * hidden + c, v);
+    typename T::storage *o = out + (size_t)row * hidden + c;
+    if constexpr (T::kVec == 8) {
+        Vec<T>::store(o, v);
+    } else {
+        const float lo[4] = {v[0], v[1], v[2], v[3]}, hi[4] = {v[4], v[5], v[6], v[7]};
+        Vec<T>::store(o, lo);
+        Vec<T>::store(o + 4, hi);
+    }
+}
+
+// ---- head RMSNorm + RoPE + cache append --------------------------------------------------------------------
+// One warp per (row, head); lane l holds elements l, l+32, l+64, l+96, so both the reference's first tree
+// level ((p[t] + p[t+64]) + (p[t+32] + p[t+96]) for t < 32) and the rotary pairs (t, t+64) are lane-local.
+template <class T>
+__global__ void __launch_bounds__(128) prepare_qk_kernel(typename T::storage *__restrict__ qkv, int64_t ld, int rows, int q_heads,
+                                                         int kv_heads, const float *__restrict__ q_gain,
+                                                         const float *__restrict__ k_gain, const float *__restrict__ table,
+                                                         const uint32_t *__restrict__ control, uint16_t *__restrict__ k_cache,
+                                                         uint16_t *__restrict__ v_cache, int capacity, uint32_t *status) {
+    dependency_wait();
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int per_row = q_heads + kv_heads;
+    if (unit >= rows * per_row) return;
+    const int row = unit / per_row, h = unit % per_row;
+    const bool is_q = h < q_heads;
+    const uint32_t pos = control[1] + (uint32_t)row;
+    if (pos >= (uint32_t)capacity) {
+        if (lane == 0) record_range_fault(status, pos);
+        return;
+    }
+    typename T::storage *x = qkv + (size_t)row * ld + (size_t)h * kHeadDim;
+    const float *gain = is_q ? q_gain : k_gain;
+    const float *trow = table + (size_t)pos * kHeadDim;
+    float v[4], g[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[i] = T::load(x + lane + 32 * i);
+        g[i] = gain[lane + 32 * i];
+    }
+    const float c0 = trow[lane], c1 = trow[lane + 32], s0 = trow[lane + 64], s1 = trow[lane + 96];
+    float sum = __fadd_rn(__fadd_rn(__fmul_rn(v[0], v[0]), __fmul_rn(v[2], v[2])),
+                          __fadd_rn(__fmul_rn(v[1], v[1]), __fmul_rn(v[3], v[3])));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum = __fadd_rn(sum, __shfl_down_sync(0xffffffffu, sum, d));
+    sum = __shfl_sync(0xffffffffu, sum, 0);
+    const float inv = rsqrt_approx(__fadd_rn(__fdiv_rn(sum, 128.0f), 1e-6f));
+    float n[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) n[i] = bf16_rne(__fmul_rn(__fmul_rn(v[i], inv), g[i]));
+    float r[4];
+    r[0] = bf16_rne(__fadd_rn(__fmul_rn(n[0], c0), -__fmul_rn(n[2], s0)));
+    r[2] = bf16_rne(__fadd_rn(__fmul_rn(n[2], c0), __fmul_rn(n[0], s0)));
+    r[1] = bf16_rne(__fadd_rn(__fmul_rn(n[1], c1), -__fmul_rn(n[3], s1)));
+    r[3] = bf16_rne(__fadd_rn(__fmul_rn(n[3], c1), __fmul_rn(n[1], s1)));
+    if (is_q) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) T::store(x + lane + 32 * i, r[i]);
+    } else {
+        const int head = h - q_heads;
+        const size_t slot = ((size_t)pos * kv_heads + head) * kHeadDim;
+        const typename T::storage *vx = qkv + (size_t)row * ld + (size_t)(per_row + head) * kHeadDim;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            T::store(x + lane + 32 * i, r[i]);
+            k_cache[slot + lane + 32 * i] = (uint16_t)(__float_as_uint(r[i]) >> 16);
+            v_cache[slot + lane + 32 * i] = (uint16_t)(__float_as_uint(T::load(vx + lane + 32 * i)) >> 16);
+        }
+    }
+}
+
+// ---- attention ---------------------------------------------------------------------------------------------
+// One CTA of 256 threads per (row, query head); the whole visible prefix is handled by that CTA, its scores
+// held in shared memory (context <= 4096).
+//   scores   eight lanes per key (16 channels each, summed in order, then a three-step butterfly), four keys per
+//            warp and sweep; score = dot * 128^-0.5, as the reference scales it
+//   softmax  maximum, e = exp(score - maximum) with the reference's ex2.approx form, one RN division e / total per key
+//            (the reference divides each weight before the P.V sum as well, src/kernels.rs:1608-1616)
+//   P.V      sixteen key slices (key j belongs to slice j % 16) x sixteen lanes of 8 channels, each slice summed
+//            in increasing j, then the sixteen partial sums added in slice order
+// The sums are reassociated relative to the reference's one-thread-per-key / one-thread-per-channel kernel, whose
+// float32 sums run strictly in key and channel order; the association here is fixed, so the result depends on
+// nothing but the inputs.
+constexpr int kAttnThreads = 256;
+constexpr int kAttnSlices = 16;
+
+__device__ __forceinline__ float dot16(const float (&qv)[16], const uint4 a, const uint4 b) {
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        s = __fadd_rn(s, __fmul_rn(qv[2 * i], __uint_as_float(w[i] << 16)));
+        s = __fadd_rn(s, __fmul_rn(qv[2 * i + 1], __uint_as_float(w[i] & 0xffff0000u)));
+    }
+    return s;
+}
+
+template <class T>
+__global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename T::storage *__restrict__ q, int64_t ldq, int q_heads,
+                                                                 int kv_heads, const uint16_t *__restrict__ k_cache,
+                                                                 const uint16_t *__restrict__ v_cache,
+                                                                 const uint32_t *__restrict__ control,
+                                                                 typename T::storage *__restrict__ out, int64_t ldo, int capacity,
+                                                                 uint32_t *status) {
+    __shared__ float scores[kMaxContext];
+    __shared__ float query[kHeadDim];
+    __shared__ float reduce[kAttnThreads / 32];
+    __shared__ float partial[kAttnSlices][kHeadDim];
+    dependency_wait();
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int row = blockIdx.x / q_heads, head = blockIdx.x % q_heads;
+    const int kv = head / (q_heads / kv_heads);
+    const uint32_t end_u = control[1] + (uint32_t)row + 1u;
+    if (end_u > (uint32_t)capacity) {
+        if (t == 0) record_range_fault(status, end_u);
+        return;
+    }
+    const int end = (int)end_u;
+    if (t < kHeadDim) query[t] = T::load(q + (size_t)row * ldq + (size_t)head * kHeadDim + t);
+    __syncthreads();
+
+    // scores
+    const int sub = lane & 7, group = lane >> 3;
+    float qv[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) qv[i] = query[16 * sub + i];
+    const size_t key_stride = (size_t)kv_heads * kHeadDim;
+    const uint16_t *kbase = k_cache + (size_t)kv * kHeadDim + 16 * sub;
+    float maximum = -INFINITY;
+#pragma unroll 2
+    for (int j0 = warp * 4; j0 < end; j0 += (kAttnThreads / 32) * 4) {
+        const int j = j0 + group;
+        float s = 0.0f;
+        if (j < end) {
+            const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)j * key_stride);
+            s = dot16(qv, kr[0], kr[1]);
+        }
+        s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 4));
+        s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 2));
+        s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
+        s = __fmul_rn(s, 0.08838834764831845f);
+        if (j < end) {
+            maximum = fmaxf(maximum, s);
+            if (sub == 0) scores[j] = s;
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, d));
+    if (lane == 0) reduce[warp] = maximum;
+    __syncthreads();
+    maximum = reduce[0];
+#pragma unroll
+    for (int i = 1; i < kAttnThreads / 32; ++i) maximum = fmaxf(maximum, reduce[i]);
+    __syncthreads();
+
+    // softmax
+    float total = 0.0f;
+    for (int j = t; j < end; j += kAttnThreads) {
+        const float e = exp_approx(__fadd_rn(scores[j], -maximum));
+        scores[j] = e;
+        total = __fadd_rn(total, e);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) total = __fadd_rn(total, __shfl_xor_sync(0xffffffffu, total, d));
+    if (lane == 0) reduce[warp] = total;
+    __syncthreads();
+    float den = reduce[0];
+#pragma unroll
+    for (int i = 1; i < kAttnThreads / 32; ++i) den = __fadd_rn(den, reduce[i]);
+    for (int j = t; j < end; j += kAttnThreads) scores[j] = __fdiv_rn(scores[j], den);
+    __syncthreads();
+
+    // P.V
+    const int slice = t >> 4, cg = t & 15;
+    const uint16_t *vbase = v_cache + (size_t)kv * kHeadDim + 8 * cg;
+    float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+    for (int j = slice; j < end; j += kAttnSlices) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(vbase + (size_t)j * key_stride);
+        const float p = scores[j];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(p, __uint_as_float(w[i] << 16)));
+            acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(p, __uint_as_float(w[i] & 0xffff0000u)));
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) partial[slice][8 * cg + i] = acc[i];
+    __syncthreads();
+    if (t < kHeadDim) {
+        float sum = partial[0][t];
+#pragma unroll
+        for (int i = 1; i < kAttnSlices; ++i) sum = __fadd_rn(sum, partial[i][t]);
+        T::store(out + (size_t)row * ldo + (size_t)head * kHeadDim + t, bf16_rne(sum));
+    }
+}
+
+bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+}  // namespace
+}  // namespace w8a8
+
+using namespace w8a8;
+
+#define REQUIRE(cond, code)         \
+    do {                            \
+        if (!(cond)) return (code); \
+    } while (0)
+
+extern "C" {
+
+int qwen3_embedding(const uint32_t *ids, const uint16_t *table, int rows, int hidden, int vocab, void *out, int dtype, void *stream) {
+    REQUIRE(device_status_ptr(), W8A8_ERR_NOT_INITIALIZED);
+    REQUIRE(ids && table && out && rows >= 0 && hidden > 0 && vocab > 0, W8A8_ERR_BAD_ARG);
+    REQUIRE(dtype == W8A8_BF16 || dtype == W8A8_F32, W8A8_ERR_BAD_ARG);
+    REQUIRE(hidden % 8 == 0 && aligned(table, 16) && aligned(out, 16), W8A8_ERR_ALIGNMENT);
+    if (rows == 0) return W8A8_OK;
+    const dim3 grid((hidden / 8 + 255) / 256, rows);
+    cudaError_t e = dtype == W8A8_BF16
+                        ? launch_kernel(embedding_kernel<Bf16>, grid, dim3(256), 0, (cudaStream_t)stream, ids, table, hidden,
+                                        (uint32_t)vocab, (uint16_t *)out, device_status_ptr())
+                        : launch_kernel(embedding_kernel<F32>, grid, dim3(256), 0, (cudaStream_t)stream, ids, table, hidden,
+                                        (uint32_t)vocab, (float *)out, device_status_ptr());
+    return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "embedding launch");
+}
+
+int qwen3_prepare_qk(void *qkv, int dtype, int64_t ld, int rows, int q_heads, int kv_heads, const float *q_gain,
+                     const float *k_gain, const float *rope_table, const uint32_t *control, uint16_t *k_cache, uint16_t *v_cache,
+                     int capacity, void *stream) {
+    REQUIRE(device_status_ptr(), W8A8_ERR_NOT_INITIALIZED);
+    REQUIRE(qkv && q_gain && k_gain && rope_table && control && k_cache && v_cache, W8A8_ERR_BAD_ARG);
+    REQUIRE(dtype == W8A8_BF16 || dtype == W8A8_F32, W8A8_ERR_BAD_ARG);
+    REQUIRE(rows >= 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0, W8A8_ERR_BAD_ARG);
+    REQUIRE(capacity > 0 && capacity <= kMaxContext && ld >= (int64_t)(q_heads + 2 * kv_heads) * kHeadDim, W8A8_ERR_BAD_ARG);
+    if (rows == 0) return W8A8_OK;
+    const int units = rows * (q_heads + kv_heads);
+    const dim3 grid((units + 3) / 4);
+    cudaError_t e =
+        dtype == W8A8_BF16
+            ? launch_kernel(prepare_qk_kernel<Bf16>, grid, dim3(128), 0, (cudaStream_t)stream, (uint16_t *)qkv, ld, rows, q_heads,
+                            kv_heads, q_gain, k_gain, rope_table, control, k_cache, v_cache, capacity, device_status_ptr())
+            : launch_kernel(prepare_qk_kernel<F32>, grid, dim3(128), 0, (cudaStream_t)stream, (float *)qkv, ld, rows, q_heads,
+                            kv_heads, q_gain, k_gain, rope_table, control, k_cache, v_cache, capacity, device_status_ptr());
+    return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "prepare_qk launch");
+}
+
+int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
+                    const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity, void *stream) {
+    REQUIRE(device_status_ptr(), W8A8_ERR_NOT_INITIALIZED);
+    REQUIRE(q && k_cache && v_cache && control && out, W8A8_ERR_BAD_ARG);
+    REQUIRE(dtype == W8A8_BF16 || dtype == W8A8_F32, W8A8_ERR_BAD_ARG);
+    REQUIRE(rows >= 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0, W8A8_ERR_BAD_ARG);
+    REQUIRE(capacity > 0 && capacity <= kMaxContext, W8A8_ERR_BAD_ARG);
+    REQUIRE(ldq >= (int64_t)q_heads * kHeadDim && ldo >= (int64_t)q_heads * kHeadDim, W8A8_ERR_BAD_ARG);
+    REQUIRE(aligned(k_cache, 16) && aligned(v_cache, 16), W8A8_ERR_ALIGNMENT);
+    if (rows == 0) return W8A8_OK;
+    const dim3 grid(rows * q_heads);
+    cudaError_t e = dtype == W8A8_BF16
+                        ? launch_kernel(attention_kernel<Bf16>, grid, dim3(kAttnThreads), 0, (cudaStream_t)stream, (const uint16_t *)q, ldq,
+                                        q_heads, kv_heads, k_cache, v_cache, control, (uint16_t *)out, ldo, capacity,
+                                        device_status_ptr())
+                        : launch_kernel(attention_kernel<F32>, grid, dim3(kAttnThreads), 0, (cudaStream_t)stream, (const float *)q, ldq,
+                                        q_heads, kv_heads, k_cache, v_cache, control, (float *)out, ldo, capacity,
+                                        device_status_ptr());
+    return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "attention launch");
+}
+
+}  // extern "C"

@@ -106,6 +106,8 @@ cudaError_t launch_tp_allreduce(const void *partial, void *out, size_t n_el, int
                                 uint32_t *seq, int rank, int tp, size_t slot_el, cudaStream_t s);
 
 int sm_count();
+// Records the failing CUDA call's text for w8a8_last_cuda_error() and returns W8A8_ERR_CUDA.
+int fail_cuda(cudaError_t e, const char *what);
 
 // Programmatic dependent launch (the reference's CLEAN_PDL switch, src/gpu.rs:317; src/graph.rs:63-127):
 // when enabled, every hot-path kernel is launched with the programmatic-stream-serialization attribute,

@@ -79,7 +79,7 @@ class Matrix:
 
     def __del__(self):
         h = getattr(self, "handle", None)
-        if h:
+        if h and capi is not None:  # module globals are already cleared when the interpreter shuts down
             capi.load().w8a8_weight_destroy(h)
             self.handle = None
 
@@ -200,3 +200,32 @@ def linear_acc_i32(q: torch.Tensor, w: Matrix, acc: torch.Tensor, variant: int =
 def rounding_probe(x: torch.Tensor, out: torch.Tensor) -> None:
     """Kernel `rounding_probe` (src/kernels.rs:326-333)."""
     capi.check(capi.load().w8a8_rounding_probe(_ptr(x), _ptr(out), x.numel(), _stream()), "w8a8_rounding_probe")
+
+
+# ---- the operators around the linear layers (include/qwen3_glue.h) ---------------------------------------
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """Kernel `embedding` (src/kernels.rs:335-345; src/gpu.rs:543-551): out[r] = table[ids[r]].  `ids` is uint32
+    (or int32 holding non-negative ids) on the device; in decode it is the control buffer, whose word 0 is the token."""
+    rows, hidden = out.shape
+    capi.check(capi.load().qwen3_embedding(_ptr(ids), _ptr(table), rows, hidden, table.shape[0], _ptr(out), _dtype_code(out),
+                                           _stream()), "qwen3_embedding")
+
+
+def prepare_qk(qkv: torch.Tensor, q_heads: int, kv_heads: int, q_gain: torch.Tensor, k_gain: torch.Tensor,
+               rope_table: torch.Tensor, control: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
+    """Kernel `prepare_qk` (src/kernels.rs:1350-1443; src/gpu.rs:626-641): in-place head RMSNorm + RoPE of the query
+    and key heads of `qkv` ([rows, (q_heads + 2 kv_heads) * 128]) and append of keys / values to the caches
+    ([capacity, kv_heads, 128] bf16) at position control[1] + row."""
+    capi.check(capi.load().qwen3_prepare_qk(_ptr(qkv), _dtype_code(qkv), qkv.stride(0), qkv.shape[0], q_heads, kv_heads,
+                                            _ptr(q_gain), _ptr(k_gain), _ptr(rope_table), _ptr(control), _ptr(k_cache),
+                                            _ptr(v_cache), k_cache.shape[0], _stream()), "qwen3_prepare_qk")
+
+
+def attention(q: torch.Tensor, q_heads: int, kv_heads: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              control: torch.Tensor, out: torch.Tensor) -> None:
+    """Kernel `attention` (src/kernels.rs:1490-1658; src/gpu.rs:659-671): causal grouped-query attention of `rows`
+    new positions over the cache.  `q` may be the qkv buffer (its leading q_heads * 128 columns are read)."""
+    capi.check(capi.load().qwen3_attention(_ptr(q), _dtype_code(q), q.stride(0), q.shape[0], q_heads, kv_heads, _ptr(k_cache),
+                                           _ptr(v_cache), _ptr(control), _ptr(out), out.stride(0), k_cache.shape[0], _stream()),
+               "qwen3_attention")

@@ -1,0 +1,271 @@
+"""A Qwen3 W8A8 forward pass and greedy generation loop over the C ABI: the caller of the linear-layer path.
+
+Mirrors `GpuModel::forward` and `GpuModel::generate` of the reference host
+(crates/inferrous-qwen3/src/gpu.rs:528-817 and :818-929): embedding, then per layer
+norm_quantize -> Q|K|V projection -> prepare_qk -> attention -> quantize -> O projection + residual ->
+norm_quantize -> gate/up projection + SwiGLU -> quantize -> down projection + residual, then the final norm,
+the head projection and greedy selection.  Every device operation is a kernel of libw8a8.so; torch supplies
+memory, the stream and CUDA-graph capture only.  As in the reference, prefill runs eagerly, one decode step is
+captured once and replayed (src/gpu.rs:303-333), and the host writes {token, position} into the control buffer
+and reads the selected token back every step (src/gpu.rs:876-906).
+
+Differences from the reference host, all outside the linear-layer arithmetic:
+  * Q, K and V (and gate, up) are stored as one concatenated matrix each; with per-output-channel scales the
+    concatenated projection equals the separate ones channel for channel.
+  * The head is a W8A8 matrix like the body (the reference keeps a packed bf16 head, src/gpu.rs:801-809); the final
+    norm is therefore fused with a quantizer and the selection with the projection.
+  * Activations are stored as bf16 (the reference stores the same values in f32 buffers).
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import torch
+
+from . import capi, ops
+
+
+@dataclasses.dataclass(frozen=True)
+class Qwen3Config:
+    layers: int = 36
+    hidden: int = 4096
+    q_heads: int = 32
+    kv_heads: int = 8
+    intermediate: int = 12288
+    vocab: int = 151936
+    context: int = 4096
+    rope_theta: float = 1e6
+    eps: float = 1e-6
+    head_dim: int = 128  # fixed by the kernels
+
+    @property
+    def q_width(self) -> int:
+        return self.q_heads * self.head_dim
+
+    @property
+    def qkv_width(self) -> int:
+        return (self.q_heads + 2 * self.kv_heads) * self.head_dim
+
+    @classmethod
+    def qwen3_8b(cls) -> "Qwen3Config":
+        return cls()
+
+    def weight_bytes(self) -> int:
+        """int8 bytes one decode step streams (body + head), the numerator of the bandwidth figure."""
+        per_layer = self.hidden * self.qkv_width + self.q_width * self.hidden + 3 * self.hidden * self.intermediate
+        return self.layers * per_layer + self.vocab * self.hidden
+
+
+def rope_table(config: Qwen3Config) -> torch.Tensor:
+    """[context, 128] float32: 64 cosines then 64 sines per position, computed as the reference's bundle
+    preparation does (tools/prepare.py:90-92), on the CPU."""
+    freq = 1.0 / (config.rope_theta ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))
+    angles = torch.arange(config.context, dtype=torch.float32)[:, None] * freq
+    return torch.cat([angles.cos(), angles.sin()], dim=1)
+
+
+class Layer:
+    """One decoder layer's tensors: gains in the activation dtype (head gains float32) and gpu::Matrix handles."""
+
+    def __init__(self, config: Qwen3Config, norm1, qkv, qkv_scale, qnorm, knorm, o, o_scale, norm2, gate_up, gate_up_scale,
+                 down, down_scale):
+        inter = config.intermediate
+        self.norm1, self.norm2 = norm1, norm2
+        self.qnorm, self.knorm = qnorm, knorm
+        self.qkv = ops.Matrix(qkv, qkv_scale)
+        self.o = ops.Matrix(o, o_scale)
+        self.gate_up = ops.Matrix(gate_up, gate_up_scale)            # prefill: one projection, then swiglu_quantize
+        self.gate = ops.Matrix(gate_up[:inter], gate_up_scale[:inter])  # decode: fused gate/up + SwiGLU kernel
+        self.up = ops.Matrix(gate_up[inter:], gate_up_scale[inter:])
+        self.down = ops.Matrix(down, down_scale)
+
+
+class Qwen3Weights:
+    def __init__(self, config: Qwen3Config, embedding, layers, final_gain, head, head_scale, device):
+        self.config = config
+        self.embedding = embedding
+        self.layers = layers
+        self.final_gain = final_gain
+        self.head = ops.Matrix(head, head_scale)
+        self.rope = rope_table(config).to(device)
+
+    @classmethod
+    def random(cls, config: Qwen3Config, seed: int = 0, device="cuda") -> "Qwen3Weights":
+        """Random-init weights of the architecture: uniform int8 codes, channel scales sized so that every
+        projection keeps the activation variance (the codes of a row quantized to +-127 have a standard deviation
+        near 30, uniform weight codes near 73)."""
+        ops.init()
+        gen = torch.Generator(device=device).manual_seed(seed)
+        act = torch.bfloat16
+
+        def matrix(n, k):
+            w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=device, generator=gen)
+            s = (0.5 + torch.rand(n, device=device, generator=gen)) / (69.0 * math.sqrt(k))
+            return w, s.float()
+
+        def gain(n, dtype):
+            return (1.0 + 0.1 * torch.randn(n, device=device, generator=gen)).to(dtype)
+
+        layers = []
+        for _ in range(config.layers):
+            qkv, qkv_s = matrix(config.qkv_width, config.hidden)
+            o, o_s = matrix(config.hidden, config.q_width)
+            gu, gu_s = matrix(2 * config.intermediate, config.hidden)
+            down, down_s = matrix(config.hidden, config.intermediate)
+            layers.append(Layer(config, gain(config.hidden, act), qkv, qkv_s, gain(128, torch.float32), gain(128, torch.float32),
+                                o, o_s, gain(config.hidden, act), gu, gu_s, down, down_s))
+        embedding = torch.randn(config.vocab, config.hidden, device=device, generator=gen).to(act)
+        head, head_s = matrix(config.vocab, config.hidden)
+        return cls(config, embedding, layers, gain(config.hidden, act), head, head_s, device)
+
+
+class Workspace:
+    """gpu::Workspace (src/gpu.rs:76-143) for a fixed row count."""
+
+    def __init__(self, config: Qwen3Config, rows: int, device="cuda", wide_gate_up: bool = True):
+        act = torch.bfloat16
+        self.rows = rows
+        self.hidden = torch.empty(rows, config.hidden, dtype=act, device=device)
+        self.residual = torch.empty(rows, config.hidden, dtype=act, device=device)
+        self.qkv = torch.empty(rows, config.qkv_width, dtype=act, device=device)
+        self.attention = torch.empty(rows, config.q_width, dtype=act, device=device)
+        self.gate_up = torch.empty(rows, 2 * config.intermediate, dtype=act, device=device) if wide_gate_up else None
+        self.act = torch.empty(rows, config.intermediate, dtype=act, device=device)
+        self.quant4 = torch.empty(rows, config.hidden, dtype=torch.int8, device=device)
+        self.quant_o = torch.empty(rows, config.q_width, dtype=torch.int8, device=device)
+        self.quant12 = torch.empty(rows, config.intermediate, dtype=torch.int8, device=device)
+        self.scales = torch.empty(rows, dtype=torch.float32, device=device)
+        self.maxima = torch.zeros(rows, dtype=torch.int32, device=device)
+        self.logits = None  # only the unfused path writes logits
+
+
+class Qwen3Runner:
+    """GpuModel: owns the caches, the decode workspace, the control buffer and the captured decode graph.
+
+    unfused=True runs every projection with the one-thread-per-output kernel (VARIANT_NAIVE) and every fused step
+    as its separate parts (swiglu then quantize; logits then selection); it exists to check that the fast kernels
+    change nothing in a whole generation."""
+
+    def __init__(self, weights: Qwen3Weights, unfused: bool = False, device="cuda"):
+        ops.init()
+        self.w = weights
+        self.c = weights.config
+        self.unfused = unfused
+        self.device = device
+        c = self.c
+        self.k_cache = [torch.zeros(c.context, c.kv_heads, 128, dtype=torch.bfloat16, device=device) for _ in range(c.layers)]
+        self.v_cache = [torch.zeros(c.context, c.kv_heads, 128, dtype=torch.bfloat16, device=device) for _ in range(c.layers)]
+        self.control = torch.zeros(2, dtype=torch.int32, device=device)   # {token, position}
+        self.next = torch.zeros(1, dtype=torch.int32, device=device)
+        self.decode = Workspace(c, 1, device, wide_gate_up=unfused)
+        self.head_q = torch.empty(1, c.hidden, dtype=torch.int8, device=device)
+        self.head_scale = torch.empty(1, dtype=torch.float32, device=device)
+        self.logits = torch.empty(1, c.vocab, dtype=torch.bfloat16, device=device) if unfused else None
+        self.graph = None
+        self._host_control = torch.zeros(2, dtype=torch.int32).pin_memory()
+        self._host_next = torch.zeros(1, dtype=torch.int32).pin_memory()
+
+    # -- one forward pass: queues kernels only ------------------------------------------------------------
+    def forward(self, ws: Workspace, ids: torch.Tensor) -> None:
+        c, w = self.c, self.w
+        variant = capi.VARIANT_NAIVE if self.unfused else capi.VARIANT_AUTO
+        rows = ws.rows
+        q4, qo = ws.quant4, ws.quant_o
+        inter = c.intermediate
+        ops.embedding(ids, w.embedding, ws.hidden)
+        for index, layer in enumerate(w.layers):
+            ops.norm_quantize(ws.hidden, layer.norm1, None, q4, ws.scales, ws.maxima, c.eps)
+            ops.linear_quantized(q4, ws.scales, layer.qkv, ws.qkv, variant)
+            ops.prepare_qk(ws.qkv, c.q_heads, c.kv_heads, layer.qnorm, layer.knorm, w.rope, self.control,
+                           self.k_cache[index], self.v_cache[index])
+            ops.attention(ws.qkv, c.q_heads, c.kv_heads, self.k_cache[index], self.v_cache[index], self.control, ws.attention)
+            ops.quantize(ws.attention, qo, ws.scales)
+            ops.linear_residual(qo, ws.scales, layer.o, None, ws.hidden, ws.residual, variant)
+            ops.norm_quantize(ws.residual, layer.norm2, None, q4, ws.scales, ws.maxima, c.eps)
+            if self.unfused:
+                ops.linear_quantized(q4, ws.scales, layer.gate_up, ws.gate_up, variant)
+                ops.swiglu(ws.gate_up[:, :inter], ws.gate_up[:, inter:], ws.act, None)
+                ops.quantize(ws.act, ws.quant12, ws.scales)
+            elif rows == 1:
+                ops.linear_swiglu(q4, ws.scales, layer.gate, layer.up, None, None, ws.act, ws.maxima)
+                ops.quantize_with_max(ws.act, ws.maxima, ws.quant12, ws.scales)
+            else:
+                ops.linear_quantized(q4, ws.scales, layer.gate_up, ws.gate_up, variant)
+                ops.swiglu_quantize(ws.gate_up[:, :inter], ws.gate_up[:, inter:], ws.quant12, ws.scales)
+            ops.linear_residual(ws.quant12, ws.scales, layer.down, None, ws.residual, ws.hidden, variant)
+        last = ws.hidden[rows - 1:rows]
+        ops.norm_quantize(last, w.final_gain, None, self.head_q, self.head_scale, None, c.eps)
+        if self.unfused:
+            ops.linear_quantized(self.head_q, self.head_scale, w.head, self.logits, variant)
+        else:
+            ops.linear_argmax(self.head_q, self.head_scale, w.head, self.next)
+
+    def _select_unfused(self) -> int:
+        """select_token (src/kernels.rs:2191-2231) on the written logits: largest value, lowest index."""
+        logits = self.logits[0].float()
+        if not bool(torch.isfinite(logits).all()):
+            return 0xFFFFFFFF
+        return int((logits == logits.max()).nonzero()[0, 0])
+
+    def capture_decode(self) -> None:
+        """Capture one decode step (src/gpu.rs:303-333).  Everything it reads that changes between steps lives in
+        the control buffer and the caches."""
+        ops.set_programmatic_launch(True)
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            self.control.zero_()
+            self.forward(self.decode, self.control)  # warm-up outside the capture
+        stream.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=stream):
+            self.forward(self.decode, self.control)
+        torch.cuda.current_stream().wait_stream(stream)
+        ops.set_programmatic_launch(False)
+
+    def _read_next(self) -> int:
+        if self.unfused:
+            return self._select_unfused()
+        self._host_next.copy_(self.next, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return int(self._host_next[0]) & 0xFFFFFFFF
+
+    def generate(self, prompt_ids, max_tokens: int, use_graph: bool = True, stop_ids=()):
+        """GpuModel::generate (src/gpu.rs:818-929): prefill the prompt, then one token per step.  Returns
+        (token ids, seconds per step); the first step is the prefill."""
+        import time
+
+        c = self.c
+        if not prompt_ids or len(prompt_ids) + max_tokens > c.context:
+            raise ValueError("prompt must be non-empty and prompt + max_tokens must fit the context")
+        if use_graph and not self.unfused and self.graph is None:
+            self.capture_decode()
+        torch.cuda.synchronize()
+        prompt = torch.tensor(list(prompt_ids), dtype=torch.int32).pin_memory()
+        prefill = Workspace(c, len(prompt_ids), self.device)
+        ids = torch.empty(len(prompt_ids), dtype=torch.int32, device=self.device)
+        generated, seconds = [], []
+        position, rows, token = 0, len(prompt_ids), 0
+        for step in range(max_tokens):
+            start = time.perf_counter()
+            self._host_control[0] = token
+            self._host_control[1] = position
+            self.control.copy_(self._host_control, non_blocking=True)
+            if step == 0:
+                ids.copy_(prompt, non_blocking=True)
+                self.forward(prefill, ids)
+            elif self.graph is not None and use_graph and not self.unfused:
+                self.graph.replay()
+            else:
+                self.forward(self.decode, self.control)
+            token = self._read_next()
+            seconds.append(time.perf_counter() - start)
+            if token == 0xFFFFFFFF:
+                raise RuntimeError("nonfinite or empty logits")
+            generated.append(token)
+            if token in stop_ids:
+                break
+            position += rows
+            rows = 1
+        return generated, seconds

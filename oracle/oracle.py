@@ -187,3 +187,91 @@ def weight_quantize(w):
     s = np.empty((N,), np.float32)
     lib().oracle_weight_quantize(_p(w), N, K, _p(q), _p(s))
     return q, s
+
+
+# ---- the operators around the linear layers (numpy; float32 operations are separately rounded) ------------
+
+def embedding(ids, table_bits):
+    """src/kernels.rs:335-345: out[r] = widen(table[ids[r]]); table holds bf16 bit patterns."""
+    return from_bf16_bits(np.asarray(table_bits, np.uint16)[np.asarray(ids, np.int64)])
+
+
+def rope(x, table, position: int):
+    """src/kernels.rs:1444-1468.  x: [rows, heads, 128] float32; table: [positions, 128] (64 cosines, 64 sines);
+    row r is rotated with table[position + r]."""
+    x = _f32(x)
+    rows = x.shape[0]
+    t = _f32(table)[position:position + rows]
+    c = t[:, None, :64]
+    s = t[:, None, 64:]
+    a, b = x[..., :64], x[..., 64:]
+    first = bf16(a * c + (-(b * s)))
+    second = bf16(b * c + a * s)
+    return np.concatenate([first, second], -1)
+
+
+def head_norm(x, gain, eps: float = 1e-6, inv_ulps: int = 0):
+    """RMSNorm of width 128 as norm_rope / prepare_qk compute it (src/kernels.rs:1304-1331): squares, the first tree
+    level (p[t] + p[t+64]) + (p[t+32] + p[t+96]) for t < 32, a shuffle-down tree of distances 16..1, then
+    bf16((x * inv) * gain) with inv = rsqrt(sum / 128 + eps).  Equal to rmsnorm() at this width.  The kernel's
+    rsqrt.approx is not correctly rounded; `inv_ulps` moves inv by that many float32 steps so that a test can ask
+    whether a result is explained by an approximation error of that size."""
+    x = _f32(x)
+    g = _f32(gain)
+    sq = x * x
+    t = (sq[..., 0:32] + sq[..., 64:96]) + (sq[..., 32:64] + sq[..., 96:128])
+    d = 16
+    while d > 0:
+        t = t[..., :d] + t[..., d:2 * d]
+        d //= 2
+    arg = t[..., 0] / np.float32(128.0) + np.float32(eps)
+    inv = (1.0 / np.sqrt(arg.astype(np.float64))).astype(np.float32)
+    if inv_ulps:
+        inv = (inv.view(np.int32) + np.int32(inv_ulps)).view(np.float32)
+    return bf16((x * inv[..., None]) * g)
+
+
+def head_norm_rope(x, gain, table, position: int, eps: float = 1e-6, inv_ulps: int = 0):
+    """norm_rope / prepare_qk (src/kernels.rs:1292-1348, 1350-1443): head_norm, then rope.  x: [rows, heads, 128]."""
+    return rope(head_norm(x, gain, eps, inv_ulps), table, position)
+
+
+def attention(q, k_bits, v_bits, position: int):
+    """src/kernels.rs:1490-1658.  q: [rows, q_heads, 128] float32 (bf16 values); k_bits, v_bits: [keys, kv_heads, 128]
+    bf16 bit patterns with keys >= position + rows.  Row r sees keys 0 .. position + r.  Summation orders follow the
+    kernel: score = sequential sum over the 128 channels, times 128^-0.5; exp(score - max) with the kernel's
+    ex2.approx replaced by a correctly rounded exp (the one approximation in this restatement); the total as
+    128 strided partial sums (key j goes to partial j % 128, in increasing j) folded by a tree of distances 64..1;
+    one RN division per key; P.V as a sequential sum over the keys."""
+    q = _f32(q)
+    k = from_bf16_bits(np.asarray(k_bits, np.uint16))
+    v = from_bf16_bits(np.asarray(v_bits, np.uint16))
+    rows, heads, d = q.shape
+    group = heads // k.shape[1]
+    out = np.empty((rows, heads, d), np.float32)
+    scale = np.float32(0.08838834764831845)
+    for r in range(rows):
+        end = position + r + 1
+        for h in range(heads):
+            kk = k[:end, h // group]          # [end, 128]
+            vv = v[:end, h // group]
+            s = np.zeros(end, np.float32)
+            for c in range(d):
+                s = s + q[r, h, c] * kk[:, c]
+            s = s * scale
+            e = np.exp((s + (-s.max())).astype(np.float64)).astype(np.float32)
+            pad = np.zeros((end + 127) // 128 * 128, np.float32)
+            pad[:end] = e
+            part = np.zeros(128, np.float32)
+            for chunk in pad.reshape(-1, 128):
+                part = part + chunk
+            n = 64
+            while n > 0:
+                part[:n] = part[:n] + part[n:2 * n]
+                n //= 2
+            p = e / part[0]
+            acc = np.zeros(d, np.float32)
+            for j in range(end):
+                acc = acc + p[j] * vv[j]
+            out[r, h] = bf16(acc)
+    return out

@@ -21,6 +21,9 @@ class Fixtures:
     raw little-endian tensors, dtype implied by the key, shape and sha256 in manifest.json."""
 
     DTYPES = {"q": np.int8, "w": np.int8}
+    # bf16 tensors are stored as their bit patterns (operator_fixtures.py:26-27)
+    OP_DTYPES = {("attention", "q"): np.float32, ("attention", "k"): np.uint16, ("attention", "v"): np.uint16,
+                 ("embedding", "ids"): np.uint32, ("embedding", "w"): np.uint16}
 
     def __init__(self, root: Path):
         self.root = root
@@ -35,7 +38,7 @@ class Fixtures:
         meta = case["tensors"][key]
         raw = (self.root / meta["file"]).read_bytes()
         assert hashlib.sha256(raw).hexdigest() == meta["sha256"], f"fixture hash: {meta['file']}"
-        dtype = self.DTYPES.get(key, np.float32)
+        dtype = self.OP_DTYPES.get((case["op"], key), self.DTYPES.get(key, np.float32))
         return np.frombuffer(raw, dtype=dtype).reshape(meta["shape"]).copy()
 
 

@@ -1,5 +1,5 @@
 """CPU-only checks of the C-ABI boundary: the built library loads without a GPU and exports exactly the
-functions include/w8a8.h declares; the ctypes binding covers each of them.  No compute call is made."""
+functions include/w8a8.h and include/qwen3_glue.h declare; the ctypes binding covers each of them.  No compute call is made."""
 import re
 from pathlib import Path
 
@@ -10,10 +10,11 @@ ROOT = Path(__file__).resolve().parent.parent
 
 @pytest.fixture(scope="module")
 def declared():
-    text = (ROOT / "include" / "w8a8.h").read_text()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    names = re.findall(r"\b(w8a8_[a-z0-9_]+)\s*\(", text)
-    return sorted(set(names))
+    names = set()
+    for header in sorted((ROOT / "include").glob("*.h")):
+        text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
+        names.update(re.findall(r"\b((?:w8a8|qwen3)_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 @pytest.fixture(scope="module")
@@ -27,13 +28,14 @@ def lib():
 
 def test_header_declares_the_expected_surface(declared):
     for name in ("w8a8_init", "w8a8_weight_create", "w8a8_quantize", "w8a8_rmsnorm_quantize", "w8a8_swiglu_quantize",
-                 "w8a8_linear", "w8a8_linear_grouped", "w8a8_linear_gate_up_swiglu", "w8a8_residual", "w8a8_device_status"):
+                 "w8a8_linear", "w8a8_linear_grouped", "w8a8_linear_gate_up_swiglu", "w8a8_residual", "w8a8_device_status",
+                 "qwen3_embedding", "qwen3_prepare_qk", "qwen3_attention"):
         assert name in declared
 
 
 def test_library_exports_every_declared_symbol(lib, declared):
     for name in declared:
-        assert hasattr(lib, name), f"{name} declared in include/w8a8.h but not exported by libw8a8.so"
+        assert hasattr(lib, name), f"{name} declared in include/*.h but not exported by libw8a8.so"
 
 
 def test_binding_covers_every_declared_symbol(declared):
@@ -56,6 +58,9 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.w8a8_linear(None, None, None, 1, None, None, None, 0, None) == 1
     assert lib.w8a8_weight_destroy(None) == 1
     assert lib.w8a8_init(-1) == 1
+    # the operators around the linear layers refuse to run before w8a8_init()
+    assert lib.qwen3_embedding(None, None, 1, 4096, 10, None, 0, None) == 6
+    assert lib.qwen3_attention(None, 0, 4096, 1, 32, 8, None, None, None, None, 4096, 4096, None) == 6
 
 
 def test_product_does_not_import_the_oracle():

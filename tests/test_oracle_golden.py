@@ -140,3 +140,52 @@ def test_weight_quantize_is_row_quantize():
     assert np.array_equal(s, np.maximum(np.abs(w).max(1), np.float32(1e-8)) / np.float32(127))
     assert np.array_equal(q, np.clip(np.rint(w / s[:, None]), -127, 127).astype(np.int8))
     assert np.abs(q).max() == 127
+
+
+# ---- the operators around the linear layers ---------------------------------------------------------------
+
+def reference_tolerance(expected: np.ndarray) -> np.ndarray:
+    """Per-element bound of the reference's own fixture test for non-exact operators (src/conformance.rs:661)."""
+    return 2e-4 + 0.01 * np.abs(expected)
+
+
+def test_rope_matches_reference_fixture_exactly(fixtures):
+    # `rope` is one of the operators the reference compares exactly (src/conformance.rs:658)
+    (case,) = fixtures.cases("rope")
+    x = fixtures.tensor(case, "x")
+    rows = fixtures.tensor(case, "table_rows")
+    table = np.zeros((case["position"] + x.shape[0], 128), np.float32)
+    table[case["position"]:] = rows
+    assert np.array_equal(oracle.rope(x, table, case["position"]), fixtures.tensor(case, "out"))
+
+
+def test_embedding_matches_reference_fixture_exactly(fixtures):
+    (case,) = fixtures.cases("embedding")
+    got = oracle.embedding(fixtures.tensor(case, "ids"), fixtures.tensor(case, "w"))
+    assert np.array_equal(got, fixtures.tensor(case, "out"))
+
+
+def test_attention_within_reference_tolerance(fixtures):
+    cases = fixtures.cases("attention")
+    assert [c["position"] for c in cases] == [0, 129]
+    for case in cases:
+        expected = fixtures.tensor(case, "out")
+        got = oracle.attention(fixtures.tensor(case, "q"), fixtures.tensor(case, "k"), fixtures.tensor(case, "v"), case["position"])
+        assert np.all(np.abs(got - expected) <= reference_tolerance(expected))
+        rel = np.sqrt(((got.astype(np.float64) - expected) ** 2).sum() / (expected.astype(np.float64) ** 2).sum())
+        assert rel <= 0.005  # src/conformance.rs:669-673
+
+
+def test_head_norm_is_the_fixture_pinned_norm_at_width_128(fixtures):
+    """The fused head norm + rope is defined by the reference as `norm` (width 128) followed by `rope`
+    (src/conformance.rs:375-401); the width-128 norm is pinned by the reference's norm fixture, and the numpy
+    restatement of the head norm equals the C restatement of `norm` bit for bit."""
+    (case,) = [c for c in fixtures.cases("norm") if c["width"] == 128]
+    x, gain = fixtures.tensor(case, "x"), fixtures.tensor(case, "gain")
+    assert np.array_equal(oracle.head_norm(x, gain), oracle.rmsnorm(x.reshape(-1, 128), gain).reshape(x.shape))
+    rng = np.random.default_rng(5)
+    y = oracle.bf16((rng.standard_normal((300, 8, 128)) * rng.uniform(0.01, 30, (300, 8, 1))).astype(np.float32))
+    g = (1 + 0.2 * rng.standard_normal(128)).astype(np.float32)
+    assert np.array_equal(oracle.head_norm(y, g), oracle.rmsnorm(y.reshape(-1, 128), g).reshape(y.shape))
+    moved = oracle.head_norm(y, g, inv_ulps=2)
+    assert 0 < (moved != oracle.head_norm(y, g)).mean() < 0.02
