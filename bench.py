@@ -379,6 +379,8 @@ def run_ours(args):
         head = sum(r["us"] for r in extra["per_shape"] if r["M"] == 1 and r["shape"] == "lm_head")
         if body > 0 and head > 0:
             extra["decode_linear_only_tok_s_estimate"] = round(1e6 / (36 * body + head), 1)
+        if not args.shapes and not args.no_model:
+            extra["qwen3_8b_generation"] = model_generation_table(torch, hbm_peak)
 
     out = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
@@ -521,6 +523,39 @@ def decode_fused_table(torch, ops, hbm_peak):
     return rows
 
 
+def model_generation_table(torch, hbm_peak):
+    """Whole-model greedy generation of the Qwen3-8B architecture with random-init weights (inferrous_b200.qwen3):
+    the prompt / generated lengths the reference's decode table uses (docs/qwen3-8b-w8a8/benchmarks.md:13-15: prompt
+    5 / 129 / 512, 32 generated) plus the 129 + 128 run.  Host-visible time per step: control upload, graph replay,
+    token read-back, as the reference's generate() measures it (src/gpu.rs:873-908)."""
+    import numpy as np
+
+    from inferrous_b200.qwen3 import Qwen3Config, Qwen3Runner, Qwen3Weights
+
+    config = Qwen3Config.qwen3_8b()
+    weights = Qwen3Weights.random(config, seed=0)
+    runner = Qwen3Runner(weights)
+    rng = np.random.default_rng(0)
+    rows = []
+    published = {5: 182.3, 129: 178.2, 512: 170.5}
+    for prompt_len, generated in [(5, 32), (129, 32), (512, 32), (129, 128)]:
+        prompt = [int(t) for t in rng.integers(0, config.vocab, prompt_len)]
+        runner.generate(prompt, generated)  # warm-up: captures the decode graph on first use
+        _, seconds = runner.generate(prompt, generated)
+        decode = seconds[1:]
+        median = float(np.median(decode))
+        rows.append({"prompt": prompt_len, "generated": generated, "prefill_ms": round(seconds[0] * 1e3, 3),
+                     "decode_ms_per_token_median": round(median * 1e3, 4),
+                     "decode_tok_s": round(len(decode) / sum(decode), 1),
+                     "weight_GB/s": round(config.weight_bytes() / median / 1e9, 1),
+                     "frac_hbm": round(config.weight_bytes() / median / 1e9 / hbm_peak, 3),
+                     "reference_tok_s_rtx_pro_6000": published.get(prompt_len) if generated == 32 else None})
+    del runner, weights
+    torch.cuda.empty_cache()
+    return {"model": "Qwen3-8B architecture, random-init W8A8 weights (body and head int8), batch 1, greedy",
+            "weight_bytes_per_token": config.weight_bytes(), "runs": rows}
+
+
 def cpu_step(oracle, host, threads):
     for M in DECODE_M:
         for name, K, N in SHAPES:
@@ -608,6 +643,7 @@ def main():
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--no-extra", action="store_true", help="skip the per-shape and prefill tables")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-model", action="store_true", help="skip the whole-model generation table")
     ap.add_argument("--shapes", default="", help="comma-separated subset of the five projections (profiling runs)")
     ap.add_argument("--ms", default="", help="comma-separated subset of the token counts (profiling runs)")
     ap.add_argument("--variant", type=int, default=0, help="force a kernel variant for every linear call (A/B runs)")

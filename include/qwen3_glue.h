@@ -47,9 +47,13 @@ int qwen3_prepare_qk(void *qkv, int dtype, int64_t ld, int rows, int q_heads, in
                      int capacity, void *stream);
 
 /* out[r, h, :] = bf16(softmax(q[r, h, :] . K[0 .. control[1] + r, h / (q_heads / kv_heads), :] * 128^-0.5) . V[...]).
- * `q` may point into the qkv buffer (row stride `ldq`); `out` is [rows][q_heads * 128] with row stride `ldo`. */
+ * `q` may point into the qkv buffer (row stride `ldq`); `out` is [rows][q_heads * 128] with row stride `ldo`.
+ * `maxima` (optional, [rows]): an atomic max of the bit patterns of |out[r, :]| is applied to maxima[r], which the
+ * caller has set to the bits of 1e-8f beforehand; it feeds w8a8_quantize_with_max / W8A8_SOURCE_WITH_MAX, whose
+ * result then equals that of w8a8_quantize on `out`. */
 int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
-                    const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity, void *stream);
+                    const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity, uint32_t *maxima,
+                    void *stream);
 
 #ifdef __cplusplus
 }

@@ -156,6 +156,28 @@ int w8a8_linear_gate_up_swiglu(const int8_t *q, const float *a_scale, w8a8_weigh
                                int M, void *gate_out, void *up_out, void *act, uint32_t *maxima, int dtype,
                                void *stream);
 
+/* One-token (decode) projections with the activation quantizer folded into the projection kernel: every CTA
+ * quantizes the row for itself while its first weight loads are in flight, so no quantizer kernel runs between the
+ * producer of the row and the projection.  Each call replaces a pair of reference launches at M = 1:
+ *   W8A8_SOURCE_RMSNORM   `norm_quantize` (src/kernels.rs:479-576; GpuModel::norm_quantize, src/gpu.rs:340-363)
+ *   W8A8_SOURCE_WITH_MAX  `quantize_with_max` (src/kernels.rs:455-475; src/gpu.rs:377-390): maxima_in[0] holds the bit
+ *                         pattern of max(1e-8, max|x|), published by the producer of x with an atomic max
+ * followed by `linear` / `linear_residual` (w8a8_quantize_linear) or `linear_swiglu`
+ * (w8a8_quantize_linear_gate_up_swiglu).  Codes, scale and outputs are bit-identical to running the two entry
+ * points one after the other; the reference itself has no fused form of these pairs.
+ * x is one row of K elements.  Optional outputs written by the first CTA: `q_out` ([K] codes) and `scale_out` ([1]).
+ * `maxima_reset`: `reset_words` (<= 8) words set to the bits of 1e-8f, the state an atomic-max consumer starts from
+ * (the side effect GpuModel::norm_quantize has on its `maxima` argument); they must not be words that a kernel
+ * between this call's predecessor and its successor still reads.  K <= 16384 (RMSNORM) / 24576 (WITH_MAX). */
+#define W8A8_SOURCE_WITH_MAX 1
+#define W8A8_SOURCE_RMSNORM 2
+int w8a8_quantize_linear(const void *x, int dtype, int source, const void *gamma, float eps, const uint32_t *maxima_in,
+                         w8a8_weight_t weight, const void *residual, void *y, void *combined, uint32_t *maxima_reset,
+                         int reset_words, int8_t *q_out, float *scale_out, void *stream);
+int w8a8_quantize_linear_gate_up_swiglu(const void *x, int dtype, int source, const void *gamma, float eps,
+                                        const uint32_t *maxima_in, w8a8_weight_t w_gate, w8a8_weight_t w_up, void *act,
+                                        uint32_t *maxima_out, int8_t *q_out, float *scale_out, void *stream);
+
 /* The same projection, y = bf16((f32(acc) * a_scale[m]) * w_scale[n]), for callers that must not
  * allocate device memory: code running where cudaMalloc is forbidden or unavailable -- inside a
  * stream capture that the host application owns, in a process whose memory pool is closed after

@@ -8,6 +8,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libw8a8.so"
 
 OK = 0
 BF16, F32 = 0, 1
+SOURCE_WITH_MAX, SOURCE_RMSNORM = 1, 2
 VARIANT_AUTO, VARIANT_NAIVE, VARIANT_GEMV_DP4A, VARIANT_GEMV_MMA, VARIANT_GEMM_TCGEN05, VARIANT_GEMM_SKINNY, VARIANT_GEMV_ROWS, VARIANT_GEMM_TCGEN05_WIDE, VARIANT_GEMM_TCGEN05_PAIR = range(9)
 
 _vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
@@ -33,6 +34,8 @@ SIGNATURES = {
     "w8a8_linear_ex": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "w8a8_linear_grouped": (_i, [_vp, _vp, C.POINTER(_vp), _i, _i, C.POINTER(_vp), _i, _vp]),
     "w8a8_linear_gate_up_swiglu": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _vp]),
+    "w8a8_quantize_linear": (_i, [_vp, _i, _i, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp]),
+    "w8a8_quantize_linear_gate_up_swiglu": (_i, [_vp, _i, _i, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "w8a8_linear_no_alloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "w8a8_linear_argmax": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp]),
     "w8a8_tp_allreduce": (_i, [_vp, _vp, _sz, _i, C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _i, _sz, _vp]),
@@ -41,7 +44,7 @@ SIGNATURES = {
     # include/qwen3_glue.h
     "qwen3_embedding": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "qwen3_prepare_qk": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
-    "qwen3_attention": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _i, _vp]),
+    "qwen3_attention": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _i, _vp, _vp]),
 }
 
 

@@ -30,6 +30,8 @@ struct DeviceState {
     int32_t *sk_scratch = nullptr;   // stream-K partial tiles, zero between launches
     uint32_t *sk_counters = nullptr; // stream-K arrival counters, zero between launches
     unsigned long long *argmax = nullptr;  // per-block candidates of the fused head projection
+    float *attn_scratch = nullptr;         // split-key attention: partial results
+    uint32_t *attn_counters = nullptr;     // split-key attention: arrival counters, zero between launches
 };
 DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;
@@ -67,6 +69,14 @@ int32_t *skinny_scratch() {
 unsigned long long *argmax_scratch() {
     int dev = current_ready_device();
     return dev < 0 ? nullptr : g_dev[dev].argmax;
+}
+float *attention_scratch() {
+    int dev = current_ready_device();
+    return dev < 0 ? nullptr : g_dev[dev].attn_scratch;
+}
+uint32_t *attention_counters() {
+    int dev = current_ready_device();
+    return dev < 0 ? nullptr : g_dev[dev].attn_counters;
 }
 uint32_t *skinny_counters() {
     int dev = current_ready_device();
@@ -142,6 +152,9 @@ int w8a8_init(int device) {
     CUDA_OK(cudaMalloc(&d.sk_counters, (size_t)d.sms * 4 * sizeof(uint32_t)), "cudaMalloc(stream-K counters)");
     CUDA_OK(cudaMemset(d.sk_counters, 0, (size_t)d.sms * 4 * sizeof(uint32_t)), "cudaMemset(stream-K counters)");
     CUDA_OK(cudaMalloc(&d.argmax, (size_t)kArgmaxMaxBlocks * 16 * sizeof(unsigned long long)), "cudaMalloc(argmax candidates)");
+    CUDA_OK(cudaMalloc(&d.attn_scratch, kAttnScratchFloats * sizeof(float)), "cudaMalloc(attention scratch)");
+    CUDA_OK(cudaMalloc(&d.attn_counters, kAttnSplitMaxUnits * sizeof(uint32_t)), "cudaMalloc(attention counters)");
+    CUDA_OK(cudaMemset(d.attn_counters, 0, kAttnSplitMaxUnits * sizeof(uint32_t)), "cudaMemset(attention counters)");
     CUDA_OK(init_quantize(), "init_quantize");
     CUDA_OK(init_gemv(), "init_gemv");
     CUDA_OK(init_gemm_tcgen05(), "init_gemm_tcgen05");
@@ -392,6 +405,56 @@ int w8a8_linear_gate_up_swiglu(const int8_t *q, const float *a_scale, w8a8_weigh
     int st = run_linear(l, nullptr, W8A8_VARIANT_GEMV_MMA, stream);
     if (st != W8A8_OK) return st;
     return w8a8_swiglu(gate_out, up_out, dtype, M, w_gate->N, w_gate->N, act, maxima, stream);
+}
+
+// One-token projections with the activation quantizer in the GEMV's prologue (gemv.cu: quantize_prologue).
+static int fused_source(LinearArgs &l, const void *x, int dtype, int source, const void *gamma, float eps,
+                        const uint32_t *maxima_in, uint32_t *maxima_reset, int reset_words, int8_t *q_out, float *scale_out) {
+    REQUIRE(x && check_dtype(dtype), W8A8_ERR_BAD_ARG);
+    REQUIRE(source == W8A8_SOURCE_WITH_MAX || source == W8A8_SOURCE_RMSNORM, W8A8_ERR_BAD_ARG);
+    REQUIRE(source != W8A8_SOURCE_WITH_MAX || maxima_in, W8A8_ERR_BAD_ARG);
+    REQUIRE(source != W8A8_SOURCE_RMSNORM || gamma, W8A8_ERR_BAD_ARG);
+    REQUIRE(reset_words >= 0 && reset_words <= 8 && (reset_words == 0 || maxima_reset), W8A8_ERR_BAD_ARG);
+    REQUIRE(aligned16(x) && (gamma == nullptr || aligned16(gamma)) && (q_out == nullptr || aligned16(q_out)), W8A8_ERR_ALIGNMENT);
+    REQUIRE(l.K <= (source == W8A8_SOURCE_RMSNORM ? 16384 : 24576), W8A8_ERR_UNSUPPORTED);
+    l.M = 1; l.dtype = dtype;
+    l.src = source == W8A8_SOURCE_WITH_MAX ? SRC_WITH_MAX : SRC_RMSNORM;
+    l.x = x; l.gamma = gamma; l.eps = eps; l.maxima_in = maxima_in; l.maxima_reset = maxima_reset; l.reset_words = reset_words;
+    l.q_out = q_out; l.scale_out = scale_out;
+    return W8A8_OK;
+}
+
+int w8a8_quantize_linear(const void *x, int dtype, int source, const void *gamma, float eps, const uint32_t *maxima_in,
+                         w8a8_weight_t weight, const void *residual, void *y, void *combined, uint32_t *maxima_reset,
+                         int reset_words, int8_t *q_out, float *scale_out, void *stream) {
+    REQUIRE(valid_weight(weight), W8A8_ERR_BAD_ARG);
+    REQUIRE((residual == nullptr) == (combined == nullptr) && (y || combined), W8A8_ERR_BAD_ARG);
+    REQUIRE((y == nullptr || aligned16(y)) && (combined == nullptr || aligned16(combined)) && (residual == nullptr || aligned16(residual)),
+            W8A8_ERR_ALIGNMENT);
+    LinearArgs l{};
+    l.K = weight->K; l.count = 1;
+    l.w[0] = weight->w; l.ws[0] = weight->w_scale; l.out[0] = y; l.n[0] = weight->N;
+    l.epilogue = residual ? EPI_RESIDUAL : EPI_PLAIN;
+    l.residual = residual; l.combined = combined;
+    const int st = fused_source(l, x, dtype, source, gamma, eps, maxima_in, maxima_reset, reset_words, q_out, scale_out);
+    if (st != W8A8_OK) return st;
+    return run_linear(l, weight, W8A8_VARIANT_GEMV_DP4A, stream);
+}
+
+int w8a8_quantize_linear_gate_up_swiglu(const void *x, int dtype, int source, const void *gamma, float eps,
+                                        const uint32_t *maxima_in, w8a8_weight_t w_gate, w8a8_weight_t w_up, void *act,
+                                        uint32_t *maxima_out, int8_t *q_out, float *scale_out, void *stream) {
+    REQUIRE(valid_weight(w_gate) && valid_weight(w_up) && act, W8A8_ERR_BAD_ARG);
+    REQUIRE(w_gate->K == w_up->K && w_gate->N == w_up->N, W8A8_ERR_BAD_ARG);
+    REQUIRE(aligned16(act), W8A8_ERR_ALIGNMENT);
+    LinearArgs l{};
+    l.K = w_gate->K; l.count = 2;
+    l.w[0] = w_gate->w; l.ws[0] = w_gate->w_scale; l.n[0] = w_gate->N;
+    l.w[1] = w_up->w; l.ws[1] = w_up->w_scale; l.n[1] = w_up->N;
+    l.epilogue = EPI_SWIGLU; l.act = act; l.maxima = maxima_out;
+    const int st = fused_source(l, x, dtype, source, gamma, eps, maxima_in, nullptr, 0, q_out, scale_out);
+    if (st != W8A8_OK) return st;
+    return run_linear(l, nullptr, W8A8_VARIANT_GEMV_DP4A, stream);
 }
 
 int w8a8_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w, const float *w_scale, int M, int N, int K,

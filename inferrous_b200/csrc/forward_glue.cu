@@ -15,6 +15,8 @@
 #include "common.cuh"
 #include "internal.h"
 
+#include <algorithm>
+
 namespace w8a8 {
 namespace {
 
@@ -113,19 +115,24 @@ __global__ void __launch_bounds__(128) prepare_qk_kernel(typename T::storage *__
 }
 
 // ---- attention ---------------------------------------------------------------------------------------------
-// One CTA of 256 threads per (row, query head); the whole visible prefix is handled by that CTA, its scores
-// held in shared memory (context <= 4096).
+// One CTA of 256 threads per (row, query head, key split).  A split owns a contiguous range of the visible keys;
+// with one split the CTA writes the output row itself, otherwise it leaves (maximum, total, unnormalised sums)
+// in scratch memory and the last split to arrive combines them (flash-decoding), so that a single decode row
+// still spreads over the whole GPU.
 //   scores   eight lanes per key (16 channels each, summed in order, then a three-step butterfly), four keys per
 //            warp and sweep; score = dot * 128^-0.5, as the reference scales it
-//   softmax  maximum, e = exp(score - maximum) with the reference's ex2.approx form, one RN division e / total per key
-//            (the reference divides each weight before the P.V sum as well, src/kernels.rs:1608-1616)
+//   softmax  e = exp(score - maximum) with the reference's ex2.approx form; total = sum of e
 //   P.V      sixteen key slices (key j belongs to slice j % 16) x sixteen lanes of 8 channels, each slice summed
-//            in increasing j, then the sixteen partial sums added in slice order
-// The sums are reassociated relative to the reference's one-thread-per-key / one-thread-per-channel kernel, whose
-// float32 sums run strictly in key and channel order; the association here is fixed, so the result depends on
-// nothing but the inputs.
+//            in increasing j, the sixteen partial sums added in slice order; one RN division by the total at the end
+//   combine  maximum M over the splits, weights exp(m_s - M), sums and totals added in split order, one division
+// The sums are reassociated relative to the reference's one-thread-per-key / one-thread-per-channel kernel (strict
+// key and channel order, each weight divided by the total before the P.V sum, src/kernels.rs:1608-1616); the
+// association here is fixed by the launch shape and the number of visible keys, so the result depends on nothing
+// but the inputs and the launched split count.
 constexpr int kAttnThreads = 256;
 constexpr int kAttnSlices = 16;
+constexpr int kAttnRecord = kHeadDim + 4;  // floats per (unit, split) in scratch: 128 sums, maximum, total, padding
+constexpr int kAttnKeysPerSplit = 64;      // a split is not worth its combine step for fewer keys
 
 __device__ __forceinline__ float dot16(const float (&qv)[16], const uint4 a, const uint4 b) {
     const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
@@ -144,21 +151,31 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
                                                                  const uint16_t *__restrict__ v_cache,
                                                                  const uint32_t *__restrict__ control,
                                                                  typename T::storage *__restrict__ out, int64_t ldo, int capacity,
+                                                                 uint32_t *maxima, float *scratch, uint32_t *counters,
                                                                  uint32_t *status) {
     __shared__ float scores[kMaxContext];
     __shared__ float query[kHeadDim];
     __shared__ float reduce[kAttnThreads / 32];
     __shared__ float partial[kAttnSlices][kHeadDim];
+    __shared__ uint32_t arrived;
     dependency_wait();
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-    const int row = blockIdx.x / q_heads, head = blockIdx.x % q_heads;
+    const int unit = blockIdx.x, split = blockIdx.y;
+    const int row = unit / q_heads, head = unit % q_heads;
     const int kv = head / (q_heads / kv_heads);
     const uint32_t end_u = control[1] + (uint32_t)row + 1u;
-    if (end_u > (uint32_t)capacity) {
-        if (t == 0) record_range_fault(status, end_u);
+    if (end_u > (uint32_t)capacity) {  // every split of the unit takes this branch: nobody waits for anybody
+        if (t == 0 && split == 0) record_range_fault(status, end_u);
         return;
     }
     const int end = (int)end_u;
+    // Splits in use: one per kAttnKeysPerSplit visible keys, at most the launched number; the rest leave at once.
+    const int splits = min((int)gridDim.y, (end + kAttnKeysPerSplit - 1) / kAttnKeysPerSplit);
+    if (split >= splits) return;
+    // this split's keys: [begin, stop), ranges of a multiple of 32 keys
+    const int chunk = (((end + splits - 1) / splits) + 31) & ~31;
+    const int begin = min(end, split * chunk), stop = min(end, begin + chunk);
+    const int count = stop - begin;
     if (t < kHeadDim) query[t] = T::load(q + (size_t)row * ldq + (size_t)head * kHeadDim + t);
     __syncthreads();
 
@@ -168,13 +185,13 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
 #pragma unroll
     for (int i = 0; i < 16; ++i) qv[i] = query[16 * sub + i];
     const size_t key_stride = (size_t)kv_heads * kHeadDim;
-    const uint16_t *kbase = k_cache + (size_t)kv * kHeadDim + 16 * sub;
+    const uint16_t *kbase = k_cache + (size_t)begin * key_stride + (size_t)kv * kHeadDim + 16 * sub;
     float maximum = -INFINITY;
 #pragma unroll 2
-    for (int j0 = warp * 4; j0 < end; j0 += (kAttnThreads / 32) * 4) {
+    for (int j0 = warp * 4; j0 < count; j0 += (kAttnThreads / 32) * 4) {
         const int j = j0 + group;
         float s = 0.0f;
-        if (j < end) {
+        if (j < count) {
             const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)j * key_stride);
             s = dot16(qv, kr[0], kr[1]);
         }
@@ -182,7 +199,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
         s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 2));
         s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
         s = __fmul_rn(s, 0.08838834764831845f);
-        if (j < end) {
+        if (j < count) {
             maximum = fmaxf(maximum, s);
             if (sub == 0) scores[j] = s;
         }
@@ -196,9 +213,9 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
     for (int i = 1; i < kAttnThreads / 32; ++i) maximum = fmaxf(maximum, reduce[i]);
     __syncthreads();
 
-    // softmax
+    // softmax numerators and their total (an empty split has maximum -inf and total 0)
     float total = 0.0f;
-    for (int j = t; j < end; j += kAttnThreads) {
+    for (int j = t; j < count; j += kAttnThreads) {
         const float e = exp_approx(__fadd_rn(scores[j], -maximum));
         scores[j] = e;
         total = __fadd_rn(total, e);
@@ -207,18 +224,16 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
     for (int d = 16; d > 0; d >>= 1) total = __fadd_rn(total, __shfl_xor_sync(0xffffffffu, total, d));
     if (lane == 0) reduce[warp] = total;
     __syncthreads();
-    float den = reduce[0];
+    total = reduce[0];
 #pragma unroll
-    for (int i = 1; i < kAttnThreads / 32; ++i) den = __fadd_rn(den, reduce[i]);
-    for (int j = t; j < end; j += kAttnThreads) scores[j] = __fdiv_rn(scores[j], den);
-    __syncthreads();
+    for (int i = 1; i < kAttnThreads / 32; ++i) total = __fadd_rn(total, reduce[i]);
 
-    // P.V
+    // P.V, unnormalised
     const int slice = t >> 4, cg = t & 15;
-    const uint16_t *vbase = v_cache + (size_t)kv * kHeadDim + 8 * cg;
+    const uint16_t *vbase = v_cache + (size_t)begin * key_stride + (size_t)kv * kHeadDim + 8 * cg;
     float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 4
-    for (int j = slice; j < end; j += kAttnSlices) {
+    for (int j = slice; j < count; j += kAttnSlices) {
         const uint4 v = *reinterpret_cast<const uint4 *>(vbase + (size_t)j * key_stride);
         const float p = scores[j];
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -231,11 +246,50 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
 #pragma unroll
     for (int i = 0; i < 8; ++i) partial[slice][8 * cg + i] = acc[i];
     __syncthreads();
+    float sum = 0.0f;
     if (t < kHeadDim) {
-        float sum = partial[0][t];
+        sum = partial[0][t];
 #pragma unroll
         for (int i = 1; i < kAttnSlices; ++i) sum = __fadd_rn(sum, partial[i][t]);
-        T::store(out + (size_t)row * ldo + (size_t)head * kHeadDim + t, bf16_rne(sum));
+    }
+
+    if (splits > 1) {
+        float *mine = scratch + ((size_t)unit * gridDim.y + split) * kAttnRecord;
+        if (t < kHeadDim) mine[t] = sum;
+        if (t == 0) {
+            mine[kHeadDim] = maximum;
+            mine[kHeadDim + 1] = total;
+        }
+        __threadfence();
+        __syncthreads();
+        if (t == 0) {
+            const uint32_t before = atomicAdd(counters + unit, 1u);
+            arrived = before;
+            if (before == (uint32_t)splits - 1u) counters[unit] = 0u;  // the counter is zero again for the next launch
+        }
+        __syncthreads();
+        if (arrived != (uint32_t)splits - 1u) return;
+        __threadfence();
+        if (t >= kHeadDim) return;
+        const float *all = scratch + (size_t)unit * gridDim.y * kAttnRecord;
+        float top = -INFINITY;
+        for (int s = 0; s < splits; ++s) top = fmaxf(top, __ldcg(all + s * kAttnRecord + kHeadDim));
+        sum = 0.0f;
+        total = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float *rec = all + s * kAttnRecord;
+            const float weight = exp_approx(__fadd_rn(__ldcg(rec + kHeadDim), -top));  // 0 for an empty split
+            total = __fadd_rn(total, __fmul_rn(__ldcg(rec + kHeadDim + 1), weight));
+            sum = __fadd_rn(sum, __fmul_rn(__ldcg(rec + t), weight));
+        }
+    }
+    if (t < kHeadDim) {
+        const float o = bf16_rne(__fdiv_rn(sum, total));
+        T::store(out + (size_t)row * ldo + (size_t)head * kHeadDim + t, o);
+        if (maxima) {  // max |out| of the row, for a quantizer that takes its maximum from the producer
+            const uint32_t m = warp_max_u32(absmax_key(o));
+            if (lane == 0) atomicMax(maxima + row, m);
+        }
     }
 }
 
@@ -289,7 +343,8 @@ int qwen3_prepare_qk(void *qkv, int dtype, int64_t ld, int rows, int q_heads, in
 }
 
 int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
-                    const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity, void *stream) {
+                    const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity, uint32_t *maxima,
+                    void *stream) {
     REQUIRE(device_status_ptr(), W8A8_ERR_NOT_INITIALIZED);
     REQUIRE(q && k_cache && v_cache && control && out, W8A8_ERR_BAD_ARG);
     REQUIRE(dtype == W8A8_BF16 || dtype == W8A8_F32, W8A8_ERR_BAD_ARG);
@@ -298,14 +353,18 @@ int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads
     REQUIRE(ldq >= (int64_t)q_heads * kHeadDim && ldo >= (int64_t)q_heads * kHeadDim, W8A8_ERR_BAD_ARG);
     REQUIRE(aligned(k_cache, 16) && aligned(v_cache, 16), W8A8_ERR_ALIGNMENT);
     if (rows == 0) return W8A8_OK;
-    const dim3 grid(rows * q_heads);
+    // Few (row, head) units: split the keys of each over several CTAs, about two CTAs per SM in all.
+    const int units = rows * q_heads;
+    int splits = 1;
+    if (units < sm_count() && units <= kAttnSplitMaxUnits) splits = std::min(kAttnMaxSplits, (2 * sm_count() + units - 1) / units);
+    const dim3 grid(units, splits);
     cudaError_t e = dtype == W8A8_BF16
                         ? launch_kernel(attention_kernel<Bf16>, grid, dim3(kAttnThreads), 0, (cudaStream_t)stream, (const uint16_t *)q, ldq,
-                                        q_heads, kv_heads, k_cache, v_cache, control, (uint16_t *)out, ldo, capacity,
-                                        device_status_ptr())
+                                        q_heads, kv_heads, k_cache, v_cache, control, (uint16_t *)out, ldo, capacity, maxima,
+                                        attention_scratch(), attention_counters(), device_status_ptr())
                         : launch_kernel(attention_kernel<F32>, grid, dim3(kAttnThreads), 0, (cudaStream_t)stream, (const float *)q, ldq,
-                                        q_heads, kv_heads, k_cache, v_cache, control, (float *)out, ldo, capacity,
-                                        device_status_ptr());
+                                        q_heads, kv_heads, k_cache, v_cache, control, (float *)out, ldo, capacity, maxima,
+                                        attention_scratch(), attention_counters(), device_status_ptr());
     return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "attention launch");
 }
 

@@ -40,6 +40,15 @@ struct GemvDev {
     uint32_t *maxima;
     int32_t *acc;
     unsigned long long *partial_best;
+    // quantizing prologue (SRC != SRC_CODES)
+    const void *x;
+    const void *gamma;
+    float eps;
+    const uint32_t *maxima_in;
+    uint32_t *maxima_reset;
+    int reset_words;
+    int8_t *q_out;
+    float *scale_out;
 };
 
 __device__ __forceinline__ int dp4a_16(const uint4 &w, const uint4 &a, int acc) {
@@ -64,10 +73,92 @@ __device__ __forceinline__ void locate(const GemvDev &a, int row, int &g, int &c
     }
 }
 
+// The activation quantizer as a prologue of the one-token GEMV: every CTA turns the unquantized row into int8 codes
+// in its own shared memory while its first weight loads are in flight, so that no quantizer kernel (and no launch
+// gap) sits between the producer of the row and the projection.  The arithmetic is that of the standalone
+// quantizers (quantize.cu), pass for pass:
+//   SRC_WITH_MAX  quantize_with_max (src/kernels.rs:455-475): s = m / 127 with m published by the producer
+//   SRC_RMSNORM   norm_quantize (src/kernels.rs:479-576): the reference's summation tree (256 strided partial sums,
+//                 distances 128..1), y = bf16((x * rsqrt(mean + eps)) * gain), m = max(1e-8, max|y|), s = m / 127
+// `extra` is K + 256 + 32 floats of shared memory for SRC_RMSNORM (unused for SRC_WITH_MAX).  Returns the scale.
+template <class T, int SRC>
+__device__ __forceinline__ float quantize_prologue(const GemvDev &a, int8_t *sq, float *extra, int tid) {
+    typedef typename T::storage S;
+    constexpr int V = T::kVec;
+    const int K = a.K;
+    const S *xr = static_cast<const S *>(a.x);
+    float s;
+    if constexpr (SRC == SRC_WITH_MAX) {
+        s = __fdiv_rn(__uint_as_float(a.maxima_in[0]), 127.0f);
+        const float inv = __frcp_rn(s);
+        for (int j = tid * V; j < K; j += kThreads * V) {
+            float v[V];
+            Vec<T>::load(xr + j, v);
+            int c[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) c[i] = quant_code(v[i], s, inv);
+            store_codes<V>(sq + j, c);
+        }
+    } else {
+        float *row = extra;
+        float *red = extra + K;
+        uint32_t *slots = reinterpret_cast<uint32_t *>(red + 256);
+        for (int j = tid * V; j < K; j += kThreads * V) {
+            float v[V];
+            Vec<T>::load(xr + j, v);
+#pragma unroll
+            for (int i = 0; i < V; i += 4)
+                *reinterpret_cast<float4 *>(row + j + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+        __syncthreads();
+        {
+            float p = 0.0f;
+            for (int j = tid; j < K; j += 256) p = __fadd_rn(p, __fmul_rn(row[j], row[j]));
+            red[tid] = p;
+        }
+        __syncthreads();
+        if (tid < 32) {
+            float t = __fadd_rn(__fadd_rn(__fadd_rn(red[tid], red[tid + 128]), __fadd_rn(red[tid + 64], red[tid + 192])),
+                                __fadd_rn(__fadd_rn(red[tid + 32], red[tid + 160]), __fadd_rn(red[tid + 96], red[tid + 224])));
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, d));
+            if (tid == 0) red[0] = t;
+        }
+        __syncthreads();
+        const float inv_norm = rsqrt_approx(__fadd_rn(__fdiv_rn(red[0], (float)K), a.eps));
+        const S *gr = static_cast<const S *>(a.gamma);
+        float m = 1e-8f;
+        for (int j = tid * V; j < K; j += kThreads * V) {
+            float g[V];
+            Vec<T>::load(gr + j, g);
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                const float y = bf16_rne(__fmul_rn(__fmul_rn(row[j + i], inv_norm), g[i]));
+                m = fmaxf(m, fabsf(y));
+                row[j + i] = y;
+            }
+        }
+        s = __fdiv_rn(block_max(m, slots, tid), 127.0f);
+        const float inv = __frcp_rn(s);
+        for (int j = tid * V; j < K; j += kThreads * V) {
+            int c[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) c[i] = quant_code(row[j + i], s, inv);
+            store_codes<V>(sq + j, c);
+        }
+    }
+    if (blockIdx.x == 0 && tid == 0) {
+        if (a.scale_out) a.scale_out[0] = s;
+        for (int i = 0; i < a.reset_words; ++i) a.maxima_reset[i] = __float_as_uint(1e-8f);
+    }
+    return s;
+}
+
 // ---------------------------------------------------------------------------------------
 // gemv_dp4a: MT tokens (1..4), R = 1 (plain) or 2 (gate+up) weight rows per warp.
+// SRC != SRC_CODES (MT == 1 only): the activation row is quantized in the prologue.
 // ---------------------------------------------------------------------------------------
-template <int MT, class T, int EPI>
+template <int MT, class T, int EPI, int SRC = SRC_CODES>
 __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const GemvDev a) {
     typedef typename T::storage S;
     constexpr int R = (EPI == EPI_SWIGLU) ? 2 : 1;
@@ -116,10 +207,21 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const GemvDev a) {
         }
 
     dependency_wait();
-    // Park the quantized activations (MT rows of K bytes) in shared memory.
-    for (int i = tid * 16; i < MT * K; i += kThreads * 16)
-        *reinterpret_cast<uint4 *>(sq + i) = *reinterpret_cast<const uint4 *>(a.q + i);
+    float own_scale = 0.0f;
+    if constexpr (SRC == SRC_CODES) {
+        // Park the quantized activations (MT rows of K bytes) in shared memory.
+        for (int i = tid * 16; i < MT * K; i += kThreads * 16)
+            *reinterpret_cast<uint4 *>(sq + i) = *reinterpret_cast<const uint4 *>(a.q + i);
+    } else {
+        static_assert(SRC == SRC_CODES || MT == 1, "the quantizing prologue handles one token");
+        own_scale = quantize_prologue<T, SRC>(a, sq, reinterpret_cast<float *>(red + kWarps * 2 * MT), tid);
+    }
     __syncthreads();
+    if constexpr (SRC != SRC_CODES) {
+        if (blockIdx.x == 0 && a.q_out)
+            for (int i = tid * 16; i < K; i += kThreads * 16)
+                *reinterpret_cast<uint4 *>(a.q_out + i) = *reinterpret_cast<const uint4 *>(sq + i);
+    }
 
     for (int base = first; base < K; base += U * step) {
 #pragma unroll
@@ -181,7 +283,7 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const GemvDev a) {
             if (lane == m) sum[r] = acc[r][m];
     }
     const int m = lane;
-    const float as = (EPI == EPI_ACC) ? 0.0f : a.a_scale[m];
+    const float as = (EPI == EPI_ACC) ? 0.0f : (SRC == SRC_CODES ? a.a_scale[m] : own_scale);
     if (EPI == EPI_ACC) {
         a.acc[(int64_t)m * a.n[0] + c] = sum[0];
     } else if (EPI == EPI_SWIGLU) {
@@ -386,6 +488,8 @@ GemvDev make_dev(const LinearArgs &l) {
     d.ks = 1;
     d.residual = l.residual; d.combined = l.combined; d.act = l.act; d.maxima = l.maxima; d.acc = l.acc;
     d.partial_best = l.partial_best;
+    d.x = l.x; d.gamma = l.gamma; d.eps = l.eps; d.maxima_in = l.maxima_in; d.maxima_reset = l.maxima_reset;
+    d.reset_words = l.maxima_reset ? l.reset_words : 0; d.q_out = l.q_out; d.scale_out = l.scale_out;
     return d;
 }
 
@@ -396,6 +500,22 @@ template <int MT, class T, int EPI> cudaError_t launch_dp4a_inst(const GemvDev &
     const unsigned grid = (unsigned)((d.ntot + rows_per_cta - 1) / rows_per_cta);
     const size_t smem = (size_t)MT * d.K + kWarps * 2 * MT * sizeof(int);
     return launch_kernel(gemv_dp4a_kernel<MT, T, EPI>, dim3(grid), dim3(kThreads), smem, s, d);
+}
+// one token, quantizing prologue
+template <class T, int EPI, int SRC> cudaError_t launch_dp4a_src_inst(const GemvDev &d, cudaStream_t s) {
+    const int rows_per_cta = kWarps / d.ks;
+    const unsigned grid = (unsigned)((d.ntot + rows_per_cta - 1) / rows_per_cta);
+    size_t smem = (size_t)d.K + kWarps * 2 * sizeof(int);
+    if (SRC == SRC_RMSNORM) smem += ((size_t)d.K + 256 + 32) * sizeof(float);
+    return launch_kernel(gemv_dp4a_kernel<1, T, EPI, SRC>, dim3(grid), dim3(kThreads), smem, s, d);
+}
+template <class T, int SRC> cudaError_t launch_dp4a_src(int epi, const GemvDev &d, cudaStream_t s) {
+    switch (epi) {
+        case EPI_PLAIN: return launch_dp4a_src_inst<T, EPI_PLAIN, SRC>(d, s);
+        case EPI_RESIDUAL: return launch_dp4a_src_inst<T, EPI_RESIDUAL, SRC>(d, s);
+        case EPI_SWIGLU: return launch_dp4a_src_inst<T, EPI_SWIGLU, SRC>(d, s);
+        default: return cudaErrorInvalidValue;
+    }
 }
 template <int MT, class T> cudaError_t launch_dp4a_epi(int epi, const GemvDev &d, cudaStream_t s) {
     switch (epi) {
@@ -446,6 +566,13 @@ template <int MT, class T> cudaError_t set_attr_dp4a() {
     if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<MT, T, EPI_ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDp4aSmem))) return e;
     return cudaSuccess;
 }
+template <class T, int SRC> cudaError_t set_attr_dp4a_src() {
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<1, T, EPI_PLAIN, SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDp4aSmem))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<1, T, EPI_RESIDUAL, SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDp4aSmem))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<1, T, EPI_SWIGLU, SRC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDp4aSmem))) return e;
+    return cudaSuccess;
+}
 
 }  // namespace
 
@@ -456,6 +583,10 @@ cudaError_t init_gemv() {
     if ((e = set_attr_dp4a<MT, F32>()) != cudaSuccess) return e;
     W8A8_SET(1) W8A8_SET(2) W8A8_SET(3) W8A8_SET(4)
 #undef W8A8_SET
+    if ((e = set_attr_dp4a_src<Bf16, SRC_WITH_MAX>()) != cudaSuccess) return e;
+    if ((e = set_attr_dp4a_src<F32, SRC_WITH_MAX>()) != cudaSuccess) return e;
+    if ((e = set_attr_dp4a_src<Bf16, SRC_RMSNORM>()) != cudaSuccess) return e;
+    if ((e = set_attr_dp4a_src<F32, SRC_RMSNORM>()) != cudaSuccess) return e;
     return cudaSuccess;
 }
 
@@ -467,6 +598,15 @@ cudaError_t launch_gemv_dp4a(const LinearArgs &l, cudaStream_t s) {
     int ks = 1;
     while (ks < kWarps && d.ntot * ks < want && l.K / (ks * 2) >= 512) ks *= 2;
     d.ks = ks;
+    if (l.src != SRC_CODES) {
+        // shared memory: codes + (RMSNorm) the row as float32; 5 bytes per element must fit beside the reductions
+        if (l.M != 1 || (l.src == SRC_RMSNORM && l.K > 16384)) return cudaErrorInvalidValue;
+        if (l.src == SRC_WITH_MAX)
+            return l.dtype == 0 ? launch_dp4a_src<Bf16, SRC_WITH_MAX>(l.epilogue, d, s) : launch_dp4a_src<F32, SRC_WITH_MAX>(l.epilogue, d, s);
+        if (l.src == SRC_RMSNORM)
+            return l.dtype == 0 ? launch_dp4a_src<Bf16, SRC_RMSNORM>(l.epilogue, d, s) : launch_dp4a_src<F32, SRC_RMSNORM>(l.epilogue, d, s);
+        return cudaErrorInvalidValue;
+    }
     return l.dtype == 0 ? launch_dp4a_m<Bf16>(l.M, l.epilogue, d, s) : launch_dp4a_m<F32>(l.M, l.epilogue, d, s);
 }
 

@@ -42,6 +42,10 @@ cudaError_t launch_swiglu(const void *gate, const void *up, int dtype, int M, in
 cudaError_t launch_residual(const void *a, const void *b, int dtype, size_t n, void *out, cudaStream_t s);
 cudaError_t launch_rounding_probe(const float *x, int8_t *out, size_t n, cudaStream_t s);
 
+// Where a decode GEMV takes its quantized activation row from: codes + scale written by a quantizer kernel, or the
+// quantizer folded into the GEMV's own prologue (one token; every CTA quantizes the row for itself).
+enum ActivationSource { SRC_CODES = 0, SRC_WITH_MAX = 1, SRC_RMSNORM = 2 };
+
 enum Epilogue { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_ACC = 3, EPI_ARGMAX = 4 };
 
 struct LinearArgs {
@@ -61,6 +65,16 @@ struct LinearArgs {
     int32_t *acc;                 // EPI_ACC: raw accumulators [M, n[0]]
     unsigned long long *partial_best;  // EPI_ARGMAX: [row blocks][16] packed (ordered value, ~index) per token
     int dtype;
+    // ActivationSource != SRC_CODES (gemv_dp4a only, M == 1): the unquantized row and what its quantizer needs
+    int src;
+    const void *x;               // [K] activations in `dtype`
+    const void *gamma;           // SRC_RMSNORM: gain row
+    float eps;                   // SRC_RMSNORM
+    const uint32_t *maxima_in;   // SRC_WITH_MAX: bit pattern of max(1e-8, max|x|), published by the producer
+    uint32_t *maxima_reset;      // optional: `reset_words` words set to the bits of 1e-8f by the first CTA
+    int reset_words;
+    int8_t *q_out;               // optional: the codes, written by the first CTA
+    float *scale_out;            // optional: the scale, written by the first CTA
 };
 cudaError_t launch_linear_naive(const LinearArgs &a, cudaStream_t s);
 cudaError_t launch_gemv_dp4a(const LinearArgs &a, cudaStream_t s);   // M <= 4
@@ -104,6 +118,14 @@ constexpr int kArgmaxMaxBlocks = 16384;  // head matrices up to 262144 output ch
 // one-shot all-reduce over peer memory (tp_allreduce.cu)
 cudaError_t launch_tp_allreduce(const void *partial, void *out, size_t n_el, int dtype, void *const *bufs, uint32_t *const *flags,
                                 uint32_t *seq, int rank, int tp, size_t slot_el, cudaStream_t s);
+
+// split-key attention (forward_glue.cu): per (row, head, split) partial results and per (row, head) arrival
+// counters (zero between launches), allocated once per device
+constexpr int kAttnSplitMaxUnits = 256;
+constexpr int kAttnMaxSplits = 16;
+constexpr size_t kAttnScratchFloats = (size_t)kAttnSplitMaxUnits * kAttnMaxSplits * 132;
+float *attention_scratch();
+uint32_t *attention_counters();
 
 int sm_count();
 // Records the failing CUDA call's text for w8a8_last_cuda_error() and returns W8A8_ERR_CUDA.

@@ -35,30 +35,6 @@ struct QuantDev {
     uint32_t *maxima_reset;
 };
 
-template <int N> __device__ __forceinline__ void store_codes(int8_t *dst, const int (&c)[N]);
-template <> __device__ __forceinline__ void store_codes<8>(int8_t *dst, const int (&c)[8]) {
-    uint2 p;
-    p.x = (c[0] & 0xff) | ((c[1] & 0xff) << 8) | ((c[2] & 0xff) << 16) | ((uint32_t)c[3] << 24);
-    p.y = (c[4] & 0xff) | ((c[5] & 0xff) << 8) | ((c[6] & 0xff) << 16) | ((uint32_t)c[7] << 24);
-    *reinterpret_cast<uint2 *>(dst) = p;
-}
-template <> __device__ __forceinline__ void store_codes<4>(int8_t *dst, const int (&c)[4]) {
-    *reinterpret_cast<uint32_t *>(dst) =
-        (c[0] & 0xff) | ((c[1] & 0xff) << 8) | ((c[2] & 0xff) << 16) | ((uint32_t)c[3] << 24);
-}
-
-// Block-wide maximum of non-negative floats (compared as unsigned bit patterns); up to 32 warps.
-__device__ __forceinline__ float block_max(float m, uint32_t *slots, int tid) {
-    const int nwarps = blockDim.x >> 5;
-    uint32_t k = warp_max_u32(__float_as_uint(m));
-    if ((tid & 31) == 0) slots[tid >> 5] = k;
-    __syncthreads();
-    uint32_t v = (tid & 31) < nwarps ? slots[tid & 31] : 0u;
-    v = warp_max_u32(v);
-    __syncthreads();  // slots may be reused by the next row
-    return __uint_as_float(v);
-}
-
 // Register-resident fast path: each thread keeps its RV 16-byte vectors of the row in registers between the
 // absmax pass and the coding pass, so shared memory carries only the reductions (plain / SwiGLU) or the one
 // copy of x that the reference's summation tree walks with stride 256 (RMSNorm; stored with a 16-byte XOR

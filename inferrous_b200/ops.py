@@ -175,6 +175,30 @@ def linear_swiglu(q: torch.Tensor, scale: torch.Tensor, w_gate: Matrix, w_up: Ma
                                                       _stream()), "w8a8_linear_gate_up_swiglu")
 
 
+def quantize_linear(x: torch.Tensor, w: Matrix, out: torch.Tensor | None, *, gain: torch.Tensor | None = None,
+                    maxima_in: torch.Tensor | None = None, eps: float = 1e-6, residual_in: torch.Tensor | None = None,
+                    combined: torch.Tensor | None = None, maxima_reset: torch.Tensor | None = None,
+                    q_out: torch.Tensor | None = None, scale_out: torch.Tensor | None = None) -> None:
+    """One token: `norm_quantize` (gain given) or `quantize_with_max` (maxima_in given) folded into the projection that
+    follows it (GpuModel::norm_quantize / linear_residual at one row, src/gpu.rs:340-423)."""
+    source = capi.SOURCE_RMSNORM if gain is not None else capi.SOURCE_WITH_MAX
+    capi.check(capi.load().w8a8_quantize_linear(_ptr(x), _dtype_code(x), source, _ptr(gain), eps, _ptr(maxima_in), w.handle,
+                                                _ptr(residual_in), _ptr(out), _ptr(combined), _ptr(maxima_reset),
+                                                0 if maxima_reset is None else maxima_reset.numel(), _ptr(q_out),
+                                                _ptr(scale_out), _stream()), "w8a8_quantize_linear")
+
+
+def quantize_linear_swiglu(x: torch.Tensor, w_gate: Matrix, w_up: Matrix, act: torch.Tensor, maxima_out: torch.Tensor | None, *,
+                           gain: torch.Tensor | None = None, maxima_in: torch.Tensor | None = None, eps: float = 1e-6,
+                           q_out: torch.Tensor | None = None, scale_out: torch.Tensor | None = None) -> None:
+    """One token: the quantizer folded into kernel `linear_swiglu` (src/kernels.rs:621-695; src/gpu.rs:730-745)."""
+    source = capi.SOURCE_RMSNORM if gain is not None else capi.SOURCE_WITH_MAX
+    capi.check(capi.load().w8a8_quantize_linear_gate_up_swiglu(_ptr(x), _dtype_code(x), source, _ptr(gain), eps, _ptr(maxima_in),
+                                                               w_gate.handle, w_up.handle, _ptr(act), _ptr(maxima_out),
+                                                               _ptr(q_out), _ptr(scale_out), _stream()),
+               "w8a8_quantize_linear_gate_up_swiglu")
+
+
 def linear_no_alloc(q: torch.Tensor, scale: torch.Tensor, w: torch.Tensor, w_scale: torch.Tensor, out: torch.Tensor) -> None:
     """The projection for callers that cannot allocate device memory (w8a8_linear_no_alloc): raw weight
     tensors instead of a Matrix handle, at most 16 tokens, scratch in a fixed array inside the library.
@@ -223,9 +247,10 @@ def prepare_qk(qkv: torch.Tensor, q_heads: int, kv_heads: int, q_gain: torch.Ten
 
 
 def attention(q: torch.Tensor, q_heads: int, kv_heads: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
-              control: torch.Tensor, out: torch.Tensor) -> None:
+              control: torch.Tensor, out: torch.Tensor, maxima: torch.Tensor | None = None) -> None:
     """Kernel `attention` (src/kernels.rs:1490-1658; src/gpu.rs:659-671): causal grouped-query attention of `rows`
-    new positions over the cache.  `q` may be the qkv buffer (its leading q_heads * 128 columns are read)."""
+    new positions over the cache.  `q` may be the qkv buffer (its leading q_heads * 128 columns are read).  `maxima`
+    ([rows] words preset to the bits of 1e-8f) receives max |out| per row for quantize_with_max."""
     capi.check(capi.load().qwen3_attention(_ptr(q), _dtype_code(q), q.stride(0), q.shape[0], q_heads, kv_heads, _ptr(k_cache),
-                                           _ptr(v_cache), _ptr(control), _ptr(out), out.stride(0), k_cache.shape[0], _stream()),
-               "qwen3_attention")
+                                           _ptr(v_cache), _ptr(control), _ptr(out), out.stride(0), k_cache.shape[0], _ptr(maxima),
+                                           _stream()), "qwen3_attention")

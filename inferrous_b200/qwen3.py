@@ -137,6 +137,7 @@ class Workspace:
         self.quant12 = torch.empty(rows, config.intermediate, dtype=torch.int8, device=device)
         self.scales = torch.empty(rows, dtype=torch.float32, device=device)
         self.maxima = torch.zeros(rows, dtype=torch.int32, device=device)
+        self.decode_maxima = torch.zeros(2, dtype=torch.int32, device=device)  # one row: {max |attention|, max |act|}
         self.logits = None  # only the unfused path writes logits
 
 
@@ -147,8 +148,9 @@ class Qwen3Runner:
     as its separate parts (swiglu then quantize; logits then selection); it exists to check that the fast kernels
     change nothing in a whole generation."""
 
-    def __init__(self, weights: Qwen3Weights, unfused: bool = False, device="cuda"):
+    def __init__(self, weights: Qwen3Weights, unfused: bool = False, device="cuda", fold_quantizers: str = "none"):
         ops.init()
+        self.fold_quantizers = fold_quantizers
         self.w = weights
         self.c = weights.config
         self.unfused = unfused
@@ -174,6 +176,9 @@ class Qwen3Runner:
         q4, qo = ws.quant4, ws.quant_o
         inter = c.intermediate
         ops.embedding(ids, w.embedding, ws.hidden)
+        if rows == 1 and self.fold_quantizers != "none" and not self.unfused:
+            self._decode_layers(ws)
+            return self._head(ws)
         for index, layer in enumerate(w.layers):
             ops.norm_quantize(ws.hidden, layer.norm1, None, q4, ws.scales, ws.maxima, c.eps)
             ops.linear_quantized(q4, ws.scales, layer.qkv, ws.qkv, variant)
@@ -194,6 +199,37 @@ class Qwen3Runner:
                 ops.linear_quantized(q4, ws.scales, layer.gate_up, ws.gate_up, variant)
                 ops.swiglu_quantize(ws.gate_up[:, :inter], ws.gate_up[:, inter:], ws.quant12, ws.scales)
             ops.linear_residual(ws.quant12, ws.scales, layer.down, None, ws.residual, ws.hidden, variant)
+        self._head(ws)
+
+    def _decode_layers(self, ws: Workspace) -> None:
+        """One row, with quantizers folded into the projections that consume them: "with_max" folds the quantizers of
+        the O and down projections (their maxima come from the producers: attention and the SwiGLU epilogue), "all"
+        also the two RMSNorm quantizers (six launches per layer instead of ten)."""
+        c, w = self.c, self.w
+        att_max, act_max = ws.decode_maxima[0:1], ws.decode_maxima[1:2]
+        fold_norm = self.fold_quantizers == "all"
+        for index, layer in enumerate(w.layers):
+            if fold_norm:
+                ops.quantize_linear(ws.hidden, layer.qkv, ws.qkv, gain=layer.norm1, eps=c.eps, maxima_reset=ws.decode_maxima)
+            else:
+                ops.norm_quantize(ws.hidden, layer.norm1, None, ws.quant4, ws.scales, att_max, c.eps)
+                ops.linear_quantized(ws.quant4, ws.scales, layer.qkv, ws.qkv)
+            ops.prepare_qk(ws.qkv, c.q_heads, c.kv_heads, layer.qnorm, layer.knorm, w.rope, self.control,
+                           self.k_cache[index], self.v_cache[index])
+            ops.attention(ws.qkv, c.q_heads, c.kv_heads, self.k_cache[index], self.v_cache[index], self.control, ws.attention,
+                          att_max)
+            ops.quantize_linear(ws.attention, layer.o, None, maxima_in=att_max, residual_in=ws.hidden, combined=ws.residual)
+            if fold_norm:
+                ops.quantize_linear_swiglu(ws.residual, layer.gate, layer.up, ws.act, act_max, gain=layer.norm2, eps=c.eps)
+            else:
+                ops.norm_quantize(ws.residual, layer.norm2, None, ws.quant4, ws.scales, act_max, c.eps)
+                ops.linear_swiglu(ws.quant4, ws.scales, layer.gate, layer.up, None, None, ws.act, act_max)
+            ops.quantize_linear(ws.act, layer.down, None, maxima_in=act_max, residual_in=ws.residual, combined=ws.hidden)
+
+    def _head(self, ws: Workspace) -> None:
+        c, w = self.c, self.w
+        rows = ws.rows
+        variant = capi.VARIANT_NAIVE if self.unfused else capi.VARIANT_AUTO
         last = ws.hidden[rows - 1:rows]
         ops.norm_quantize(last, w.final_gain, None, self.head_q, self.head_scale, None, c.eps)
         if self.unfused:

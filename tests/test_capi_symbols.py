@@ -60,7 +60,7 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.w8a8_init(-1) == 1
     # the operators around the linear layers refuse to run before w8a8_init()
     assert lib.qwen3_embedding(None, None, 1, 4096, 10, None, 0, None) == 6
-    assert lib.qwen3_attention(None, 0, 4096, 1, 32, 8, None, None, None, None, 4096, 4096, None) == 6
+    assert lib.qwen3_attention(None, 0, 4096, 1, 32, 8, None, None, None, None, 4096, 4096, None, None) == 6
 
 
 def test_product_does_not_import_the_oracle():

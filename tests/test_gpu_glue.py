@@ -167,3 +167,35 @@ def test_attention_strided_query_and_small_head_counts(ops):
     got = to_host(out).reshape(cpu.shape)
     assert np.all(np.abs(got - cpu) <= np.abs(cpu) * 2.0 ** -7 + 5e-6)
     assert ops.device_status() == (0, 0)
+
+
+@pytest.mark.parametrize("rows,position", [(1, 1500), (2, 700), (1, 63), (1, 64)])
+def test_attention_split_over_several_ctas(ops, rows, position):
+    """Few rows: the keys of each (row, head) are split over several CTAs and combined by the last one to arrive.
+    Same bound as above against the sequential CPU restatement; a second launch (the arrival counters must be back
+    at zero) gives the same bits."""
+    import torch
+
+    rng = np.random.default_rng(position)
+    keys = position + rows
+    q = oracle.bf16(rng.standard_normal((rows, Q_HEADS, 128)).astype(np.float32))
+    k = oracle.bf16_bits((rng.standard_normal((keys, KV_HEADS, 128)) * 0.7).astype(np.float32))
+    v = oracle.bf16_bits(rng.standard_normal((keys, KV_HEADS, 128)).astype(np.float32))
+    kc = torch.zeros(2048, KV_HEADS, 128, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    kc[:keys] = to_dev(k.view(np.int16)).view(torch.bfloat16)
+    vc[:keys] = to_dev(v.view(np.int16)).view(torch.bfloat16)
+    qd = to_dev(q.reshape(rows, -1), "bf16")
+    outs = []
+    for _ in range(2):
+        out = torch.full((rows, Q_HEADS * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+        mx = to_dev(np.full(rows, np.float32(1e-8).view(np.uint32), np.uint32))
+        ops.attention(qd, Q_HEADS, KV_HEADS, kc, vc, control(0, position), out, mx)
+        outs.append(to_host(out))
+        # the published maximum is the row's max |out|
+        assert np.array_equal(to_host(mx).view(np.uint32), np.abs(outs[-1]).max(1).astype(np.float32).view(np.uint32))
+    assert np.array_equal(outs[0], outs[1])
+    cpu = oracle.attention(q, k, v, position).reshape(rows, -1)
+    assert np.all(np.abs(outs[0] - cpu) <= np.abs(cpu) * 2.0 ** -7 + 5e-6)
+    assert (outs[0] != cpu).mean() < 0.05
+    assert ops.device_status() == (0, 0)

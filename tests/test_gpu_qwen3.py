@@ -69,6 +69,11 @@ def test_fast_kernels_change_nothing_in_a_generation(prompt_len, steps, cfg):
     tokens_eager, _ = fast.generate(prompt, steps, use_graph=False)
     assert tokens_eager == tokens_plain
     assert np.array_equal(to_host(fast.decode.hidden), hidden_graph)
+    for fold in ("with_max", "all"):  # quantizers inside the projection kernels
+        folded = Qwen3Runner(weights, fold_quantizers=fold)
+        tokens_folded, _ = folded.generate(prompt, steps)
+        assert tokens_folded == tokens_plain
+        assert np.array_equal(to_host(folded.decode.hidden), hidden_graph)
     for cache_fast, cache_plain in zip(fast.k_cache + fast.v_cache, plain.k_cache + plain.v_cache):
         n = prompt_len + steps - 1
         assert np.array_equal(to_host(cache_fast[:n]), to_host(cache_plain[:n]))
