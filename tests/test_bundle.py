@@ -1,0 +1,78 @@
+"""The on-disk bundle reader (inferrous_b200/bundle.py; format of the reference's tools/prepare.py and src/model.rs):
+CPU checks of the format handling, and on a GPU a generation from a bundle through the Python and the C++ hosts."""
+import json
+import subprocess
+
+import numpy as np
+import pytest
+
+from tests.bundle_writer import write_bundle
+
+
+def test_bundle_tensors_round_trip_and_are_verified(tmp_path):
+    from inferrous_b200.bundle import Bundle, BundleError
+
+    manifest = write_bundle(tmp_path / "b", seed=3)
+    b = Bundle(tmp_path / "b")
+    assert (b.config.layers, b.config.hidden, b.config.q_heads, b.config.kv_heads) == (2, 256, 4, 2)
+    assert (b.config.intermediate, b.config.vocab, b.config.context) == (512, 640, 64)
+    w = b.tensor("layer.1.down.w", "|i1", (256, 512))
+    assert w.dtype == np.int8 and np.abs(w).max() == 127
+    assert b.tensor("rope", "<f4", (64, 128))[0, :64].tolist() == [1.0] * 64  # cos(0)
+    with pytest.raises(BundleError, match="wrong type or shape"):
+        b.tensor("layer.1.down.w", "|i1", (512, 256))
+    with pytest.raises(BundleError, match="missing"):
+        b.tensor("layer.2.down.w", "|i1", (256, 512))
+    # a flipped byte is caught by the digest
+    p = tmp_path / "b" / "final_gain.bin"
+    raw = bytearray(p.read_bytes())
+    raw[5] ^= 1
+    p.write_bytes(bytes(raw))
+    with pytest.raises(BundleError, match="hash mismatch"):
+        b.tensor("final_gain", "<f4", (256,))
+    assert Bundle(tmp_path / "b", verify_hashes=False).tensor("final_gain", "<f4", (256,)).shape == (256,)
+    # unsupported operators and versions are refused like src/model.rs:50-77
+    for key, value in [("hidden_act", "gelu"), ("head_dim", 64), ("tie_word_embeddings", True)]:
+        bad = json.loads(json.dumps(manifest))
+        bad["config"][key] = value
+        (tmp_path / "b" / "manifest.json").write_text(json.dumps(bad))
+        with pytest.raises(BundleError):
+            Bundle(tmp_path / "b")
+    bad = json.loads(json.dumps(manifest))
+    bad["format_version"] = 2
+    (tmp_path / "b" / "manifest.json").write_text(json.dumps(bad))
+    with pytest.raises(BundleError, match="version"):
+        Bundle(tmp_path / "b")
+
+
+def test_cpp_generation_program_compiles():
+    from tests.cpp.build import build
+
+    assert build("generate").exists()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("prompt_len,steps,shape", [
+    (5, 8, dict()),
+    (130, 6, dict(layers=2, hidden=512, q_heads=4, kv_heads=1, intermediate=1024, vocab=1024, context=192)),
+])
+def test_generation_from_a_bundle_python_cpp_and_cpu_agree(tmp_path, prompt_len, steps, shape):
+    """The same bundle through three hosts: inferrous_b200.qwen3 (bf16 activations, concatenated gate|up, CUDA graph),
+    the C++ harness (f32 carrier, separate gate and up, graph and eager) and the CPU restatement."""
+    from inferrous_b200.bundle import load_bundle
+    from inferrous_b200.qwen3 import Qwen3Runner
+    from tests.cpp.build import build
+    from tests.qwen3_oracle import OracleModel, export
+
+    write_bundle(tmp_path / "b", seed=11, **shape)
+    weights = load_bundle(tmp_path / "b")
+    rng = np.random.default_rng(1)
+    prompt = [int(t) for t in rng.integers(0, weights.config.vocab, prompt_len)]
+    tokens, _ = Qwen3Runner(weights).generate(prompt, steps)
+    for use_graph in (1, 0):
+        r = subprocess.run([str(build("generate")), str(tmp_path / "b"), str(steps), str(use_graph), *map(str, prompt)],
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout + r.stderr
+        assert [int(t) for t in r.stdout.split("tokens:")[1].split()] == tokens
+    if prompt_len <= 16:
+        assert OracleModel(export(weights)).generate(prompt, steps) == tokens
