@@ -74,6 +74,15 @@ const char *w8a8_version(void);
 const char *w8a8_status_string(int status);
 /* Text of the last failing CUDA call on this host thread ("" if none). */
 const char *w8a8_last_cuda_error(void);
+/* Next-weight L2 prefetch (the role of the reference's prefetch CTAs and row tables, src/kernels.rs:173-237,
+ * src/gpu.rs:19-42): registers [weights, weights + bytes) -- device memory that no kernel writes, normally int8 rows
+ * of a projection that runs a few launches later -- with the calling thread; up to four ranges may be pending.  The
+ * next qwen3_attention launch, or quantizer launch (w8a8_quantize, w8a8_quantize_with_max, w8a8_rmsnorm_quantize,
+ * w8a8_swiglu_quantize) of at most 16 rows, from that thread carries one extra CTA per SM that issues
+ * `prefetch.global.L2` for those lines and leaves.  The hints are consumed by that launch (inside a stream capture they become part of the captured
+ * kernel node).  A hint only moves data towards L2 earlier; results never depend on it.  (NULL, 0) clears the list. */
+int w8a8_prefetch_hint(const void *weights, size_t bytes);
+
 /* Programmatic dependent launch, the reference's CLEAN_PDL switch (src/gpu.rs:317; the graph rewrite of
  * src/graph.rs:63-127).  When enabled (default off; env W8A8_PDL=1 at init), every hot-path kernel is
  * launched with the programmatic-stream-serialization attribute: it may begin while its predecessor on

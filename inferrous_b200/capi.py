@@ -20,6 +20,7 @@ SIGNATURES = {
     "w8a8_status_string": (C.c_char_p, [_i]),
     "w8a8_last_cuda_error": (C.c_char_p, []),
     "w8a8_set_programmatic_launch": (_i, [_i]),
+    "w8a8_prefetch_hint": (_i, [_vp, _sz]),
     "w8a8_device_status": (_i, [_vp, C.POINTER(C.c_uint32)]),
     "w8a8_weight_create": (_i, [_vp, _vp, _i, _i, C.POINTER(_vp)]),
     "w8a8_weight_destroy": (_i, [_vp]),

@@ -37,6 +37,7 @@ DeviceState g_dev[kMaxDevices];
 std::mutex g_mu;
 bool g_pdl = false;
 thread_local char g_err[256] = "";
+thread_local PrefetchHint g_hint = {};
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -48,6 +49,12 @@ int current_ready_device() {
 }  // namespace
 
 bool programmatic_launch_enabled() { return g_pdl; }
+
+PrefetchHint take_prefetch_hint() {
+    const PrefetchHint h = g_hint;
+    g_hint = PrefetchHint{};
+    return h;
+}
 
 int fail_cuda(cudaError_t e, const char *what) {
     snprintf(g_err, sizeof g_err, "%s: %s", what, cudaGetErrorString(e));
@@ -123,6 +130,19 @@ const char *w8a8_status_string(int status) {
 }
 
 const char *w8a8_last_cuda_error(void) { return g_err; }
+
+int w8a8_prefetch_hint(const void *weights, size_t bytes) {
+    REQUIRE((weights != nullptr) == (bytes != 0), W8A8_ERR_BAD_ARG);
+    if (!weights) {
+        g_hint = PrefetchHint{};
+        return W8A8_OK;
+    }
+    REQUIRE(g_hint.count < kMaxPrefetchRanges, W8A8_ERR_UNSUPPORTED);
+    g_hint.ptr[g_hint.count] = static_cast<const char *>(weights);
+    g_hint.bytes[g_hint.count] = bytes;
+    ++g_hint.count;
+    return W8A8_OK;
+}
 
 int w8a8_set_programmatic_launch(int enabled) {
     g_pdl = enabled != 0;

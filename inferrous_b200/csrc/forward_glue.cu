@@ -152,7 +152,13 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
                                                                  const uint32_t *__restrict__ control,
                                                                  typename T::storage *__restrict__ out, int64_t ldo, int capacity,
                                                                  uint32_t *maxima, float *scratch, uint32_t *counters,
-                                                                 uint32_t *status) {
+                                                                 uint32_t *status, int units, const PrefetchHint hint) {
+    if ((int)blockIdx.x >= units) {
+        // Extra CTAs: L2 prefetch hints for weights that a later projection will stream (immutable, so no dependency
+        // wait).  The hints are issued and the CTA leaves; the lines arrive while the attention CTAs work.
+        if (blockIdx.y == 0) prefetch_ranges(hint, blockIdx.x - units, gridDim.x - units);
+        return;
+    }
     __shared__ float scores[kMaxContext];
     __shared__ float query[kHeadDim];
     __shared__ float reduce[kAttnThreads / 32];
@@ -357,14 +363,16 @@ int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads
     const int units = rows * q_heads;
     int splits = 1;
     if (units < sm_count() && units <= kAttnSplitMaxUnits) splits = std::min(kAttnMaxSplits, (2 * sm_count() + units - 1) / units);
-    const dim3 grid(units, splits);
+    const PrefetchHint hint = take_prefetch_hint();
+    const int prefetch_ctas = hint.count ? sm_count() : 0;
+    const dim3 grid(units + prefetch_ctas, splits);
     cudaError_t e = dtype == W8A8_BF16
                         ? launch_kernel(attention_kernel<Bf16>, grid, dim3(kAttnThreads), 0, (cudaStream_t)stream, (const uint16_t *)q, ldq,
                                         q_heads, kv_heads, k_cache, v_cache, control, (uint16_t *)out, ldo, capacity, maxima,
-                                        attention_scratch(), attention_counters(), device_status_ptr())
+                                        attention_scratch(), attention_counters(), device_status_ptr(), units, hint)
                         : launch_kernel(attention_kernel<F32>, grid, dim3(kAttnThreads), 0, (cudaStream_t)stream, (const float *)q, ldq,
                                         q_heads, kv_heads, k_cache, v_cache, control, (float *)out, ldo, capacity, maxima,
-                                        attention_scratch(), attention_counters(), device_status_ptr());
+                                        attention_scratch(), attention_counters(), device_status_ptr(), units, hint);
     return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "attention launch");
 }
 

@@ -127,6 +127,34 @@ constexpr size_t kAttnScratchFloats = (size_t)kAttnSplitMaxUnits * kAttnMaxSplit
 float *attention_scratch();
 uint32_t *attention_counters();
 
+// L2 prefetch hint for immutable weights (w8a8_prefetch_hint): consumed by the next launch that carries prefetch CTAs.
+constexpr int kMaxPrefetchRanges = 4;
+constexpr int kPrefetchMaxRows = 16;  // quantizer launches with more rows leave pending hints alone
+struct PrefetchHint {
+    const char *ptr[kMaxPrefetchRanges];
+    unsigned long long bytes[kMaxPrefetchRanges];
+    int count;
+};
+PrefetchHint take_prefetch_hint();
+
+#ifdef __CUDACC__
+// The whole 128-byte lines inside [base, base + bytes), dealt round-robin to the threads of `ctas` CTAs (partial
+// lines at either end are left alone, so no address outside the range is ever named).
+__device__ __forceinline__ void prefetch_lines(const char *base, unsigned long long bytes, int cta, int ctas) {
+    const unsigned long long begin = (reinterpret_cast<unsigned long long>(base) + 127ull) & ~127ull;
+    const unsigned long long end = (reinterpret_cast<unsigned long long>(base) + bytes) & ~127ull;
+    if (end <= begin) return;
+    const unsigned long long lines = (end - begin) / 128;
+    for (unsigned long long i = (unsigned long long)cta * blockDim.x + threadIdx.x; i < lines; i += (unsigned long long)ctas * blockDim.x)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(begin + i * 128));
+}
+
+// The role of a prefetch CTA: hint every pending range, `cta` of `ctas`.
+__device__ __forceinline__ void prefetch_ranges(const PrefetchHint &hint, int cta, int ctas) {
+    for (int r = 0; r < hint.count; ++r) prefetch_lines(hint.ptr[r], hint.bytes[r], cta, ctas);
+}
+#endif
+
 int sm_count();
 // Records the failing CUDA call's text for w8a8_last_cuda_error() and returns W8A8_ERR_CUDA.
 int fail_cuda(cudaError_t e, const char *what);

@@ -33,6 +33,7 @@ struct QuantDev {
     float *scale;
     void *y_out;
     uint32_t *maxima_reset;
+    PrefetchHint hint;  // CTAs beyond the M row CTAs issue these L2 prefetches and leave
 };
 
 // Register-resident fast path: each thread keeps its RV 16-byte vectors of the row in registers between the
@@ -53,6 +54,10 @@ __global__ void __launch_bounds__(THREADS) quantize_rows_reg_kernel(const QuantD
     // float index swizzle: 16-byte group ^= bit 5 of the element index
     auto swz = [](int e) { return e ^ (((e >> 5) & 1) << 2); };
 
+    if ((int)blockIdx.x >= a.M) {  // prefetch CTA: immutable weights only, so no dependency wait
+        prefetch_ranges(a.hint, blockIdx.x - a.M, gridDim.x - a.M);
+        return;
+    }
     dependency_wait();
 
     for (int r = blockIdx.x; r < a.M; r += gridDim.x) {
@@ -153,6 +158,10 @@ __global__ void __launch_bounds__(1024) quantize_rows_kernel(const QuantDev a) {
     const int K = a.K;
     const int nthreads = blockDim.x;
 
+    if ((int)blockIdx.x >= a.M) {  // prefetch CTA: immutable weights only, so no dependency wait
+        prefetch_ranges(a.hint, blockIdx.x - a.M, gridDim.x - a.M);
+        return;
+    }
     dependency_wait();
 
     for (int r = blockIdx.x; r < a.M; r += gridDim.x) {
@@ -329,7 +338,8 @@ constexpr int kMaxQuantSmem = 100 * 1024;
 inline size_t quant_smem(int K) { return (size_t)(K + 256 + 32) * sizeof(float); }
 
 template <class T, int MODE> cudaError_t launch_q(const QuantDev &d, cudaStream_t s) {
-    const int grid = d.M;
+    // one CTA per row; with pending prefetch hints (few rows only) one more CTA per SM
+    const int grid = d.M + (d.hint.count ? sm_count() : 0);
     if (MODE != QUANT_WITH_MAX) {
         // Register-resident kernels.  Few rows: 1024 threads so that the kernel is one memory round trip long.
         // Many rows: the smallest CTA that holds the row in <= 3 vectors per thread, which keeps the register
@@ -374,7 +384,8 @@ cudaError_t init_quantize() {
 
 cudaError_t launch_quantize(const QuantArgs &a, cudaStream_t s) {
     if (quant_smem(a.K) > (size_t)kMaxQuantSmem) return cudaErrorInvalidValue;
-    QuantDev d{a.x, a.x2, a.ld, a.M, a.K, a.eps, a.maxima_in, a.q, a.scale, a.y_out, a.maxima_reset};
+    QuantDev d{a.x, a.x2, a.ld, a.M, a.K, a.eps, a.maxima_in, a.q, a.scale, a.y_out, a.maxima_reset, PrefetchHint{}};
+    if (a.M <= kPrefetchMaxRows) d.hint = take_prefetch_hint();
 #define W8A8_DISPATCH(T)                                                           \
     switch (a.mode) {                                                              \
         case QUANT_PLAIN: return launch_q<T, QUANT_PLAIN>(d, s);                   \

@@ -56,6 +56,19 @@ def set_programmatic_launch(enabled: bool) -> None:
     capi.check(capi.load().w8a8_set_programmatic_launch(1 if enabled else 0), "w8a8_set_programmatic_launch")
 
 
+def prefetch_hint(weights: torch.Tensor | None, offset_bytes: int = 0, nbytes: int | None = None) -> None:
+    """Attach an L2 prefetch of (part of) an immutable weight tensor to the next attention launch of this thread
+    (the reference's next-weight prefetch, src/gpu.rs:19-42)."""
+    if weights is None:
+        capi.check(capi.load().w8a8_prefetch_hint(None, 0), "w8a8_prefetch_hint")
+        return
+    total = weights.numel() * weights.element_size()
+    nbytes = total - offset_bytes if nbytes is None else min(nbytes, total - offset_bytes)
+    if nbytes <= 0:
+        return
+    capi.check(capi.load().w8a8_prefetch_hint(C.c_void_p(weights.data_ptr() + offset_bytes), nbytes), "w8a8_prefetch_hint")
+
+
 def device_status() -> tuple[int, int]:
     """(status, detail) of the device-side bounded waits; synchronises the current stream."""
     detail = C.c_uint32(0)

@@ -144,12 +144,21 @@ class Workspace:
 class Qwen3Runner:
     """GpuModel: owns the caches, the decode workspace, the control buffer and the captured decode graph.
 
+    Decode launches may carry L2 prefetch hints for weights that a later projection streams (the reference's
+    next-weight prefetch, src/gpu.rs:19-42).  Measured on a B200 (2.75 ms per token without hints): the down matrix
+    hinted at the launch that quantizes the attention output gives 2.67 ms, at the quantize_with_max launch 2.68 ms;
+    hinting the trailing gate / up rows at the attention launch costs time (2.77-2.91 ms).  Hence the defaults.
+
     unfused=True runs every projection with the one-thread-per-output kernel (VARIANT_NAIVE) and every fused step
     as its separate parts (swiglu then quantize; logits then selection); it exists to check that the fast kernels
     change nothing in a whole generation."""
 
-    def __init__(self, weights: Qwen3Weights, unfused: bool = False, device="cuda", fold_quantizers: str = "none"):
+    def __init__(self, weights: Qwen3Weights, unfused: bool = False, device="cuda", fold_quantizers: str = "none",
+                 prefetch_rows: int = 0, prefetch_down_at: str = "quant", prefetch_o: bool = False):
         ops.init()
+        self.prefetch_rows = prefetch_rows
+        self.prefetch_down_at = prefetch_down_at
+        self.prefetch_o = prefetch_o
         self.fold_quantizers = fold_quantizers
         self.w = weights
         self.c = weights.config
@@ -184,9 +193,23 @@ class Qwen3Runner:
             ops.linear_quantized(q4, ws.scales, layer.qkv, ws.qkv, variant)
             ops.prepare_qk(ws.qkv, c.q_heads, c.kv_heads, layer.qnorm, layer.knorm, w.rope, self.control,
                            self.k_cache[index], self.v_cache[index])
+            if rows == 1 and self.prefetch_rows and not self.unfused:
+                # Decode: the attention launch also pulls the last rows of gate and up towards L2; the gate/up kernel's
+                # first wave of CTAs fetches the leading rows by itself before its dependency wait.
+                first = max(0, inter - self.prefetch_rows) * c.hidden
+                ops.prefetch_hint(layer.gate_up.w, first, self.prefetch_rows * c.hidden)
+                ops.prefetch_hint(layer.gate_up.w, inter * c.hidden + first, self.prefetch_rows * c.hidden)
+            if rows == 1 and self.prefetch_o and not self.unfused:
+                ops.prefetch_hint(layer.o.w)
+            if rows == 1 and self.prefetch_down_at == "attention" and not self.unfused:
+                ops.prefetch_hint(layer.down.w)
             ops.attention(ws.qkv, c.q_heads, c.kv_heads, self.k_cache[index], self.v_cache[index], self.control, ws.attention)
+            if rows == 1 and self.prefetch_down_at == "quant" and not self.unfused:
+                ops.prefetch_hint(layer.down.w)
             ops.quantize(ws.attention, qo, ws.scales)
             ops.linear_residual(qo, ws.scales, layer.o, None, ws.hidden, ws.residual, variant)
+            if rows == 1 and self.prefetch_down_at == "norm2" and not self.unfused:
+                ops.prefetch_hint(layer.down.w)
             ops.norm_quantize(ws.residual, layer.norm2, None, q4, ws.scales, ws.maxima, c.eps)
             if self.unfused:
                 ops.linear_quantized(q4, ws.scales, layer.gate_up, ws.gate_up, variant)
@@ -194,6 +217,8 @@ class Qwen3Runner:
                 ops.quantize(ws.act, ws.quant12, ws.scales)
             elif rows == 1:
                 ops.linear_swiglu(q4, ws.scales, layer.gate, layer.up, None, None, ws.act, ws.maxima)
+                if self.prefetch_down_at == "qwm":
+                    ops.prefetch_hint(layer.down.w)
                 ops.quantize_with_max(ws.act, ws.maxima, ws.quant12, ws.scales)
             else:
                 ops.linear_quantized(q4, ws.scales, layer.gate_up, ws.gate_up, variant)

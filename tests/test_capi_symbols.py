@@ -58,6 +58,16 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.w8a8_linear(None, None, None, 1, None, None, None, 0, None) == 1
     assert lib.w8a8_weight_destroy(None) == 1
     assert lib.w8a8_init(-1) == 1
+    # prefetch hints: a thread-local list of at most four ranges, cleared by (NULL, 0)
+    assert lib.w8a8_prefetch_hint(None, 5) == 1
+    import ctypes
+    buf = ctypes.create_string_buffer(256)
+    for _ in range(4):
+        assert lib.w8a8_prefetch_hint(ctypes.addressof(buf), 256) == 0
+    assert lib.w8a8_prefetch_hint(ctypes.addressof(buf), 256) == 3
+    assert lib.w8a8_prefetch_hint(None, 0) == 0
+    assert lib.w8a8_prefetch_hint(ctypes.addressof(buf), 256) == 0
+    assert lib.w8a8_prefetch_hint(None, 0) == 0
     # the operators around the linear layers refuse to run before w8a8_init()
     assert lib.qwen3_embedding(None, None, 1, 4096, 10, None, 0, None) == 6
     assert lib.qwen3_attention(None, 0, 4096, 1, 32, 8, None, None, None, None, 4096, 4096, None, None) == 6

@@ -199,3 +199,25 @@ def test_attention_split_over_several_ctas(ops, rows, position):
     assert np.all(np.abs(outs[0] - cpu) <= np.abs(cpu) * 2.0 ** -7 + 5e-6)
     assert (outs[0] != cpu).mean() < 0.05
     assert ops.device_status() == (0, 0)
+
+
+def test_attention_with_prefetch_hints_changes_nothing(ops):
+    """A launch that carries L2 prefetch CTAs for some weight ranges computes the same bits; the hints are consumed."""
+    import torch
+
+    rng = np.random.default_rng(4)
+    position, keys = 300, 301
+    q = to_dev(oracle.bf16(rng.standard_normal((1, Q_HEADS * 128)).astype(np.float32)), "bf16")
+    kc = to_dev(oracle.bf16(rng.standard_normal((512, KV_HEADS, 128)).astype(np.float32)), "bf16")
+    vc = to_dev(oracle.bf16(rng.standard_normal((512, KV_HEADS, 128)).astype(np.float32)), "bf16")
+    weights = torch.zeros(3 << 20, dtype=torch.int8, device="cuda")
+    outs = []
+    for hinted in (False, True, False):
+        if hinted:
+            ops.prefetch_hint(weights, 0, 1 << 20)
+            ops.prefetch_hint(weights, (2 << 20) + 128, (1 << 20) - 128 - 77)  # an end that is not a multiple of a line
+        out = torch.full((1, Q_HEADS * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.attention(q, Q_HEADS, KV_HEADS, kc, vc, control(0, position), out)
+        outs.append(to_host(out))
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    assert ops.device_status() == (0, 0)

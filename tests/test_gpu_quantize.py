@@ -255,3 +255,38 @@ def test_quantize_near_rounding_ties_exact(ops, carrier):
     eq, es = oracle.quantize(x)
     assert np.array_equal(bits(s), bits(es))
     assert np.array_equal(q, eq), int((q != eq).sum())
+
+
+def test_quantizer_launch_with_prefetch_hints_changes_nothing(ops):
+    """Few-row quantizer launches carry pending L2 prefetch hints as extra CTAs; codes and scales are unchanged, and a
+    many-row launch leaves the hints for a later one."""
+    import torch
+
+    rng = np.random.default_rng(8)
+    weights = torch.zeros(5 << 20, dtype=torch.int8, device="cuda")
+    for M, K in [(1, 4096), (3, 12288)]:
+        x = synth_activations(rng, M, K)
+        gamma = synth_gamma(rng, K)
+        xd, gd = to_dev(x, "bf16"), to_dev(gamma, "bf16")
+        results = []
+        for hinted in (False, True):
+            out = []
+            for kind in ("plain", "norm", "with_max"):
+                if hinted:
+                    ops.prefetch_hint(weights, 128, (4 << 20) + 5)
+                q = torch.zeros((M, K), dtype=torch.int8, device="cuda")
+                s = torch.zeros((M,), dtype=torch.float32, device="cuda")
+                if kind == "plain":
+                    ops.quantize(xd, q, s)
+                elif kind == "norm":
+                    ops.norm_quantize(xd, gd, None, q, s, None)
+                else:
+                    mx = to_dev(np.abs(x).max(1).astype(np.float32).view(np.uint32))
+                    ops.quantize_with_max(xd, mx, q, s)
+                out.append((to_host(q), to_host(s)))
+            results.append(out)
+        for (q0, s0), (q1, s1) in zip(*results):
+            assert np.array_equal(q0, q1) and np.array_equal(bits(s0), bits(s1))
+    eq, es = oracle.quantize(x)
+    assert np.array_equal(results[0][0][0], eq)
+    assert ops.device_status() == (0, 0)
