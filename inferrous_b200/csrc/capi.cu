@@ -182,6 +182,7 @@ int w8a8_init(int device) {
     CUDA_OK(init_gemm_tcgen05_pair(), "init_gemm_tcgen05_pair");
     CUDA_OK(init_gemm_skinny(), "init_gemm_skinny");
     CUDA_OK(init_gemv_rows(), "init_gemv_rows");
+    CUDA_OK(init_forward_glue(), "init_forward_glue");
     d.ready = true;
     return W8A8_OK;
 }

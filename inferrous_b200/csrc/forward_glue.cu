@@ -299,9 +299,199 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
     }
 }
 
+// ---- attention, many rows (prefill) --------------------------------------------------------------------------
+// One CTA of 256 threads per (row, key/value head, group of GH query heads that share it): every key and value is
+// read once for the GH heads instead of once per head, which is what bounds the one-head kernel when thousands of
+// (row, head) pairs walk the same cache through L2.  Per head the arithmetic and its association are exactly those
+// of attention_kernel with one split.  Shared memory: GH * capacity scores (98 KB at 4 heads and 4096 positions).
+template <class T, int GH>
+__global__ void __launch_bounds__(kAttnThreads) attention_grouped_kernel(const typename T::storage *__restrict__ q, int64_t ldq,
+                                                                         int q_heads, int kv_heads,
+                                                                         const uint16_t *__restrict__ k_cache,
+                                                                         const uint16_t *__restrict__ v_cache,
+                                                                         const uint32_t *__restrict__ control,
+                                                                         typename T::storage *__restrict__ out, int64_t ldo,
+                                                                         int capacity, uint32_t *maxima, uint32_t *status) {
+    extern __shared__ __align__(16) float attn_smem[];
+    float *scores = attn_smem;                                            // [GH][capacity]
+    float(*partial)[GH][kHeadDim] = reinterpret_cast<float(*)[GH][kHeadDim]>(attn_smem + (size_t)GH * capacity);  // [slices]
+    float *query = reinterpret_cast<float *>(partial + kAttnSlices);      // [GH][128]
+    float *reduce = query + GH * kHeadDim;                                // [warps][GH]
+    dependency_wait();
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int group = q_heads / kv_heads;            // query heads per key/value head
+    const int chunks = group / GH;                   // CTAs per (row, kv head)
+    const int row = blockIdx.x / (kv_heads * chunks);
+    const int kv = (blockIdx.x / chunks) % kv_heads;
+    const int head0 = kv * group + (blockIdx.x % chunks) * GH;
+    const uint32_t end_u = control[1] + (uint32_t)row + 1u;
+    if (end_u > (uint32_t)capacity) {
+        if (t == 0) record_range_fault(status, end_u);
+        return;
+    }
+    const int end = (int)end_u;
+    for (int i = t; i < GH * kHeadDim; i += kAttnThreads)
+        query[i] = T::load(q + (size_t)row * ldq + (size_t)head0 * kHeadDim + i);
+    __syncthreads();
+
+    const int sub = lane & 7, grp = lane >> 3;
+    float qv[GH][16];
+#pragma unroll
+    for (int h = 0; h < GH; ++h)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) qv[h][i] = query[h * kHeadDim + 16 * sub + i];
+    const size_t key_stride = (size_t)kv_heads * kHeadDim;
+    const uint16_t *kbase = k_cache + (size_t)kv * kHeadDim + 16 * sub;
+    float maximum[GH];
+#pragma unroll
+    for (int h = 0; h < GH; ++h) maximum[h] = -INFINITY;
+#pragma unroll 2
+    for (int j0 = warp * 4; j0 < end; j0 += (kAttnThreads / 32) * 4) {
+        const int j = j0 + grp;
+        uint4 a = make_uint4(0, 0, 0, 0), b = a;
+        if (j < end) {
+            const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)j * key_stride);
+            a = kr[0];
+            b = kr[1];
+        }
+#pragma unroll
+        for (int h = 0; h < GH; ++h) {
+            float s = j < end ? dot16(qv[h], a, b) : 0.0f;
+            s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 4));
+            s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 2));
+            s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
+            s = __fmul_rn(s, 0.08838834764831845f);
+            if (j < end) {
+                maximum[h] = fmaxf(maximum[h], s);
+                if (sub == 0) scores[(size_t)h * capacity + j] = s;
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < GH; ++h) {
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) maximum[h] = fmaxf(maximum[h], __shfl_xor_sync(0xffffffffu, maximum[h], d));
+        if (lane == 0) reduce[warp * GH + h] = maximum[h];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < GH; ++h) {
+        maximum[h] = reduce[h];
+#pragma unroll
+        for (int i = 1; i < kAttnThreads / 32; ++i) maximum[h] = fmaxf(maximum[h], reduce[i * GH + h]);
+    }
+    __syncthreads();
+
+    float total[GH];
+#pragma unroll
+    for (int h = 0; h < GH; ++h) {
+        total[h] = 0.0f;
+        float *sc = scores + (size_t)h * capacity;
+        for (int j = t; j < end; j += kAttnThreads) {
+            const float e = exp_approx(__fadd_rn(sc[j], -maximum[h]));
+            sc[j] = e;
+            total[h] = __fadd_rn(total[h], e);
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) total[h] = __fadd_rn(total[h], __shfl_xor_sync(0xffffffffu, total[h], d));
+        if (lane == 0) reduce[warp * GH + h] = total[h];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < GH; ++h) {
+        total[h] = reduce[h];
+#pragma unroll
+        for (int i = 1; i < kAttnThreads / 32; ++i) total[h] = __fadd_rn(total[h], reduce[i * GH + h]);
+    }
+
+    const int slice = t >> 4, cg = t & 15;
+    const uint16_t *vbase = v_cache + (size_t)kv * kHeadDim + 8 * cg;
+    float acc[GH][8];
+#pragma unroll
+    for (int h = 0; h < GH; ++h)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[h][i] = 0.0f;
+#pragma unroll 2
+    for (int j = slice; j < end; j += kAttnSlices) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(vbase + (size_t)j * key_stride);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int h = 0; h < GH; ++h) {
+            const float p = scores[(size_t)h * capacity + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                acc[h][2 * i] = __fadd_rn(acc[h][2 * i], __fmul_rn(p, __uint_as_float(w[i] << 16)));
+                acc[h][2 * i + 1] = __fadd_rn(acc[h][2 * i + 1], __fmul_rn(p, __uint_as_float(w[i] & 0xffff0000u)));
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < GH; ++h)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) partial[slice][h][8 * cg + i] = acc[h][i];
+    __syncthreads();
+    // GH * 128 outputs over 256 threads
+    for (int o = t; o < GH * kHeadDim; o += kAttnThreads) {
+        const int h = o / kHeadDim, c = o % kHeadDim;
+        float sum = partial[0][h][c];
+#pragma unroll
+        for (int i = 1; i < kAttnSlices; ++i) sum = __fadd_rn(sum, partial[i][h][c]);
+        float den = total[0];
+#pragma unroll
+        for (int k = 1; k < GH; ++k)
+            if (h == k) den = total[k];
+        const float v = bf16_rne(__fdiv_rn(sum, den));
+        T::store(out + (size_t)row * ldo + (size_t)(head0 + h) * kHeadDim + c, v);
+        if (maxima) {
+            const uint32_t m = warp_max_u32(absmax_key(v));
+            if (lane == 0) atomicMax(maxima + row, m);
+        }
+    }
+}
+
+size_t grouped_smem(int gh, int capacity) {
+    return ((size_t)gh * capacity + (size_t)kAttnSlices * gh * kHeadDim + (size_t)gh * kHeadDim + (kAttnThreads / 32) * gh) * sizeof(float);
+}
+
+template <class T, int GH>
+cudaError_t launch_grouped(const typename T::storage *q, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
+                           const uint16_t *v_cache, const uint32_t *control, typename T::storage *out, int64_t ldo, int capacity,
+                           uint32_t *maxima, cudaStream_t s) {
+    const size_t smem = grouped_smem(GH, capacity);
+    const dim3 grid(rows * kv_heads * ((q_heads / kv_heads) / GH));
+    return launch_kernel(attention_grouped_kernel<T, GH>, grid, dim3(kAttnThreads), smem, s, q, ldq, q_heads, kv_heads, k_cache,
+                         v_cache, control, out, ldo, capacity, maxima, device_status_ptr());
+}
+
+template <class T>
+cudaError_t launch_grouped_any(const void *q, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
+                               const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity,
+                               uint32_t *maxima, cudaStream_t s) {
+    typedef typename T::storage S;
+    const int group = q_heads / kv_heads;
+    if (group % 4 == 0)
+        return launch_grouped<T, 4>((const S *)q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, control, (S *)out, ldo, capacity, maxima, s);
+    if (group % 2 == 0)
+        return launch_grouped<T, 2>((const S *)q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, control, (S *)out, ldo, capacity, maxima, s);
+    return launch_grouped<T, 1>((const S *)q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, control, (S *)out, ldo, capacity, maxima, s);
+}
+
 bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+template <class T> cudaError_t raise_grouped_smem() {
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(attention_grouped_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)grouped_smem(1, kMaxContext)))) return e;
+    if ((e = cudaFuncSetAttribute(attention_grouped_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)grouped_smem(2, kMaxContext)))) return e;
+    return cudaFuncSetAttribute(attention_grouped_kernel<T, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)grouped_smem(4, kMaxContext));
+}
+
 }  // namespace
+
+cudaError_t init_forward_glue() {
+    cudaError_t e = raise_grouped_smem<Bf16>();
+    return e != cudaSuccess ? e : raise_grouped_smem<F32>();
+}
+
 }  // namespace w8a8
 
 using namespace w8a8;
@@ -363,6 +553,15 @@ int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads
     const int units = rows * q_heads;
     int splits = 1;
     if (units < sm_count() && units <= kAttnSplitMaxUnits) splits = std::min(kAttnMaxSplits, (2 * sm_count() + units - 1) / units);
+    if (splits == 1 && units >= sm_count()) {
+        // many rows: one CTA per (row, key/value head) serves the query heads that share it
+        cudaError_t eg = dtype == W8A8_BF16
+                             ? launch_grouped_any<Bf16>(q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, control, out, ldo, capacity,
+                                                        maxima, (cudaStream_t)stream)
+                             : launch_grouped_any<F32>(q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, control, out, ldo, capacity,
+                                                       maxima, (cudaStream_t)stream);
+        return eg == cudaSuccess ? W8A8_OK : fail_cuda(eg, "attention launch");
+    }
     const PrefetchHint hint = take_prefetch_hint();
     const int prefetch_ctas = hint.count ? sm_count() : 0;
     const dim3 grid(units + prefetch_ctas, splits);

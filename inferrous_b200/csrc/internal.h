@@ -105,6 +105,7 @@ cudaError_t launch_linear_no_alloc(const int8_t *q, const float *a_scale, const 
 constexpr size_t kSkinnySlotInts = 4 * (size_t)kSkinnyMaxTokens * 32;  // one 128-channel tile: [quarter][token][32]
 cudaError_t init_gemv();
 cudaError_t init_quantize();
+cudaError_t init_forward_glue();
 
 // Device status word (bounded waits report here instead of trapping).
 uint32_t *device_status_ptr();  // device address of the 2-word status block of the current device

@@ -353,7 +353,7 @@ template <class T, int MODE> cudaError_t launch_q(const QuantDev &d, cudaStream_
         if (d.K <= 3 * 1024 * V)
             return launch_kernel(quantize_rows_reg_kernel<T, MODE, 3, 1024>, dim3(grid), dim3(1024), smem, s, d);
     }
-    const int threads = (d.M <= 64 && MODE != QUANT_WITH_MAX) ? 1024 : kThreads;
+    const int threads = d.M <= 64 ? 1024 : kThreads;  // few rows: one memory round trip per thread
     return launch_kernel(quantize_rows_kernel<T, MODE>, dim3(grid), dim3(threads), quant_smem(d.K), s, d);
 }
 template <class T, int MODE> cudaError_t set_attr() {
