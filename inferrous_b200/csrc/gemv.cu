@@ -206,7 +206,27 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const GemvDev a) {
             wv[r][u] = (live && off < K) ? ld_stream_16(wr[r] + off) : make_uint4(0, 0, 0, 0);
         }
 
+    // What the epilogue needs is fetched early, so that the end of the kernel waits on registers only: the channel's
+    // weight scale(s) now (immutable), the token's activation scale and residual element right after the dependency
+    // wait.  Lane m of the warp finishes token m.
+    float ws_pre[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) ws_pre[r] = 0.0f;
+    if (live && EPI != EPI_ACC) {
+        if (EPI == EPI_SWIGLU) {
+            ws_pre[0] = a.ws[0][c];
+            ws_pre[R - 1] = a.ws[1][c];
+        } else {
+            ws_pre[0] = a.ws[g][c];
+        }
+    }
+
     dependency_wait();
+    float as_pre = 0.0f, res_pre = 0.0f;
+    if (live && lane < MT) {
+        if (EPI != EPI_ACC && SRC == SRC_CODES) as_pre = a.a_scale[lane];
+        if (EPI == EPI_RESIDUAL) res_pre = T::load(static_cast<const S *>(a.residual) + (int64_t)lane * a.n[g] + c);
+    }
     float own_scale = 0.0f;
     if constexpr (SRC == SRC_CODES) {
         // Park the quantized activations (MT rows of K bytes) in shared memory.
@@ -283,12 +303,12 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const GemvDev a) {
             if (lane == m) sum[r] = acc[r][m];
     }
     const int m = lane;
-    const float as = (EPI == EPI_ACC) ? 0.0f : (SRC == SRC_CODES ? a.a_scale[m] : own_scale);
+    const float as = (SRC == SRC_CODES) ? as_pre : own_scale;
     if (EPI == EPI_ACC) {
         a.acc[(int64_t)m * a.n[0] + c] = sum[0];
     } else if (EPI == EPI_SWIGLU) {
-        const float gv = dequant(sum[0], as, a.ws[0][c]);
-        const float uv = dequant(sum[R - 1], as, a.ws[1][c]);
+        const float gv = dequant(sum[0], as, ws_pre[0]);
+        const float uv = dequant(sum[R - 1], as, ws_pre[R - 1]);
         const float v = swiglu_value(gv, uv);
         const int64_t o = (int64_t)m * a.n[0] + c;
         if (a.out[0]) T::store(static_cast<S *>(a.out[0]) + o, gv);
@@ -296,13 +316,10 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const GemvDev a) {
         T::store(static_cast<S *>(a.act) + o, v);
         if (a.maxima) atomicMax(a.maxima + m, absmax_key(v));
     } else {
-        const float y = dequant(sum[0], as, a.ws[g][c]);
+        const float y = dequant(sum[0], as, ws_pre[0]);
         const int64_t o = (int64_t)m * a.n[g] + c;
         if (a.out[g]) T::store(static_cast<S *>(a.out[g]) + o, y);
-        if (EPI == EPI_RESIDUAL) {
-            const float res = T::load(static_cast<const S *>(a.residual) + o);
-            T::store(static_cast<S *>(a.combined) + o, bf16_rne(__fadd_rn(res, y)));
-        }
+        if (EPI == EPI_RESIDUAL) T::store(static_cast<S *>(a.combined) + o, bf16_rne(__fadd_rn(res_pre, y)));
     }
 }
 
