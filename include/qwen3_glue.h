@@ -18,6 +18,10 @@
  *
  * `control` is the reference's two-word device buffer {token id, absolute position of the first row}
  * (src/gpu.rs:189); the position is read on the device so that a captured graph can be replayed for every step.
+ * qwen3_prepare_qk and qwen3_attention read the position BEFORE their programmatic-launch dependency wait (it decides
+ * which cache lines they prefetch): when kernels are launched with programmatic edges, `control` must have been written
+ * by an operation that completed before the PRECEDING kernel started -- the host upload the reference does before each
+ * step qualifies; a kernel launched immediately before them that writes `control` does not.
  * A position or token id beyond its limit is not an error the host can see at launch time: the kernel skips the
  * access and records code 6 in the device status word (w8a8_device_status).
  *

@@ -125,6 +125,13 @@ template <> struct Vec<Bf16> {
         v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xffff0000u);
         v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xffff0000u);
     }
+    // a 16-byte vector fetched earlier, kept packed until it is needed
+    __device__ static __forceinline__ void unpack(const uint4 &r, float (&v)[8]) {
+        v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+        v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+        v[4] = __uint_as_float(r.z << 16); v[5] = __uint_as_float(r.z & 0xffff0000u);
+        v[6] = __uint_as_float(r.w << 16); v[7] = __uint_as_float(r.w & 0xffff0000u);
+    }
     // v holds bf16-representable floats
     __device__ static __forceinline__ void store(uint16_t *p, const float (&v)[8]) {
         uint4 r;
@@ -139,6 +146,9 @@ template <> struct Vec<F32> {
     __device__ static __forceinline__ void load(const float *p, float (&v)[4]) {
         float4 r = *reinterpret_cast<const float4 *>(p);
         v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    }
+    __device__ static __forceinline__ void unpack(const uint4 &r, float (&v)[4]) {
+        v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y); v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
     }
     __device__ static __forceinline__ void store(float *p, const float (&v)[4]) {
         *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);

@@ -62,28 +62,29 @@ __global__ void __launch_bounds__(128) prepare_qk_kernel(typename T::storage *__
                                                          const float *__restrict__ k_gain, const float *__restrict__ table,
                                                          const uint32_t *__restrict__ control, uint16_t *__restrict__ k_cache,
                                                          uint16_t *__restrict__ v_cache, int capacity, uint32_t *status) {
-    dependency_wait();
     const int lane = threadIdx.x & 31;
     const int unit = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int per_row = q_heads + kv_heads;
     if (unit >= rows * per_row) return;
     const int row = unit / per_row, h = unit % per_row;
     const bool is_q = h < q_heads;
+    // Position, gains and the rotary row do not depend on the preceding kernel (see the note on `control` in the
+    // header): they are fetched before the dependency wait.
     const uint32_t pos = control[1] + (uint32_t)row;
     if (pos >= (uint32_t)capacity) {
         if (lane == 0) record_range_fault(status, pos);
         return;
     }
-    typename T::storage *x = qkv + (size_t)row * ld + (size_t)h * kHeadDim;
     const float *gain = is_q ? q_gain : k_gain;
     const float *trow = table + (size_t)pos * kHeadDim;
     float v[4], g[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        v[i] = T::load(x + lane + 32 * i);
-        g[i] = gain[lane + 32 * i];
-    }
+    for (int i = 0; i < 4; ++i) g[i] = gain[lane + 32 * i];
     const float c0 = trow[lane], c1 = trow[lane + 32], s0 = trow[lane + 64], s1 = trow[lane + 96];
+    dependency_wait();
+    typename T::storage *x = qkv + (size_t)row * ld + (size_t)h * kHeadDim;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = T::load(x + lane + 32 * i);
     float sum = __fadd_rn(__fadd_rn(__fmul_rn(v[0], v[0]), __fmul_rn(v[2], v[2])),
                           __fadd_rn(__fmul_rn(v[1], v[1]), __fmul_rn(v[3], v[3])));
 #pragma unroll
@@ -164,11 +165,13 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
     __shared__ float reduce[kAttnThreads / 32];
     __shared__ float partial[kAttnSlices][kHeadDim];
     __shared__ uint32_t arrived;
-    dependency_wait();
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int unit = blockIdx.x, split = blockIdx.y;
     const int row = unit / q_heads, head = unit % q_heads;
     const int kv = head / (q_heads / kv_heads);
+    // The position does not depend on the preceding kernel (see the note on `control` in the header), so the key
+    // range of this CTA is known before the dependency wait and its cache lines are pulled towards L2 meanwhile; the
+    // one line the preceding kernel is still writing (the newest key) is simply fetched again by the loads below.
     const uint32_t end_u = control[1] + (uint32_t)row + 1u;
     if (end_u > (uint32_t)capacity) {  // every split of the unit takes this branch: nobody waits for anybody
         if (t == 0 && split == 0) record_range_fault(status, end_u);
@@ -182,6 +185,17 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
     const int chunk = (((end + splits - 1) / splits) + 31) & ~31;
     const int begin = min(end, split * chunk), stop = min(end, begin + chunk);
     const int count = stop - begin;
+    {
+        const size_t stride_bytes = (size_t)kv_heads * kHeadDim * sizeof(uint16_t);
+        const char *kline = reinterpret_cast<const char *>(k_cache) + (size_t)kv * kHeadDim * sizeof(uint16_t);
+        const char *vline = reinterpret_cast<const char *>(v_cache) + (size_t)kv * kHeadDim * sizeof(uint16_t);
+        for (int i = t; i < 2 * count; i += kAttnThreads) {  // two 128-byte lines per key and per cache
+            const size_t off = (size_t)(begin + (i >> 1)) * stride_bytes + (size_t)(i & 1) * 128;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(kline + off));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(vline + off));
+        }
+    }
+    dependency_wait();
     if (t < kHeadDim) query[t] = T::load(q + (size_t)row * ldq + (size_t)head * kHeadDim + t);
     __syncthreads();
 

@@ -58,6 +58,17 @@ __global__ void __launch_bounds__(THREADS) quantize_rows_reg_kernel(const QuantD
         prefetch_ranges(a.hint, blockIdx.x - a.M, gridDim.x - a.M);
         return;
     }
+    // Few rows (the 1024-thread shape): the gain row is a weight, so it is fetched before the dependency wait and
+    // kept packed; the pass that needs it then waits on registers, not on L2.
+    constexpr bool kEarlyGain = MODE == QUANT_RMSNORM && THREADS == 1024 && V == 8;  // (the f32 carrier would spill)
+    uint4 gain_raw[kEarlyGain ? RV : 1];
+    if (kEarlyGain) {
+#pragma unroll
+        for (int c = 0; c < RV; ++c) {
+            const int j = (c * THREADS + tid) * V;
+            if (j < K) gain_raw[c] = *reinterpret_cast<const uint4 *>(static_cast<const S *>(a.x2) + j);
+        }
+    }
     dependency_wait();
 
     for (int r = blockIdx.x; r < a.M; r += gridDim.x) {
@@ -114,7 +125,10 @@ __global__ void __launch_bounds__(THREADS) quantize_rows_reg_kernel(const QuantD
                 const int j = (c * THREADS + tid) * V;
                 if (j < K) {
                     float g[V];
-                    Vec<T>::load(gr + j, g);
+                    if (kEarlyGain)
+                        Vec<T>::unpack(gain_raw[c], g);
+                    else
+                        Vec<T>::load(gr + j, g);
 #pragma unroll
                     for (int i = 0; i < V; ++i) {
                         v[c][i] = bf16_rne(__fmul_rn(__fmul_rn(v[c][i], inv), g[i]));
