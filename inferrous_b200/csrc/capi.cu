@@ -317,7 +317,8 @@ int w8a8_rounding_probe(const float *x, int8_t *out, size_t n, void *stream) {
 //   9..16 tokens       gemm_skinny for the very large matrices (>= 256 MB), gemv_mma otherwise
 //   17..64 tokens      gemm_skinny for the large matrices (>= 48 MB of weights), gemv_mma otherwise
 //   65..128 tokens     gemm_skinny for the very large ones (>= 256 MB), gemm_tcgen05 otherwise
-//   more               gemm_tcgen05_pair (256x256 tiles over CTA pairs)
+//   more               gemm_tcgen05_pair (256x256 tiles over CTA pairs); gemm_tcgen05 with 128- or 64-channel tiles
+//                      while the pair kernel would have tiles for less than three quarters of the CTA pairs
 static int pick_variant(int M, int epilogue, bool single_matrix, long long weight_bytes, int K) {
     if (M <= 1) return W8A8_VARIANT_GEMV_DP4A;
     if (epilogue == EPI_SWIGLU) return W8A8_VARIANT_GEMV_DP4A;  // fused gate/up exists only there (M <= 4)
@@ -326,7 +327,16 @@ static int pick_variant(int M, int epilogue, bool single_matrix, long long weigh
     if (M <= 16) return weight_bytes >= (256ll << 20) ? W8A8_VARIANT_GEMM_SKINNY : W8A8_VARIANT_GEMV_MMA;
     if (M <= 64) return weight_bytes >= (48ll << 20) ? W8A8_VARIANT_GEMM_SKINNY : W8A8_VARIANT_GEMV_MMA;
     if (M <= 128) return weight_bytes >= (256ll << 20) ? W8A8_VARIANT_GEMM_SKINNY : W8A8_VARIANT_GEMM_TCGEN05;
-    return W8A8_VARIANT_GEMM_TCGEN05_PAIR;  // 256x256 tiles over CTA pairs: 5-16 % faster than 128x256 tiles from 129 tokens up
+    // 256x256 tiles over CTA pairs: 5-16 % faster than 128x256 tiles from 129 tokens up, as long as there are tiles
+    // for most of the 74 pairs; otherwise (O, down, Q|K|V at a few hundred tokens) the single-CTA kernel, which then
+    // narrows its tiles to 128 or 64 channels to put the matrix on more SMs.
+    const long long N = weight_bytes / K;
+    const long long pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    if (pair_tiles * 4 < (long long)(sm_count() / 2) * 3) return W8A8_VARIANT_GEMM_TCGEN05;
+    // Token counts just above a multiple of 256 (300 -> 512 padded rows against 384): the 128-row tiles do a quarter
+    // less work, which outweighs the pair kernel's advantage per tile.
+    if (((M + 255) / 256) * 256 * 100 > ((M + 127) / 128) * 128 * 115) return W8A8_VARIANT_GEMM_TCGEN05;
+    return W8A8_VARIANT_GEMM_TCGEN05_PAIR;
 }
 
 static int run_linear(LinearArgs &l, const w8a8_weight *wt, int variant, void *stream) {

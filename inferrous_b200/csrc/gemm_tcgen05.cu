@@ -8,9 +8,10 @@
 // tensor::map (src/tensor.rs:5-39) and the separate `residual` pass of prefill
 // (src/gpu.rs:419-420).  The reference feeds warp-level mma.sync from a single-buffered TMA
 // stage; here one persistent CTA per SM runs three specialised roles:
-//   warp 0      TMA producer: a 4-deep ring of {A 128x128 B, B 256x128 B} stages
-//   warp 1      MMA issuer: one elected lane issues 4 x tcgen05.mma (M128 N256 K32) per stage
-//               into one of two 256-column accumulators, and owns the TMEM allocation
+//   warp 0      TMA producer: a ring of {A 128x128 B, B BNx128 B} stages (BN = 256, 128 or 64 output channels per
+//               tile; 4, 6 or 8 stages, 192 KiB in flight either way)
+//   warp 1      MMA issuer: one elected lane issues 4 x tcgen05.mma (M128 N=BN K32) per stage
+//               into one of two BN-column accumulators, and owns the TMEM allocation
 //   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns, (f32(acc)*a_scale[m])*w_scale[n],
 //               bf16, optional residual add, 16-byte stores -- overlapped with the next tile
 // Every wait on an mbarrier is bounded (about two seconds); on expiry the CTA records a code
@@ -27,22 +28,33 @@ namespace w8a8 {
 namespace {
 
 constexpr int BLOCK_M = 128;   // tokens per tile  (UMMA M)
-constexpr int BLOCK_N = 256;   // output channels per tile (UMMA N)
 constexpr int BLOCK_K = 128;   // bytes of K per stage = one 128-byte swizzle atom
 constexpr int UMMA_K = 32;     // bytes of K per tcgen05.mma kind::i8
-constexpr int STAGES = 4;
 constexpr int A_BYTES = BLOCK_M * BLOCK_K;
-constexpr int B_BYTES = BLOCK_N * BLOCK_K;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int TMEM_COLS = 512;  // two accumulators of BLOCK_N columns
 constexpr int kThreads = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+// Output channels per tile (UMMA N) are a template parameter: 256 when the matrix has enough of them to give every
+// SM a tile, 128 or 64 when it does not (O, down and Q|K|V at up to a few hundred tokens).  With few CTAs the kernel
+// is bound by the latency of its own TMA round trips, not by the tensor pipe, so narrower tiles on more SMs win
+// although each re-reads the activation tile.  Every shape keeps 192 KiB of stages in flight per CTA.
+template <int BN> struct Tile {
+    static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int kBBytes = BN * BLOCK_K;
+    static constexpr int kStageBytes = A_BYTES + kBBytes;
+    static constexpr int kTmemCols = 2 * BN;  // two accumulators of BN columns (a power of two >= 32)
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 
 
-template <class T, int EPI>
+template <class T, int EPI, int BLOCK_N>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmDev p) {
     typedef typename T::storage S;
+    constexpr int STAGES = Tile<BLOCK_N>::kStages;
+    constexpr int B_BYTES = Tile<BLOCK_N>::kBBytes;
+    constexpr int STAGE_BYTES = Tile<BLOCK_N>::kStageBytes;
+    constexpr int TMEM_COLS = Tile<BLOCK_N>::kTmemCols;
+    (void)B_BYTES;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: the swizzle pattern of TMA and of the UMMA descriptor is a function
     // of the address bits, and both assume an atom-aligned tile base.
@@ -212,21 +224,27 @@ cudaError_t encode_map_impl(CUtensorMap *map, const void *base, int rows, int K,
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <class T, int EPI> cudaError_t launch_inst(const CUtensorMap &ma, const CUtensorMap &mb, const GemmDev &d, cudaStream_t s) {
-    const int tiles = ((d.M + BLOCK_M - 1) / BLOCK_M) * ((d.N + BLOCK_N - 1) / BLOCK_N);
+template <class T, int EPI, int BN> cudaError_t launch_inst(const CUtensorMap &ma, const CUtensorMap &mb, const GemmDev &d, cudaStream_t s) {
+    const int tiles = ((d.M + BLOCK_M - 1) / BLOCK_M) * ((d.N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    return launch_kernel(gemm_tcgen05_kernel<T, EPI>, dim3(grid), dim3(kThreads), (size_t)SMEM_BYTES, s, ma, mb, d);
+    return launch_kernel(gemm_tcgen05_kernel<T, EPI, BN>, dim3(grid), dim3(kThreads), (size_t)Tile<BN>::kSmemBytes, s, ma, mb, d);
 }
-template <class T> cudaError_t launch_epi(int epi, const CUtensorMap &ma, const CUtensorMap &mb, const GemmDev &d, cudaStream_t s) {
+template <class T, int BN> cudaError_t launch_epi(int epi, const CUtensorMap &ma, const CUtensorMap &mb, const GemmDev &d, cudaStream_t s) {
     switch (epi) {
-        case EPI_PLAIN: return launch_inst<T, EPI_PLAIN>(ma, mb, d, s);
-        case EPI_RESIDUAL: return launch_inst<T, EPI_RESIDUAL>(ma, mb, d, s);
-        case EPI_ACC: return launch_inst<T, EPI_ACC>(ma, mb, d, s);
+        case EPI_PLAIN: return launch_inst<T, EPI_PLAIN, BN>(ma, mb, d, s);
+        case EPI_RESIDUAL: return launch_inst<T, EPI_RESIDUAL, BN>(ma, mb, d, s);
+        case EPI_ACC: return launch_inst<T, EPI_ACC, BN>(ma, mb, d, s);
         default: return cudaErrorInvalidValue;
     }
 }
-template <class T, int EPI> cudaError_t set_attr() {
-    return cudaFuncSetAttribute(gemm_tcgen05_kernel<T, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+template <class T, int EPI, int BN> cudaError_t set_attr() {
+    return cudaFuncSetAttribute(gemm_tcgen05_kernel<T, EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tile<BN>::kSmemBytes);
+}
+template <class T, int BN> cudaError_t set_attrs() {
+    cudaError_t e;
+    if ((e = set_attr<T, EPI_PLAIN, BN>()) != cudaSuccess) return e;
+    if ((e = set_attr<T, EPI_RESIDUAL, BN>()) != cudaSuccess) return e;
+    return set_attr<T, EPI_ACC, BN>();
 }
 
 }  // namespace
@@ -238,19 +256,43 @@ cudaError_t encode_tile_map(CUtensorMap *map, const void *base, int rows, int K,
 cudaError_t init_gemm_tcgen05() {
     cudaError_t e;
     if ((e = load_encode()) != cudaSuccess) return e;
-    if ((e = set_attr<Bf16, EPI_PLAIN>()) != cudaSuccess) return e;
-    if ((e = set_attr<Bf16, EPI_RESIDUAL>()) != cudaSuccess) return e;
-    if ((e = set_attr<Bf16, EPI_ACC>()) != cudaSuccess) return e;
-    if ((e = set_attr<F32, EPI_PLAIN>()) != cudaSuccess) return e;
-    if ((e = set_attr<F32, EPI_RESIDUAL>()) != cudaSuccess) return e;
-    if ((e = set_attr<F32, EPI_ACC>()) != cudaSuccess) return e;
+    if ((e = set_attrs<Bf16, 256>()) != cudaSuccess) return e;
+    if ((e = set_attrs<Bf16, 128>()) != cudaSuccess) return e;
+    if ((e = set_attrs<Bf16, 64>()) != cudaSuccess) return e;
+    if ((e = set_attrs<F32, 256>()) != cudaSuccess) return e;
+    if ((e = set_attrs<F32, 128>()) != cudaSuccess) return e;
+    if ((e = set_attrs<F32, 64>()) != cudaSuccess) return e;
     return cudaSuccess;
 }
 
+// Output channels per tile.  With a tile for (nearly) every SM at 256 channels the kernel is bound by the tensor pipe
+// and the widest tile is right.  Below that it is bound by the serial TMA round trips of one tile's K loop, whose
+// number is K blocks / stages, i.e. proportional to 1/8, 1/6 and 1/4 for 64, 128 and 256 channels: take the shape
+// with the smallest (waves of tiles) x (round trips per tile), the wider one on a tie.
+int tcgen05_tile_channels(int M, int N) {
+    const int m_tiles = (M + BLOCK_M - 1) / BLOCK_M;
+    const int sms = sm_count();
+    if (m_tiles * ((N + 255) / 256) >= sms * 3 / 4) return 256;
+    int best = 256;
+    long long best_cost = -1;
+    for (int bn = 256; bn >= 64; bn /= 2) {
+        const long long tiles = (long long)m_tiles * ((N + bn - 1) / bn);
+        const long long waves = (tiles + sms - 1) / sms;
+        const long long cost = waves * (bn == 256 ? 6 : (bn == 128 ? 4 : 3));  // 24 / stages
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = bn;
+        }
+    }
+    return best;
+}
+
 cudaError_t make_weight_maps(w8a8_weight *wt) {
-    cudaError_t e = encode_map_impl(&wt->map_rows256, wt->w, wt->N, wt->K, BLOCK_N);
+    cudaError_t e = encode_map_impl(&wt->map_rows256, wt->w, wt->N, wt->K, 256);
     if (e != cudaSuccess) return e;
     e = encode_map_impl(&wt->map_rows128, wt->w, wt->N, wt->K, 128);
+    if (e != cudaSuccess) return e;
+    e = encode_map_impl(&wt->map_rows64, wt->w, wt->N, wt->K, 64);
     if (e != cudaSuccess) return e;
     wt->has_maps = true;
     return cudaSuccess;
@@ -268,8 +310,17 @@ cudaError_t launch_gemm_tcgen05(const LinearArgs &l, const w8a8_weight *wt, cuda
     d.a_scale = l.a_scale; d.w_scale = wt->w_scale; d.M = l.M; d.N = wt->N; d.K = l.K;
     d.y = l.out[0]; d.residual = l.residual; d.combined = l.combined; d.acc = l.acc;
     d.status = device_status_ptr();
-    return l.dtype == 0 ? launch_epi<Bf16>(l.epilogue, map_a, wt->map_rows256, d, s)
-                        : launch_epi<F32>(l.epilogue, map_a, wt->map_rows256, d, s);
+    switch (tcgen05_tile_channels(l.M, wt->N)) {
+        case 256:
+            return l.dtype == 0 ? launch_epi<Bf16, 256>(l.epilogue, map_a, wt->map_rows256, d, s)
+                                : launch_epi<F32, 256>(l.epilogue, map_a, wt->map_rows256, d, s);
+        case 128:
+            return l.dtype == 0 ? launch_epi<Bf16, 128>(l.epilogue, map_a, wt->map_rows128, d, s)
+                                : launch_epi<F32, 128>(l.epilogue, map_a, wt->map_rows128, d, s);
+        default:
+            return l.dtype == 0 ? launch_epi<Bf16, 64>(l.epilogue, map_a, wt->map_rows64, d, s)
+                                : launch_epi<F32, 64>(l.epilogue, map_a, wt->map_rows64, d, s);
+    }
 }
 
 }  // namespace w8a8

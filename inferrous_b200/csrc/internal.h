@@ -12,6 +12,7 @@ struct w8a8_weight {
     int N, K;
     CUtensorMap map_rows256;  // [N,K] uint8, box 128 bytes x 256 rows, SWIZZLE_128B
     CUtensorMap map_rows128;  // same with a 128-row box
+    CUtensorMap map_rows64;   // same with a 64-row box
     bool has_maps;
 };
 
@@ -84,6 +85,7 @@ cudaError_t init_gemv_rows();
 // tcgen05 path: one matrix, EPI_PLAIN / EPI_RESIDUAL / EPI_ACC
 cudaError_t launch_gemm_tcgen05(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);
 cudaError_t init_gemm_tcgen05();
+int tcgen05_tile_channels(int M, int N);  // 256, 128 or 64: output channels per tile the launcher will use
 cudaError_t launch_gemm_tcgen05_wide(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);  // 256x256 tiles
 cudaError_t init_gemm_tcgen05_wide();
 cudaError_t launch_gemm_tcgen05_pair(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);  // CTA pairs
