@@ -31,7 +31,9 @@ MAX_ATTENTION_POSITION = 1024
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_fixtures.py /path/to/reference-checkout")
+    ref = Path(sys.argv[1])
     gen = ref / "crates/inferrous-qwen3/tools/operator_fixtures.py"
     out = Path(__file__).resolve().parent / "operator_fixtures"
     with tempfile.TemporaryDirectory() as tmp:
