@@ -59,6 +59,11 @@ int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads
                     const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity, uint32_t *maxima,
                     void *stream);
 
+/* Launches of 32 rows or more (prefill) run both attention products on the tensor cores (bf16 warp-level MMA, float32
+ * accumulation, softmax weights carried as two bf16 parts); 0 keeps them on the CUDA-core kernel that shorter launches
+ * use, for comparison.  Process-wide; default 1. */
+int qwen3_attention_use_tensor_cores(int enabled);
+
 #ifdef __cplusplus
 }
 #endif

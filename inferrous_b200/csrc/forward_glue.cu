@@ -23,6 +23,8 @@ namespace {
 constexpr int kHeadDim = 128;
 constexpr int kMaxContext = 4096;  // src/lib.rs:18
 
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
 __device__ __forceinline__ void record_range_fault(uint32_t *status, uint32_t detail) {
     if (status && atomicCAS(status, 0u, (uint32_t)FAULT_CACHE_RANGE) == 0u) status[1] = detail;
 }
@@ -463,6 +465,203 @@ __global__ void __launch_bounds__(kAttnThreads) attention_grouped_kernel(const t
     }
 }
 
+// ---- attention, many rows, on the tensor cores -----------------------------------------------------------------
+// Prefill of 32 rows or more: one CTA of 4 warps per (block of 64 rows, query head), each warp 16 rows, keys and values
+// staged 64 at a time in shared memory, both products on mma.sync.m16n8k16 (bf16 x bf16 -> f32), running maximum and
+// total per row (flash attention).  What keeps it inside the same bound as the CUDA-core kernels:
+//   * q, k and v ARE bf16 values, so Q.K^T has exact products and float32 sums (association differs, nothing else);
+//   * the softmax weights are float32; each enters the P.V product as hi + lo, two bf16 numbers with hi = bf16(p) and
+//     lo = bf16(p - hi), so p is carried to 16 mantissa bits instead of 8 and the second product costs one more MMA;
+//   * exp is the same ex2.approx form, the division by the total happens once at the end.
+// This is the one place where the library uses the legacy warp-level MMA: a 16 x 64 score tile per warp is far below
+// the 128-row granularity of tcgen05, and attention is not on the W8A8 path.
+constexpr int kMmaRows = 64;     // rows per CTA
+constexpr int kMmaKeys = 64;     // keys per shared-memory tile
+constexpr int kMmaPitch = kHeadDim + 8;  // bf16 elements per staged row: 272 bytes, conflict-free for the fragment loads
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {  // both already bf16-representable
+    return (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xffff0000u);
+}
+template <class T> __device__ __forceinline__ uint32_t load_pair(const typename T::storage *p);
+template <> __device__ __forceinline__ uint32_t load_pair<Bf16>(const uint16_t *p) { return *reinterpret_cast<const uint32_t *>(p); }
+template <> __device__ __forceinline__ uint32_t load_pair<F32>(const float *p) {
+    const float2 v = *reinterpret_cast<const float2 *>(p);
+    return pack_bf16(v.x, v.y);
+}
+template <class T> __device__ __forceinline__ void store_pair(typename T::storage *p, float a, float b);
+template <> __device__ __forceinline__ void store_pair<Bf16>(uint16_t *p, float a, float b) { *reinterpret_cast<uint32_t *>(p) = pack_bf16(a, b); }
+template <> __device__ __forceinline__ void store_pair<F32>(float *p, float a, float b) { *reinterpret_cast<float2 *>(p) = make_float2(a, b); }
+
+template <class T>
+__global__ void __launch_bounds__(128) attention_mma_kernel(const typename T::storage *__restrict__ q, int64_t ldq, int rows, int q_heads,
+                                                            int kv_heads, const uint16_t *__restrict__ k_cache,
+                                                            const uint16_t *__restrict__ v_cache,
+                                                            const uint32_t *__restrict__ control,
+                                                            typename T::storage *__restrict__ out, int64_t ldo, int capacity,
+                                                            uint32_t *maxima, uint32_t *status) {
+    __shared__ __align__(16) uint16_t ks[kMmaKeys][kMmaPitch];
+    __shared__ __align__(16) uint16_t vs[kMmaKeys][kMmaPitch];
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tq = lane & 3;
+    const int head = blockIdx.y, kv = head / (q_heads / kv_heads);
+    const int row0 = blockIdx.x * kMmaRows;                    // first row of the CTA
+    const int last_row = min(rows, row0 + kMmaRows) - 1;       // last valid row of the CTA
+    const uint32_t position = control[1];
+    if (position + (uint32_t)rows > (uint32_t)capacity) {      // the same verdict in every CTA of the launch
+        if (t == 0 && blockIdx.x == 0 && head == 0) record_range_fault(status, position + (uint32_t)rows);
+        return;
+    }
+    dependency_wait();
+    const int r_lo = row0 + warp * 16 + g, r_hi = r_lo + 8;   // the two rows this thread holds
+    const int rl = min(r_lo, rows - 1), rh = min(r_hi, rows - 1);  // clamped for loads; stores are guarded
+    // Q fragments: 8 steps of 16 channels
+    uint32_t qa[8][4];
+    {
+        const typename T::storage *ql = q + (size_t)rl * ldq + (size_t)head * kHeadDim + 2 * tq;
+        const typename T::storage *qh = q + (size_t)rh * ldq + (size_t)head * kHeadDim + 2 * tq;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            qa[s][0] = load_pair<T>(ql + 16 * s);
+            qa[s][1] = load_pair<T>(qh + 16 * s);
+            qa[s][2] = load_pair<T>(ql + 16 * s + 8);
+            qa[s][3] = load_pair<T>(qh + 16 * s + 8);
+        }
+    }
+    float o[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[n][i] = 0.0f;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
+    const int end_cta = (int)position + last_row + 1;          // keys visible to the CTA's last row
+    const int vis_lo = (int)position + r_lo, vis_hi = (int)position + r_hi;  // last visible key of each row
+    const size_t key_stride = (size_t)kv_heads * kHeadDim;
+
+    for (int k0 = 0; k0 < end_cta; k0 += kMmaKeys) {
+        __syncthreads();  // the previous tile has been consumed
+        for (int i = t; i < kMmaKeys * (kHeadDim / 8); i += 128) {  // 16 vectors of 16 bytes per key and per cache
+            const int key = i >> 4, part = i & 15;
+            uint4 kvec = make_uint4(0, 0, 0, 0), vvec = kvec;
+            if (k0 + key < end_cta) {
+                const size_t off = (size_t)(k0 + key) * key_stride + (size_t)kv * kHeadDim + 8 * part;
+                kvec = *reinterpret_cast<const uint4 *>(k_cache + off);
+                vvec = *reinterpret_cast<const uint4 *>(v_cache + off);
+            }
+            *reinterpret_cast<uint4 *>(&ks[key][8 * part]) = kvec;
+            *reinterpret_cast<uint4 *>(&vs[key][8 * part]) = vvec;
+        }
+        __syncthreads();
+        if (k0 > (int)position + row0 + warp * 16 + 15) continue;  // no key of this tile is visible to this warp's rows
+
+        // scores of 16 rows x 64 keys
+        float sc[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sc[n][i] = 0.0f;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&ks[n * 8 + g][16 * s + 2 * tq]);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t *>(&ks[n * 8 + g][16 * s + 2 * tq + 8]);
+                mma_bf16(sc[n], qa[s], b0, b1);
+            }
+        }
+        // scale, causal mask, running maximum
+        float t_lo = -INFINITY, t_hi = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const int key = k0 + n * 8 + 2 * tq;
+            sc[n][0] = key <= vis_lo ? __fmul_rn(sc[n][0], 0.08838834764831845f) : -INFINITY;
+            sc[n][1] = key + 1 <= vis_lo ? __fmul_rn(sc[n][1], 0.08838834764831845f) : -INFINITY;
+            sc[n][2] = key <= vis_hi ? __fmul_rn(sc[n][2], 0.08838834764831845f) : -INFINITY;
+            sc[n][3] = key + 1 <= vis_hi ? __fmul_rn(sc[n][3], 0.08838834764831845f) : -INFINITY;
+            t_lo = fmaxf(t_lo, fmaxf(sc[n][0], sc[n][1]));
+            t_hi = fmaxf(t_hi, fmaxf(sc[n][2], sc[n][3]));
+        }
+        t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 1));
+        t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 2));
+        t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 1));
+        t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 2));
+        const float n_lo = fmaxf(m_lo, t_lo), n_hi = fmaxf(m_hi, t_hi);
+        // a row with nothing visible yet keeps maximum -inf: its weights are 0 and nothing is rescaled
+        const float c_lo = n_lo == -INFINITY ? 1.0f : exp_approx(__fadd_rn(m_lo, -n_lo));
+        const float c_hi = n_hi == -INFINITY ? 1.0f : exp_approx(__fadd_rn(m_hi, -n_hi));
+        const float b_lo = n_lo == -INFINITY ? 0.0f : n_lo, b_hi = n_hi == -INFINITY ? 0.0f : n_hi;
+        m_lo = n_lo;
+        m_hi = n_hi;
+        l_lo = __fmul_rn(l_lo, c_lo);
+        l_hi = __fmul_rn(l_hi, c_hi);
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+            o[n][0] = __fmul_rn(o[n][0], c_lo);
+            o[n][1] = __fmul_rn(o[n][1], c_lo);
+            o[n][2] = __fmul_rn(o[n][2], c_hi);
+            o[n][3] = __fmul_rn(o[n][3], c_hi);
+        }
+        // weights, split into two bf16 parts, and the P.V product
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // 16 keys per step: score tiles 2j and 2j+1
+            uint32_t ph[4], pl[4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float p[4];
+                p[0] = exp_approx(__fadd_rn(sc[2 * j + h][0], -b_lo));
+                p[1] = exp_approx(__fadd_rn(sc[2 * j + h][1], -b_lo));
+                p[2] = exp_approx(__fadd_rn(sc[2 * j + h][2], -b_hi));
+                p[3] = exp_approx(__fadd_rn(sc[2 * j + h][3], -b_hi));
+                l_lo = __fadd_rn(l_lo, __fadd_rn(p[0], p[1]));
+                l_hi = __fadd_rn(l_hi, __fadd_rn(p[2], p[3]));
+                float hi[4], lo[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    hi[i] = bf16_rne(p[i]);
+                    lo[i] = bf16_rne(__fadd_rn(p[i], -hi[i]));
+                }
+                ph[2 * h] = pack_bf16(hi[0], hi[1]);
+                ph[2 * h + 1] = pack_bf16(hi[2], hi[3]);
+                pl[2 * h] = pack_bf16(lo[0], lo[1]);
+                pl[2 * h + 1] = pack_bf16(lo[2], lo[3]);
+            }
+            const uint32_t vrow = smem_addr(&vs[16 * j + (lane & 15)][0]);
+#pragma unroll
+            for (int n = 0; n < 16; ++n) {
+                uint32_t b0, b1;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(vrow + 16u * n));
+                mma_bf16(o[n], ph, b0, b1);
+                mma_bf16(o[n], pl, b0, b1);
+            }
+        }
+    }
+    // totals over the four lanes that share a row, then the one division
+    l_lo = __fadd_rn(l_lo, __shfl_xor_sync(0xffffffffu, l_lo, 1));
+    l_lo = __fadd_rn(l_lo, __shfl_xor_sync(0xffffffffu, l_lo, 2));
+    l_hi = __fadd_rn(l_hi, __shfl_xor_sync(0xffffffffu, l_hi, 1));
+    l_hi = __fadd_rn(l_hi, __shfl_xor_sync(0xffffffffu, l_hi, 2));
+    uint32_t mx_lo = 0, mx_hi = 0;
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+        const float a0 = bf16_rne(__fdiv_rn(o[n][0], l_lo)), a1 = bf16_rne(__fdiv_rn(o[n][1], l_lo));
+        const float a2 = bf16_rne(__fdiv_rn(o[n][2], l_hi)), a3 = bf16_rne(__fdiv_rn(o[n][3], l_hi));
+        if (r_lo < rows) store_pair<T>(out + (size_t)r_lo * ldo + (size_t)head * kHeadDim + 8 * n + 2 * tq, a0, a1);
+        if (r_hi < rows) store_pair<T>(out + (size_t)r_hi * ldo + (size_t)head * kHeadDim + 8 * n + 2 * tq, a2, a3);
+        mx_lo = max(mx_lo, max(absmax_key(a0), absmax_key(a1)));
+        mx_hi = max(mx_hi, max(absmax_key(a2), absmax_key(a3)));
+    }
+    if (maxima) {
+        mx_lo = max(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = max(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = max(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = max(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        if (tq == 0 && r_lo < rows) atomicMax(maxima + r_lo, mx_lo);
+        if (tq == 0 && r_hi < rows) atomicMax(maxima + r_hi, mx_hi);
+    }
+}
+
 size_t grouped_smem(int gh, int capacity) {
     return ((size_t)gh * capacity + (size_t)kAttnSlices * gh * kHeadDim + (size_t)gh * kHeadDim + (kAttnThreads / 32) * gh) * sizeof(float);
 }
@@ -491,6 +690,9 @@ cudaError_t launch_grouped_any(const void *q, int64_t ldq, int rows, int q_heads
 }
 
 bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+constexpr int kMmaMinRows = 32;
+bool g_attention_no_mma = false;  // test switch (qwen3_attention_use_tensor_cores): keep many-row launches on the CUDA cores
 
 template <class T> cudaError_t raise_grouped_smem() {
     cudaError_t e;
@@ -567,6 +769,18 @@ int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads
     const int units = rows * q_heads;
     int splits = 1;
     if (units < sm_count() && units <= kAttnSplitMaxUnits) splits = std::min(kAttnMaxSplits, (2 * sm_count() + units - 1) / units);
+    if (rows >= kMmaMinRows && (ldq % 2) == 0 && (ldo % 2) == 0 && aligned(q, 8) && aligned(out, 8) && !g_attention_no_mma) {
+        // prefill: tensor-core kernel, 64 rows per CTA
+        const dim3 grid_mma((rows + kMmaRows - 1) / kMmaRows, q_heads);
+        cudaError_t em = dtype == W8A8_BF16
+                             ? launch_kernel(attention_mma_kernel<Bf16>, grid_mma, dim3(128), 0, (cudaStream_t)stream, (const uint16_t *)q,
+                                             ldq, rows, q_heads, kv_heads, k_cache, v_cache, control, (uint16_t *)out, ldo, capacity,
+                                             maxima, device_status_ptr())
+                             : launch_kernel(attention_mma_kernel<F32>, grid_mma, dim3(128), 0, (cudaStream_t)stream, (const float *)q,
+                                             ldq, rows, q_heads, kv_heads, k_cache, v_cache, control, (float *)out, ldo, capacity,
+                                             maxima, device_status_ptr());
+        return em == cudaSuccess ? W8A8_OK : fail_cuda(em, "attention launch");
+    }
     if (splits == 1 && units >= sm_count()) {
         // many rows: one CTA per (row, key/value head) serves the query heads that share it
         cudaError_t eg = dtype == W8A8_BF16
@@ -587,6 +801,11 @@ int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads
                                         q_heads, kv_heads, k_cache, v_cache, control, (float *)out, ldo, capacity, maxima,
                                         attention_scratch(), attention_counters(), device_status_ptr(), units, hint);
     return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "attention launch");
+}
+
+int qwen3_attention_use_tensor_cores(int enabled) {
+    g_attention_no_mma = enabled == 0;
+    return W8A8_OK;
 }
 
 }  // extern "C"

@@ -267,3 +267,8 @@ def attention(q: torch.Tensor, q_heads: int, kv_heads: int, k_cache: torch.Tenso
     capi.check(capi.load().qwen3_attention(_ptr(q), _dtype_code(q), q.stride(0), q.shape[0], q_heads, kv_heads, _ptr(k_cache),
                                            _ptr(v_cache), _ptr(control), _ptr(out), out.stride(0), k_cache.shape[0], _ptr(maxima),
                                            _stream()), "qwen3_attention")
+
+
+def attention_use_tensor_cores(enabled: bool) -> None:
+    """Many-row attention launches on the tensor cores (default) or on the CUDA-core kernel (comparison runs)."""
+    capi.check(capi.load().qwen3_attention_use_tensor_cores(1 if enabled else 0), "qwen3_attention_use_tensor_cores")

@@ -221,3 +221,43 @@ def test_attention_with_prefetch_hints_changes_nothing(ops):
         outs.append(to_host(out))
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
     assert ops.device_status() == (0, 0)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("rows,position,qh,kvh", [(70, 50, 32, 8), (33, 0, 4, 2), (200, 3, 8, 2)])
+def test_attention_on_tensor_cores(ops, dtype, rows, position, qh, kvh):
+    """Launches of 32 rows or more take the tensor-core kernel: the same bound against the sequential CPU restatement as
+    the CUDA-core kernels, the same published maxima rule, and agreement with the CUDA-core kernel on the same inputs
+    to within one bf16 step."""
+    import torch
+
+    rng = np.random.default_rng(rows * 7 + position)
+    keys = position + rows
+    q = oracle.bf16(rng.standard_normal((rows, qh, 128)).astype(np.float32))
+    k = oracle.bf16_bits((rng.standard_normal((keys, kvh, 128)) * 0.8).astype(np.float32))
+    v = oracle.bf16_bits(rng.standard_normal((keys, kvh, 128)).astype(np.float32))
+    capacity = 256
+    kc = torch.full((capacity, kvh, 128), float("nan"), dtype=torch.bfloat16, device="cuda")  # unwritten slots must not leak
+    vc = torch.full((capacity, kvh, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    kc[:keys] = to_dev(k.view(np.int16)).view(torch.bfloat16)
+    vc[:keys] = to_dev(v.view(np.int16)).view(torch.bfloat16)
+    qd = to_dev(q.reshape(rows, -1), dtype)
+    td = torch.bfloat16 if dtype == "bf16" else torch.float32
+    results = {}
+    for tensor_cores in (True, False):
+        ops.attention_use_tensor_cores(tensor_cores)
+        try:
+            out = torch.full((rows, qh * 128), float("nan"), dtype=td, device="cuda")
+            mx = to_dev(np.full(rows, np.float32(1e-8).view(np.uint32), np.uint32))
+            ops.attention(qd, qh, kvh, kc, vc, control(0, position), out, mx)
+            got = to_host(out)
+            assert np.array_equal(to_host(mx).view(np.uint32), np.abs(got).max(1).astype(np.float32).view(np.uint32))
+            results[tensor_cores] = got
+        finally:
+            ops.attention_use_tensor_cores(True)
+    cpu = oracle.attention(q, k, v, position).reshape(rows, -1)
+    for got in results.values():
+        assert np.all(np.abs(got - cpu) <= np.abs(cpu) * 2.0 ** -7 + 5e-6)
+        assert (got != cpu).mean() < 0.05
+    assert np.all(np.abs(results[True] - results[False]) <= np.abs(results[False]) * 2.0 ** -7 + 5e-6)
+    assert ops.device_status() == (0, 0)
