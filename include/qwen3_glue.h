@@ -1,9 +1,10 @@
 /* C ABI of the three operators that surround the W8A8 linear layers inside one Qwen3 decoder layer, so that a
  * host can run a whole forward pass through libw8a8.so: token embedding, per-head RMSNorm + rotary embedding +
  * KV-cache append, and causal grouped-query attention.  They are the callers on either side of the linear-layer
- * path declared in w8a8.h, not part of it: plain kernels that restate the reference's arithmetic.  Embedding, head
+ * path declared in w8a8.h, not part of it: kernels that restate the reference's arithmetic.  Embedding, head
  * norm and rotary embedding keep the reference's summation order (bit-identical but for rsqrt.approx); attention
- * reassociates its float32 sums for parallelism and stays within the reference's own tolerance for that operator.
+ * reassociates its float32 sums for parallelism (and runs its two products on the tensor cores from 32 rows up) and
+ * stays within the reference's own tolerance for that operator.
  *
  * Reference interfaces replaced (paths under crates/inferrous-qwen3/):
  *   qwen3_embedding    kernel `embedding`   src/kernels.rs:335-345   launched at src/gpu.rs:543-551

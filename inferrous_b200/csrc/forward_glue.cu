@@ -2,8 +2,7 @@
 // per-head RMSNorm + rotary embedding + KV-cache append, and causal grouped-query attention.
 //
 // They exist so that the linear-layer kernels can be driven through a whole forward pass (the callers of
-// the hot path); they are plain CUDA kernels restating the reference's arithmetic (paths under
-// crates/inferrous-qwen3/):
+// the hot path); they restate the reference's arithmetic (paths under crates/inferrous-qwen3/):
 //   embedding    src/kernels.rs:335-345
 //   prepare_qk   src/kernels.rs:1350-1443  (= norm :347-413 at width 128, rope :1444-1468, cache :1470-1488)
 //   attention    src/kernels.rs:1490-1658  (scores, maximum, exp / total, RN division per key, P.V; the float32
@@ -478,6 +477,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_grouped_kernel(const t
 constexpr int kMmaRows = 64;     // rows per CTA
 constexpr int kMmaKeys = 64;     // keys per shared-memory tile
 constexpr int kMmaPitch = kHeadDim + 8;  // bf16 elements per staged row: 272 bytes, conflict-free for the fragment loads
+constexpr size_t kMmaSmemBytes = (size_t)2 * 2 * kMmaKeys * kMmaPitch * sizeof(uint16_t);  // 2 stages x {K, V}: 68 KiB
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -505,15 +505,17 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const typename T::st
                                                             const uint32_t *__restrict__ control,
                                                             typename T::storage *__restrict__ out, int64_t ldo, int capacity,
                                                             uint32_t *maxima, uint32_t *status) {
-    __shared__ __align__(16) uint16_t ks[kMmaKeys][kMmaPitch];
-    __shared__ __align__(16) uint16_t vs[kMmaKeys][kMmaPitch];
+    // two stages of {keys, values}: the next tile is copied (cp.async) while the current one is multiplied
+    extern __shared__ __align__(16) uint16_t mma_smem[];
+    typedef uint16_t (*TilePtr)[kMmaPitch];
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tq = lane & 3;
     const int head = blockIdx.y, kv = head / (q_heads / kv_heads);
-    const int row0 = blockIdx.x * kMmaRows;                    // first row of the CTA
+    // causal attention: the last row blocks see the most keys, so they are scheduled first
+    const int row0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kMmaRows;  // first row of the CTA
     const int last_row = min(rows, row0 + kMmaRows) - 1;       // last valid row of the CTA
     const uint32_t position = control[1];
     if (position + (uint32_t)rows > (uint32_t)capacity) {      // the same verdict in every CTA of the launch
-        if (t == 0 && blockIdx.x == 0 && head == 0) record_range_fault(status, position + (uint32_t)rows);
+        if (t == 0 && row0 == 0 && head == 0) record_range_fault(status, position + (uint32_t)rows);
         return;
     }
     dependency_wait();
@@ -542,100 +544,115 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const typename T::st
     const int vis_lo = (int)position + r_lo, vis_hi = (int)position + r_hi;  // last visible key of each row
     const size_t key_stride = (size_t)kv_heads * kHeadDim;
 
-    for (int k0 = 0; k0 < end_cta; k0 += kMmaKeys) {
-        __syncthreads();  // the previous tile has been consumed
-        for (int i = t; i < kMmaKeys * (kHeadDim / 8); i += 128) {  // 16 vectors of 16 bytes per key and per cache
+    auto stage = [&](int buf, int k0) {  // 16 vectors of 16 bytes per key and per cache; keys past the end are zeros
+        TilePtr kd = reinterpret_cast<TilePtr>(mma_smem + (size_t)buf * 2 * kMmaKeys * kMmaPitch);
+        TilePtr vd = kd + kMmaKeys;
+        for (int i = t; i < kMmaKeys * (kHeadDim / 8); i += 128) {
             const int key = i >> 4, part = i & 15;
-            uint4 kvec = make_uint4(0, 0, 0, 0), vvec = kvec;
             if (k0 + key < end_cta) {
                 const size_t off = (size_t)(k0 + key) * key_stride + (size_t)kv * kHeadDim + 8 * part;
-                kvec = *reinterpret_cast<const uint4 *>(k_cache + off);
-                vvec = *reinterpret_cast<const uint4 *>(v_cache + off);
-            }
-            *reinterpret_cast<uint4 *>(&ks[key][8 * part]) = kvec;
-            *reinterpret_cast<uint4 *>(&vs[key][8 * part]) = vvec;
-        }
-        __syncthreads();
-        if (k0 > (int)position + row0 + warp * 16 + 15) continue;  // no key of this tile is visible to this warp's rows
-
-        // scores of 16 rows x 64 keys
-        float sc[8][4];
-#pragma unroll
-        for (int n = 0; n < 8; ++n) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) sc[n][i] = 0.0f;
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {
-                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&ks[n * 8 + g][16 * s + 2 * tq]);
-                const uint32_t b1 = *reinterpret_cast<const uint32_t *>(&ks[n * 8 + g][16 * s + 2 * tq + 8]);
-                mma_bf16(sc[n], qa[s], b0, b1);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&kd[key][8 * part])), "l"(k_cache + off));
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&vd[key][8 * part])), "l"(v_cache + off));
+            } else {
+                *reinterpret_cast<uint4 *>(&kd[key][8 * part]) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4 *>(&vd[key][8 * part]) = make_uint4(0, 0, 0, 0);
             }
         }
-        // scale, causal mask, running maximum
-        float t_lo = -INFINITY, t_hi = -INFINITY;
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage(0, 0);
+    int buf = 0;
+    for (int k0 = 0; k0 < end_cta; k0 += kMmaKeys, buf ^= 1) {
+        const bool more = k0 + kMmaKeys < end_cta;
+        if (more) stage(buf ^ 1, k0 + kMmaKeys);  // that buffer was released by the barrier that ended the previous iteration
+        if (more)
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();  // tile k0 has landed for every thread
+        TilePtr ks = reinterpret_cast<TilePtr>(mma_smem + (size_t)buf * 2 * kMmaKeys * kMmaPitch);
+        TilePtr vs = ks + kMmaKeys;
+        if (k0 <= (int)position + row0 + warp * 16 + 15) {  // else: no key of this tile is visible to this warp's rows
+            // scores of 16 rows x 64 keys
+            float sc[8][4];
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-            const int key = k0 + n * 8 + 2 * tq;
-            sc[n][0] = key <= vis_lo ? __fmul_rn(sc[n][0], 0.08838834764831845f) : -INFINITY;
-            sc[n][1] = key + 1 <= vis_lo ? __fmul_rn(sc[n][1], 0.08838834764831845f) : -INFINITY;
-            sc[n][2] = key <= vis_hi ? __fmul_rn(sc[n][2], 0.08838834764831845f) : -INFINITY;
-            sc[n][3] = key + 1 <= vis_hi ? __fmul_rn(sc[n][3], 0.08838834764831845f) : -INFINITY;
-            t_lo = fmaxf(t_lo, fmaxf(sc[n][0], sc[n][1]));
-            t_hi = fmaxf(t_hi, fmaxf(sc[n][2], sc[n][3]));
-        }
-        t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 1));
-        t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 2));
-        t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 1));
-        t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 2));
-        const float n_lo = fmaxf(m_lo, t_lo), n_hi = fmaxf(m_hi, t_hi);
-        // a row with nothing visible yet keeps maximum -inf: its weights are 0 and nothing is rescaled
-        const float c_lo = n_lo == -INFINITY ? 1.0f : exp_approx(__fadd_rn(m_lo, -n_lo));
-        const float c_hi = n_hi == -INFINITY ? 1.0f : exp_approx(__fadd_rn(m_hi, -n_hi));
-        const float b_lo = n_lo == -INFINITY ? 0.0f : n_lo, b_hi = n_hi == -INFINITY ? 0.0f : n_hi;
-        m_lo = n_lo;
-        m_hi = n_hi;
-        l_lo = __fmul_rn(l_lo, c_lo);
-        l_hi = __fmul_rn(l_hi, c_hi);
+            for (int n = 0; n < 8; ++n) {
 #pragma unroll
-        for (int n = 0; n < 16; ++n) {
-            o[n][0] = __fmul_rn(o[n][0], c_lo);
-            o[n][1] = __fmul_rn(o[n][1], c_lo);
-            o[n][2] = __fmul_rn(o[n][2], c_hi);
-            o[n][3] = __fmul_rn(o[n][3], c_hi);
-        }
-        // weights, split into two bf16 parts, and the P.V product
+                for (int i = 0; i < 4; ++i) sc[n][i] = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {  // 16 keys per step: score tiles 2j and 2j+1
-            uint32_t ph[4], pl[4];
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                float p[4];
-                p[0] = exp_approx(__fadd_rn(sc[2 * j + h][0], -b_lo));
-                p[1] = exp_approx(__fadd_rn(sc[2 * j + h][1], -b_lo));
-                p[2] = exp_approx(__fadd_rn(sc[2 * j + h][2], -b_hi));
-                p[3] = exp_approx(__fadd_rn(sc[2 * j + h][3], -b_hi));
-                l_lo = __fadd_rn(l_lo, __fadd_rn(p[0], p[1]));
-                l_hi = __fadd_rn(l_hi, __fadd_rn(p[2], p[3]));
-                float hi[4], lo[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    hi[i] = bf16_rne(p[i]);
-                    lo[i] = bf16_rne(__fadd_rn(p[i], -hi[i]));
+                for (int s = 0; s < 8; ++s) {
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&ks[n * 8 + g][16 * s + 2 * tq]);
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t *>(&ks[n * 8 + g][16 * s + 2 * tq + 8]);
+                    mma_bf16(sc[n], qa[s], b0, b1);
                 }
-                ph[2 * h] = pack_bf16(hi[0], hi[1]);
-                ph[2 * h + 1] = pack_bf16(hi[2], hi[3]);
-                pl[2 * h] = pack_bf16(lo[0], lo[1]);
-                pl[2 * h + 1] = pack_bf16(lo[2], lo[3]);
             }
-            const uint32_t vrow = smem_addr(&vs[16 * j + (lane & 15)][0]);
+            // scale, causal mask, running maximum
+            float t_lo = -INFINITY, t_hi = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                const int key = k0 + n * 8 + 2 * tq;
+                sc[n][0] = key <= vis_lo ? __fmul_rn(sc[n][0], 0.08838834764831845f) : -INFINITY;
+                sc[n][1] = key + 1 <= vis_lo ? __fmul_rn(sc[n][1], 0.08838834764831845f) : -INFINITY;
+                sc[n][2] = key <= vis_hi ? __fmul_rn(sc[n][2], 0.08838834764831845f) : -INFINITY;
+                sc[n][3] = key + 1 <= vis_hi ? __fmul_rn(sc[n][3], 0.08838834764831845f) : -INFINITY;
+                t_lo = fmaxf(t_lo, fmaxf(sc[n][0], sc[n][1]));
+                t_hi = fmaxf(t_hi, fmaxf(sc[n][2], sc[n][3]));
+            }
+            t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 1));
+            t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 2));
+            t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 1));
+            t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 2));
+            const float n_lo = fmaxf(m_lo, t_lo), n_hi = fmaxf(m_hi, t_hi);
+            // a row with nothing visible yet keeps maximum -inf: its weights are 0 and nothing is rescaled
+            const float c_lo = n_lo == -INFINITY ? 1.0f : exp_approx(__fadd_rn(m_lo, -n_lo));
+            const float c_hi = n_hi == -INFINITY ? 1.0f : exp_approx(__fadd_rn(m_hi, -n_hi));
+            const float b_lo = n_lo == -INFINITY ? 0.0f : n_lo, b_hi = n_hi == -INFINITY ? 0.0f : n_hi;
+            m_lo = n_lo;
+            m_hi = n_hi;
+            l_lo = __fmul_rn(l_lo, c_lo);
+            l_hi = __fmul_rn(l_hi, c_hi);
 #pragma unroll
             for (int n = 0; n < 16; ++n) {
-                uint32_t b0, b1;
-                asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(vrow + 16u * n));
-                mma_bf16(o[n], ph, b0, b1);
-                mma_bf16(o[n], pl, b0, b1);
+                o[n][0] = __fmul_rn(o[n][0], c_lo);
+                o[n][1] = __fmul_rn(o[n][1], c_lo);
+                o[n][2] = __fmul_rn(o[n][2], c_hi);
+                o[n][3] = __fmul_rn(o[n][3], c_hi);
+            }
+            // weights, split into two bf16 parts, and the P.V product
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {  // 16 keys per step: score tiles 2j and 2j+1
+                uint32_t ph[4], pl[4];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float p[4];
+                    p[0] = exp_approx(__fadd_rn(sc[2 * j + h][0], -b_lo));
+                    p[1] = exp_approx(__fadd_rn(sc[2 * j + h][1], -b_lo));
+                    p[2] = exp_approx(__fadd_rn(sc[2 * j + h][2], -b_hi));
+                    p[3] = exp_approx(__fadd_rn(sc[2 * j + h][3], -b_hi));
+                    l_lo = __fadd_rn(l_lo, __fadd_rn(p[0], p[1]));
+                    l_hi = __fadd_rn(l_hi, __fadd_rn(p[2], p[3]));
+                    float hi[4], lo[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        hi[i] = bf16_rne(p[i]);
+                        lo[i] = bf16_rne(__fadd_rn(p[i], -hi[i]));
+                    }
+                    ph[2 * h] = pack_bf16(hi[0], hi[1]);
+                    ph[2 * h + 1] = pack_bf16(hi[2], hi[3]);
+                    pl[2 * h] = pack_bf16(lo[0], lo[1]);
+                    pl[2 * h + 1] = pack_bf16(lo[2], lo[3]);
+                }
+                const uint32_t vrow = smem_addr(&vs[16 * j + (lane & 15)][0]);
+#pragma unroll
+                for (int n = 0; n < 16; ++n) {
+                    uint32_t b0, b1;
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(vrow + 16u * n));
+                    mma_bf16(o[n], ph, b0, b1);
+                    mma_bf16(o[n], pl, b0, b1);
+                }
             }
         }
+        __syncthreads();  // every warp is done with this buffer; the next iteration refills it
     }
     // totals over the four lanes that share a row, then the one division
     l_lo = __fadd_rn(l_lo, __shfl_xor_sync(0xffffffffu, l_lo, 1));
@@ -705,7 +722,10 @@ template <class T> cudaError_t raise_grouped_smem() {
 
 cudaError_t init_forward_glue() {
     cudaError_t e = raise_grouped_smem<Bf16>();
-    return e != cudaSuccess ? e : raise_grouped_smem<F32>();
+    if (e == cudaSuccess) e = raise_grouped_smem<F32>();
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_mma_kernel<Bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmemBytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_mma_kernel<F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmaSmemBytes);
+    return e;
 }
 
 }  // namespace w8a8
@@ -773,10 +793,10 @@ int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads
         // prefill: tensor-core kernel, 64 rows per CTA
         const dim3 grid_mma((rows + kMmaRows - 1) / kMmaRows, q_heads);
         cudaError_t em = dtype == W8A8_BF16
-                             ? launch_kernel(attention_mma_kernel<Bf16>, grid_mma, dim3(128), 0, (cudaStream_t)stream, (const uint16_t *)q,
+                             ? launch_kernel(attention_mma_kernel<Bf16>, grid_mma, dim3(128), kMmaSmemBytes, (cudaStream_t)stream, (const uint16_t *)q,
                                              ldq, rows, q_heads, kv_heads, k_cache, v_cache, control, (uint16_t *)out, ldo, capacity,
                                              maxima, device_status_ptr())
-                             : launch_kernel(attention_mma_kernel<F32>, grid_mma, dim3(128), 0, (cudaStream_t)stream, (const float *)q,
+                             : launch_kernel(attention_mma_kernel<F32>, grid_mma, dim3(128), kMmaSmemBytes, (cudaStream_t)stream, (const float *)q,
                                              ldq, rows, q_heads, kv_heads, k_cache, v_cache, control, (float *)out, ldo, capacity,
                                              maxima, device_status_ptr());
         return em == cudaSuccess ? W8A8_OK : fail_cuda(em, "attention launch");
