@@ -89,6 +89,35 @@ class Qwen3Weights:
         self.final_gain = final_gain
         self.head = ops.Matrix(head, head_scale)
         self.rope = rope_table(config).to(device)
+        self.tp, self.rank = 1, 0          # tensor-parallel degree and this process's rank (see shard())
+        self.full_config = config          # the unsharded model
+
+    def shard(self, rank: int, tp: int) -> "Qwen3Weights":
+        """This rank's share of the model under tensor parallelism (inferrous_b200/tp.py): query / key / value heads and
+        gate / up channels by output rows, O and down by input columns (their partial outputs are summed by an
+        all-reduce), the head by vocabulary rows; embedding, gains and the rotary table are replicated."""
+        from . import tp as tpmod
+
+        if tp == 1:
+            return self
+        c = self.config
+        if c.vocab % tp:
+            raise ValueError(f"vocabulary {c.vocab} cannot be split {tp} ways")
+        local = dataclasses.replace(c, q_heads=c.q_heads // tp, kv_heads=c.kv_heads // tp, intermediate=c.intermediate // tp)
+        qw, il = local.q_width, local.intermediate
+        layers = []
+        for l in self.layers:
+            qkv, qkv_s = tpmod.take_rows(l.qkv.w, l.qkv.scale, tpmod.qkv_rows(c.q_heads, c.kv_heads, rank, tp))
+            gu, gu_s = tpmod.take_rows(l.gate_up.w, l.gate_up.scale, tpmod.gate_up_rows(c.intermediate, rank, tp))
+            o = l.o.w[:, rank * qw:(rank + 1) * qw].contiguous()
+            down = l.down.w[:, rank * il:(rank + 1) * il].contiguous()
+            layers.append(Layer(local, l.norm1, qkv, qkv_s, l.qnorm, l.knorm, o, l.o.scale, l.norm2, gu, gu_s, down, l.down.scale))
+        vl = c.vocab // tp
+        out = Qwen3Weights(local, self.embedding, layers, self.final_gain, self.head.w[rank * vl:(rank + 1) * vl].contiguous(),
+                           self.head.scale[rank * vl:(rank + 1) * vl].contiguous(), self.embedding.device)
+        out.rope = self.rope
+        out.tp, out.rank, out.full_config = tp, rank, c
+        return out
 
     @classmethod
     def random(cls, config: Qwen3Config, seed: int = 0, device="cuda") -> "Qwen3Weights":
@@ -138,6 +167,7 @@ class Workspace:
         self.scales = torch.empty(rows, dtype=torch.float32, device=device)
         self.maxima = torch.zeros(rows, dtype=torch.int32, device=device)
         self.decode_maxima = torch.zeros(2, dtype=torch.int32, device=device)  # one row: {max |attention|, max |act|}
+        self.partial = torch.empty(rows, config.hidden, dtype=act, device=device)  # tensor parallel: O / down partial sums
         self.logits = None  # only the unfused path writes logits
 
 
@@ -154,8 +184,11 @@ class Qwen3Runner:
     change nothing in a whole generation."""
 
     def __init__(self, weights: Qwen3Weights, unfused: bool = False, device="cuda", fold_quantizers: str = "none",
-                 prefetch_rows: int = 0, prefetch_down_at: str = "quant", prefetch_o: bool = False):
+                 prefetch_rows: int = 0, prefetch_down_at: str = "quant", prefetch_o: bool = False, group=None):
         ops.init()
+        self.group = group  # torch.distributed process group of the tensor-parallel ranks (weights.tp > 1)
+        if weights.tp > 1 and fold_quantizers != "none":
+            raise ValueError("folded quantizers are a single-GPU option")
         self.prefetch_rows = prefetch_rows
         self.prefetch_down_at = prefetch_down_at
         self.prefetch_o = prefetch_o
@@ -172,7 +205,11 @@ class Qwen3Runner:
         self.decode = Workspace(c, 1, device, wide_gate_up=unfused)
         self.head_q = torch.empty(1, c.hidden, dtype=torch.int8, device=device)
         self.head_scale = torch.empty(1, dtype=torch.float32, device=device)
-        self.logits = torch.empty(1, c.vocab, dtype=torch.bfloat16, device=device) if unfused else None
+        self.logits = torch.empty(1, weights.full_config.vocab, dtype=torch.bfloat16, device=device) if unfused else None
+        if weights.tp > 1:
+            self.local_logits = torch.empty(1, weights.head.n, dtype=torch.bfloat16, device=device) if unfused else None
+            self.local_best = torch.zeros(2, dtype=torch.int32, device=device)         # {token within the shard, value bits}
+            self.all_best = torch.zeros(weights.tp, 2, dtype=torch.int32, device=device)
         self.graph = None
         self._host_control = torch.zeros(2, dtype=torch.int32).pin_memory()
         self._host_next = torch.zeros(1, dtype=torch.int32).pin_memory()
@@ -207,7 +244,7 @@ class Qwen3Runner:
             if rows == 1 and self.prefetch_down_at == "quant" and not self.unfused:
                 ops.prefetch_hint(layer.down.w)
             ops.quantize(ws.attention, qo, ws.scales)
-            ops.linear_residual(qo, ws.scales, layer.o, None, ws.hidden, ws.residual, variant)
+            self._project_residual(ws, qo, layer.o, ws.hidden, ws.residual, variant)
             if rows == 1 and self.prefetch_down_at == "norm2" and not self.unfused:
                 ops.prefetch_hint(layer.down.w)
             ops.norm_quantize(ws.residual, layer.norm2, None, q4, ws.scales, ws.maxima, c.eps)
@@ -223,8 +260,21 @@ class Qwen3Runner:
             else:
                 ops.linear_quantized(q4, ws.scales, layer.gate_up, ws.gate_up, variant)
                 ops.swiglu_quantize(ws.gate_up[:, :inter], ws.gate_up[:, inter:], ws.quant12, ws.scales)
-            ops.linear_residual(ws.quant12, ws.scales, layer.down, None, ws.residual, ws.hidden, variant)
+            self._project_residual(ws, ws.quant12, layer.down, ws.residual, ws.hidden, variant)
         self._head(ws)
+
+    def _project_residual(self, ws: Workspace, q: torch.Tensor, matrix, residual_in: torch.Tensor, combined: torch.Tensor,
+                          variant: int) -> None:
+        """combined = bf16(residual_in + projection).  One GPU: the residual sum is the projection's epilogue.  Tensor
+        parallel (O and down own a slice of the input channels): bf16 partial projection, all-reduce, then `residual`."""
+        if self.w.tp == 1:
+            ops.linear_residual(q, ws.scales, matrix, None, residual_in, combined, variant)
+            return
+        import torch.distributed as dist
+
+        ops.linear_quantized(q, ws.scales, matrix, ws.partial, variant)
+        dist.all_reduce(ws.partial, op=dist.ReduceOp.SUM, group=self.group)
+        ops.residual(residual_in, ws.partial, combined)
 
     def _decode_layers(self, ws: Workspace) -> None:
         """One row, with quantizers folded into the projections that consume them: "with_max" folds the quantizers of
@@ -257,10 +307,26 @@ class Qwen3Runner:
         variant = capi.VARIANT_NAIVE if self.unfused else capi.VARIANT_AUTO
         last = ws.hidden[rows - 1:rows]
         ops.norm_quantize(last, w.final_gain, None, self.head_q, self.head_scale, None, c.eps)
+        if w.tp == 1:
+            if self.unfused:
+                ops.linear_quantized(self.head_q, self.head_scale, w.head, self.logits, variant)
+            else:
+                ops.linear_argmax(self.head_q, self.head_scale, w.head, self.next)
+            return
+        # vocabulary split: every rank projects its rows; logits (unfused) or (token, value) candidates are gathered
+        import torch.distributed as dist
+
         if self.unfused:
-            ops.linear_quantized(self.head_q, self.head_scale, w.head, self.logits, variant)
-        else:
-            ops.linear_argmax(self.head_q, self.head_scale, w.head, self.next)
+            ops.linear_quantized(self.head_q, self.head_scale, w.head, self.local_logits, variant)
+            dist.all_gather_into_tensor(self.logits.view(-1), self.local_logits.view(-1), group=self.group)
+            return
+        ops.linear_argmax(self.head_q, self.head_scale, w.head, self.local_best[0:1], self.local_best[1:2].view(torch.float32))
+        dist.all_gather_into_tensor(self.all_best.view(-1), self.local_best, group=self.group)
+        tokens, values = self.all_best[:, 0], self.all_best[:, 1].view(torch.float32)
+        # device-side selection (no host synchronisation: this runs inside the captured step)
+        rank_of_best = values.argmax().reshape(1)  # first maximal value: the lowest rank, hence the lowest token id among equals
+        best = tokens.index_select(0, rank_of_best) + rank_of_best.to(torch.int32) * w.head.n
+        self.next.copy_(torch.where((tokens < 0).any().reshape(1), torch.full_like(best, -1), best))
 
     def _select_unfused(self) -> int:
         """select_token (src/kernels.rs:2191-2231) on the written logits: largest value, lowest index."""

@@ -108,3 +108,35 @@ class PeerAllReduce:
                                          C.c_void_p(torch.cuda.current_stream().cuda_stream))
         self._capi.check(st, "w8a8_tp_allreduce")
         return out
+
+
+# ---- whole-model sharding: which rows / columns of the concatenated matrices a rank owns ---------------------
+
+def qkv_rows(q_heads: int, kv_heads: int, rank: int, tp: int, head_dim: int = 128):
+    """Row ranges (start, stop) of the concatenated Q|K|V matrix owned by `rank`: its query heads, then the key heads and
+    value heads they attend to.  Heads are dealt in contiguous blocks, so query head h keeps key/value head h // group."""
+    if q_heads % tp or kv_heads % tp:
+        raise ValueError(f"{q_heads} query / {kv_heads} key-value heads cannot be split {tp} ways")
+    ql, kl = q_heads // tp * head_dim, kv_heads // tp * head_dim
+    q_width, kv_width = q_heads * head_dim, kv_heads * head_dim
+    return [(rank * ql, (rank + 1) * ql), (q_width + rank * kl, q_width + (rank + 1) * kl),
+            (q_width + kv_width + rank * kl, q_width + kv_width + (rank + 1) * kl)]
+
+
+def gate_up_rows(intermediate: int, rank: int, tp: int):
+    """Row ranges of the concatenated gate|up matrix owned by `rank` (the same channels of both, so SwiGLU stays local)."""
+    if intermediate % (128 * tp):
+        raise ValueError(f"intermediate width {intermediate} cannot be split {tp} ways in multiples of 128")
+    il = intermediate // tp
+    return [(rank * il, (rank + 1) * il), (intermediate + rank * il, intermediate + (rank + 1) * il)]
+
+
+def take_rows(w, w_scale, ranges):
+    """Concatenate row ranges of a weight [N,K] and of its per-channel scales (numpy arrays or torch tensors)."""
+    if hasattr(w, "numpy") or type(w).__module__.startswith("torch"):
+        import torch
+
+        return (torch.cat([w[a:b] for a, b in ranges]).contiguous(), torch.cat([w_scale[a:b] for a, b in ranges]).contiguous())
+    import numpy as np
+
+    return np.concatenate([w[a:b] for a, b in ranges]), np.concatenate([w_scale[a:b] for a, b in ranges])

@@ -1,0 +1,70 @@
+"""One rank of a tensor-parallel generation check; launched by torch.distributed.run from tests/test_gpu_tp_model.py.
+
+Every rank builds the same random model (same seed), keeps its shard, and generates greedily in lockstep; rank 0 also
+runs the unsharded model.  Rank 0 prints one JSON line: the tokens of both, and how far the tensor-parallel logits of
+the prompt's last position are from the single-GPU ones (tensor parallelism rounds the partial outputs of O and down to
+bf16 before they are summed, so the two are close, not identical)."""
+import json
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+
+def main() -> None:
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, tp = dist.get_rank(), dist.get_world_size()
+
+    from inferrous_b200 import ops
+    from inferrous_b200.qwen3 import Qwen3Config, Qwen3Runner, Qwen3Weights, Workspace
+
+    ops.init()
+    config = Qwen3Config(layers=2, hidden=512, q_heads=4, kv_heads=2, intermediate=1024, vocab=1024, context=192)
+    full = Qwen3Weights.random(config, seed=21)
+    shard = full.shard(rank, tp)
+    prompt = [int(t) for t in np.random.default_rng(3).integers(0, config.vocab, int(sys.argv[1]))]
+    steps = int(sys.argv[2])
+    group = dist.group.WORLD
+
+    tokens_tp, _ = Qwen3Runner(shard, group=group).generate(prompt, steps)
+    tokens_eager, _ = Qwen3Runner(shard, group=group).generate(prompt, steps, use_graph=False)
+
+    def prompt_logits(weights, grp):
+        runner = Qwen3Runner(weights, unfused=True, group=grp)
+        ws = Workspace(weights.config, len(prompt))
+        runner.control.zero_()
+        runner.forward(ws, torch.tensor(prompt, dtype=torch.int32, device="cuda"))
+        torch.cuda.synchronize()
+        return runner.logits[0].float().cpu().numpy()
+
+    logits_tp = prompt_logits(shard, group)
+    result = {"rank": rank, "tp": tp, "tokens_tp": tokens_tp, "tokens_tp_eager": tokens_eager}
+    if rank == 0:
+        tokens_single, _ = Qwen3Runner(full).generate(prompt, steps)
+        logits_single = prompt_logits(full, None)
+        diff = logits_tp.astype(np.float64) - logits_single
+        result.update(tokens_single=tokens_single,
+                      logit_rel_l2=float(np.sqrt((diff ** 2).sum() / (logits_single.astype(np.float64) ** 2).sum())),
+                      logit_cosine=float((logits_tp.astype(np.float64) * logits_single).sum()
+                                         / np.linalg.norm(logits_tp.astype(np.float64)) / np.linalg.norm(logits_single.astype(np.float64))),
+                      argmax_equal=bool(logits_tp.argmax() == logits_single.argmax()),
+                      device_status=list(ops.device_status()))
+    gathered = [None] * tp
+    dist.all_gather_object(gathered, result)
+    if rank == 0:
+        print("RESULT " + json.dumps(gathered), flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)  # captured graphs hold NCCL work: skip the communicator teardown
+
+
+if __name__ == "__main__":
+    main()
