@@ -409,6 +409,8 @@ def run_ours(args):
             extra["decode_linear_only_tok_s_estimate"] = round(1e6 / (36 * body + head), 1)
         if not args.shapes and not args.no_model:
             extra["qwen3_8b_generation"] = model_generation_table(torch, hbm_peak)
+    if world > 1 and not args.no_extra and not args.shapes and not args.no_model:
+        extra["qwen3_8b_generation"] = model_generation_table(torch, hbm_peak, rank, world, dist.group.WORLD)
 
     out = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
@@ -551,18 +553,24 @@ def decode_fused_table(torch, ops, hbm_peak):
     return rows
 
 
-def model_generation_table(torch, hbm_peak):
+def model_generation_table(torch, hbm_peak, rank=0, world=1, group=None):
     """Whole-model greedy generation of the Qwen3-8B architecture with random-init weights (inferrous_b200.qwen3):
     the prompt / generated lengths the reference's decode table uses (docs/qwen3-8b-w8a8/benchmarks.md:13-15: prompt
     5 / 129 / 512, 32 generated) plus the 129 + 128 run.  Host-visible time per step: control upload, graph replay,
-    token read-back, as the reference's generate() measures it (src/gpu.rs:873-908)."""
+    token read-back, as the reference's generate() measures it (src/gpu.rs:873-908).  With several GPUs the model is
+    tensor-parallel (heads, gate/up channels and vocabulary split; bf16 all-reduce after O and down), every rank
+    generates in lockstep and the slowest rank's time counts."""
     import numpy as np
+    import torch.distributed as dist
 
     from inferrous_b200.qwen3 import Qwen3Config, Qwen3Runner, Qwen3Weights
 
     config = Qwen3Config.qwen3_8b()
-    weights = Qwen3Weights.random(config, seed=0)
-    runner = Qwen3Runner(weights)
+    full = Qwen3Weights.random(config, seed=0)
+    weights = full.shard(rank, world)
+    del full
+    torch.cuda.empty_cache()
+    runner = Qwen3Runner(weights, group=group)
     rng = np.random.default_rng(0)
     rows = []
     published = {5: 182.3, 129: 178.2, 512: 170.5}
@@ -570,17 +578,22 @@ def model_generation_table(torch, hbm_peak):
         prompt = [int(t) for t in rng.integers(0, config.vocab, prompt_len)]
         runner.generate(prompt, generated)  # warm-up: captures the decode graph on first use
         _, seconds = runner.generate(prompt, generated)
+        if world > 1:
+            slowest = torch.tensor(seconds, dtype=torch.float64, device="cuda")
+            dist.all_reduce(slowest, op=dist.ReduceOp.MAX, group=group)
+            seconds = slowest.tolist()
         decode = seconds[1:]
         median = float(np.median(decode))
         rows.append({"prompt": prompt_len, "generated": generated, "prefill_ms": round(seconds[0] * 1e3, 3),
                      "decode_ms_per_token_median": round(median * 1e3, 4),
                      "decode_tok_s": round(len(decode) / sum(decode), 1),
                      "weight_GB/s": round(config.weight_bytes() / median / 1e9, 1),
-                     "frac_hbm": round(config.weight_bytes() / median / 1e9 / hbm_peak, 3),
+                     "frac_hbm": round(config.weight_bytes() / median / 1e9 / (hbm_peak * world), 3),
                      "reference_tok_s_rtx_pro_6000": published.get(prompt_len) if generated == 32 else None})
     del runner, weights
     torch.cuda.empty_cache()
     return {"model": "Qwen3-8B architecture, random-init W8A8 weights (body and head int8), batch 1, greedy",
+            "parallelism": f"tp{world}" if world > 1 else "single",
             "weight_bytes_per_token": config.weight_bytes(), "runs": rows}
 
 
