@@ -407,10 +407,13 @@ def run_ours(args):
         head = sum(r["us"] for r in extra["per_shape"] if r["M"] == 1 and r["shape"] == "lm_head")
         if body > 0 and head > 0:
             extra["decode_linear_only_tok_s_estimate"] = round(1e6 / (36 * body + head), 1)
-        if not args.shapes and not args.no_model:
-            extra["qwen3_8b_generation"] = model_generation_table(torch, hbm_peak)
-    if world > 1 and not args.no_extra and not args.shapes and not args.no_model:
-        extra["qwen3_8b_generation"] = model_generation_table(torch, hbm_peak, rank, world, dist.group.WORLD)
+    if not args.no_extra and not args.shapes and not args.no_model:
+        # A shape the library rejects raises before any kernel or collective is queued, identically on every rank, so
+        # reporting the error instead of the table cannot leave ranks waiting for one another.
+        try:
+            extra["qwen3_8b_generation"] = model_generation_table(torch, hbm_peak, rank, world, dist.group.WORLD if world > 1 else None)
+        except (ValueError, RuntimeError) as exc:
+            extra["qwen3_8b_generation"] = {"error": f"{type(exc).__name__}: {exc}"}
 
     out = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,

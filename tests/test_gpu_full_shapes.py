@@ -105,3 +105,34 @@ def test_full_shape_accumulators_are_linear(ops, weights, name, M):
     ops.linear_acc_i32(q1 + q2, mat, acc[2], 0)
     assert torch.equal(acc[0] + acc[1], acc[2])
     assert ops.device_status()[0] == 0
+
+
+@pytest.mark.parametrize("tp", [2, 4, 8])
+@pytest.mark.parametrize("M", [1, 4, 16, 129, 512])
+def test_tensor_parallel_shard_shapes_fast_equals_naive(ops, tp, M):
+    """The shapes one rank multiplies under tensor parallelism (inferrous_b200/tp.py): output rows / tp for Q|K|V, gate|up
+    and the head, input columns / tp for O and down.  The kernel w8a8_linear picks == the one-thread-per-output kernel."""
+    import torch
+
+    from inferrous_b200 import capi
+    from inferrous_b200.tp import shard_shape
+
+    for i, (name, (K, N)) in enumerate(SHAPES.items()):
+        k, n = shard_shape(name, K, N, tp)
+        g = torch.Generator(device="cuda").manual_seed(tp * 100 + i)
+        w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda", generator=g)
+        s = (0.5 + torch.rand(n, device="cuda", generator=g)) / (69.0 * k ** 0.5)
+        mat = ops.Matrix(w, s.float())
+        x = activations(torch, M, k, seed=M + i)
+        q = torch.empty((M, k), dtype=torch.int8, device="cuda")
+        a = torch.empty((M,), dtype=torch.float32, device="cuda")
+        ops.quantize(x, q, a)
+        res = activations(torch, M, n, seed=7)
+        fast, naive = [torch.full((M, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        fast_c, naive_c = torch.zeros_like(fast), torch.zeros_like(fast)
+        ops.linear_residual(q, a, mat, fast, res, fast_c)
+        ops.linear_residual(q, a, mat, naive, res, naive_c, capi.VARIANT_NAIVE)
+        assert torch.equal(fast.view(torch.int16), naive.view(torch.int16)), (name, k, n)
+        assert torch.equal(fast_c.view(torch.int16), naive_c.view(torch.int16)), (name, k, n)
+        del mat, w
+    assert ops.device_status() == (0, 0)
