@@ -183,9 +183,18 @@ def run_ours(args):
     ops.set_programmatic_launch(not args.no_pdl)
     # Sum of the row-split partial outputs: NCCL, or (--peer-allreduce) the library's one-shot peer-memory kernel.
     reducer, reduce_kind, reduce_check = None, "none", None
+    fused = None  # row-split projections with the all-reduce fused in (w8a8_linear_allreduce)
     if world > 1:
         reduce_kind = "nccl"
-        if args.peer_allreduce:
+        if args.fused_allreduce:
+            try:
+                from inferrous_b200.tp import PeerLinear
+                fused = PeerLinear(dist.group.WORLD, max(DECODE_M) * 4096)
+                reduce_kind = "fused_into_projection_over_peer_memory"
+            except Exception as exc:
+                print(f"bench: fused projection + all-reduce unavailable ({exc}); using NCCL", file=sys.stderr)
+                fused = None
+        elif args.peer_allreduce:
             try:
                 from inferrous_b200.tp import PeerAllReduce
                 reducer = PeerAllReduce(dist.group.WORLD, slot_elems=max(DECODE_M) * 4096)
@@ -258,6 +267,9 @@ def run_ours(args):
                 if record:
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record()
+                if fused is not None and name in ROW_SPLIT and not record:
+                    fused.linear_residual(b["q"], b["s"], mats[name], b["y"], None, None)  # GEMV that pushes + consumer
+                    continue
                 ops.linear_quantized(b["q"], b["s"], mats[name], b["y"], args.variant)
                 if record:
                     e1.record()
@@ -684,6 +696,9 @@ def main():
     ap.add_argument("--peer-allreduce", action="store_true",
                     help="tensor parallel: the library's one-shot peer-memory all-reduce instead of NCCL (measured 3 us per "
                          "call slower than NCCL at 2 and 4 GPUs, so NCCL is the default)")
+    ap.add_argument("--fused-allreduce", action="store_true",
+                    help="tensor parallel: O and down as w8a8_linear_allreduce (GEMV epilogue pushes tagged packets to every rank, "
+                         "a consumer kernel sums them) instead of projection + NCCL all-reduce")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--no-extra", action="store_true", help="skip the per-shape and prefill tables")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")

@@ -213,6 +213,23 @@ int w8a8_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w,
 int w8a8_linear_argmax(const int8_t *q, const float *a_scale, w8a8_weight_t weight, int M, uint32_t *token, float *value,
                        void *stream);
 
+/* Row-split projection (O, down) under tensor parallelism with its all-reduce fused in, for decode-sized launches
+ * (M <= 64); no counterpart in the reference, which is single-GPU.  Two kernels per call and rank, no library collective:
+ *   1. the weight-streaming GEMV of w8a8_linear, whose epilogue, instead of writing its partial output, sends every
+ *      value to the same slot of EVERY rank as one 8-byte packet {float32 bits of the bf16 value, tag of this call} --
+ *      a single peer store, so value and tag arrive together and no fence or flag write follows;
+ *   2. a consumer that waits (bounded, about 2 s) until the tp packets of an element carry this call's tag, adds them in
+ *      rank order in float32, rounds to bf16 (= y) and adds the residual (combined = bf16(residual + y)) -- the
+ *      epilogue of `linear_residual`, with the sum over ranks in between; identical on every rank.
+ *   peer_packets[p]  packet buffer of rank p as seen from this GPU: 2 * tp * slot_packets packets of 8 bytes, zero
+ *                    before the first call (two halves used alternately, so nothing is cleared between calls)
+ *   seq              2 uint32 in local memory, zero before the first call (completed calls, CTAs done), kept by the kernels
+ * Every rank must issue the same sequence of calls with the same M and N (M * N <= slot_packets).  An expired wait is
+ * reported by w8a8_device_status.  Only plain stores and loads touch peer memory. */
+int w8a8_linear_allreduce(const int8_t *q, const float *a_scale, w8a8_weight_t weight, int M, const void *residual, void *y,
+                          void *combined, int dtype, void *const *peer_packets, uint32_t *seq, int rank, int tp,
+                          size_t slot_packets, void *stream);
+
 /* Tensor-parallel sum of the row-split projections' partial outputs (O, down) over peer memory; no counterpart in
  * the reference, which is single-GPU.  One kernel per rank pushes the local partial into every rank's staging buffer
  * with plain peer stores, waits (bounded) for the other ranks' pushes and writes out = bf16(sum over ranks, in rank

@@ -39,6 +39,7 @@ SIGNATURES = {
     "w8a8_quantize_linear_gate_up_swiglu": (_i, [_vp, _i, _i, _vp, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "w8a8_linear_no_alloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "w8a8_linear_argmax": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp]),
+    "w8a8_linear_allreduce": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _i, C.POINTER(_vp), _vp, _i, _i, _sz, _vp]),
     "w8a8_tp_allreduce": (_i, [_vp, _vp, _sz, _i, C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _i, _sz, _vp]),
     "w8a8_linear_acc_i32": (_i, [_vp, _vp, _i, _vp, _i, _vp]),
     "w8a8_rounding_probe": (_i, [_vp, _vp, _sz, _vp]),

@@ -518,6 +518,31 @@ int w8a8_linear_argmax(const int8_t *q, const float *a_scale, w8a8_weight_t weig
     return W8A8_OK;
 }
 
+int w8a8_linear_allreduce(const int8_t *q, const float *a_scale, w8a8_weight_t weight, int M, const void *residual, void *y,
+                          void *combined, int dtype, void *const *peer_packets, uint32_t *seq, int rank, int tp,
+                          size_t slot_packets, void *stream) {
+    REQUIRE(valid_weight(weight) && q && a_scale && M > 0 && check_dtype(dtype), W8A8_ERR_BAD_ARG);
+    REQUIRE(peer_packets && seq && tp >= 1 && tp <= kTpMaxRanks && rank >= 0 && rank < tp, W8A8_ERR_BAD_ARG);
+    REQUIRE((residual == nullptr) == (combined == nullptr) && (y || combined), W8A8_ERR_BAD_ARG);
+    REQUIRE(M <= 64 && (size_t)M * weight->N <= slot_packets, W8A8_ERR_UNSUPPORTED);
+    REQUIRE(aligned16(q), W8A8_ERR_ALIGNMENT);
+    LinearArgs l{};
+    l.q = q; l.a_scale = a_scale; l.M = M; l.K = weight->K; l.count = 1;
+    l.w[0] = weight->w; l.ws[0] = weight->w_scale; l.n[0] = weight->N;
+    l.epilogue = EPI_PUSH; l.dtype = dtype;
+    for (int p = 0; p < tp; ++p) {
+        REQUIRE(peer_packets[p] && (reinterpret_cast<uintptr_t>(peer_packets[p]) & 7u) == 0, W8A8_ERR_ALIGNMENT);
+        l.push.ll[p] = static_cast<uint2 *>(peer_packets[p]);
+    }
+    l.push.seq = seq; l.push.rank = rank; l.push.tp = tp; l.push.slot = slot_packets;
+    const int st = run_linear(l, weight, M == 1 ? W8A8_VARIANT_GEMV_DP4A : W8A8_VARIANT_GEMV_MMA, stream);
+    if (st != W8A8_OK) return st;
+    CUDA_OK(launch_tp_reduce(static_cast<const uint2 *>(peer_packets[rank]), seq, residual, y, combined, (size_t)M * weight->N, dtype, tp,
+                             slot_packets, (cudaStream_t)stream),
+            "launch_tp_reduce");
+    return W8A8_OK;
+}
+
 int w8a8_tp_allreduce(const void *partial, void *out, size_t n_el, int dtype, void *const *peer_bufs, uint32_t *const *peer_flags,
                       uint32_t *seq, int rank, int tp, size_t slot_el, void *stream) {
     REQUIRE(partial && out && peer_bufs && peer_flags && seq && check_dtype(dtype), W8A8_ERR_BAD_ARG);

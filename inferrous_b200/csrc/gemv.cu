@@ -49,7 +49,16 @@ struct GemvDev {
     int reset_words;
     int8_t *q_out;
     float *scale_out;
+    PushTarget push;
 };
+
+// One 8-byte packet {value bits, tag of the call} to the same slot of every rank (plain peer stores over NVLink).
+__device__ __forceinline__ void push_packet(const PushTarget &t, uint32_t call, size_t element, float value) {
+    const size_t at = ((size_t)(call & 1u) * t.tp + t.rank) * t.slot + element;
+    const uint32_t bits = __float_as_uint(value), tag = call + 1u;
+    for (int p = 0; p < t.tp; ++p)
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(t.ll[p] + at), "r"(bits), "r"(tag) : "memory");
+}
 
 __device__ __forceinline__ int dp4a_16(const uint4 &w, const uint4 &a, int acc) {
     acc = __dp4a((int)w.x, (int)a.x, acc);
@@ -223,6 +232,8 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const GemvDev a) {
 
     dependency_wait();
     float as_pre = 0.0f, res_pre = 0.0f;
+    uint32_t call_pre = 0;
+    if (EPI == EPI_PUSH) call_pre = *reinterpret_cast<const volatile uint32_t *>(a.push.seq);
     if (live && lane < MT) {
         if (EPI != EPI_ACC && SRC == SRC_CODES) as_pre = a.a_scale[lane];
         if (EPI == EPI_RESIDUAL) res_pre = T::load(static_cast<const S *>(a.residual) + (int64_t)lane * a.n[g] + c);
@@ -315,6 +326,8 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(const GemvDev a) {
         if (a.out[1]) T::store(static_cast<S *>(a.out[1]) + o, uv);
         T::store(static_cast<S *>(a.act) + o, v);
         if (a.maxima) atomicMax(a.maxima + m, absmax_key(v));
+    } else if (EPI == EPI_PUSH) {
+        push_packet(a.push, call_pre, (size_t)m * a.n[0] + c, dequant(sum[0], as, ws_pre[0]));
     } else {
         const float y = dequant(sum[0], as, ws_pre[0]);
         const int64_t o = (int64_t)m * a.n[g] + c;
@@ -444,6 +457,11 @@ __global__ void __launch_bounds__(kThreads) gemv_mma_kernel(const GemvDev a) {
             a.acc[o] = sum;
             continue;
         }
+        if (EPI == EPI_PUSH) {
+            push_packet(a.push, *reinterpret_cast<const volatile uint32_t *>(a.push.seq), (size_t)o,
+                        dequant(sum, a.a_scale[tok], a.ws[g][row]));
+            continue;
+        }
         const float y = dequant(sum, a.a_scale[tok], a.ws[g][row]);
         if (a.out[g]) T::store(static_cast<S *>(a.out[g]) + o, y);
         if (EPI == EPI_RESIDUAL) {
@@ -507,6 +525,7 @@ GemvDev make_dev(const LinearArgs &l) {
     d.partial_best = l.partial_best;
     d.x = l.x; d.gamma = l.gamma; d.eps = l.eps; d.maxima_in = l.maxima_in; d.maxima_reset = l.maxima_reset;
     d.reset_words = l.maxima_reset ? l.reset_words : 0; d.q_out = l.q_out; d.scale_out = l.scale_out;
+    d.push = l.push;
     return d;
 }
 
@@ -540,6 +559,7 @@ template <int MT, class T> cudaError_t launch_dp4a_epi(int epi, const GemvDev &d
         case EPI_RESIDUAL: return launch_dp4a_inst<MT, T, EPI_RESIDUAL>(d, s);
         case EPI_SWIGLU: return launch_dp4a_inst<MT, T, EPI_SWIGLU>(d, s);
         case EPI_ACC: return launch_dp4a_inst<MT, T, EPI_ACC>(d, s);
+        case EPI_PUSH: return launch_dp4a_inst<MT, T, EPI_PUSH>(d, s);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -564,6 +584,7 @@ template <int NT, class T> cudaError_t launch_mma_epi(int epi, const GemvDev &d,
         case EPI_RESIDUAL: return launch_mma_inst<NT, T, EPI_RESIDUAL>(d, s);
         case EPI_ACC: return launch_mma_inst<NT, T, EPI_ACC>(d, s);
         case EPI_ARGMAX: return launch_mma_inst<NT, T, EPI_ARGMAX>(d, s);
+        case EPI_PUSH: return launch_mma_inst<NT, T, EPI_PUSH>(d, s);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -581,6 +602,7 @@ template <int MT, class T> cudaError_t set_attr_dp4a() {
     if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<MT, T, EPI_RESIDUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDp4aSmem))) return e;
     if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<MT, T, EPI_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDp4aSmem))) return e;
     if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<MT, T, EPI_ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDp4aSmem))) return e;
+    if ((e = cudaFuncSetAttribute(gemv_dp4a_kernel<MT, T, EPI_PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDp4aSmem))) return e;
     return cudaSuccess;
 }
 template <class T, int SRC> cudaError_t set_attr_dp4a_src() {

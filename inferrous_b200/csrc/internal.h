@@ -47,7 +47,18 @@ cudaError_t launch_rounding_probe(const float *x, int8_t *out, size_t n, cudaStr
 // quantizer folded into the GEMV's own prologue (one token; every CTA quantizes the row for itself).
 enum ActivationSource { SRC_CODES = 0, SRC_WITH_MAX = 1, SRC_RMSNORM = 2 };
 
-enum Epilogue { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_ACC = 3, EPI_ARGMAX = 4 };
+enum Epilogue { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_ACC = 3, EPI_ARGMAX = 4, EPI_PUSH = 5 };
+
+// EPI_PUSH (tensor parallel, row-split projections in decode): the partial output is not written locally but sent to
+// every rank as 8-byte packets {float32 bits of the bf16 value, tag}; a packet is one store, so data and tag arrive
+// together and the consumer (tp_reduce) needs no fence, only to see the tag of the current call.
+constexpr int kTpMaxRanks = 8;
+struct PushTarget {
+    uint2 *ll[kTpMaxRanks];   // packet buffer of every rank: [2 halves][tp sources][slot packets]
+    const uint32_t *seq;      // local: [0] = number of completed calls
+    int rank, tp;
+    unsigned long long slot;  // packets per (half, source)
+};
 
 struct LinearArgs {
     const int8_t *q;
@@ -76,6 +87,7 @@ struct LinearArgs {
     int reset_words;
     int8_t *q_out;               // optional: the codes, written by the first CTA
     float *scale_out;            // optional: the scale, written by the first CTA
+    PushTarget push;             // EPI_PUSH
 };
 cudaError_t launch_linear_naive(const LinearArgs &a, cudaStream_t s);
 cudaError_t launch_gemv_dp4a(const LinearArgs &a, cudaStream_t s);   // M <= 4
@@ -118,6 +130,9 @@ cudaError_t launch_argmax_finish(const unsigned long long *partial, int blocks, 
 unsigned long long *argmax_scratch();  // per device: kArgmaxMaxBlocks x 16 candidates
 constexpr int kArgmaxMaxBlocks = 16384;  // head matrices up to 262144 output channels
 
+// consumer of EPI_PUSH packets: sum over the ranks in rank order, optional residual (tp_allreduce.cu)
+cudaError_t launch_tp_reduce(const uint2 *ll, uint32_t *seq, const void *residual, void *out, void *combined, size_t n_el, int dtype,
+                             int tp, unsigned long long slot, cudaStream_t s);
 // one-shot all-reduce over peer memory (tp_allreduce.cu)
 cudaError_t launch_tp_allreduce(const void *partial, void *out, size_t n_el, int dtype, void *const *bufs, uint32_t *const *flags,
                                 uint32_t *seq, int rank, int tp, size_t slot_el, cudaStream_t s);

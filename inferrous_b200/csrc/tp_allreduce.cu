@@ -143,7 +143,72 @@ __global__ void __launch_bounds__(kThreads) tp_allreduce_kernel(const TpDev a) {
     }
 }
 
+// Consumer of the packets a row-split projection pushed with EPI_PUSH (gemv.cu): every thread waits (bounded) for the
+// tp packets of its element to carry the tag of the current call, adds them in rank order in fp32, rounds to bf16 and
+// optionally adds the residual -- what `linear_residual` does on one GPU, with the sum over ranks in between.  No CTA
+// waits for another CTA; the last one to finish advances the call number that the next push reads.
+template <class T>
+__global__ void __launch_bounds__(kThreads) tp_reduce_kernel(const uint2 *__restrict__ ll, uint32_t *seq, const typename T::storage *residual,
+                                                             typename T::storage *out, typename T::storage *combined, size_t n_el,
+                                                             int tp, unsigned long long slot, uint32_t *status) {
+    dependency_wait();
+    const uint32_t call = *reinterpret_cast<volatile uint32_t *>(seq);
+    const uint32_t want = call + 1u;
+    const uint2 *base = ll + (size_t)(call & 1u) * tp * slot;
+    for (size_t e = (size_t)blockIdx.x * kThreads + threadIdx.x; e < n_el; e += (size_t)gridDim.x * kThreads) {
+        float sum = 0.0f;
+        bool ok = true;
+        for (int r = 0; r < tp && ok; ++r) {
+            const uint2 *p = base + (size_t)r * slot + e;
+            uint2 v;
+            unsigned long long t0 = 0;
+            uint32_t spin = 0;
+            for (;;) {
+                asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+                if (v.y == want) break;
+                if ((++spin & 255u) == 0) {
+                    const unsigned long long now = global_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > kWaitLimitNs) {
+                        if (status && atomicCAS(status, 0u, (uint32_t)WAIT_PEER) == 0u) status[1] = (uint32_t)r;
+                        ok = false;
+                        break;
+                    }
+                }
+            }
+            sum = __fadd_rn(sum, __uint_as_float(v.x));
+        }
+        if (!ok) continue;
+        const float y = bf16_rne(sum);
+        if (out) T::store(out + e, y);
+        if (combined) T::store(combined + e, bf16_rne(__fadd_rn(T::load(residual + e), y)));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const uint32_t done = atomicAdd(seq + 1, 1u) + 1u;
+        if (done == gridDim.x) {
+            seq[1] = 0;
+            __threadfence();
+            seq[0] = call + 1u;
+        }
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_tp_reduce(const uint2 *ll, uint32_t *seq, const void *residual, void *out, void *combined, size_t n_el, int dtype,
+                             int tp, unsigned long long slot, cudaStream_t s) {
+    if (!ll || !seq || tp < 1 || tp > kMaxRanks || n_el == 0 || n_el > slot || (!out && !combined) || (combined && !residual))
+        return cudaErrorInvalidValue;
+    int grid = (int)((n_el + 4 * kThreads - 1) / (4 * kThreads));
+    grid = grid < 1 ? 1 : (grid > 128 ? 128 : grid);
+    if (dtype == 0)
+        return launch_kernel(tp_reduce_kernel<Bf16>, dim3(grid), dim3(kThreads), (size_t)0, s, ll, seq, (const uint16_t *)residual,
+                             (uint16_t *)out, (uint16_t *)combined, n_el, tp, slot, device_status_ptr());
+    return launch_kernel(tp_reduce_kernel<F32>, dim3(grid), dim3(kThreads), (size_t)0, s, ll, seq, (const float *)residual, (float *)out,
+                         (float *)combined, n_el, tp, slot, device_status_ptr());
+}
 
 cudaError_t launch_tp_allreduce(const void *partial, void *out, size_t n_el, int dtype, void *const *bufs, uint32_t *const *flags,
                                 uint32_t *seq, int rank, int tp, size_t slot_el, cudaStream_t s) {

@@ -184,9 +184,16 @@ class Qwen3Runner:
     change nothing in a whole generation."""
 
     def __init__(self, weights: Qwen3Weights, unfused: bool = False, device="cuda", fold_quantizers: str = "none",
-                 prefetch_rows: int = 0, prefetch_down_at: str = "quant", prefetch_o: bool = False, group=None):
+                 prefetch_rows: int = 0, prefetch_down_at: str = "quant", prefetch_o: bool = False, group=None,
+                 fused_allreduce: bool = True):
         ops.init()
         self.group = group  # torch.distributed process group of the tensor-parallel ranks (weights.tp > 1)
+        # Tensor parallel decode: O and down with the all-reduce fused in (tp.PeerLinear) instead of NCCL + `residual`.
+        self.peer = None
+        if weights.tp > 1 and fused_allreduce and not unfused:
+            from .tp import PeerLinear
+
+            self.peer = PeerLinear(group, 16 * weights.config.hidden)
         if weights.tp > 1 and fold_quantizers != "none":
             raise ValueError("folded quantizers are a single-GPU option")
         self.prefetch_rows = prefetch_rows
@@ -269,6 +276,9 @@ class Qwen3Runner:
         parallel (O and down own a slice of the input channels): bf16 partial projection, all-reduce, then `residual`."""
         if self.w.tp == 1:
             ops.linear_residual(q, ws.scales, matrix, None, residual_in, combined, variant)
+            return
+        if self.peer is not None and ws.rows <= 16:
+            self.peer.linear_residual(q, ws.scales, matrix, None, residual_in, combined)
             return
         import torch.distributed as dist
 

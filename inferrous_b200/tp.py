@@ -140,3 +140,48 @@ def take_rows(w, w_scale, ranges):
     import numpy as np
 
     return np.concatenate([w[a:b] for a, b in ranges]), np.concatenate([w_scale[a:b] for a, b in ranges])
+
+
+class PeerLinear:
+    """Row-split projections with the all-reduce fused in (w8a8_linear_allreduce): the GEMV's epilogue sends its partial
+    output to every rank as tagged 8-byte packets over NVLink and a small consumer kernel sums them in rank order and adds
+    the residual.  Owns the packet buffer in symmetric memory ([2 halves][tp sources][slot] packets per rank) and the
+    call counter.  Decode-sized launches only (rows * output channels <= slot_packets).  Capturable in a CUDA graph."""
+
+    def __init__(self, group, slot_packets: int):
+        import ctypes as C
+
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        from . import capi
+
+        self.tp = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.slot = int(slot_packets)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.buf = symm.empty(2 * self.tp * self.slot * 2, dtype=torch.int32, device=dev)  # 8 bytes per packet
+        self.handle = symm.rendezvous(self.buf, group.group_name if hasattr(group, "group_name") else group)
+        self.buf.zero_()
+        self.seq = torch.zeros(4, dtype=torch.int32, device=dev)
+        self._peers = (C.c_void_p * self.tp)(*[int(p) for p in self.handle.buffer_ptrs])
+        self._lib = capi.load()
+        self._capi = capi
+        torch.cuda.synchronize()
+        dist.barrier(group)
+
+    def linear_residual(self, q, scale, matrix, out, residual_in, combined):
+        """combined = bf16(residual_in + bf16(sum over ranks of the partial projections)); `out` (the sum) and the
+        residual pair are both optional, at least one is required."""
+        import ctypes as C
+
+        import torch
+
+        ref = combined if combined is not None else out
+        code = 0 if ref.dtype == torch.bfloat16 else 1
+        ptr = lambda t: None if t is None else C.c_void_p(t.data_ptr())
+        st = self._lib.w8a8_linear_allreduce(ptr(q), ptr(scale), matrix.handle, q.shape[0], ptr(residual_in), ptr(out), ptr(combined),
+                                             code, self._peers, ptr(self.seq), self.rank, self.tp, self.slot,
+                                             C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        self._capi.check(st, "w8a8_linear_allreduce")

@@ -409,3 +409,39 @@ def test_linear_argmax_rejects_non_finite_rows(ops):
     y = oracle.linear(q, asc, w, ws)
     assert got[1] == 0xFFFFFFFF
     assert got[0] == np.argmax(y[0]) and got[2] == np.argmax(y[2])
+
+
+@pytest.mark.parametrize("M", [1, 3, 4, 16, 40])
+def test_fused_allreduce_with_one_rank_is_linear_residual(ops, M):
+    """w8a8_linear_allreduce with a tensor-parallel group of one: the packets go to this GPU's own buffer, the consumer sums
+    one contribution, and the result must be the single-GPU `linear_residual`, over several calls (both halves of the
+    packet buffer, tags that keep growing)."""
+    import ctypes as C
+
+    import torch
+
+    from inferrous_b200 import capi
+
+    rng = np.random.default_rng(M)
+    K, N = 512, 384
+    w, ws = synth_weights(rng, N, K)
+    mat = make_matrix(ops, w, ws)
+    slot = 64 * N
+    packets = torch.zeros(2 * slot * 2, dtype=torch.int32, device="cuda")
+    seq = torch.zeros(4, dtype=torch.int32, device="cuda")
+    peers = (C.c_void_p * 1)(packets.data_ptr())
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for call in range(5):
+        q = to_dev(rng.integers(-127, 128, (M, K), dtype=np.int8))
+        a = to_dev(rng.uniform(0.01, 0.02, M).astype(np.float32), "f32")
+        res = to_dev(oracle.bf16(rng.standard_normal((M, N)).astype(np.float32)), "bf16")
+        y_ref, c_ref = empty_act((M, N), "bf16"), empty_act((M, N), "bf16")
+        ops.linear_residual(q, a, mat, y_ref, res, c_ref)
+        y, comb = empty_act((M, N), "bf16"), empty_act((M, N), "bf16")
+        capi.check(capi.load().w8a8_linear_allreduce(q.data_ptr(), a.data_ptr(), mat.handle, M, res.data_ptr(), y.data_ptr(),
+                                                     comb.data_ptr(), 0, peers, seq.data_ptr(), 0, 1, slot, stream),
+                   "w8a8_linear_allreduce")
+        assert torch.equal(y.view(torch.int16), y_ref.view(torch.int16)), call
+        assert torch.equal(comb.view(torch.int16), c_ref.view(torch.int16)), call
+    assert int(seq[0]) == 5
+    check_status(ops)

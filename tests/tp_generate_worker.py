@@ -33,8 +33,35 @@ def main() -> None:
     steps = int(sys.argv[2])
     group = dist.group.WORLD
 
-    tokens_tp, _ = Qwen3Runner(shard, group=group).generate(prompt, steps)
+    tokens_tp, _ = Qwen3Runner(shard, group=group).generate(prompt, steps)                     # fused projection + all-reduce
     tokens_eager, _ = Qwen3Runner(shard, group=group).generate(prompt, steps, use_graph=False)
+    tokens_nccl, _ = Qwen3Runner(shard, group=group, fused_allreduce=False).generate(prompt, steps)
+
+    # the fused projection + all-reduce against projection, gathered partials and a sum in rank order, bit for bit
+    from inferrous_b200.tp import PeerLinear
+
+    fused_exact = True
+    peer = PeerLinear(group, 16 * 512)
+    gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+    w = torch.randint(-127, 128, (512, 256), dtype=torch.int8, device="cuda", generator=gen)
+    ws = (0.5 + torch.rand(512, device="cuda", generator=gen)) / 2000.0
+    mat = ops.Matrix(w, ws.float())
+    for call, rows in enumerate([1, 4, 16, 1, 3, 16, 2]):
+        q = torch.randint(-127, 128, (rows, 256), dtype=torch.int8, device="cuda", generator=gen)
+        a = 0.01 + torch.rand(rows, device="cuda", generator=gen) * 0.01
+        res = torch.randn(rows, 512, device="cuda", generator=torch.Generator(device="cuda").manual_seed(call)).to(torch.bfloat16)
+        y = torch.empty(rows, 512, dtype=torch.bfloat16, device="cuda")
+        comb = torch.empty_like(y)
+        peer.linear_residual(q, a.float(), mat, y, res, comb)
+        part = torch.empty_like(y)
+        ops.linear_quantized(q, a.float(), mat, part)
+        parts = [torch.empty_like(part) for _ in range(tp)]
+        dist.all_gather(parts, part)
+        total = torch.zeros(rows, 512, dtype=torch.float32, device="cuda")
+        for p in parts:
+            total = total + p.float()
+        expect = total.to(torch.bfloat16)
+        fused_exact &= bool(torch.equal(y, expect)) and bool(torch.equal(comb, (res.float() + expect.float()).to(torch.bfloat16)))
 
     def prompt_logits(weights, grp):
         runner = Qwen3Runner(weights, unfused=True, group=grp)
@@ -45,7 +72,8 @@ def main() -> None:
         return runner.logits[0].float().cpu().numpy()
 
     logits_tp = prompt_logits(shard, group)
-    result = {"rank": rank, "tp": tp, "tokens_tp": tokens_tp, "tokens_tp_eager": tokens_eager}
+    result = {"rank": rank, "tp": tp, "tokens_tp": tokens_tp, "tokens_tp_eager": tokens_eager, "tokens_nccl": tokens_nccl,
+              "fused_exact": fused_exact}
     if rank == 0:
         tokens_single, _ = Qwen3Runner(full).generate(prompt, steps)
         logits_single = prompt_logits(full, None)
