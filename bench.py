@@ -186,7 +186,7 @@ def run_ours(args):
     fused = None  # row-split projections with the all-reduce fused in (w8a8_linear_allreduce)
     if world > 1:
         reduce_kind = "nccl"
-        if args.fused_allreduce:
+        if args.fused_allreduce and not args.peer_allreduce:
             try:
                 from inferrous_b200.tp import PeerLinear
                 fused = PeerLinear(dist.group.WORLD, max(DECODE_M) * 4096)
@@ -694,11 +694,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-pdl", action="store_true", help="ordinary launches instead of programmatic dependent launches")
     ap.add_argument("--peer-allreduce", action="store_true",
-                    help="tensor parallel: the library's one-shot peer-memory all-reduce instead of NCCL (measured 3 us per "
-                         "call slower than NCCL at 2 and 4 GPUs, so NCCL is the default)")
-    ap.add_argument("--fused-allreduce", action="store_true",
-                    help="tensor parallel: O and down as w8a8_linear_allreduce (GEMV epilogue pushes tagged packets to every rank, "
-                         "a consumer kernel sums them) instead of projection + NCCL all-reduce")
+                    help="tensor parallel, with --nccl-allreduce: the library's stand-alone one-shot peer-memory all-reduce instead "
+                         "of NCCL (measured 3 us per call slower than NCCL at 2 and 4 GPUs)")
+    ap.add_argument("--nccl-allreduce", dest="fused_allreduce", action="store_false",
+                    help="tensor parallel: projection + NCCL all-reduce for O and down instead of w8a8_linear_allreduce (GEMV "
+                         "epilogue pushes tagged packets to every rank, a consumer kernel sums them; the default: 0.286 against "
+                         "0.319 ms per step at 2 GPUs)")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--no-extra", action="store_true", help="skip the per-shape and prefill tables")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
