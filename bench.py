@@ -315,6 +315,15 @@ def run_ours(args):
             fn()
         return g
 
+    if fused is not None:
+        # One eager step first: if a wait for another rank's packets ran out (the kernels give up after two seconds and
+        # report it), every rank falls back to NCCL together rather than timing a broken exchange.
+        step()
+        expired = torch.tensor([float(ops.device_status()[0] != 0)], device="cuda")
+        dist.all_reduce(expired, op=dist.ReduceOp.MAX)
+        if expired.item() > 0:
+            print("bench: a wait in the fused projection + all-reduce expired; using NCCL", file=sys.stderr)
+            fused, reduce_kind = None, "nccl"
     for _ in range(args.warmup):
         step()
     launch_mode = "eager"
