@@ -447,7 +447,8 @@ def run_ours(args):
                       "l2": f"weights ({sum(shard(n, K, N, tp)[0] * shard(n, K, N, tp)[1] for n, K, N in SHAPES) >> 20} MiB streamed per "
                             "pass, each matrix revisited only after all the others) exceed the 126 MB L2; no flush",
                       "bytes_per_step": step_bytes},
-           "roofline": roofline, "e2e": e2e, "gpu_launches": 2 * len(SHAPES) * len(DECODE_M) * args.steps, "clocks": clocks}
+           "roofline": roofline, "e2e": e2e, "gpu_launches": (2 * len(SHAPES) + (sum(1 for n, _, _ in SHAPES if n in ROW_SPLIT) if fused is not None else 0))
+           * len(DECODE_M) * args.steps,  # quantize + linear per projection (+ the packet consumer of a fused exchange) "clocks": clocks}
     if world == 1 and not args.no_cpu:
         out["cpu_baseline"] = cpu_baseline(torch, mats, bufs, reps=3)
     out.update(extra)
@@ -595,6 +596,17 @@ def model_generation_table(torch, hbm_peak, rank=0, world=1, group=None):
     del full
     torch.cuda.empty_cache()
     runner = Qwen3Runner(weights, group=group)
+    exchange = "single GPU"
+    if world > 1:
+        # two tokens first: if a wait for another rank's packets expired, all ranks switch to NCCL together
+        exchange = "fused into the O / down projections over peer memory"
+        runner.generate([1, 2, 3], 2, use_graph=False)
+        from inferrous_b200 import ops as _ops
+        expired = torch.tensor([float(_ops.device_status()[0] != 0)], device="cuda")
+        dist.all_reduce(expired, op=dist.ReduceOp.MAX, group=group)
+        if expired.item() > 0:
+            exchange = "NCCL all-reduce (a wait of the fused exchange expired)"
+            runner = Qwen3Runner(weights, group=group, fused_allreduce=False)
     rng = np.random.default_rng(0)
     rows = []
     published = {5: 182.3, 129: 178.2, 512: 170.5}
@@ -617,7 +629,7 @@ def model_generation_table(torch, hbm_peak, rank=0, world=1, group=None):
     del runner, weights
     torch.cuda.empty_cache()
     return {"model": "Qwen3-8B architecture, random-init W8A8 weights (body and head int8), batch 1, greedy",
-            "parallelism": f"tp{world}" if world > 1 else "single",
+            "parallelism": f"tp{world}" if world > 1 else "single", "all_reduce": exchange,
             "weight_bytes_per_token": config.weight_bytes(), "runs": rows}
 
 
