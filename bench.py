@@ -436,6 +436,8 @@ def run_ours(args):
         except (ValueError, RuntimeError) as exc:
             extra["qwen3_8b_generation"] = {"error": f"{type(exc).__name__}: {exc}"}
 
+    # quantize + linear per projection, plus the packet consumer of every fused projection + all-reduce
+    launches_per_step = (2 * len(SHAPES) + (sum(1 for n, _, _ in SHAPES if n in ROW_SPLIT) if fused is not None else 0)) * len(DECODE_M)
     out = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8xint8->int32 (bf16 in/out)",
@@ -447,8 +449,7 @@ def run_ours(args):
                       "l2": f"weights ({sum(shard(n, K, N, tp)[0] * shard(n, K, N, tp)[1] for n, K, N in SHAPES) >> 20} MiB streamed per "
                             "pass, each matrix revisited only after all the others) exceed the 126 MB L2; no flush",
                       "bytes_per_step": step_bytes},
-           "roofline": roofline, "e2e": e2e, "gpu_launches": (2 * len(SHAPES) + (sum(1 for n, _, _ in SHAPES if n in ROW_SPLIT) if fused is not None else 0))
-           * len(DECODE_M) * args.steps,  # quantize + linear per projection (+ the packet consumer of a fused exchange) "clocks": clocks}
+           "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
     if world == 1 and not args.no_cpu:
         out["cpu_baseline"] = cpu_baseline(torch, mats, bufs, reps=3)
     out.update(extra)
