@@ -190,7 +190,31 @@ def run_ours(args):
             try:
                 from inferrous_b200.tp import PeerLinear
                 fused = PeerLinear(dist.group.WORLD, max(DECODE_M) * 4096)
+                # self-check before anything is timed: fused result == projection, all-gather, sum in rank order (bit for bit)
+                gen = torch.Generator(device="cuda").manual_seed(1000 + rank)
+                cw = torch.randint(-127, 128, (4096, 512), dtype=torch.int8, device="cuda", generator=gen)
+                cmat = ops.Matrix(cw, torch.full((4096,), 1e-4, dtype=torch.float32, device="cuda"))
+                agree = torch.ones(1, device="cuda")
+                for rows in (1, 4, 16, 1):
+                    cq = torch.randint(-127, 128, (rows, 512), dtype=torch.int8, device="cuda", generator=gen)
+                    cs = torch.full((rows,), 0.01, dtype=torch.float32, device="cuda")
+                    got = torch.empty(rows, 4096, dtype=torch.bfloat16, device="cuda")
+                    fused.linear_residual(cq, cs, cmat, got, None, None)
+                    part = torch.empty_like(got)
+                    ops.linear_quantized(cq, cs, cmat, part)
+                    parts = [torch.empty_like(part) for _ in range(world)]
+                    dist.all_gather(parts, part)
+                    total = torch.zeros(rows, 4096, dtype=torch.float32, device="cuda")
+                    for p in parts:
+                        total = total + p.float()
+                    if not torch.equal(got, total.to(torch.bfloat16)):
+                        agree.zero_()
+                dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+                if agree.item() < 1.0 or ops.device_status()[0] != 0:
+                    raise RuntimeError("fused result differs from the sum of the gathered partial outputs")
+                del cmat, cw
                 reduce_kind = "fused_into_projection_over_peer_memory"
+                reduce_check = "bit-identical to projection + all-gather + sum in rank order (4 seeded calls)"
             except Exception as exc:
                 print(f"bench: fused projection + all-reduce unavailable ({exc}); using NCCL", file=sys.stderr)
                 fused = None
