@@ -186,7 +186,7 @@ def run_ours(args):
     fused = None  # row-split projections with the all-reduce fused in (w8a8_linear_allreduce)
     if world > 1:
         reduce_kind = "nccl"
-        if args.fused_allreduce and not args.peer_allreduce:
+        if args.fused_allreduce and not args.peer_allreduce and world <= args.fused_max_ranks:
             try:
                 from inferrous_b200.tp import PeerLinear
                 fused = PeerLinear(dist.group.WORLD, max(DECODE_M) * 4096)
@@ -475,7 +475,8 @@ def run_ours(args):
         # A shape the library rejects raises before any kernel or collective is queued, identically on every rank, so
         # reporting the error instead of the table cannot leave ranks waiting for one another.
         try:
-            extra["qwen3_8b_generation"] = model_generation_table(torch, hbm_peak, rank, world, dist.group.WORLD if world > 1 else None)
+            extra["qwen3_8b_generation"] = model_generation_table(torch, hbm_peak, rank, world, dist.group.WORLD if world > 1 else None,
+                                                                  fused_allreduce=fused is not None)
         except (ValueError, RuntimeError) as exc:
             extra["qwen3_8b_generation"] = {"error": f"{type(exc).__name__}: {exc}"}
 
@@ -622,7 +623,7 @@ def decode_fused_table(torch, ops, hbm_peak):
     return rows
 
 
-def model_generation_table(torch, hbm_peak, rank=0, world=1, group=None):
+def model_generation_table(torch, hbm_peak, rank=0, world=1, group=None, fused_allreduce=True):
     """Whole-model greedy generation of the Qwen3-8B architecture with random-init weights (inferrous_b200.qwen3):
     the prompt / generated lengths the reference's decode table uses (docs/qwen3-8b-w8a8/benchmarks.md:13-15: prompt
     5 / 129 / 512, 32 generated) plus the 129 + 128 run.  Host-visible time per step: control upload, graph replay,
@@ -639,9 +640,11 @@ def model_generation_table(torch, hbm_peak, rank=0, world=1, group=None):
     weights = full.shard(rank, world)
     del full
     torch.cuda.empty_cache()
-    runner = Qwen3Runner(weights, group=group)
+    runner = Qwen3Runner(weights, group=group, fused_allreduce=fused_allreduce)
     exchange = "single GPU"
-    if world > 1:
+    if world > 1 and not fused_allreduce:
+        exchange = "NCCL all-reduce"
+    elif world > 1:
         # two tokens first: if a wait for another rank's packets expired, all ranks switch to NCCL together
         exchange = "fused into the O / down projections over peer memory"
         runner.generate([1, 2, 3], 2, use_graph=False)
@@ -761,6 +764,9 @@ def main():
     ap.add_argument("--peer-allreduce", action="store_true",
                     help="tensor parallel, with --nccl-allreduce: the library's stand-alone one-shot peer-memory all-reduce instead "
                          "of NCCL (measured 3 us per call slower than NCCL at 2 and 4 GPUs)")
+    ap.add_argument("--fused-max-ranks", type=int, default=4,
+                    help="largest tensor-parallel degree that uses the fused exchange by default; it has been run on 2 GPUs (its "
+                         "symmetric-memory set-up also on 4), larger groups use NCCL unless this is raised")
     ap.add_argument("--nccl-allreduce", dest="fused_allreduce", action="store_false",
                     help="tensor parallel: projection + NCCL all-reduce for O and down instead of w8a8_linear_allreduce (GEMV "
                          "epilogue pushes tagged packets to every rank, a consumer kernel sums them; the default: 0.286 against "
