@@ -60,6 +60,14 @@ int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads
                     const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity, uint32_t *maxima,
                     void *stream);
 
+/* qwen3_attention for a few rows (rows * q_heads below the SM count: decode) with the quantizer of its output folded in:
+ * the CTA that finishes the last head of a row also writes the row's int8 codes ([rows][q_heads * 128]) and scale, with
+ * the arithmetic of w8a8_quantize, so the O projection can follow without a quantizer launch in between (the reference
+ * launches `attention` then `quantize`, src/gpu.rs:659-671 and :377-398).  Larger launches return W8A8_ERR_UNSUPPORTED. */
+int qwen3_attention_quantize(const void *q, int dtype, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
+                             const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity,
+                             int8_t *codes, float *scale, void *stream);
+
 /* Launches of 32 rows or more (prefill) run both attention products on the tensor cores (bf16 warp-level MMA, float32
  * accumulation, softmax weights carried as two bf16 parts); 0 keeps them on the CUDA-core kernel that shorter launches
  * use, for comparison.  Process-wide; default 1. */

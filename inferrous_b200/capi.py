@@ -47,6 +47,7 @@ SIGNATURES = {
     "qwen3_embedding": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "qwen3_prepare_qk": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "qwen3_attention_use_tensor_cores": (_i, [_i]),
+    "qwen3_attention_quantize": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp]),
     "qwen3_attention": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _i, _vp, _vp]),
 }
 

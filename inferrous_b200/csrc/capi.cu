@@ -173,8 +173,9 @@ int w8a8_init(int device) {
     CUDA_OK(cudaMemset(d.sk_counters, 0, (size_t)d.sms * 4 * sizeof(uint32_t)), "cudaMemset(stream-K counters)");
     CUDA_OK(cudaMalloc(&d.argmax, (size_t)kArgmaxMaxBlocks * 16 * sizeof(unsigned long long)), "cudaMalloc(argmax candidates)");
     CUDA_OK(cudaMalloc(&d.attn_scratch, kAttnScratchFloats * sizeof(float)), "cudaMalloc(attention scratch)");
-    CUDA_OK(cudaMalloc(&d.attn_counters, kAttnSplitMaxUnits * sizeof(uint32_t)), "cudaMalloc(attention counters)");
-    CUDA_OK(cudaMemset(d.attn_counters, 0, kAttnSplitMaxUnits * sizeof(uint32_t)), "cudaMemset(attention counters)");
+    // arrival counters: one per (row, head) for the key splits, then one per row for the folded quantizer
+    CUDA_OK(cudaMalloc(&d.attn_counters, 2 * kAttnSplitMaxUnits * sizeof(uint32_t)), "cudaMalloc(attention counters)");
+    CUDA_OK(cudaMemset(d.attn_counters, 0, 2 * kAttnSplitMaxUnits * sizeof(uint32_t)), "cudaMemset(attention counters)");
     CUDA_OK(init_quantize(), "init_quantize");
     CUDA_OK(init_gemv(), "init_gemv");
     CUDA_OK(init_gemm_tcgen05(), "init_gemm_tcgen05");

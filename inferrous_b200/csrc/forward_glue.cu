@@ -24,6 +24,11 @@ constexpr int kMaxContext = 4096;  // src/lib.rs:18
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// A value another SM wrote during this kernel: read it from L2.
+template <class T> __device__ __forceinline__ float load_cg(const typename T::storage *p);
+template <> __device__ __forceinline__ float load_cg<Bf16>(const uint16_t *p) { return bf16_to_f32(__ldcg(p)); }
+template <> __device__ __forceinline__ float load_cg<F32>(const float *p) { return __ldcg(p); }
+
 __device__ __forceinline__ void record_range_fault(uint32_t *status, uint32_t detail) {
     if (status && atomicCAS(status, 0u, (uint32_t)FAULT_CACHE_RANGE) == 0u) status[1] = detail;
 }
@@ -154,7 +159,8 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
                                                                  const uint32_t *__restrict__ control,
                                                                  typename T::storage *__restrict__ out, int64_t ldo, int capacity,
                                                                  uint32_t *maxima, float *scratch, uint32_t *counters,
-                                                                 uint32_t *status, int units, const PrefetchHint hint) {
+                                                                 uint32_t *status, int units, const PrefetchHint hint,
+                                                                 int8_t *__restrict__ q_out, float *__restrict__ scale_out) {
     if ((int)blockIdx.x >= units) {
         // Extra CTAs: L2 prefetch hints for weights that a later projection will stream (immutable, so no dependency
         // wait).  The hints are issued and the CTA leaves; the lines arrive while the attention CTAs work.
@@ -291,17 +297,18 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
         __syncthreads();
         if (arrived != (uint32_t)splits - 1u) return;
         __threadfence();
-        if (t >= kHeadDim) return;
-        const float *all = scratch + (size_t)unit * gridDim.y * kAttnRecord;
-        float top = -INFINITY;
-        for (int s = 0; s < splits; ++s) top = fmaxf(top, __ldcg(all + s * kAttnRecord + kHeadDim));
-        sum = 0.0f;
-        total = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float *rec = all + s * kAttnRecord;
-            const float weight = exp_approx(__fadd_rn(__ldcg(rec + kHeadDim), -top));  // 0 for an empty split
-            total = __fadd_rn(total, __fmul_rn(__ldcg(rec + kHeadDim + 1), weight));
-            sum = __fadd_rn(sum, __fmul_rn(__ldcg(rec + t), weight));
+        if (t < kHeadDim) {
+            const float *all = scratch + (size_t)unit * gridDim.y * kAttnRecord;
+            float top = -INFINITY;
+            for (int s = 0; s < splits; ++s) top = fmaxf(top, __ldcg(all + s * kAttnRecord + kHeadDim));
+            sum = 0.0f;
+            total = 0.0f;
+            for (int s = 0; s < splits; ++s) {
+                const float *rec = all + s * kAttnRecord;
+                const float weight = exp_approx(__fadd_rn(__ldcg(rec + kHeadDim), -top));  // 0 for an empty split
+                total = __fadd_rn(total, __fmul_rn(__ldcg(rec + kHeadDim + 1), weight));
+                sum = __fadd_rn(sum, __fmul_rn(__ldcg(rec + t), weight));
+            }
         }
     }
     if (t < kHeadDim) {
@@ -311,6 +318,41 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
             const uint32_t m = warp_max_u32(absmax_key(o));
             if (lane == 0) atomicMax(maxima + row, m);
         }
+    }
+    if (q_out == nullptr) return;
+
+    // Quantizer of the finished row, folded in: the head that completes a row (per-row arrival counter, zero between
+    // launches) turns the whole row into int8 codes and its scale, with the arithmetic of `quantize`
+    // (src/kernels.rs:415-452): m = max(1e-8, max|x|) ignoring NaN, s = m / 127, q = rne(clamp(x / s)).
+    __threadfence();
+    __syncthreads();
+    if (t == 0) {
+        const uint32_t before = atomicAdd(counters + kAttnSplitMaxUnits + row, 1u);
+        arrived = before;
+        if (before == (uint32_t)q_heads - 1u) counters[kAttnSplitMaxUnits + row] = 0u;
+    }
+    __syncthreads();
+    if (arrived != (uint32_t)q_heads - 1u) return;
+    __threadfence();
+    const int width = q_heads * kHeadDim;
+    const typename T::storage *finished = out + (size_t)row * ldo;
+    float m = 1e-8f;
+    for (int j = t; j < width; j += kAttnThreads) m = fmaxf(m, fabsf(load_cg<T>(finished + j)));  // fmaxf drops a NaN operand
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    if (lane == 0) reduce[warp] = m;
+    __syncthreads();
+    m = reduce[0];
+#pragma unroll
+    for (int i = 1; i < kAttnThreads / 32; ++i) m = fmaxf(m, reduce[i]);
+    const float scale = __fdiv_rn(m, 127.0f), inv = __frcp_rn(scale);
+    if (t == 0) scale_out[row] = scale;
+    int8_t *codes = q_out + (size_t)row * width;
+    for (int j = 4 * t; j < width; j += 4 * kAttnThreads) {
+        int c[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) c[i] = quant_code(load_cg<T>(finished + j + i), scale, inv);
+        store_codes<4>(codes + j, c);
     }
 }
 
@@ -774,9 +816,9 @@ int qwen3_prepare_qk(void *qkv, int dtype, int64_t ld, int rows, int q_heads, in
     return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "prepare_qk launch");
 }
 
-int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
-                    const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity, uint32_t *maxima,
-                    void *stream) {
+static int attention_impl(const void *q, int dtype, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
+                          const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity, uint32_t *maxima,
+                          int8_t *q_out, float *scale_out, void *stream) {
     REQUIRE(device_status_ptr(), W8A8_ERR_NOT_INITIALIZED);
     REQUIRE(q && k_cache && v_cache && control && out, W8A8_ERR_BAD_ARG);
     REQUIRE(dtype == W8A8_BF16 || dtype == W8A8_F32, W8A8_ERR_BAD_ARG);
@@ -789,6 +831,8 @@ int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads
     const int units = rows * q_heads;
     int splits = 1;
     if (units < sm_count() && units <= kAttnSplitMaxUnits) splits = std::min(kAttnMaxSplits, (2 * sm_count() + units - 1) / units);
+    // the folded quantizer exists in the few-row kernel only
+    REQUIRE(q_out == nullptr || (rows * q_heads < sm_count() && rows * q_heads <= kAttnSplitMaxUnits), W8A8_ERR_UNSUPPORTED);
     if (rows >= kMmaMinRows && (ldq % 2) == 0 && (ldo % 2) == 0 && aligned(q, 8) && aligned(out, 8) && !g_attention_no_mma) {
         // prefill: tensor-core kernel, 64 rows per CTA
         const dim3 grid_mma((rows + kMmaRows - 1) / kMmaRows, q_heads);
@@ -816,11 +860,26 @@ int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads
     cudaError_t e = dtype == W8A8_BF16
                         ? launch_kernel(attention_kernel<Bf16>, grid, dim3(kAttnThreads), 0, (cudaStream_t)stream, (const uint16_t *)q, ldq,
                                         q_heads, kv_heads, k_cache, v_cache, control, (uint16_t *)out, ldo, capacity, maxima,
-                                        attention_scratch(), attention_counters(), device_status_ptr(), units, hint)
+                                        attention_scratch(), attention_counters(), device_status_ptr(), units, hint, q_out, scale_out)
                         : launch_kernel(attention_kernel<F32>, grid, dim3(kAttnThreads), 0, (cudaStream_t)stream, (const float *)q, ldq,
                                         q_heads, kv_heads, k_cache, v_cache, control, (float *)out, ldo, capacity, maxima,
-                                        attention_scratch(), attention_counters(), device_status_ptr(), units, hint);
+                                        attention_scratch(), attention_counters(), device_status_ptr(), units, hint, q_out, scale_out);
     return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "attention launch");
+}
+
+int qwen3_attention(const void *q, int dtype, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
+                    const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity, uint32_t *maxima,
+                    void *stream) {
+    return attention_impl(q, dtype, ldq, rows, q_heads, kv_heads, k_cache, v_cache, control, out, ldo, capacity, maxima, nullptr,
+                          nullptr, stream);
+}
+
+int qwen3_attention_quantize(const void *q, int dtype, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
+                             const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity,
+                             int8_t *codes, float *scale, void *stream) {
+    REQUIRE(codes && scale && (reinterpret_cast<uintptr_t>(codes) & 3u) == 0, W8A8_ERR_BAD_ARG);
+    return attention_impl(q, dtype, ldq, rows, q_heads, kv_heads, k_cache, v_cache, control, out, ldo, capacity, nullptr, codes,
+                          scale, stream);
 }
 
 int qwen3_attention_use_tensor_cores(int enabled) {

@@ -272,3 +272,13 @@ def attention(q: torch.Tensor, q_heads: int, kv_heads: int, k_cache: torch.Tenso
 def attention_use_tensor_cores(enabled: bool) -> None:
     """Many-row attention launches on the tensor cores (default) or on the CUDA-core kernel (comparison runs)."""
     capi.check(capi.load().qwen3_attention_use_tensor_cores(1 if enabled else 0), "qwen3_attention_use_tensor_cores")
+
+
+def attention_quantize(q: torch.Tensor, q_heads: int, kv_heads: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                       control: torch.Tensor, out: torch.Tensor, codes: torch.Tensor, scale: torch.Tensor) -> None:
+    """`attention` for a few rows with `quantize` of its output folded in (decode): the O projection's input codes and
+    scale come out of the attention launch itself."""
+    capi.check(capi.load().qwen3_attention_quantize(_ptr(q), _dtype_code(q), q.stride(0), q.shape[0], q_heads, kv_heads,
+                                                    _ptr(k_cache), _ptr(v_cache), _ptr(control), _ptr(out), out.stride(0),
+                                                    k_cache.shape[0], _ptr(codes), _ptr(scale), _stream()),
+               "qwen3_attention_quantize")

@@ -261,3 +261,49 @@ def test_attention_on_tensor_cores(ops, dtype, rows, position, qh, kvh):
         assert (got != cpu).mean() < 0.05
     assert np.all(np.abs(results[True] - results[False]) <= np.abs(results[False]) * 2.0 ** -7 + 5e-6)
     assert ops.device_status() == (0, 0)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+@pytest.mark.parametrize("rows,position", [(1, 0), (1, 40), (1, 700), (3, 130)])
+def test_attention_with_folded_quantizer(ops, dtype, rows, position):
+    """Few rows: the attention launch also writes the int8 codes and the scale of its output row; they must be exactly
+    what w8a8_quantize makes of that output, the output itself must be unchanged, and a second launch must agree."""
+    import torch
+
+    rng = np.random.default_rng(position + rows)
+    keys = position + rows
+    qd = to_dev(oracle.bf16(rng.standard_normal((rows, Q_HEADS * 128)).astype(np.float32)), dtype)
+    kc = to_dev(oracle.bf16(rng.standard_normal((1024, KV_HEADS, 128)).astype(np.float32)), "bf16")
+    vc = to_dev(oracle.bf16((rng.standard_normal((1024, KV_HEADS, 128)) * 3).astype(np.float32)), "bf16")
+    td = torch.bfloat16 if dtype == "bf16" else torch.float32
+    plain = torch.full((rows, Q_HEADS * 128), float("nan"), dtype=td, device="cuda")
+    ops.attention(qd, Q_HEADS, KV_HEADS, kc, vc, control(0, position), plain)
+    q_ref = torch.zeros((rows, Q_HEADS * 128), dtype=torch.int8, device="cuda")
+    s_ref = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    ops.quantize(plain, q_ref, s_ref)
+    for _ in range(2):
+        out = torch.full_like(plain, float("nan"))
+        codes = torch.full_like(q_ref, 99)
+        scale = torch.zeros_like(s_ref)
+        ops.attention_quantize(qd, Q_HEADS, KV_HEADS, kc, vc, control(0, position), out, codes, scale)
+        assert torch.equal(out.view(torch.int16 if dtype == "bf16" else torch.int32), plain.view(torch.int16 if dtype == "bf16" else torch.int32))
+        assert torch.equal(codes, q_ref)
+        assert np.array_equal(to_host(scale).view(np.uint32), to_host(s_ref).view(np.uint32))
+    eq, es = oracle.quantize(to_host(plain))
+    assert np.array_equal(to_host(q_ref), eq) and np.array_equal(to_host(s_ref).view(np.uint32), es.view(np.uint32))
+    assert ops.device_status() == (0, 0)
+
+
+def test_attention_with_folded_quantizer_refuses_many_rows(ops):
+    import torch
+
+    from inferrous_b200 import capi
+
+    rows = 8  # 8 rows x 32 heads is past the SM count: that launch takes another kernel
+    qd = torch.zeros(rows, Q_HEADS * 128, dtype=torch.bfloat16, device="cuda")
+    kc = torch.zeros(64, KV_HEADS, 128, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros_like(qd)
+    with pytest.raises(capi.W8A8Error) as e:
+        ops.attention_quantize(qd, Q_HEADS, KV_HEADS, kc, kc, control(0, 0), out, torch.zeros(rows, Q_HEADS * 128, dtype=torch.int8, device="cuda"),
+                               torch.zeros(rows, device="cuda"))
+    assert e.value.status == 3

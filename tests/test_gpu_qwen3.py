@@ -69,7 +69,8 @@ def test_fast_kernels_change_nothing_in_a_generation(prompt_len, steps, cfg):
     tokens_eager, _ = fast.generate(prompt, steps, use_graph=False)
     assert tokens_eager == tokens_plain
     assert np.array_equal(to_host(fast.decode.hidden), hidden_graph)
-    for kw in (dict(prefetch_down_at="none"), dict(prefetch_rows=64, prefetch_down_at="qwm", prefetch_o=True)):
+    for kw in (dict(prefetch_down_at="none"), dict(prefetch_rows=64, prefetch_down_at="qwm", prefetch_o=True),
+               dict(fold_attention_quantizer=True)):
         other = Qwen3Runner(weights, **kw)  # L2 prefetch hints on other launches, or none at all
         assert other.generate(prompt, steps)[0] == tokens_plain
     for fold in ("with_max", "all"):  # quantizers inside the projection kernels
