@@ -68,6 +68,43 @@ int qwen3_attention_quantize(const void *q, int dtype, int64_t ldq, int rows, in
                              const uint16_t *v_cache, const uint32_t *control, void *out, int64_t ldo, int capacity,
                              int8_t *codes, float *scale, void *stream);
 
+/* ---- batched decode: one new token for each of `rows` independent sequences ------------------------------------------
+ * The reference serves one request at a time (GpuModel::generate, src/gpu.rs:818-929; batching is deferred,
+ * docs/plans/production.md:87), so these three have no launcher of their own there: they run the arithmetic of
+ * `prepare_qk` (src/kernels.rs:1350-1443) and `attention` (src/kernels.rs:1490-1658) once per row, each row against its
+ * own sequence.  Row r is the newest token of sequence r: it sits at absolute position positions[r] (a device array the
+ * host uploads before the step, like `control`), and sequence r's caches start `cache_stride` elements after sequence
+ * r - 1's ([sequences][capacity][kv_heads][128] bf16 when dense).  A position beyond `capacity` skips the access and
+ * records code 6 in the device status word. */
+
+/* qwen3_prepare_qk for a batch of sequences: the rotary row and the cache slot of row r are those of positions[r]. */
+int qwen3_prepare_qk_batched(void *qkv, int dtype, int64_t ld, int rows, int q_heads, int kv_heads, const float *q_gain,
+                             const float *k_gain, const float *rope_table, const uint32_t *positions, uint16_t *k_cache,
+                             uint16_t *v_cache, int capacity, int64_t cache_stride, void *stream);
+
+/* out[r, h, :] = bf16(softmax(q[r, h, :] . K_r[0 .. positions[r], h / (q_heads / kv_heads), :] * 128^-0.5) . V_r[...]) with
+ * K_r, V_r the caches of sequence r.  One CTA serves the query heads that share a key/value head, and the keys of a row
+ * are split over up to 16 CTAs as a function of positions[r] alone, so a sequence gives the same bits whether it is
+ * decoded alone or inside a batch.  `workspace` (16-byte aligned, at least qwen3_attention_batched_workspace() bytes,
+ * zero before the first call; the kernel leaves its counters at zero) holds the partial results of the splits; calls
+ * that share a workspace must not overlap on the GPU.  `maxima` as in qwen3_attention. */
+size_t qwen3_attention_batched_workspace(int rows, int q_heads, int kv_heads);
+int qwen3_attention_batched(const void *q, int dtype, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
+                            const uint16_t *v_cache, int64_t cache_stride, const uint32_t *positions, void *out, int64_t ldo,
+                            int capacity, uint32_t *maxima, void *workspace, size_t workspace_size, void *stream);
+
+/* `select_token` (src/kernels.rs:2191-2231; launched at src/gpu.rs:811) on stored logits [rows, n] (row stride ld):
+ * token[r] = index of the largest value, the lowest index among equals, 0xffffffff if any logit of the row is not
+ * finite.  `value` (optional) receives the winning logit. */
+int qwen3_select_token(const void *logits, int dtype, int rows, int n, int64_t ld, uint32_t *token, float *value, void *stream);
+
+/* Vocabulary split over `parts` ranks (no counterpart in the reference, which is single-GPU): candidates is
+ * [parts][2][rows] = per part, `rows` tokens within the part and then the float32 bits of their logits (the `token` and
+ * `value` outputs of w8a8_linear_argmax or qwen3_select_token side by side), gathered from the ranks in rank order;
+ * token[r] = part * part_width + local token of the largest value (the lowest part among equals, i.e. the lowest token
+ * id), or 0xffffffff if any part reported 0xffffffff or a non-finite value. */
+int qwen3_merge_candidates(const uint32_t *candidates, int parts, int rows, int part_width, uint32_t *token, void *stream);
+
 /* Launches of 32 rows or more (prefill) run both attention products on the tensor cores (bf16 warp-level MMA, float32
  * accumulation, softmax weights carried as two bf16 parts); 0 keeps them on the CUDA-core kernel that shorter launches
  * use, for comparison.  Process-wide; default 1. */

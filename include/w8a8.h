@@ -89,8 +89,16 @@ int w8a8_prefetch_hint(const void *weights, size_t bytes);
  * the stream drains, and its own griddepcontrol.wait orders the data.  Captured into a CUDA graph the
  * launches become programmatic edges.  Process-wide switch; set it before capturing. */
 int w8a8_set_programmatic_launch(int enabled);
-/* Reads (and clears) the device-side status word of the current device: 0, or
- * W8A8_ERR_DEVICE_TIMEOUT with *detail = code of the wait that gave up.  Synchronises `stream`. */
+/* Reads (and clears) the device-side status words of the current device: 0, or
+ * W8A8_ERR_DEVICE_TIMEOUT with *detail = code of the wait that gave up (code << 24 | low bits of its argument).
+ * Synchronises `stream`.  It covers both the status word w8a8_init() allocated and the one inside the fixed array of
+ * w8a8_linear_no_alloc, so it also works on a device where only that entry point has run.  Scratch that launches
+ * share and leave at zero (stream-K partial tiles and arrival counters of w8a8_linear for 9..128 tokens, the
+ * key-split counters of qwen3_attention) may be left dirty by a launch whose wait ran out; when this call finds
+ * such a code it returns that scratch to zero in stream order, so that the launches which follow are right again.
+ * Until then results on that device are undefined: after a device timeout, call this before anything else.
+ * That scratch is per device, not per stream: launches of w8a8_linear (9..128 tokens), w8a8_linear_argmax and
+ * qwen3_attention on different streams of one device must not overlap on the GPU. */
 int w8a8_device_status(void *stream, uint32_t *detail);
 
 /* ---- weights ------------------------------------------------------------------------ */
@@ -197,9 +205,13 @@ int w8a8_quantize_linear_gate_up_swiglu(const void *x, int dtype, int source, co
  * There is no counterpart in the reference; it is an addition of this library.
  * Limits: M <= 16 tokens (W8A8_ERR_UNSUPPORTED beyond, with the reason in w8a8_last_cuda_error()),
  * plain epilogue only.  The first call on a device resolves the array's address and raises the
- * kernel's shared-memory limit; make that first call before any stream capture.  Every call clears
- * the array in stream order and then uses it, so two calls that overlap on the GPU (different
- * streams, or a captured graph replayed concurrently with itself) race on it: keep them in order. */
+ * kernel's shared-memory limit (host threads may race for that first call; it is done under a lock);
+ * make that first call before any stream capture.  Every call clears the array's partial tiles and
+ * counters in stream order and then uses them, so two calls that overlap on the GPU (different
+ * streams, or a captured graph replayed concurrently with itself) race on it: keep them in order.
+ * A bounded device-side wait that runs out leaves y undefined and its code in two status words of
+ * the same array, which calls do NOT clear: w8a8_device_status reports and clears them (it needs no
+ * w8a8_init for that). */
 int w8a8_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w, const float *w_scale, int M, int N,
                          int K, void *y, int dtype, void *stream);
 

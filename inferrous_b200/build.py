@@ -17,7 +17,7 @@ CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB = LIB_DIR / "libw8a8.so"
 OBJ_DIR = PKG / "lib" / "obj"
-SOURCES = ["capi.cu", "quantize.cu", "naive.cu", "gemv.cu", "gemv_rows.cu", "gemm_tcgen05.cu", "gemm_tcgen05_wide.cu", "gemm_tcgen05_pair.cu", "gemm_skinny.cu", "tp_allreduce.cu", "forward_glue.cu"]
+SOURCES = ["capi.cu", "quantize.cu", "naive.cu", "gemv.cu", "gemv_rows.cu", "gemm_tcgen05.cu", "gemm_tcgen05_wide.cu", "gemm_tcgen05_pair.cu", "gemm_skinny.cu", "tp_allreduce.cu", "forward_glue.cu", "batched_decode.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -43,7 +43,7 @@ def _stale(target: Path, deps) -> bool:
 
 
 def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
-    headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "w8a8.h", Path(__file__)]
+    headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "w8a8.h", PKG.parent / "include" / "qwen3_glue.h", Path(__file__)]
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
     cc = nvcc()
     jobs = []

@@ -46,6 +46,11 @@ SIGNATURES = {
     # include/qwen3_glue.h
     "qwen3_embedding": (_i, [_vp, _vp, _i, _i, _i, _vp, _i, _vp]),
     "qwen3_prepare_qk": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "qwen3_prepare_qk_batched": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _vp]),
+    "qwen3_attention_batched_workspace": (_sz, [_i, _i, _i]),
+    "qwen3_attention_batched": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _i64, _vp, _vp, _i64, _i, _vp, _vp, _sz, _vp]),
+    "qwen3_select_token": (_i, [_vp, _i, _i, _i, _i64, _vp, _vp, _vp]),
+    "qwen3_merge_candidates": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "qwen3_attention_use_tensor_cores": (_i, [_i]),
     "qwen3_attention_quantize": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp]),
     "qwen3_attention": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _i, _vp, _vp]),

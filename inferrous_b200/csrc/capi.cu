@@ -89,6 +89,18 @@ uint32_t *skinny_counters() {
     int dev = current_ready_device();
     return dev < 0 ? nullptr : g_dev[dev].sk_counters;
 }
+// After an abandoned launch (a bounded wait ran out) the scratch that every launch is meant to leave at zero may hold
+// partial sums or arrival counts: return it to zero, in stream order, so that later launches are right again.
+void reset_shared_scratch(cudaStream_t s) {
+    int dev = current_ready_device();
+    if (dev < 0) return;
+    DeviceState &d = g_dev[dev];
+    cudaMemsetAsync(d.sk_scratch, 0, (size_t)d.sms * kSkinnySlotInts * sizeof(int32_t), s);
+    cudaMemsetAsync(d.sk_counters, 0, (size_t)d.sms * 4 * sizeof(uint32_t), s);
+    cudaMemsetAsync(d.attn_counters, 0, 2 * kAttnSplitMaxUnits * sizeof(uint32_t), s);
+    cudaStreamSynchronize(s);
+}
+
 cudaError_t read_device_status(cudaStream_t s, uint32_t out[2]) {
     uint32_t *p = device_status_ptr();
     if (!p) return cudaErrorInitializationError;
@@ -189,9 +201,22 @@ int w8a8_init(int device) {
 }
 
 int w8a8_device_status(void *stream, uint32_t *detail) {
-    REQUIRE(current_ready_device() >= 0, W8A8_ERR_NOT_INITIALIZED);
+    // Two places record an expired wait: the status word w8a8_init() allocated, and the one inside the fixed array of
+    // w8a8_linear_no_alloc (which may be the only one: that entry point needs no w8a8_init).
+    uint32_t fixed[2] = {0, 0};
+    bool fixed_present = false;
+    CUDA_OK(read_no_alloc_status((cudaStream_t)stream, fixed, &fixed_present), "read_no_alloc_status");
+    const bool ready = current_ready_device() >= 0;
+    REQUIRE(ready || fixed_present, W8A8_ERR_NOT_INITIALIZED);
     uint32_t words[2] = {0, 0};
-    CUDA_OK(read_device_status((cudaStream_t)stream, words), "read_device_status");
+    if (ready) {
+        CUDA_OK(read_device_status((cudaStream_t)stream, words), "read_device_status");
+        if (words[0]) reset_shared_scratch((cudaStream_t)stream);
+    }
+    if (!words[0]) {
+        words[0] = fixed[0];
+        words[1] = fixed[1];
+    }
     if (detail) *detail = words[0] ? ((words[0] << 24) | (words[1] & 0xffffffu)) : 0;
     return words[0] ? W8A8_ERR_DEVICE_TIMEOUT : W8A8_OK;
 }

@@ -67,7 +67,8 @@ __global__ void __launch_bounds__(128) prepare_qk_kernel(typename T::storage *__
                                                          int kv_heads, const float *__restrict__ q_gain,
                                                          const float *__restrict__ k_gain, const float *__restrict__ table,
                                                          const uint32_t *__restrict__ control, uint16_t *__restrict__ k_cache,
-                                                         uint16_t *__restrict__ v_cache, int capacity, uint32_t *status) {
+                                                         uint16_t *__restrict__ v_cache, int capacity, uint32_t *status,
+                                                         const uint32_t *__restrict__ positions, int64_t cache_stride) {
     const int lane = threadIdx.x & 31;
     const int unit = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int per_row = q_heads + kv_heads;
@@ -76,10 +77,16 @@ __global__ void __launch_bounds__(128) prepare_qk_kernel(typename T::storage *__
     const bool is_q = h < q_heads;
     // Position, gains and the rotary row do not depend on the preceding kernel (see the note on `control` in the
     // header): they are fetched before the dependency wait.
-    const uint32_t pos = control[1] + (uint32_t)row;
+    // One sequence (positions == nullptr): row r sits at position control[1] + r of the one cache.  Batched decode: row r is
+    // the newest token of sequence r, at positions[r] of that sequence's cache (cache_stride elements further on per row).
+    const uint32_t pos = positions ? positions[row] : control[1] + (uint32_t)row;
     if (pos >= (uint32_t)capacity) {
         if (lane == 0) record_range_fault(status, pos);
         return;
+    }
+    if (positions) {
+        k_cache += (size_t)row * cache_stride;
+        v_cache += (size_t)row * cache_stride;
     }
     const float *gain = is_q ? q_gain : k_gain;
     const float *trow = table + (size_t)pos * kHeadDim;
@@ -796,11 +803,11 @@ int qwen3_embedding(const uint32_t *ids, const uint16_t *table, int rows, int hi
     return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "embedding launch");
 }
 
-int qwen3_prepare_qk(void *qkv, int dtype, int64_t ld, int rows, int q_heads, int kv_heads, const float *q_gain,
-                     const float *k_gain, const float *rope_table, const uint32_t *control, uint16_t *k_cache, uint16_t *v_cache,
-                     int capacity, void *stream) {
+static int prepare_qk_impl(void *qkv, int dtype, int64_t ld, int rows, int q_heads, int kv_heads, const float *q_gain,
+                           const float *k_gain, const float *rope_table, const uint32_t *control, const uint32_t *positions,
+                           int64_t cache_stride, uint16_t *k_cache, uint16_t *v_cache, int capacity, void *stream) {
     REQUIRE(device_status_ptr(), W8A8_ERR_NOT_INITIALIZED);
-    REQUIRE(qkv && q_gain && k_gain && rope_table && control && k_cache && v_cache, W8A8_ERR_BAD_ARG);
+    REQUIRE(qkv && q_gain && k_gain && rope_table && (control || positions) && k_cache && v_cache, W8A8_ERR_BAD_ARG);
     REQUIRE(dtype == W8A8_BF16 || dtype == W8A8_F32, W8A8_ERR_BAD_ARG);
     REQUIRE(rows >= 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0, W8A8_ERR_BAD_ARG);
     REQUIRE(capacity > 0 && capacity <= kMaxContext && ld >= (int64_t)(q_heads + 2 * kv_heads) * kHeadDim, W8A8_ERR_BAD_ARG);
@@ -810,10 +817,28 @@ int qwen3_prepare_qk(void *qkv, int dtype, int64_t ld, int rows, int q_heads, in
     cudaError_t e =
         dtype == W8A8_BF16
             ? launch_kernel(prepare_qk_kernel<Bf16>, grid, dim3(128), 0, (cudaStream_t)stream, (uint16_t *)qkv, ld, rows, q_heads,
-                            kv_heads, q_gain, k_gain, rope_table, control, k_cache, v_cache, capacity, device_status_ptr())
+                            kv_heads, q_gain, k_gain, rope_table, control, k_cache, v_cache, capacity, device_status_ptr(), positions,
+                            cache_stride)
             : launch_kernel(prepare_qk_kernel<F32>, grid, dim3(128), 0, (cudaStream_t)stream, (float *)qkv, ld, rows, q_heads,
-                            kv_heads, q_gain, k_gain, rope_table, control, k_cache, v_cache, capacity, device_status_ptr());
+                            kv_heads, q_gain, k_gain, rope_table, control, k_cache, v_cache, capacity, device_status_ptr(), positions,
+                            cache_stride);
     return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "prepare_qk launch");
+}
+
+int qwen3_prepare_qk(void *qkv, int dtype, int64_t ld, int rows, int q_heads, int kv_heads, const float *q_gain,
+                     const float *k_gain, const float *rope_table, const uint32_t *control, uint16_t *k_cache, uint16_t *v_cache,
+                     int capacity, void *stream) {
+    REQUIRE(control, W8A8_ERR_BAD_ARG);
+    return prepare_qk_impl(qkv, dtype, ld, rows, q_heads, kv_heads, q_gain, k_gain, rope_table, control, nullptr, 0, k_cache, v_cache,
+                           capacity, stream);
+}
+
+int qwen3_prepare_qk_batched(void *qkv, int dtype, int64_t ld, int rows, int q_heads, int kv_heads, const float *q_gain,
+                             const float *k_gain, const float *rope_table, const uint32_t *positions, uint16_t *k_cache,
+                             uint16_t *v_cache, int capacity, int64_t cache_stride, void *stream) {
+    REQUIRE(positions && cache_stride >= (int64_t)capacity * kv_heads * kHeadDim, W8A8_ERR_BAD_ARG);
+    return prepare_qk_impl(qkv, dtype, ld, rows, q_heads, kv_heads, q_gain, k_gain, rope_table, nullptr, positions, cache_stride, k_cache,
+                           v_cache, capacity, stream);
 }
 
 static int attention_impl(const void *q, int dtype, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,

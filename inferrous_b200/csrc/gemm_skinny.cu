@@ -23,6 +23,8 @@
 #include "internal.h"
 #include "ptx.cuh"
 
+#include <mutex>
+
 namespace w8a8 {
 namespace {
 
@@ -300,6 +302,16 @@ template <class T, int EPI> cudaError_t set_attr() {
     return cudaFuncSetAttribute(gemm_skinny_kernel<T, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048);
 }
 
+// K blocks per stage and ring depth: the widest stage (4, 2 or 1 blocks of 128 bytes, wider stages keep DRAM pages
+// open) that divides K and still leaves a ring of at least three stages in shared memory.
+bool pick_stages(int K, int ntok, int &kps, int &stages) {
+    kps = 4;
+    while (kps > 1 && ((K / BLOCK_K) % kps != 0 || (kSmemBudget - 1024) / (kps * (A_BYTES + ntok * BLOCK_K)) < 3)) kps /= 2;
+    stages = (kSmemBudget - 1024) / (kps * (A_BYTES + ntok * BLOCK_K));
+    if (stages > 16) stages = 16;
+    return stages >= 2;
+}
+
 }  // namespace
 
 cudaError_t init_gemm_skinny() {
@@ -322,15 +334,9 @@ cudaError_t launch_gemm_skinny(const LinearArgs &l, const w8a8_weight *wt, cudaS
     if (e != cudaSuccess) return e;
     SkinnyDev d{};
     d.a_scale = l.a_scale; d.w_scale = wt->w_scale; d.M = l.M; d.N = wt->N; d.K = l.K; d.ntok = ntok;
-    int kps = 4;
-    while (kps > 1 && ((l.K / BLOCK_K) % kps != 0 || (kSmemBudget - 1024) / (kps * (A_BYTES + ntok * BLOCK_K)) < 3)) kps /= 2;
-    if (kps < 1) kps = 1;
-    d.kps = kps;
+    if (!pick_stages(l.K, ntok, d.kps, d.stages)) return cudaErrorInvalidValue;
+    const int kps = d.kps, stages = d.stages;
     const int stage_bytes = kps * (A_BYTES + ntok * BLOCK_K);
-    int stages = (kSmemBudget - 1024) / stage_bytes;
-    if (stages > 16) stages = 16;
-    if (stages < 2) return cudaErrorInvalidValue;
-    d.stages = stages;
     d.y = l.out[0]; d.residual = l.residual; d.combined = l.combined; d.acc = l.acc;
     d.scratch = skinny_scratch(); d.counters = skinny_counters(); d.status = device_status_ptr();
     const long long units = (long long)((wt->N + TILE_N - 1) / TILE_N) * (l.K / (BLOCK_K * kps));
@@ -349,7 +355,8 @@ constexpr int kStaticMaxTokens = 16;   // token limit of the allocation-free ent
 constexpr int kStaticSlots = 160;      // CTAs (one scratch tile each); the grid is capped to this
 constexpr size_t kStaticTileInts = (size_t)kStaticSlots * 4 * kStaticMaxTokens * 32;
 constexpr size_t kStaticCounterInts = (size_t)kStaticSlots * 4;
-constexpr size_t kStaticInts = kStaticTileInts + kStaticCounterInts + 2 /* status words */ + 62 /* pad */;
+constexpr size_t kStaticClearInts = kStaticTileInts + kStaticCounterInts;  // what every call returns to zero
+constexpr size_t kStaticInts = kStaticClearInts + 2 /* status words */ + 62 /* pad */;
 
 // 1.25 MiB, resident on every GPU that loads the library until the process exits.
 // In host code this name is only a stand-in for the symbol: the device address comes from
@@ -362,10 +369,12 @@ struct StaticState {
     int sms = 0;
 };
 StaticState g_static[64];
+std::mutex g_static_mu;  // two host threads may make their first call on a device at the same time
 
 // Once per device, with that device current: resolve the array's device address and raise the
 // kernels' shared-memory limit.  Neither call allocates.
 cudaError_t static_setup(int dev) {
+    std::lock_guard<std::mutex> lock(g_static_mu);
     StaticState &st = g_static[dev];
     if (st.ready) return cudaSuccess;
     void *ptr = nullptr;
@@ -403,20 +412,18 @@ cudaError_t launch_linear_no_alloc(const int8_t *q, const float *a_scale, const 
 
     SkinnyDev d{};
     d.a_scale = a_scale; d.w_scale = w_scale; d.M = M; d.N = N; d.K = K; d.ntok = ntok;
-    int kps = 4;
-    while (kps > 1 && (K / BLOCK_K) % kps != 0) kps /= 2;
-    d.kps = kps;
+    if (!pick_stages(K, ntok, d.kps, d.stages)) return cudaErrorInvalidValue;  // the same rule as the regular launcher
+    const int kps = d.kps, stages = d.stages;
     const int stage_bytes = kps * (A_BYTES + ntok * BLOCK_K);
-    int stages = (kSmemBudget - 1024) / stage_bytes;
-    if (stages > 16) stages = 16;
-    d.stages = stages;
     d.y = y;
     d.scratch = st.base;
     d.counters = reinterpret_cast<uint32_t *>(st.base + kStaticTileInts);
     d.status = reinterpret_cast<uint32_t *>(st.base + kStaticTileInts + kStaticCounterInts);
     // The array keeps whatever the previous call left (normally zeros, but not after an abandoned
-    // launch): partial tiles, counters and status must start at zero, so clear them in stream order.
-    if ((e = cudaMemsetAsync(st.base, 0, kStaticInts * sizeof(int32_t), s)) != cudaSuccess) return e;
+    // launch): partial tiles and counters must start at zero, so clear them in stream order.  The
+    // status words behind them are NOT cleared here: a wait that ran out stays on record until
+    // w8a8_device_status reads it.
+    if ((e = cudaMemsetAsync(st.base, 0, kStaticClearInts * sizeof(int32_t), s)) != cudaSuccess) return e;
 
     const long long units = (long long)((N + TILE_N - 1) / TILE_N) * (K / (BLOCK_K * kps));
     int grid = st.sms < kStaticSlots ? st.sms : kStaticSlots;
@@ -427,6 +434,28 @@ cudaError_t launch_linear_no_alloc(const int8_t *q, const float *a_scale, const 
     else
         gemm_skinny_kernel<F32, EPI_PLAIN, kStaticMaxTokens><<<grid, kThreads, smem, s>>>(map_w, map_q, d);
     return cudaGetLastError();
+}
+
+// The status words of the allocation-free entry point on the current device, read and cleared in stream order
+// (no allocation: the copy lands in the caller's host words).  *present = false when that entry point has never
+// run on the device.
+cudaError_t read_no_alloc_status(cudaStream_t s, uint32_t out[2], bool *present) {
+    *present = false;
+    out[0] = out[1] = 0;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaSuccess;
+    int32_t *words = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_mu);
+        if (!g_static[dev].ready) return cudaSuccess;
+        words = g_static[dev].base + kStaticClearInts;
+    }
+    *present = true;
+    if ((e = cudaMemcpyAsync(out, words, 8, cudaMemcpyDeviceToHost, s)) != cudaSuccess) return e;
+    if ((e = cudaMemsetAsync(words, 0, 8, s)) != cudaSuccess) return e;
+    return cudaStreamSynchronize(s);
 }
 
 }  // namespace w8a8

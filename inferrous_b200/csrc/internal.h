@@ -116,6 +116,8 @@ constexpr int kNoAllocMaxTokens = 16;
 // Allocation-free projection: stream-K scratch in a fixed device array of the library (gemm_skinny.cu).
 cudaError_t launch_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w, const float *w_scale, int M, int N,
                                    int K, void *y, int dtype, cudaStream_t s);
+// Status words of that entry point (an expired wait), read and cleared; *present = it has run on the current device.
+cudaError_t read_no_alloc_status(cudaStream_t s, uint32_t out[2], bool *present);
 constexpr size_t kSkinnySlotInts = 4 * (size_t)kSkinnyMaxTokens * 32;  // one 128-channel tile: [quarter][token][32]
 cudaError_t init_gemv();
 cudaError_t init_quantize();

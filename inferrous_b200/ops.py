@@ -282,3 +282,47 @@ def attention_quantize(q: torch.Tensor, q_heads: int, kv_heads: int, k_cache: to
                                                     _ptr(k_cache), _ptr(v_cache), _ptr(control), _ptr(out), out.stride(0),
                                                     k_cache.shape[0], _ptr(codes), _ptr(scale), _stream()),
                "qwen3_attention_quantize")
+
+
+# ---- batched decode: one new token for each of `rows` independent sequences --------------------------------
+
+def prepare_qk_batched(qkv: torch.Tensor, q_heads: int, kv_heads: int, q_gain: torch.Tensor, k_gain: torch.Tensor,
+                       rope_table: torch.Tensor, positions: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
+    """`prepare_qk` (src/kernels.rs:1350-1443) per sequence: row r of `qkv` is the newest token of sequence r, at
+    position positions[r]; the caches are [sequences, capacity, kv_heads, 128] bf16."""
+    assert k_cache.dim() == 4 and k_cache.shape[0] >= qkv.shape[0] and k_cache.stride() == v_cache.stride()
+    capi.check(capi.load().qwen3_prepare_qk_batched(_ptr(qkv), _dtype_code(qkv), qkv.stride(0), qkv.shape[0], q_heads, kv_heads,
+                                                    _ptr(q_gain), _ptr(k_gain), _ptr(rope_table), _ptr(positions), _ptr(k_cache),
+                                                    _ptr(v_cache), k_cache.shape[1], k_cache.stride(0), _stream()),
+               "qwen3_prepare_qk_batched")
+
+
+def attention_batched_workspace(rows: int, q_heads: int, kv_heads: int, device="cuda") -> torch.Tensor:
+    """Zeroed scratch for attention_batched (partial results of the key splits and their arrival counters)."""
+    nbytes = capi.load().qwen3_attention_batched_workspace(rows, q_heads, kv_heads)
+    return torch.zeros((nbytes + 3) // 4, dtype=torch.int32, device=device)
+
+
+def attention_batched(q: torch.Tensor, q_heads: int, kv_heads: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      positions: torch.Tensor, out: torch.Tensor, workspace: torch.Tensor, maxima: torch.Tensor | None = None) -> None:
+    """`attention` (src/kernels.rs:1490-1658) per sequence: row r attends to keys 0 .. positions[r] of sequence r's cache."""
+    assert k_cache.dim() == 4 and k_cache.shape[0] >= q.shape[0] and k_cache.stride() == v_cache.stride()
+    capi.check(capi.load().qwen3_attention_batched(_ptr(q), _dtype_code(q), q.stride(0), q.shape[0], q_heads, kv_heads, _ptr(k_cache),
+                                                   _ptr(v_cache), k_cache.stride(0), _ptr(positions), _ptr(out), out.stride(0),
+                                                   k_cache.shape[1], _ptr(maxima), _ptr(workspace),
+                                                   workspace.numel() * workspace.element_size(), _stream()), "qwen3_attention_batched")
+
+
+def select_token(logits: torch.Tensor, token: torch.Tensor, value: torch.Tensor | None = None) -> None:
+    """Kernel `select_token` (src/kernels.rs:2191-2231; src/gpu.rs:811) per row of stored logits."""
+    rows, n = logits.shape
+    capi.check(capi.load().qwen3_select_token(_ptr(logits), _dtype_code(logits), rows, n, logits.stride(0), _ptr(token), _ptr(value),
+                                              _stream()), "qwen3_select_token")
+
+
+def merge_candidates(candidates: torch.Tensor, part_width: int, token: torch.Tensor) -> None:
+    """Vocabulary-split head: candidates [parts, 2, rows] = per part the tokens within the part, then the bits of their
+    logits -> global token per row."""
+    parts, _, rows = candidates.shape
+    capi.check(capi.load().qwen3_merge_candidates(_ptr(candidates), parts, rows, part_width, _ptr(token), _stream()),
+               "qwen3_merge_candidates")

@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import dataclasses
 import math
+import os
 
 import torch
 
@@ -170,6 +171,19 @@ class Workspace:
         self.partial = torch.empty(rows, config.hidden, dtype=act, device=device)  # tensor parallel: O / down partial sums
         self.logits = None  # only the unfused path writes logits
 
+    def first_rows(self, rows: int) -> "Workspace":
+        """The same buffers cut down to their first `rows` rows (a shorter prompt in a workspace sized for the longest)."""
+        if rows > self.rows:
+            raise ValueError(f"workspace holds {self.rows} rows, {rows} asked for")
+        view = object.__new__(Workspace)
+        view.rows = rows
+        for name, value in vars(self).items():
+            if name == "rows":
+                continue
+            cut = isinstance(value, torch.Tensor) and name != "decode_maxima"
+            setattr(view, name, value[:rows] if cut else value)
+        return view
+
 
 class Qwen3Runner:
     """GpuModel: owns the caches, the decode workspace, the control buffer and the captured decode graph.
@@ -185,8 +199,11 @@ class Qwen3Runner:
 
     def __init__(self, weights: Qwen3Weights, unfused: bool = False, device="cuda", fold_quantizers: str = "none",
                  prefetch_rows: int = 0, prefetch_down_at: str = "quant", prefetch_o: bool = False, group=None,
-                 fused_allreduce: bool = True, fold_attention_quantizer: bool = False):
+                 fused_allreduce: bool = True, fold_attention_quantizer: bool = False, batch: int = 1):
         ops.init()
+        if batch < 1:
+            raise ValueError("batch must be at least 1")
+        self.batch = batch  # sequences decoded side by side (generate_batch); 1 = the reference's single request
         self.group = group  # torch.distributed process group of the tensor-parallel ranks (weights.tp > 1)
         # decode: attention also writes the O projection's input codes (qwen3_attention_quantize).  Off: measured 2.69 ms per
         # token against 2.47 with the separate quantizer launch, whose latency programmatic launch already hides.
@@ -196,7 +213,7 @@ class Qwen3Runner:
         if weights.tp > 1 and fused_allreduce and not unfused:
             from .tp import PeerLinear
 
-            self.peer = PeerLinear(group, 16 * weights.config.hidden)
+            self.peer = PeerLinear(group, max(16, min(batch, self.PEER_MAX_ROWS)) * weights.config.hidden)
         if weights.tp > 1 and fold_quantizers != "none":
             raise ValueError("folded quantizers are a single-GPU option")
         self.prefetch_rows = prefetch_rows
@@ -208,8 +225,11 @@ class Qwen3Runner:
         self.unfused = unfused
         self.device = device
         c = self.c
-        self.k_cache = [torch.zeros(c.context, c.kv_heads, 128, dtype=torch.bfloat16, device=device) for _ in range(c.layers)]
-        self.v_cache = [torch.zeros(c.context, c.kv_heads, 128, dtype=torch.bfloat16, device=device) for _ in range(c.layers)]
+        # [sequence][position][kv head][128] per layer; k_cache / v_cache are sequence 0's caches (the single request)
+        self.k_cache_all = [torch.zeros(batch, c.context, c.kv_heads, 128, dtype=torch.bfloat16, device=device) for _ in range(c.layers)]
+        self.v_cache_all = [torch.zeros(batch, c.context, c.kv_heads, 128, dtype=torch.bfloat16, device=device) for _ in range(c.layers)]
+        self.k_cache = [cache[0] for cache in self.k_cache_all]
+        self.v_cache = [cache[0] for cache in self.v_cache_all]
         self.control = torch.zeros(2, dtype=torch.int32, device=device)   # {token, position}
         self.next = torch.zeros(1, dtype=torch.int32, device=device)
         self.decode = Workspace(c, 1, device, wide_gate_up=unfused)
@@ -223,23 +243,60 @@ class Qwen3Runner:
         self.graph = None
         self._host_control = torch.zeros(2, dtype=torch.int32).pin_memory()
         self._host_next = torch.zeros(1, dtype=torch.int32).pin_memory()
+        # batched decode: one row per sequence
+        self.batch_graph = None
+        self.batch_ws = None
+        if batch > 1 or os.environ.get("W8A8_BATCH_BUFFERS"):
+            self._make_batch_buffers()
+
+    PEER_MAX_ROWS = 64  # w8a8_linear_allreduce takes decode-sized launches only
+
+    def _make_batch_buffers(self) -> None:
+        c, w, device, rows = self.c, self.w, self.device, self.batch
+        self.batch_ws = Workspace(c, rows, device, wide_gate_up=self.unfused or rows > 4)
+        self.batch_state = torch.zeros(2, rows, dtype=torch.int32, device=device)   # {token, position} per sequence
+        self.tokens, self.positions = self.batch_state[0], self.batch_state[1]
+        self.next_tokens = torch.zeros(rows, dtype=torch.int32, device=device)
+        self.attention_ws = ops.attention_batched_workspace(rows, c.q_heads, c.kv_heads, device)
+        self.batch_head_q = torch.empty(rows, c.hidden, dtype=torch.int8, device=device)
+        self.batch_head_scale = torch.empty(rows, dtype=torch.float32, device=device)
+        stored = self.unfused or rows > 16  # the fused head + selection kernel takes at most 16 rows
+        self.batch_logits = torch.empty(rows, w.head.n, dtype=torch.bfloat16, device=device) if stored else None
+        if w.tp > 1:
+            self.batch_best = torch.zeros(2, rows, dtype=torch.int32, device=device)        # local {tokens, value bits}
+            self.batch_all_best = torch.zeros(w.tp, 2, rows, dtype=torch.int32, device=device)
+        self._host_state = torch.zeros(2, rows, dtype=torch.int32).pin_memory()
+        self._host_next_tokens = torch.zeros(rows, dtype=torch.int32).pin_memory()
 
     # -- one forward pass: queues kernels only ------------------------------------------------------------
-    def forward(self, ws: Workspace, ids: torch.Tensor) -> None:
+    def forward(self, ws: Workspace, ids: torch.Tensor, slot: int = 0, batched: bool = False) -> None:
+        """One pass over `ws.rows` rows.  batched=False: the rows are consecutive tokens of the sequence in cache `slot`,
+        the first at position control[1] (prefill, or one decode step of the single request).  batched=True: row r is the
+        newest token of sequence r at position positions[r] (one decode step of every sequence; `ids` is self.tokens)."""
         c, w = self.c, self.w
         variant = capi.VARIANT_NAIVE if self.unfused else capi.VARIANT_AUTO
         rows = ws.rows
         q4, qo = ws.quant4, ws.quant_o
         inter = c.intermediate
+        single = rows == 1 and not batched  # the reference's decode step: hints and folded quantizers apply
         ops.embedding(ids, w.embedding, ws.hidden)
-        if rows == 1 and self.fold_quantizers != "none" and not self.unfused:
+        if single and self.fold_quantizers != "none" and not self.unfused:
             self._decode_layers(ws)
             return self._head(ws)
         for index, layer in enumerate(w.layers):
+            k_cache, v_cache = self.k_cache_all[index][slot], self.v_cache_all[index][slot]
             ops.norm_quantize(ws.hidden, layer.norm1, None, q4, ws.scales, ws.maxima, c.eps)
             ops.linear_quantized(q4, ws.scales, layer.qkv, ws.qkv, variant)
-            ops.prepare_qk(ws.qkv, c.q_heads, c.kv_heads, layer.qnorm, layer.knorm, w.rope, self.control,
-                           self.k_cache[index], self.v_cache[index])
+            if batched:
+                ops.prepare_qk_batched(ws.qkv, c.q_heads, c.kv_heads, layer.qnorm, layer.knorm, w.rope, self.positions,
+                                       self.k_cache_all[index], self.v_cache_all[index])
+                ops.attention_batched(ws.qkv, c.q_heads, c.kv_heads, self.k_cache_all[index], self.v_cache_all[index],
+                                      self.positions, ws.attention, self.attention_ws)
+                ops.quantize(ws.attention, qo, ws.scales)
+                self._project_residual(ws, qo, layer.o, ws.hidden, ws.residual, variant)
+                self._mlp(ws, layer, variant, single)
+                continue
+            ops.prepare_qk(ws.qkv, c.q_heads, c.kv_heads, layer.qnorm, layer.knorm, w.rope, self.control, k_cache, v_cache)
             if rows == 1 and self.prefetch_rows and not self.unfused:
                 # Decode: the attention launch also pulls the last rows of gate and up towards L2; the gate/up kernel's
                 # first wave of CTAs fetches the leading rows by itself before its dependency wait.
@@ -253,31 +310,40 @@ class Qwen3Runner:
             if rows == 1 and self.fold_attention_quantizer and not self.unfused:
                 if self.prefetch_down_at == "quant":  # the quantizer launch is gone: the hint rides on the attention launch
                     ops.prefetch_hint(layer.down.w)
-                ops.attention_quantize(ws.qkv, c.q_heads, c.kv_heads, self.k_cache[index], self.v_cache[index], self.control,
-                                       ws.attention, qo, ws.scales)
+                ops.attention_quantize(ws.qkv, c.q_heads, c.kv_heads, k_cache, v_cache, self.control, ws.attention, qo, ws.scales)
             else:
-                ops.attention(ws.qkv, c.q_heads, c.kv_heads, self.k_cache[index], self.v_cache[index], self.control, ws.attention)
+                ops.attention(ws.qkv, c.q_heads, c.kv_heads, k_cache, v_cache, self.control, ws.attention)
                 if rows == 1 and self.prefetch_down_at == "quant" and not self.unfused:
                     ops.prefetch_hint(layer.down.w)
                 ops.quantize(ws.attention, qo, ws.scales)
             self._project_residual(ws, qo, layer.o, ws.hidden, ws.residual, variant)
             if rows == 1 and self.prefetch_down_at == "norm2" and not self.unfused:
                 ops.prefetch_hint(layer.down.w)
-            ops.norm_quantize(ws.residual, layer.norm2, None, q4, ws.scales, ws.maxima, c.eps)
-            if self.unfused:
-                ops.linear_quantized(q4, ws.scales, layer.gate_up, ws.gate_up, variant)
-                ops.swiglu(ws.gate_up[:, :inter], ws.gate_up[:, inter:], ws.act, None)
-                ops.quantize(ws.act, ws.quant12, ws.scales)
-            elif rows == 1:
-                ops.linear_swiglu(q4, ws.scales, layer.gate, layer.up, None, None, ws.act, ws.maxima)
-                if self.prefetch_down_at == "qwm":
-                    ops.prefetch_hint(layer.down.w)
-                ops.quantize_with_max(ws.act, ws.maxima, ws.quant12, ws.scales)
-            else:
-                ops.linear_quantized(q4, ws.scales, layer.gate_up, ws.gate_up, variant)
-                ops.swiglu_quantize(ws.gate_up[:, :inter], ws.gate_up[:, inter:], ws.quant12, ws.scales)
-            self._project_residual(ws, ws.quant12, layer.down, ws.residual, ws.hidden, variant)
-        self._head(ws)
+            self._mlp(ws, layer, variant, single)
+        if batched:
+            self._head_rows(ws)
+        else:
+            self._head(ws)
+
+    def _mlp(self, ws: Workspace, layer: Layer, variant: int, single: bool) -> None:
+        """norm_quantize -> gate / up projections -> SwiGLU -> quantize -> down projection + residual."""
+        c = self.c
+        rows, inter, q4 = ws.rows, c.intermediate, ws.quant4
+        ops.norm_quantize(ws.residual, layer.norm2, None, q4, ws.scales, ws.maxima, c.eps)
+        if self.unfused:
+            ops.linear_quantized(q4, ws.scales, layer.gate_up, ws.gate_up, variant)
+            ops.swiglu(ws.gate_up[:, :inter], ws.gate_up[:, inter:], ws.act, None)
+            ops.quantize(ws.act, ws.quant12, ws.scales)
+        elif rows == 1 or (rows <= 4 and ws.gate_up is None):
+            # few rows: gate and up share every activation load and the SwiGLU is the projection's epilogue
+            ops.linear_swiglu(q4, ws.scales, layer.gate, layer.up, None, None, ws.act, ws.maxima)
+            if single and self.prefetch_down_at == "qwm":
+                ops.prefetch_hint(layer.down.w)
+            ops.quantize_with_max(ws.act, ws.maxima, ws.quant12, ws.scales)
+        else:
+            ops.linear_quantized(q4, ws.scales, layer.gate_up, ws.gate_up, variant)
+            ops.swiglu_quantize(ws.gate_up[:, :inter], ws.gate_up[:, inter:], ws.quant12, ws.scales)
+        self._project_residual(ws, ws.quant12, layer.down, ws.residual, ws.hidden, variant)
 
     def _project_residual(self, ws: Workspace, q: torch.Tensor, matrix, residual_in: torch.Tensor, combined: torch.Tensor,
                           variant: int) -> None:
@@ -286,7 +352,7 @@ class Qwen3Runner:
         if self.w.tp == 1:
             ops.linear_residual(q, ws.scales, matrix, None, residual_in, combined, variant)
             return
-        if self.peer is not None and ws.rows <= 16:
+        if self.peer is not None and ws.rows * matrix.n <= self.peer.slot and ws.rows <= self.PEER_MAX_ROWS:
             self.peer.linear_residual(q, ws.scales, matrix, None, residual_in, combined)
             return
         import torch.distributed as dist
@@ -341,11 +407,29 @@ class Qwen3Runner:
             return
         ops.linear_argmax(self.head_q, self.head_scale, w.head, self.local_best[0:1], self.local_best[1:2].view(torch.float32))
         dist.all_gather_into_tensor(self.all_best.view(-1), self.local_best, group=self.group)
-        tokens, values = self.all_best[:, 0], self.all_best[:, 1].view(torch.float32)
-        # device-side selection (no host synchronisation: this runs inside the captured step)
-        rank_of_best = values.argmax().reshape(1)  # first maximal value: the lowest rank, hence the lowest token id among equals
-        best = tokens.index_select(0, rank_of_best) + rank_of_best.to(torch.int32) * w.head.n
-        self.next.copy_(torch.where((tokens < 0).any().reshape(1), torch.full_like(best, -1), best))
+        # device-side selection over the ranks' candidates (no host synchronisation: this runs inside the captured step)
+        ops.merge_candidates(self.all_best.view(w.tp, 2, 1), w.head.n, self.next)
+
+    def _head_rows(self, ws: Workspace) -> None:
+        """Final norm, head projection and greedy selection for every row (batched decode): next_tokens[r]."""
+        c, w = self.c, self.w
+        rows = ws.rows
+        variant = capi.VARIANT_NAIVE if self.unfused else capi.VARIANT_AUTO
+        ops.norm_quantize(ws.hidden, w.final_gain, None, self.batch_head_q, self.batch_head_scale, None, c.eps)
+        if w.tp == 1:
+            token, value = self.next_tokens, None
+        else:
+            token, value = self.batch_best[0], self.batch_best[1].view(torch.float32)
+        if self.batch_logits is None:
+            ops.linear_argmax(self.batch_head_q, self.batch_head_scale, w.head, token, value)
+        else:  # more rows than the fused kernel takes: store this rank's logits, then `select_token` per row
+            ops.linear_quantized(self.batch_head_q, self.batch_head_scale, w.head, self.batch_logits, variant)
+            ops.select_token(self.batch_logits, token, value)
+        if w.tp > 1:
+            import torch.distributed as dist
+
+            dist.all_gather_into_tensor(self.batch_all_best.view(-1), self.batch_best.view(-1), group=self.group)
+            ops.merge_candidates(self.batch_all_best, w.head.n, self.next_tokens)
 
     def _select_unfused(self) -> int:
         """select_token (src/kernels.rs:2191-2231) on the written logits: largest value, lowest index."""
@@ -369,6 +453,78 @@ class Qwen3Runner:
             self.forward(self.decode, self.control)
         torch.cuda.current_stream().wait_stream(stream)
         ops.set_programmatic_launch(False)
+
+    def capture_batch_decode(self) -> None:
+        """One decode step of every sequence, captured once: what changes between steps lives in `batch_state`
+        ({token, position} per sequence) and the caches."""
+        ops.set_programmatic_launch(True)
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            self.batch_state.zero_()
+            self.forward(self.batch_ws, self.tokens, batched=True)  # warm-up outside the capture
+        stream.synchronize()
+        self.batch_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.batch_graph, stream=stream):
+            self.forward(self.batch_ws, self.tokens, batched=True)
+        torch.cuda.current_stream().wait_stream(stream)
+        ops.set_programmatic_launch(False)
+
+    def generate_batch(self, prompts, max_tokens: int, use_graph: bool = True):
+        """Greedy generation for `batch` independent sequences side by side: each prompt is prefilled on its own into its
+        sequence's caches (the reference's first step, src/gpu.rs:893-901, once per sequence), then every decode step
+        advances all sequences by one token in ONE pass of `batch` rows -- the sequences may have any mix of context
+        lengths.  Returns (one token list per sequence, seconds per step; the first entry is the whole prefill phase)."""
+        import time
+
+        c = self.c
+        if self.batch_ws is None:
+            self._make_batch_buffers()
+        if len(prompts) != self.batch:
+            raise ValueError(f"this runner decodes {self.batch} sequences side by side, {len(prompts)} prompts given")
+        for prompt in prompts:
+            if not prompt or len(prompt) + max_tokens > c.context:
+                raise ValueError("every prompt must be non-empty and prompt + max_tokens must fit the context")
+        if use_graph and not self.unfused and self.batch_graph is None:
+            self.capture_batch_decode()
+        torch.cuda.synchronize()
+        start = time.perf_counter()
+        longest = Workspace(c, max(len(p) for p in prompts), self.device)
+        ids = torch.empty(longest.rows, dtype=torch.int32, device=self.device)
+        generated = []
+        for slot, prompt in enumerate(prompts):
+            self._host_control[0] = 0
+            self._host_control[1] = 0
+            self.control.copy_(self._host_control, non_blocking=True)
+            ids[:len(prompt)].copy_(torch.tensor(list(prompt), dtype=torch.int32), non_blocking=False)
+            self.forward(longest.first_rows(len(prompt)), ids[:len(prompt)], slot=slot)
+            token = self._read_next()
+            if token == 0xFFFFFFFF:
+                raise RuntimeError("nonfinite or empty logits")
+            generated.append([token])
+        del longest
+        seconds = [time.perf_counter() - start]
+        positions = [len(p) for p in prompts]
+        for _ in range(1, max_tokens):
+            start = time.perf_counter()
+            for r in range(self.batch):
+                self._host_state[0, r] = generated[r][-1]
+                self._host_state[1, r] = positions[r]
+            self.batch_state.copy_(self._host_state, non_blocking=True)
+            if self.batch_graph is not None and use_graph and not self.unfused:
+                self.batch_graph.replay()
+            else:
+                self.forward(self.batch_ws, self.tokens, batched=True)
+            self._host_next_tokens.copy_(self.next_tokens, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            seconds.append(time.perf_counter() - start)
+            for r in range(self.batch):
+                token = int(self._host_next_tokens[r]) & 0xFFFFFFFF
+                if token == 0xFFFFFFFF:
+                    raise RuntimeError("nonfinite or empty logits")
+                generated[r].append(token)
+                positions[r] += 1
+        return generated, seconds
 
     def _read_next(self) -> int:
         if self.unfused:

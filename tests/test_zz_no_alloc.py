@@ -78,3 +78,28 @@ def test_no_alloc_rejects_what_its_fixed_scratch_cannot_hold():
     assert st == 3
     assert b"16 tokens" in lib.w8a8_last_cuda_error()
     assert lib.w8a8_linear_no_alloc(None, a.data_ptr(), w.data_ptr(), ws.data_ptr(), 1, 128, 128, y.data_ptr(), 0, None) == 1
+
+
+@pytest.mark.parametrize("M,K,N", [
+    (3, 4096, 200),    # a partial last tile of 128 channels
+    (16, 4096, 64),    # fewer channels than one tile
+    (7, 128, 384),     # one K block: one block per stage, no tile is split
+    (2, 384, 1000),    # three K blocks: one block per stage
+    (1, 12288, 4096),  # one token, the longest K of the model
+    (9, 512, 128),     # a single tile whose four K blocks make one unit: one CTA, nothing split
+])
+def test_no_alloc_small_and_ragged_shapes(M, K, N):
+    """Partial tiles, every stage width, one token, split and unsplit tiles: bit for bit the one-thread-per-output kernel.
+    Afterwards no wait is on record: w8a8_device_status also reads the status words inside the fixed array."""
+    from inferrous_b200 import capi, ops
+
+    q, w, asc, ws = make_case(M * 1000 + N, M, K, N)
+    qd, ad, wd, wsd = to_dev(q), to_dev(asc, "f32"), to_dev(w), to_dev(ws, "f32")
+    for _ in range(2):
+        y = empty_act((M, N), "bf16")
+        ops.linear_no_alloc(qd, ad, wd, wsd, y)
+        ops.init()
+        ref = empty_act((M, N), "bf16")
+        ops.linear_quantized(qd, ad, ops.Matrix(wd, wsd), ref, capi.VARIANT_NAIVE)
+        assert np.array_equal(bits(to_host(y)), bits(to_host(ref)))
+    assert ops.device_status() == (0, 0)
