@@ -42,12 +42,12 @@ WORKLOAD = "configs[1]: quantize+linear over 5 Qwen3-8B projections x M in {1,4,
 # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, per kernel family, from the ncu captures
 # summarised under profiles/ (captured on the 50 MB and 100 MB projections; traffic grows with the weight bytes, so
 # the ratio is applied to the bench's average algorithmic bytes per launch).
-NCU_TRAFFIC_RATIO = {"gemv_mma": 1.025, "gemv_dp4a": 1.035, "gemm_skinny": 1.003, "gemv_rows": 1.03}
+NCU_TRAFFIC_RATIO = {"gemv_mma": 1.025, "gemv_dp4a": 1.035, "gemm_skinny": 1.003}
 
 
 def kernel_family(M, weight_bytes, K, forced=0):
     """Which kernel w8a8_linear picks (mirrors pick_variant in inferrous_b200/csrc/capi.cu)."""
-    names = {1: "naive_linear", 2: "gemv_dp4a", 3: "gemv_mma", 4: "gemm_tcgen05", 5: "gemm_skinny", 6: "gemv_rows", 7: "gemm_tcgen05_wide", 8: "gemm_tcgen05_pair"}
+    names = {1: "naive_linear", 2: "gemv_dp4a", 3: "gemv_mma", 4: "gemm_tcgen05", 5: "gemm_skinny", 8: "gemm_tcgen05_pair"}
     if forced:
         return names[forced]
     if M <= 1:
@@ -74,6 +74,28 @@ def quant_bytes(M, K):
 def shard(name, K, N, tp):
     from inferrous_b200.tp import shard_shape
     return shard_shape(name, K, N, tp)
+
+
+def workload_config(tp):
+    """The `config` object of the JSON line: the workload only, identical for both arms (`--impl ours` / `reference`).
+    How an arm executes it (launch mode, collective) is reported under `execution`."""
+    per_rank = sum(shard(n, K, N, tp)[0] * shard(n, K, N, tp)[1] for n, K, N in SHAPES)
+    step_bytes = sum(linear_bytes(M, *shard(n, K, N, tp)) + quant_bytes(M, shard(n, K, N, tp)[0]) for M in DECODE_M for n, K, N in SHAPES)
+    l2_bytes = 126 << 20
+    if per_rank >= 2 * l2_bytes:
+        l2 = (f"weights ({per_rank >> 20} MiB streamed per pass and rank, each matrix revisited only after all the others) "
+              "exceed the 126 MB L2; no flush")
+    else:
+        l2 = (f"weights per rank ({per_rank >> 20} MiB per pass) do not exceed twice the 126 MB L2: the pass rotates over "
+              f"{weight_copies(tp)} copies of every matrix, so that more than twice the L2 is streamed between two visits of a copy; no flush")
+    return {"workload": WORKLOAD, "shapes": {n: [K, N] for n, K, N in SHAPES}, "M": DECODE_M,
+            "parallelism": f"tp{tp}" if tp > 1 else "single", "l2": l2, "bytes_per_step": step_bytes}
+
+
+def weight_copies(tp):
+    """Distinct copies of every weight matrix that a rank rotates over, so that its passes stream from HBM, not from L2."""
+    per_rank = sum(shard(n, K, N, tp)[0] * shard(n, K, N, tp)[1] for n, K, N in SHAPES)
+    return max(1, -(-2 * (126 << 20) // per_rank))
 
 
 def measured_peaks():
@@ -673,11 +695,99 @@ def model_generation_table(torch, hbm_peak, rank=0, world=1, group=None, fused_a
                      "weight_GB/s": round(config.weight_bytes() / median / 1e9, 1),
                      "frac_hbm": round(config.weight_bytes() / median / 1e9 / (hbm_peak * world), 3),
                      "reference_tok_s_rtx_pro_6000": published.get(prompt_len) if generated == 32 else None})
-    del runner, weights
+    del runner
     torch.cuda.empty_cache()
-    return {"model": "Qwen3-8B architecture, random-init W8A8 weights (body and head int8), batch 1, greedy",
-            "parallelism": f"tp{world}" if world > 1 else "single", "all_reduce": exchange,
-            "weight_bytes_per_token": config.weight_bytes(), "runs": rows}
+    table = {"model": "Qwen3-8B architecture, random-init W8A8 weights (body and head int8), batch 1, greedy",
+             "parallelism": f"tp{world}" if world > 1 else "single", "all_reduce": exchange,
+             "weight_bytes_per_token": config.weight_bytes(), "runs": rows}
+    try:
+        table["config4"] = config4_table(torch, weights, config, hbm_peak, rank, world, group,
+                                         fused_allreduce and not exchange.startswith("NCCL"))
+    except (ValueError, RuntimeError) as exc:
+        table["config4"] = {"error": f"{type(exc).__name__}: {exc}"}
+    del weights
+    torch.cuda.empty_cache()
+    return table
+
+
+def config4_table(torch, weights, config, hbm_peak, rank, world, group, fused_allreduce, sequences=64, timed_steps=16):
+    """BASELINE.json configs[4] on the whole model: (i) ragged decode of 64 concurrent sequences whose context lengths are
+    drawn uniformly from [128, 4096] (seeded), every step advancing all of them by one token in one pass of 64 rows;
+    (ii) one 4096-token prefill.  Prompts are uniform-random token ids; every sequence is really prefilled into its own
+    KV cache first.  Host-visible time per decode step (state upload, graph replay, read-back of the 64 tokens), the
+    slowest rank's.  Bytes per decode step: the int8 weights once, plus every visible key and value once."""
+    import numpy as np
+    import torch.distributed as dist
+
+    from inferrous_b200.qwen3 import Qwen3Runner, Workspace
+
+    full = weights.full_config
+    rng = np.random.default_rng(4)
+    warm = 3
+    total_steps = warm + timed_steps
+    contexts = [int(n) for n in rng.integers(128, 4097, sequences)]
+    # a sequence must be able to grow by the decode steps that are timed: the longest contexts start that many tokens short
+    prompt_lens = [min(n, full.context - total_steps - 1) for n in contexts]
+    prompts = [[int(t) for t in rng.integers(0, full.vocab, n)] for n in prompt_lens]
+    runner = Qwen3Runner(weights, group=group, fused_allreduce=fused_allreduce, batch=sequences)
+    runner.generate_batch(prompts, 2)  # captures the step graph; also the first check of the exchange at 64 rows
+    if world > 1 and fused_allreduce:
+        from inferrous_b200 import ops as _ops
+        expired = torch.tensor([float(_ops.device_status()[0] != 0)], device="cuda")
+        dist.all_reduce(expired, op=dist.ReduceOp.MAX, group=group)
+        if expired.item() > 0:
+            fused_allreduce = False
+            runner = Qwen3Runner(weights, group=group, fused_allreduce=False, batch=sequences)
+    tokens, seconds = runner.generate_batch(prompts, 1 + total_steps)
+    if world > 1:
+        slowest = torch.tensor(seconds, dtype=torch.float64, device="cuda")
+        dist.all_reduce(slowest, op=dist.ReduceOp.MAX, group=group)
+        seconds = slowest.tolist()
+    decode = seconds[1 + warm:]
+    median = float(np.median(decode))
+    # keys visible to step s of the timed region: prompt + warm + s + 1 per sequence (the new token's own key included)
+    mid = warm + timed_steps // 2
+    kv_bytes = sum(p + mid + 1 for p in prompt_lens) * full.layers * 2 * full.kv_heads * 128 * 2
+    step_bytes = full.weight_bytes() + kv_bytes
+    ragged = {"sequences": sequences, "context_min": min(contexts), "context_max": max(contexts),
+              "context_mean": round(sum(contexts) / sequences, 1), "prefill_all_sequences_s": round(seconds[0], 3),
+              "timed_steps": timed_steps, "decode_ms_per_step_median": round(median * 1e3, 4),
+              "tok_s": round(sequences * len(decode) / sum(decode), 1),
+              "bytes_per_step": step_bytes, "kv_bytes_per_step": kv_bytes,
+              "GB/s": round(step_bytes / median / 1e9, 1), "frac_hbm": round(step_bytes / median / 1e9 / (hbm_peak * world), 3),
+              "distinct_first_tokens": len({t[0] for t in tokens})}
+    del runner
+    torch.cuda.empty_cache()
+
+    # (ii) one prefill of 4096 tokens, every position of the context
+    runner = Qwen3Runner(weights, group=group, fused_allreduce=fused_allreduce)
+    ws = Workspace(weights.config, full.context)
+    ids = torch.tensor([int(t) for t in rng.integers(0, full.vocab, full.context)], dtype=torch.int32, device="cuda")
+    times = []
+    for _ in range(4):
+        runner.control.zero_()
+        if world > 1:
+            dist.barrier(group)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        runner.forward(ws, ids)
+        token = runner._read_next()
+        times.append(time.perf_counter() - t0)
+    if world > 1:
+        slowest = torch.tensor(times, dtype=torch.float64, device="cuda")
+        dist.all_reduce(slowest, op=dist.ReduceOp.MAX, group=group)
+        times = slowest.tolist()
+    best = float(np.median(times[1:]))
+    ops_total = 2.0 * full.context * (full.weight_bytes() - full.vocab * full.hidden) + 2.0 * full.vocab * full.hidden
+    prefill = {"tokens": full.context, "ms": round(best * 1e3, 3), "tok_s": round(full.context / best, 1),
+               "projection_TOPS": round(ops_total / best / 1e12, 1), "first_token": token,
+               "all_reduce": "single GPU" if world == 1 else "NCCL all-reduce + residual kernel (4096 rows)"}
+    del runner, ws
+    torch.cuda.empty_cache()
+    return {"workload": "configs[4]: 64 ragged sequences decoded side by side; one 4096-token prefill",
+            "parallelism": f"tp{world}" if world > 1 else "single",
+            "all_reduce": ("fused into the O / down projections over peer memory" if fused_allreduce else "NCCL all-reduce") if world > 1 else "single GPU",
+            "ragged_decode": ragged, "prefill_4096": prefill}
 
 
 def cpu_step(oracle, host, threads):

@@ -54,8 +54,7 @@ typedef enum {
     W8A8_VARIANT_GEMV_MMA = 3,   /* M <= 64: 16-byte weight streaming + warp-level int8 MMA */
     W8A8_VARIANT_GEMM_TCGEN05 = 4, /* any M: TMA-staged 128x256 tiles + tcgen05.mma kind::i8 into TMEM */
     W8A8_VARIANT_GEMM_SKINNY = 5,  /* M <= 256: tcgen05 with the weights on the MMA's M side, stream-K split */
-    W8A8_VARIANT_GEMV_ROWS = 6,    /* M <= 16: whole weight rows through a bulk-copy ring + warp-level int8 MMA */
-    W8A8_VARIANT_GEMM_TCGEN05_WIDE = 7, /* any M: as GEMM_TCGEN05 with 256x256 tiles (less operand traffic per MMA) */
+    /* 6 and 7 named two kernels that lost to the others on every shape and were removed; the values stay unused */
     W8A8_VARIANT_GEMM_TCGEN05_PAIR = 8  /* any M: 256x256 tiles over CTA pairs (tcgen05.mma.cta_group::2) */
 } w8a8_variant_t;
 
@@ -153,7 +152,10 @@ int w8a8_residual(const void *a, const void *b, int dtype, size_t n, void *out, 
  *   y[m,n]   = bf16((f32(acc) * a_scale[m]) * w_scale[n])
  *   combined[m,n] = bf16(residual[m,n] + y[m,n])   when residual != NULL
  * y may be NULL when combined is requested and the un-summed projection is not needed.
- * The regime (decode GEMV / tensor-core GEMM) is chosen from M. */
+ * The regime (decode GEMV / tensor-core GEMM) is chosen from M.
+ * Operands must not share memory (docs/qwen3-8b-w8a8/safety.md:15: residual, out and combined are three distinct
+ * buffers): a byte range that y or combined shares with each other or with q, a_scale, the weights, their scales or
+ * residual is rejected with W8A8_ERR_BAD_ARG (the pair is named in w8a8_last_cuda_error()) before anything is queued. */
 int w8a8_linear(const int8_t *q, const float *a_scale, w8a8_weight_t weight, int M, const void *residual,
                 void *y, void *combined, int dtype, void *stream);
 /* Same with an explicit kernel variant (tests: every variant must equal the naive one). */

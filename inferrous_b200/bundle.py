@@ -74,6 +74,17 @@ class Bundle:
             raise BundleError(f"{name}: nonfinite float")
         return a
 
+    def weight(self, name: str, n: int, k: int):
+        """An int8 matrix and its per-channel scales as Model::load admits them (src/model.rs:143-145): symmetric
+        quantization never produces the code -128, and a scale must be positive."""
+        w = self.tensor(f"{name}.w", "|i1", (n, k))
+        if (w == -128).any():
+            raise BundleError(f"{name}.w: invalid quantized weight")
+        scale = self.tensor(f"{name}.scale", "<f4", (n,))
+        if not (scale > 0).all():
+            raise BundleError(f"{name}.scale: invalid weight scale")
+        return w, scale
+
 
 def quantize_rows(w: torch.Tensor):
     """Per-output-channel symmetric int8 (tools/prepare.py:79-81): scale = max(|row|, 1e-8) / 127, q = rne(w / scale)."""
@@ -100,9 +111,8 @@ def load_bundle(path, device="cuda", verify_hashes: bool = True) -> Qwen3Weights
               "down": (c.hidden, c.intermediate)}
 
     def matrix(layer, names):
-        ws = [dev(b.tensor(f"layer.{layer}.{n}.w", "|i1", shapes[n])) for n in names]
-        ss = [dev(b.tensor(f"layer.{layer}.{n}.scale", "<f4", (shapes[n][0],))) for n in names]
-        return torch.cat(ws).contiguous(), torch.cat(ss).contiguous()
+        pairs = [b.weight(f"layer.{layer}.{n}", *shapes[n]) for n in names]
+        return torch.cat([dev(w) for w, _ in pairs]).contiguous(), torch.cat([dev(s) for _, s in pairs]).contiguous()
 
     layers = []
     for l in range(c.layers):

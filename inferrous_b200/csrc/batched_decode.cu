@@ -10,267 +10,404 @@
 //   * one CTA serves the GH query heads that share a key/value head (grouped-query attention): every key and value
 //     line is fetched once for the group instead of once per head -- in batched decode the KV cache, not the weights,
 //     is the larger stream (64 sequences of 2 000 keys read 0.55 GB per layer against 0.19 GB of weights);
-//   * the keys of a row are split over up to 16 CTAs (one per 64 visible keys, at most 256 keys each) whose partial
-//     (maximum, total, sums) the last CTA to arrive combines, so a short and a long sequence in the same batch both
-//     spread over the GPU.  The number of splits is a function of the row's context length alone, never of the batch:
-//     a sequence decoded alone and the same sequence decoded inside a batch produce the same bits.
-// float32 sums are reassociated relative to the reference's one-thread-per-key kernel, and products are fused
-// multiply-adds (q, k, v are bf16 values, so a product is exact either way and only the additions round); the result
-// stays inside the reference's own bound for this operator (|err| <= 2e-4 + 1 % |x|, docs/qwen3-8b-w8a8/coverage.md:28).
+//   * the keys of a row are split over one CTA per 128 visible keys (up to 32) whose partial (maximum, total, sums)
+//     the last CTA to arrive combines, so a short and a long sequence in the same batch both spread over the GPU.  The
+//     number of splits is a function of the row's context length alone, never of the batch: a sequence decoded alone
+//     and the same sequence decoded inside a batch produce the same bits;
+//   * both products run on the tensor cores (warp-level bf16 MMA, float32 accumulation) with the keys, not the query
+//     rows, on the MMA's 16-row side; the kernel is bound by the stream of keys and values from HBM.
+// float32 sums are reassociated relative to the reference's one-thread-per-key kernel (q, k, v are bf16 values, so every
+// product is exact and only the additions round; the softmax weights are carried as two bf16 parts); the result stays
+// inside the reference's own bound for this operator (|err| <= 2e-4 + 1 % |x|, docs/qwen3-8b-w8a8/coverage.md:28).
+// The legacy warp-level MMA is deliberate: a tile of 32 keys x 4 heads per warp is far below tcgen05's 128-row
+// granularity, and attention is not on the W8A8 path.
 #include "../../include/qwen3_glue.h"
 #include "../../include/w8a8.h"
 #include "common.cuh"
 #include "internal.h"
+
+#include <algorithm>
 
 namespace w8a8 {
 namespace {
 
 constexpr int kHeadDim = 128;
 constexpr int kMaxContext = 4096;     // src/lib.rs:18
-constexpr int kThreads = 256;
-constexpr int kSlices = 16;           // key slices of the P.V product
-constexpr int kMaxSplits = 16;        // CTAs per (row, key/value head group)
-constexpr int kKeysPerSplit = 64;     // a split is not worth its combine step for fewer keys
-constexpr int kMaxChunk = kMaxContext / kMaxSplits;  // keys per split at the longest context: 256
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kSplitKeys = 128;       // keys per CTA: 32 per warp
+constexpr int kMaxSplits = kMaxContext / kSplitKeys;  // 32 CTAs for the longest context
+constexpr int kPitch = kHeadDim + 8;  // bf16 elements per staged row: 272 bytes, conflict-free for ldmatrix
+constexpr size_t kSmemBytes = (size_t)2 * kSplitKeys * kPitch * sizeof(uint16_t);  // keys + values: 68 KiB, three CTAs per SM
 constexpr int kRecord = kHeadDim + 4;  // floats per (row, head, split) in the workspace: 128 sums, maximum, total, padding
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void record_range_fault(uint32_t *status, uint32_t detail) {
     if (status && atomicCAS(status, 0u, (uint32_t)FAULT_CACHE_RANGE) == 0u) status[1] = detail;
 }
 
-__device__ __forceinline__ float dot16_fma(const float (&qv)[16], const uint4 a, const uint4 b) {
-    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    float s = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        s = __fmaf_rn(qv[2 * i], __uint_as_float(w[i] << 16), s);
-        s = __fmaf_rn(qv[2 * i + 1], __uint_as_float(w[i] & 0xffff0000u), s);
-    }
-    return s;
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {  // both already bf16-representable
+    return (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xffff0000u);
+}
+// The transpose of an 8 x 8 matrix of 16-bit elements held one 32-bit register per lane (row = lane / 4, two columns).
+__device__ __forceinline__ uint32_t transpose_8x8(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
 }
 
-// Key range of one split.  `chunk` keys per split: a multiple of 32, at least 64 (but for the last split), at most 256.
-struct SplitPlan {
-    int splits, chunk;
-};
-__host__ __device__ __forceinline__ SplitPlan plan_splits(int end) {
-    int splits = (end + kKeysPerSplit - 1) / kKeysPerSplit;
-    if (splits > kMaxSplits) splits = kMaxSplits;
-    const int chunk = (((end + splits - 1) / splits) + 31) & ~31;
-    SplitPlan p;
-    p.chunk = chunk;
-    p.splits = (end + chunk - 1) / chunk;  // rounding the chunk up can empty the trailing splits: they are not used
-    return p;
-}
+// A fixed number of CTAs (as many as the GPU holds at once, three per SM) of four warps each work through the launch's
+// items -- one item per (row, split of 128 keys, group of GH query heads that share a key/value head), found from the
+// rows' positions by a prefix sum that every CTA computes for itself and handed out through a ticket counter, so rows
+// with short contexts cost nothing and the launch shape never depends on the positions (a captured graph replays for any
+// of them).  Per item every warp is an independent pipeline over 32 keys:
+//   stage    its 32 key rows and 32 value rows go to shared memory with 16-byte asynchronous copies (all of them in flight
+//            at once: 64 KiB per CTA)
+//   scores   S^T = K . Q^T on mma.sync.m16n8k16 (bf16 x bf16 -> f32): the keys are the MMA's 16 rows, the GH query heads
+//            its 8 columns, so no tensor-core work is spent on absent rows; score = dot * 128^-0.5
+//   softmax  within the warp: maximum over its keys, e = exp(score - maximum) in the reference's ex2.approx form, total
+//   P.V      O^T = V^T . P^T on the same MMA: the value tile is read through ldmatrix.trans, each float32 weight enters
+//            as hi + lo, two bf16 numbers (hi = bf16(p), lo = bf16(p - hi)), moved from the accumulator layout of the
+//            first product to the operand layout of the second with movmatrix
+//   combine  (maximum, total, sums) of the four warps, then of the row's splits by the last CTA to arrive, with weights
+//            exp(m - M) -- flash decoding.  No CTA ever waits for another.
+// The association depends on nothing but the row's context length.
+constexpr int kMaxRows = 256;  // rows per launch (the prefix sum over the rows lives in shared memory); the entry point cuts larger batches
 
 template <class T, int GH>
-__global__ void __launch_bounds__(kThreads) attention_batched_kernel(const typename T::storage *__restrict__ q, int64_t ldq, int q_heads,
-                                                                     int kv_heads, const uint16_t *__restrict__ k_cache,
-                                                                     const uint16_t *__restrict__ v_cache, int64_t cache_stride,
-                                                                     const uint32_t *__restrict__ positions,
-                                                                     typename T::storage *__restrict__ out, int64_t ldo, int capacity,
-                                                                     uint32_t *maxima, float *scratch, uint32_t *counters,
-                                                                     uint32_t *status) {
-    __shared__ float scores[GH][kMaxChunk];
-    __shared__ float query[GH][kHeadDim];
-    __shared__ float reduce[kThreads / 32][GH];
-    __shared__ float partial[kSlices][GH][kHeadDim];
-    __shared__ uint32_t arrived;
-    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+__global__ void __launch_bounds__(kThreads, 3) attention_batched_kernel(const typename T::storage *__restrict__ q, int64_t ldq, int rows,
+                                                                        int q_heads, int kv_heads, const uint16_t *__restrict__ k_cache,
+                                                                        const uint16_t *__restrict__ v_cache, int64_t cache_stride,
+                                                                        const uint32_t *__restrict__ positions,
+                                                                        typename T::storage *__restrict__ out, int64_t ldo, int capacity,
+                                                                        uint32_t *maxima, float *scratch, uint32_t *counters,
+                                                                        uint32_t *tickets, uint32_t *status) {
+    extern __shared__ __align__(16) uint16_t tile_smem[];
+    typedef uint16_t (*TilePtr)[kPitch];
+    TilePtr ks = reinterpret_cast<TilePtr>(tile_smem);
+    TilePtr vs = ks + kSplitKeys;
+    __shared__ float warp_max[kWarps][8], warp_total[kWarps][8];
+    __shared__ float split_weight[8][kMaxSplits], split_den[8];
+    __shared__ int first_split[kMaxRows + 1];  // exclusive prefix sum of the rows' split counts
+    __shared__ int scan_warp[kWarps];
+    __shared__ uint32_t arrived, ticket[2];
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tq = lane & 3;
     const int group = q_heads / kv_heads, chunks = group / GH;
-    const int row = blockIdx.x / (kv_heads * chunks);
-    const int kv = (blockIdx.x / chunks) % kv_heads;
-    const int head0 = kv * group + (blockIdx.x % chunks) * GH;
-    const int split = blockIdx.y;
-    // The position was uploaded by the host before the step began, so it does not depend on the preceding kernel: the key
-    // range of this CTA is known before the dependency wait, and its cache lines are pulled towards L2 meanwhile.  The one
-    // line the preceding kernel is still writing (the newest key) is simply fetched again by the loads below.
-    const uint32_t end_u = positions[row] + 1u;
-    if (end_u > (uint32_t)capacity) {  // every split of the row takes this branch: nobody waits for anybody
-        if (t == 0 && split == 0) record_range_fault(status, end_u);
-        return;
-    }
-    const int end = (int)end_u;
-    const SplitPlan plan = plan_splits(end);
-    if (split >= plan.splits) return;
-    const int begin = split * plan.chunk, stop = min(end, begin + plan.chunk);
-    const int count = stop - begin;  // 1 .. 256
-    const size_t key_stride = (size_t)kv_heads * kHeadDim;
-    const uint16_t *kc = k_cache + (size_t)row * cache_stride + (size_t)kv * kHeadDim;
-    const uint16_t *vc = v_cache + (size_t)row * cache_stride + (size_t)kv * kHeadDim;
-    for (int i = t; i < 2 * count; i += kThreads) {  // two 128-byte lines per key and per cache
-        const size_t off = ((size_t)(begin + (i >> 1)) * key_stride) * sizeof(uint16_t) + (size_t)(i & 1) * 128;
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char *>(kc) + off));
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char *>(vc) + off));
-    }
-    dependency_wait();
-    for (int i = t; i < GH * kHeadDim; i += kThreads)
-        query[i / kHeadDim][i % kHeadDim] = T::load(q + (size_t)row * ldq + (size_t)head0 * kHeadDim + i);
-    __syncthreads();
+    const int groups = kv_heads * chunks;  // head groups per row
 
-    // scores: eight lanes per key (16 channels each), four keys per warp and sweep
-    const int sub = lane & 7, grp = lane >> 3;
-    float maximum[GH];
+    // Work list: row r has ceil((positions[r] + 1) / 128) splits (none if its position lies beyond the cache: the row is
+    // skipped and reported).  The positions were uploaded by the host before the step began, so they do not depend on the
+    // preceding kernel and all of this runs before the dependency wait.
     {
-        float qv[GH][16];
+        constexpr int kPer = kMaxRows / kThreads;  // consecutive rows per thread
+        int mine[kPer], total = 0;
 #pragma unroll
-        for (int h = 0; h < GH; ++h)
-#pragma unroll
-            for (int i = 0; i < 16; ++i) qv[h][i] = query[h][16 * sub + i];
-        const uint16_t *kbase = kc + (size_t)begin * key_stride + 16 * sub;
-#pragma unroll
-        for (int h = 0; h < GH; ++h) maximum[h] = -INFINITY;
-#pragma unroll 2
-        for (int j0 = warp * 4; j0 < count; j0 += (kThreads / 32) * 4) {
-            const int j = j0 + grp;
-            uint4 a = make_uint4(0, 0, 0, 0), b = a;
-            if (j < count) {
-                const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)j * key_stride);
-                a = kr[0];
-                b = kr[1];
-            }
-#pragma unroll
-            for (int h = 0; h < GH; ++h) {
-                float s = dot16_fma(qv[h], a, b);
-                s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 4));
-                s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 2));
-                s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
-                s = __fmul_rn(s, 0.08838834764831845f);
-                if (j < count) {
-                    maximum[h] = fmaxf(maximum[h], s);
-                    if (sub == 0) scores[h][j] = s;
+        for (int i = 0; i < kPer; ++i) {
+            const int r = t * kPer + i;
+            int n = 0;
+            if (r < rows) {
+                const uint32_t end_u = positions[r] + 1u;
+                if (end_u > (uint32_t)capacity) {
+                    if (blockIdx.x == 0) record_range_fault(status, end_u);
+                } else {
+                    n = ((int)end_u + kSplitKeys - 1) / kSplitKeys;
                 }
             }
+            mine[i] = total;
+            total += n;
         }
-    }
+        int incl = total;
 #pragma unroll
-    for (int h = 0; h < GH; ++h) {
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) maximum[h] = fmaxf(maximum[h], __shfl_xor_sync(0xffffffffu, maximum[h], d));
-        if (lane == 0) reduce[warp][h] = maximum[h];
-    }
-    __syncthreads();
-#pragma unroll
-    for (int h = 0; h < GH; ++h) {
-        maximum[h] = reduce[0][h];
-#pragma unroll
-        for (int i = 1; i < kThreads / 32; ++i) maximum[h] = fmaxf(maximum[h], reduce[i][h]);
-    }
-    __syncthreads();
-
-    // softmax numerators (the reference's ex2.approx form) and their total; a split holds at most one key per thread
-    float total[GH];
-#pragma unroll
-    for (int h = 0; h < GH; ++h) {
-        float e = 0.0f;
-        if (t < count) {
-            e = exp_approx(__fadd_rn(scores[h][t], -maximum[h]));
-            scores[h][t] = e;
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += up;
         }
+        if (lane == 31) scan_warp[warp] = incl;
+        __syncthreads();
+        int base = incl - total;
+        for (int w = 0; w < warp; ++w) base += scan_warp[w];
 #pragma unroll
-        for (int d = 16; d > 0; d >>= 1) e = __fadd_rn(e, __shfl_xor_sync(0xffffffffu, e, d));
-        if (lane == 0) reduce[warp][h] = e;
+        for (int i = 0; i < kPer; ++i) {
+            const int r = t * kPer + i;
+            if (r < rows) first_split[r] = base + mine[i];
+        }
+        if (t == kThreads - 1) first_split[rows] = base + total;  // rows beyond `rows` contributed nothing
+        __syncthreads();
     }
-    __syncthreads();
-#pragma unroll
-    for (int h = 0; h < GH; ++h) {
-        total[h] = reduce[0][h];
-#pragma unroll
-        for (int i = 1; i < kThreads / 32; ++i) total[h] = __fadd_rn(total[h], reduce[i][h]);
-    }
+    const uint32_t items = (uint32_t)first_split[rows] * (uint32_t)groups;
+    const size_t key_stride = (size_t)kv_heads * kHeadDim;
+    const int r0 = warp * 32;  // this warp's rows of the tile
+    float *mine_o = reinterpret_cast<float *>(&ks[r0][0]);  // [GH][128] partial sums, over this warp's key rows once read
 
-    // P.V, unnormalised: sixteen key slices x sixteen lanes of 8 channels
-    {
-        const int slice = t >> 4, cg = t & 15;
-        const uint16_t *vbase = vc + (size_t)begin * key_stride + 8 * cg;
-        float acc[GH][8];
-#pragma unroll
-        for (int h = 0; h < GH; ++h)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[h][i] = 0.0f;
+    // Items are handed out through a ticket counter (tickets[0]; zero between launches), so a CTA that starts late or
+    // runs on a slower SM simply takes fewer; which CTA computes an item has no influence on the result.  The counter
+    // belongs to this launch only after the preceding kernels have finished, hence after the dependency wait.  The next
+    // ticket is drawn while the current item is being worked on.
+    dependency_wait();
+    if (t == 0) ticket[0] = atomicAdd(tickets, 1u);
+    __syncthreads();
+    for (int turn = 0;; turn ^= 1) {
+        const uint32_t item = ticket[turn];
+        if (item >= items) break;
+        if (t == 0) ticket[turn ^ 1] = atomicAdd(tickets, 1u);  // read after the barrier that ends this item
+        const int js = (int)(item / (uint32_t)groups), kvg = (int)(item % (uint32_t)groups);
+        int row;
+        {  // the row whose range of splits holds js: the last r with first_split[r] <= js
+            int lo = 0, hi = rows;
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (first_split[mid] <= js) lo = mid; else hi = mid;
+            }
+            row = lo;
+        }
+        const int split = js - first_split[row];
+        const int splits = first_split[row + 1] - first_split[row];
+        const int kv = kvg / chunks, head0 = kv * group + (kvg % chunks) * GH;
+        const int end = (int)positions[row] + 1;
+        const int begin = split * kSplitKeys;
+        const int count = min(kSplitKeys, end - begin);  // 1 .. 128 keys of this item
+        const bool live = r0 < count;
+        const uint16_t *kc = k_cache + (size_t)row * cache_stride + (size_t)kv * kHeadDim;
+        const uint16_t *vc = v_cache + (size_t)row * cache_stride + (size_t)kv * kHeadDim;
+
+        // 16 chunks of 16 bytes per row and cache: a half-warp copies one row, the warp two rows per step
+        if (live) {
+            const int part = lane & 15;
+            const uint16_t *ksrc = kc + (size_t)(begin + r0 + (lane >> 4)) * key_stride + 8 * part;
+            const uint16_t *vsrc = vc + (size_t)(begin + r0 + (lane >> 4)) * key_stride + 8 * part;
 #pragma unroll 4
-        for (int j = slice; j < count; j += kSlices) {
-            const uint4 v = *reinterpret_cast<const uint4 *>(vbase + (size_t)j * key_stride);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            for (int i = 0; i < 16; ++i) {
+                const int r = r0 + 2 * i + (lane >> 4);
+                if (r < count) {
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&ks[r][8 * part])), "l"(ksrc));
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&vs[r][8 * part])), "l"(vsrc));
+                } else {  // rows past the end: zeros, so that 0 * value stays 0 in the second product
+                    *reinterpret_cast<uint4 *>(&ks[r][8 * part]) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4 *>(&vs[r][8 * part]) = make_uint4(0, 0, 0, 0);
+                }
+                ksrc += 2 * key_stride;
+                vsrc += 2 * key_stride;
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        float m_w[2] = {-INFINITY, -INFINITY}, l_w[2] = {0.0f, 0.0f};  // this lane's two heads: 2 tq and 2 tq + 1
+        if (live) {
+            // Q^T as the B operand: lane g holds head g (zeros beyond GH), 16 channels per step
+            uint32_t qf[8][2];
+            {
+                const typename T::storage *qr = q + (size_t)row * ldq + (size_t)(head0 + (g < GH ? g : 0)) * kHeadDim + 2 * tq;
 #pragma unroll
-            for (int h = 0; h < GH; ++h) {
-                const float p = scores[h][j];
+                for (int s = 0; s < 8; ++s) {
+                    qf[s][0] = g < GH ? pack_bf16(T::load(qr + 16 * s), T::load(qr + 16 * s + 1)) : 0u;
+                    qf[s][1] = g < GH ? pack_bf16(T::load(qr + 16 * s + 8), T::load(qr + 16 * s + 9)) : 0u;
+                }
+            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncwarp();
+
+            // scores of 32 keys x GH heads, transposed: sc[mt] = keys r0 + 16 mt + {g, g + 8} x heads {2 tq, 2 tq + 1}
+            float sc[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sc[mt][i] = 0.0f;
+            const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    uint32_t a[4];
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                                 : "r"(smem_addr(&ks[r0 + 16 * mt + a_row][16 * s + a_col])));
+                    mma_bf16(sc[mt], a, qf[s][0], qf[s][1]);
+                }
+            }
+            __syncwarp();  // the key rows are read: mine_o may overwrite them
+            // scale, mask, maximum over the warp's keys per head
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    acc[h][2 * i] = __fmaf_rn(p, __uint_as_float(w[i] << 16), acc[h][2 * i]);
-                    acc[h][2 * i + 1] = __fmaf_rn(p, __uint_as_float(w[i] & 0xffff0000u), acc[h][2 * i + 1]);
+                    const int key = r0 + 16 * mt + g + 8 * (i >> 1), head = 2 * tq + (i & 1);
+                    sc[mt][i] = (key < count && head < GH) ? __fmul_rn(sc[mt][i], 0.08838834764831845f) : -INFINITY;
+                    m_w[i & 1] = fmaxf(m_w[i & 1], sc[mt][i]);
+                }
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                m_w[e] = fmaxf(m_w[e], __shfl_xor_sync(0xffffffffu, m_w[e], 4));
+                m_w[e] = fmaxf(m_w[e], __shfl_xor_sync(0xffffffffu, m_w[e], 8));
+                m_w[e] = fmaxf(m_w[e], __shfl_xor_sync(0xffffffffu, m_w[e], 16));
+            }
+            // weights (hi + lo) in the operand layout of the second product, and their totals
+            uint32_t ph[2][2], pl[2][2];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                float hi[4], lo[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float base = m_w[i & 1];
+                    const float p = base == -INFINITY ? 0.0f : exp_approx(__fadd_rn(sc[mt][i], -base));  // a masked score gives 0
+                    l_w[i & 1] = __fadd_rn(l_w[i & 1], p);
+                    hi[i] = bf16_rne(p);
+                    lo[i] = bf16_rne(__fadd_rn(p, -hi[i]));
+                }
+                ph[mt][0] = transpose_8x8(pack_bf16(hi[0], hi[1]));
+                ph[mt][1] = transpose_8x8(pack_bf16(hi[2], hi[3]));
+                pl[mt][0] = transpose_8x8(pack_bf16(lo[0], lo[1]));
+                pl[mt][1] = transpose_8x8(pack_bf16(lo[2], lo[3]));
+            }
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                l_w[e] = __fadd_rn(l_w[e], __shfl_xor_sync(0xffffffffu, l_w[e], 4));
+                l_w[e] = __fadd_rn(l_w[e], __shfl_xor_sync(0xffffffffu, l_w[e], 8));
+                l_w[e] = __fadd_rn(l_w[e], __shfl_xor_sync(0xffffffffu, l_w[e], 16));
+            }
+            // O^T = V^T . P^T: eight tiles of 16 channels, two steps of 16 keys
+            float o[8][4];
+#pragma unroll
+            for (int dt = 0; dt < 8; ++dt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o[dt][i] = 0.0f;
+            const int v_row = (lane & 7) + 8 * (lane >> 4), v_col = 8 * ((lane >> 3) & 1);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+#pragma unroll
+                for (int dt = 0; dt < 8; ++dt) {
+                    uint32_t a[4];
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                                 : "r"(smem_addr(&vs[r0 + 16 * mt + v_row][16 * dt + v_col])));
+                    mma_bf16(o[dt], a, ph[mt][0], ph[mt][1]);
+                    mma_bf16(o[dt], a, pl[mt][0], pl[mt][1]);
+                }
+            }
+            // o[dt] = channels 16 dt + {g, g + 8} x heads {2 tq, 2 tq + 1}
+#pragma unroll
+            for (int dt = 0; dt < 8; ++dt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int head = 2 * tq + (i & 1);
+                    if (head < GH) mine_o[head * kHeadDim + 16 * dt + g + 8 * (i >> 1)] = o[dt][i];
+                }
+        }
+        if (g == 0) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                warp_max[warp][2 * tq + e] = m_w[e];
+                warp_total[warp][2 * tq + e] = l_w[e];
+            }
+        }
+        __syncthreads();
+
+        // the four warps' partial results, thread = channel
+        float sums[GH], tops[GH], dens[GH];
+#pragma unroll
+        for (int h = 0; h < GH; ++h) {
+            float top = warp_max[0][h];
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) top = fmaxf(top, warp_max[w][h]);
+            float sum = 0.0f, den = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float mw = warp_max[w][h];
+                if (mw != -INFINITY) {  // a warp without keys left nothing behind
+                    const float weight = exp_approx(__fadd_rn(mw, -top));
+                    den = __fmaf_rn(warp_total[w][h], weight, den);
+                    sum = __fmaf_rn(reinterpret_cast<const float *>(&ks[32 * w][0])[h * kHeadDim + t], weight, sum);
+                }
+            }
+            sums[h] = sum;
+            tops[h] = top;
+            dens[h] = den;
+        }
+        bool finish = true;
+        if (splits > 1) {
+            // leave (sums, maximum, total) of this split; the last split of the row's head group to arrive combines them
+            float *group_records = scratch + ((size_t)row * q_heads + head0) * kMaxSplits * kRecord;
+#pragma unroll
+            for (int h = 0; h < GH; ++h) {
+                float *mine = group_records + ((size_t)h * kMaxSplits + split) * kRecord;
+                mine[t] = sums[h];
+                if (t == 0) {
+                    mine[kHeadDim] = tops[h];
+                    mine[kHeadDim + 1] = dens[h];
+                }
+            }
+            __threadfence();
+            __syncthreads();
+            if (t == 0) {
+                uint32_t *counter = counters + (size_t)row * groups + kvg;
+                const uint32_t before = atomicAdd(counter, 1u);
+                arrived = before;
+                if (before == (uint32_t)splits - 1u) *counter = 0u;  // zero again for the next launch
+            }
+            __syncthreads();
+            finish = arrived == (uint32_t)splits - 1u;
+            if (finish) {
+                __threadfence();
+                // weights of the splits: one warp per head, lane = split (at most 32 splits)
+                for (int h = warp; h < GH; h += kWarps) {
+                    const float *all = group_records + (size_t)h * kMaxSplits * kRecord;
+                    const float m = lane < splits ? __ldcg(all + lane * kRecord + kHeadDim) : -INFINITY;
+                    const float l = lane < splits ? __ldcg(all + lane * kRecord + kHeadDim + 1) : 0.0f;
+                    float top = m;
+#pragma unroll
+                    for (int d = 16; d > 0; d >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, d));
+                    const float weight = lane < splits ? exp_approx(__fadd_rn(m, -top)) : 0.0f;
+                    float den = __fmul_rn(l, weight);
+#pragma unroll
+                    for (int d = 16; d > 0; d >>= 1) den = __fadd_rn(den, __shfl_xor_sync(0xffffffffu, den, d));
+                    split_weight[h][lane] = weight;
+                    if (lane == 0) split_den[h] = den;
+                }
+                __syncthreads();
+                // sums over the splits in split order, eight independent loads in flight; thread = channel
+#pragma unroll
+                for (int h = 0; h < GH; ++h) {
+                    const float *all = group_records + (size_t)h * kMaxSplits * kRecord + t;
+                    float sum = 0.0f;
+                    for (int s0 = 0; s0 < splits; s0 += 8) {
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[i] = s0 + i < splits ? __ldcg(all + (s0 + i) * kRecord) : 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if (s0 + i < splits) sum = __fmaf_rn(v[i], split_weight[h][s0 + i], sum);
+                    }
+                    sums[h] = sum;
+                    dens[h] = split_den[h];
                 }
             }
         }
+        if (finish) {
+            uint32_t row_max = 0;
 #pragma unroll
-        for (int h = 0; h < GH; ++h)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) partial[slice][h][8 * cg + i] = acc[h][i];
-    }
-    __syncthreads();
-
-    const bool combine = plan.splits > 1;
-    if (combine) {
-        // leave (sums, maximum, total) of this split; the last split of the row's head group to arrive combines them
-        for (int o = t; o < GH * kHeadDim; o += kThreads) {
-            const int h = o / kHeadDim, c = o % kHeadDim;
-            float sum = partial[0][h][c];
-#pragma unroll
-            for (int i = 1; i < kSlices; ++i) sum = __fadd_rn(sum, partial[i][h][c]);
-            float *mine = scratch + (((size_t)row * q_heads + head0 + h) * kMaxSplits + split) * kRecord;
-            mine[c] = sum;
-            if (c == 0) {
-                float mx = maximum[0], tot = total[0];
-#pragma unroll
-                for (int k = 1; k < GH; ++k)
-                    if (h == k) {
-                        mx = maximum[k];
-                        tot = total[k];
-                    }
-                mine[kHeadDim] = mx;
-                mine[kHeadDim + 1] = tot;
+            for (int h = 0; h < GH; ++h) {
+                const float v = bf16_rne(__fdiv_rn(sums[h], dens[h]));
+                T::store(out + (size_t)row * ldo + (size_t)(head0 + h) * kHeadDim + t, v);
+                row_max = max(row_max, absmax_key(v));
+            }
+            if (maxima) {  // max |out| of the row, for a quantizer that takes its maximum from the producer
+                row_max = warp_max_u32(row_max);
+                if (lane == 0) atomicMax(maxima + row, row_max);
             }
         }
-        __threadfence();
-        __syncthreads();
-        if (t == 0) {
-            const uint32_t before = atomicAdd(counters + blockIdx.x, 1u);
-            arrived = before;
-            if (before == (uint32_t)plan.splits - 1u) counters[blockIdx.x] = 0u;  // zero again for the next launch
-        }
-        __syncthreads();
-        if (arrived != (uint32_t)plan.splits - 1u) return;
-        __threadfence();
+        __syncthreads();  // the tile and the per-warp slots are free for the next item; the next ticket has been written
     }
-    for (int o = t; o < GH * kHeadDim; o += kThreads) {
-        const int h = o / kHeadDim, c = o % kHeadDim;
-        float sum, den;
-        if (combine) {
-            const float *all = scratch + ((size_t)row * q_heads + head0 + h) * kMaxSplits * kRecord;
-            float top = -INFINITY;
-            for (int s = 0; s < plan.splits; ++s) top = fmaxf(top, __ldcg(all + s * kRecord + kHeadDim));
-            sum = 0.0f;
-            den = 0.0f;
-            for (int s = 0; s < plan.splits; ++s) {
-                const float *rec = all + s * kRecord;
-                const float weight = exp_approx(__fadd_rn(__ldcg(rec + kHeadDim), -top));
-                den = __fmaf_rn(__ldcg(rec + kHeadDim + 1), weight, den);
-                sum = __fmaf_rn(__ldcg(rec + c), weight, sum);
-            }
-        } else {
-            sum = partial[0][h][c];
-#pragma unroll
-            for (int i = 1; i < kSlices; ++i) sum = __fadd_rn(sum, partial[i][h][c]);
-            den = total[0];
-#pragma unroll
-            for (int k = 1; k < GH; ++k)
-                if (h == k) den = total[k];
-        }
-        const float v = bf16_rne(__fdiv_rn(sum, den));
-        T::store(out + (size_t)row * ldo + (size_t)(head0 + h) * kHeadDim + c, v);
-        if (maxima) {  // max |out| of the row, for a quantizer that takes its maximum from the producer
-            const uint32_t m = warp_max_u32(absmax_key(v));
-            if (lane == 0) atomicMax(maxima + row, m);
+    // every CTA draws exactly one ticket beyond the last item; the CTA that leaves last returns both counters to zero
+    if (t == 0) {
+        const uint32_t before = atomicAdd(tickets + 1, 1u);
+        if (before == gridDim.x - 1u) {
+            tickets[0] = 0u;
+            tickets[1] = 0u;
         }
     }
 }
@@ -343,40 +480,65 @@ __global__ void __launch_bounds__(256) merge_candidates_kernel(const uint32_t *_
 
 bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+// Workspace: ticket counters (two words per launch of kMaxRows rows), arrival counters (at most one per (row, head)),
+// both padded to 256 bytes and zero between launches, then the partial results of every (row, head, split).
+size_t ticket_bytes(int rows) { return ((((size_t)(rows + kMaxRows - 1) / kMaxRows) * 2 * sizeof(uint32_t)) + 255) & ~(size_t)255; }
+size_t counter_bytes(int rows, int q_heads) { return (((size_t)rows * q_heads * sizeof(uint32_t)) + 255) & ~(size_t)255; }
 size_t workspace_bytes(int rows, int q_heads, int kv_heads) {
-    // arrival counters (one per CTA column of the launch, at most one per (row, head)), padded to 256 bytes, then the
-    // partial results of every (row, head, split)
-    const size_t counters = (((size_t)rows * q_heads * sizeof(uint32_t)) + 255) & ~(size_t)255;
     (void)kv_heads;
-    return counters + (size_t)rows * q_heads * kMaxSplits * kRecord * sizeof(float);
+    return ticket_bytes(rows) + counter_bytes(rows, q_heads) + (size_t)rows * q_heads * kMaxSplits * kRecord * sizeof(float);
 }
 
 template <class T, int GH>
 cudaError_t launch_batched(const void *q, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache, const uint16_t *v_cache,
                            int64_t cache_stride, const uint32_t *positions, void *out, int64_t ldo, int capacity, uint32_t *maxima,
-                           void *workspace, cudaStream_t s) {
+                           uint32_t *counters, float *scratch, uint32_t *tickets, cudaStream_t s) {
     typedef typename T::storage S;
-    const size_t counters = (((size_t)rows * q_heads * sizeof(uint32_t)) + 255) & ~(size_t)255;
-    uint32_t *cnt = static_cast<uint32_t *>(workspace);
-    float *scratch = reinterpret_cast<float *>(static_cast<char *>(workspace) + counters);
-    const dim3 grid(rows * kv_heads * ((q_heads / kv_heads) / GH), kMaxSplits);
-    return launch_kernel(attention_batched_kernel<T, GH>, grid, dim3(kThreads), (size_t)0, s, (const S *)q, ldq, q_heads, kv_heads, k_cache,
-                         v_cache, cache_stride, positions, (S *)out, ldo, capacity, maxima, scratch, cnt, device_status_ptr());
+    // As many CTAs as the GPU holds at once walk the work items (the items are dealt round-robin, so a CTA that had to
+    // wait for a free SM would start its share only when others have finished theirs); fewer when the launch cannot have
+    // that many items.
+    static int per_sm = 0;  // of this instance; the same on every device this library runs on (sm_100a only)
+    if (per_sm == 0) {
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_batched_kernel<T, GH>, kThreads, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        per_sm = n > 0 ? n : 1;
+    }
+    const long long most = (long long)rows * kv_heads * ((q_heads / kv_heads) / GH) * ((capacity + kSplitKeys - 1) / kSplitKeys);
+    const dim3 grid((unsigned)std::min<long long>(most, (long long)per_sm * sm_count()));
+    return launch_kernel(attention_batched_kernel<T, GH>, grid, dim3(kThreads), kSmemBytes, s, (const S *)q, ldq, rows, q_heads, kv_heads, k_cache,
+                         v_cache, cache_stride, positions, (S *)out, ldo, capacity, maxima, scratch, counters, tickets, device_status_ptr());
 }
 
 template <class T>
 cudaError_t launch_batched_any(const void *q, int64_t ldq, int rows, int q_heads, int kv_heads, const uint16_t *k_cache,
                                const uint16_t *v_cache, int64_t cache_stride, const uint32_t *positions, void *out, int64_t ldo,
-                               int capacity, uint32_t *maxima, void *workspace, cudaStream_t s) {
+                               int capacity, uint32_t *maxima, uint32_t *counters, float *scratch, uint32_t *tickets, cudaStream_t s) {
     const int group = q_heads / kv_heads;
+    if (group % 8 == 0)
+        return launch_batched<T, 8>(q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, cache_stride, positions, out, ldo, capacity, maxima, counters, scratch, tickets, s);
     if (group % 4 == 0)
-        return launch_batched<T, 4>(q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, cache_stride, positions, out, ldo, capacity, maxima, workspace, s);
+        return launch_batched<T, 4>(q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, cache_stride, positions, out, ldo, capacity, maxima, counters, scratch, tickets, s);
     if (group % 2 == 0)
-        return launch_batched<T, 2>(q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, cache_stride, positions, out, ldo, capacity, maxima, workspace, s);
-    return launch_batched<T, 1>(q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, cache_stride, positions, out, ldo, capacity, maxima, workspace, s);
+        return launch_batched<T, 2>(q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, cache_stride, positions, out, ldo, capacity, maxima, counters, scratch, tickets, s);
+    return launch_batched<T, 1>(q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, cache_stride, positions, out, ldo, capacity, maxima, counters, scratch, tickets, s);
+}
+
+template <class T> cudaError_t raise_smem() {
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(attention_batched_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes))) return e;
+    if ((e = cudaFuncSetAttribute(attention_batched_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes))) return e;
+    if ((e = cudaFuncSetAttribute(attention_batched_kernel<T, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes))) return e;
+    return cudaFuncSetAttribute(attention_batched_kernel<T, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
 }
 
 }  // namespace
+
+cudaError_t init_batched_decode() {
+    cudaError_t e = raise_smem<Bf16>();
+    return e == cudaSuccess ? raise_smem<F32>() : e;
+}
+
 }  // namespace w8a8
 
 using namespace w8a8;
@@ -406,13 +568,27 @@ int qwen3_attention_batched(const void *q, int dtype, int64_t ldq, int rows, int
     REQUIRE(aligned(k_cache, 16) && aligned(v_cache, 16) && cache_stride % 8 == 0 && aligned(workspace, 16), W8A8_ERR_ALIGNMENT);
     if (rows == 0) return W8A8_OK;
     REQUIRE(workspace_size >= workspace_bytes(rows, q_heads, kv_heads), W8A8_ERR_BAD_ARG);
-    REQUIRE((long long)rows * q_heads <= 2147483647ll / 64, W8A8_ERR_UNSUPPORTED);
-    cudaError_t e = dtype == W8A8_BF16
-                        ? launch_batched_any<Bf16>(q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, cache_stride, positions, out, ldo,
-                                                   capacity, maxima, workspace, (cudaStream_t)stream)
-                        : launch_batched_any<F32>(q, ldq, rows, q_heads, kv_heads, k_cache, v_cache, cache_stride, positions, out, ldo,
-                                                  capacity, maxima, workspace, (cudaStream_t)stream);
-    return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "batched attention launch");
+    // one launch per kMaxRows rows; the launches run one after the other on the stream and share the workspace
+    const size_t esize = dtype == W8A8_BF16 ? 2 : 4;
+    uint32_t *tickets = static_cast<uint32_t *>(workspace);
+    uint32_t *counters = reinterpret_cast<uint32_t *>(static_cast<char *>(workspace) + ticket_bytes(rows));
+    float *scratch = reinterpret_cast<float *>(static_cast<char *>(workspace) + ticket_bytes(rows) + counter_bytes(rows, q_heads));
+    for (int r0 = 0; r0 < rows; r0 += kMaxRows) {
+        const int n = std::min(kMaxRows, rows - r0);
+        const void *qc = static_cast<const char *>(q) + (size_t)r0 * ldq * esize;
+        void *oc = static_cast<char *>(out) + (size_t)r0 * ldo * esize;
+        const uint16_t *kc = k_cache + (size_t)r0 * cache_stride, *vc = v_cache + (size_t)r0 * cache_stride;
+        uint32_t *mc = maxima ? maxima + r0 : nullptr;
+        cudaError_t e = dtype == W8A8_BF16
+                            ? launch_batched_any<Bf16>(qc, ldq, n, q_heads, kv_heads, kc, vc, cache_stride, positions + r0, oc, ldo, capacity,
+                                                       mc, counters + (size_t)r0 * q_heads, scratch + (size_t)r0 * q_heads * kMaxSplits * kRecord,
+                                                       tickets + 2 * (r0 / kMaxRows), (cudaStream_t)stream)
+                            : launch_batched_any<F32>(qc, ldq, n, q_heads, kv_heads, kc, vc, cache_stride, positions + r0, oc, ldo, capacity,
+                                                      mc, counters + (size_t)r0 * q_heads, scratch + (size_t)r0 * q_heads * kMaxSplits * kRecord,
+                                                      tickets + 2 * (r0 / kMaxRows), (cudaStream_t)stream);
+        if (e != cudaSuccess) return fail_cuda(e, "batched attention launch");
+    }
+    return W8A8_OK;
 }
 
 int qwen3_select_token(const void *logits, int dtype, int rows, int n, int64_t ld, uint32_t *token, float *value, void *stream) {

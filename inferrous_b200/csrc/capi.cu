@@ -5,11 +5,9 @@
 // 32..255 -> linear_tiled, >= 256 (and N >= 4096) -> linear_large.  Here:
 //   gemv_dp4a      weight streaming with 16-byte loads + dp4a (1 token; fused gate/up up to 4)
 //   gemv_mma       weight streaming + warp-level int8 MMA (2..64 tokens, small and mid matrices)
-//   gemv_rows      bulk-copied weight rows in a shared-memory ring + warp-level int8 MMA (selectable variant)
 //   gemm_skinny    TMA + tcgen05.mma kind::i8, weights on the MMA's M side, stream-K (large matrices, <= 256 tokens)
 //   gemm_tcgen05   TMA + tcgen05.mma kind::i8, 128x256 tiles, persistent (65..128 tokens)
 //   gemm_tcgen05_pair  the same over CTA pairs (cta_group::2), 256x256 tiles (prefill, >= 129 tokens)
-//   gemm_tcgen05_wide  256x256 tiles in one CTA (selectable variant; slower than the pair kernel)
 // see pick_variant() for the thresholds.
 #include "../../include/w8a8.h"
 #include "internal.h"
@@ -191,11 +189,10 @@ int w8a8_init(int device) {
     CUDA_OK(init_quantize(), "init_quantize");
     CUDA_OK(init_gemv(), "init_gemv");
     CUDA_OK(init_gemm_tcgen05(), "init_gemm_tcgen05");
-    CUDA_OK(init_gemm_tcgen05_wide(), "init_gemm_tcgen05_wide");
     CUDA_OK(init_gemm_tcgen05_pair(), "init_gemm_tcgen05_pair");
     CUDA_OK(init_gemm_skinny(), "init_gemm_skinny");
-    CUDA_OK(init_gemv_rows(), "init_gemv_rows");
     CUDA_OK(init_forward_glue(), "init_forward_glue");
+    CUDA_OK(init_batched_decode(), "init_batched_decode");
     d.ready = true;
     return W8A8_OK;
 }
@@ -380,17 +377,9 @@ static int run_linear(LinearArgs &l, const w8a8_weight *wt, int variant, void *s
             REQUIRE(l.M <= 64 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);
             CUDA_OK(launch_gemv_mma(l, s), "launch_gemv_mma");
             return W8A8_OK;
-        case W8A8_VARIANT_GEMV_ROWS:
-            REQUIRE(l.M <= 16 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);
-            CUDA_OK(launch_gemv_rows(l, s), "launch_gemv_rows");
-            return W8A8_OK;
         case W8A8_VARIANT_GEMM_TCGEN05:
             REQUIRE(wt && l.count == 1 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);
             CUDA_OK(launch_gemm_tcgen05(l, wt, s), "launch_gemm_tcgen05");
-            return W8A8_OK;
-        case W8A8_VARIANT_GEMM_TCGEN05_WIDE:
-            REQUIRE(wt && l.count == 1 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);
-            CUDA_OK(launch_gemm_tcgen05_wide(l, wt, s), "launch_gemm_tcgen05_wide");
             return W8A8_OK;
         case W8A8_VARIANT_GEMM_TCGEN05_PAIR:
             REQUIRE(wt && l.count == 1 && l.epilogue != EPI_SWIGLU, W8A8_ERR_UNSUPPORTED);
@@ -406,6 +395,38 @@ static int run_linear(LinearArgs &l, const w8a8_weight *wt, int variant, void *s
 
 static bool valid_weight(const w8a8_weight *w) { return w && w->magic == kWeightMagic; }
 
+// The reference keeps every input and output of a projection in its own allocation (docs/qwen3-8b-w8a8/safety.md:15:
+// residual, out and combined are three distinct buffers) and the kernels rely on it (weights and activations are read
+// through the non-coherent path while outputs are written).  A byte range that an output shares with another operand
+// is rejected here, on the host, before anything is queued.
+struct ByteRange {
+    const void *p;
+    size_t n;
+    const char *name;
+};
+static bool overlaps(const ByteRange &a, const ByteRange &b) {
+    if (!a.p || !b.p || a.n == 0 || b.n == 0) return false;
+    const uintptr_t a0 = reinterpret_cast<uintptr_t>(a.p), b0 = reinterpret_cast<uintptr_t>(b.p);
+    return a0 < b0 + b.n && b0 < a0 + a.n;
+}
+// outputs[0 .. n_out) against each other and against inputs[0 .. n_in)
+static int reject_aliasing(const ByteRange *outputs, int n_out, const ByteRange *inputs, int n_in, const char *where) {
+    for (int i = 0; i < n_out; ++i) {
+        for (int j = i + 1; j < n_out; ++j)
+            if (overlaps(outputs[i], outputs[j])) {
+                snprintf(g_err, sizeof g_err, "%s: outputs %s and %s overlap", where, outputs[i].name, outputs[j].name);
+                return W8A8_ERR_BAD_ARG;
+            }
+        for (int j = 0; j < n_in; ++j)
+            if (overlaps(outputs[i], inputs[j])) {
+                snprintf(g_err, sizeof g_err, "%s: output %s overlaps input %s", where, outputs[i].name, inputs[j].name);
+                return W8A8_ERR_BAD_ARG;
+            }
+    }
+    return W8A8_OK;
+}
+static size_t elem_bytes(int dtype) { return dtype == W8A8_BF16 ? 2 : 4; }
+
 int w8a8_linear_ex(const int8_t *q, const float *a_scale, w8a8_weight_t weight, int M, const void *residual, void *y,
                    void *combined, int dtype, int variant, void *stream) {
     REQUIRE(valid_weight(weight) && q && a_scale && M > 0 && check_dtype(dtype), W8A8_ERR_BAD_ARG);
@@ -413,6 +434,15 @@ int w8a8_linear_ex(const int8_t *q, const float *a_scale, w8a8_weight_t weight, 
     REQUIRE(y || combined, W8A8_ERR_BAD_ARG);
     REQUIRE(aligned16(q) && (y == nullptr || aligned16(y)) && (combined == nullptr || aligned16(combined)) &&
                 (residual == nullptr || aligned16(residual)), W8A8_ERR_ALIGNMENT);
+    {
+        const size_t out_bytes = (size_t)M * weight->N * elem_bytes(dtype);
+        const ByteRange outputs[] = {{y, out_bytes, "y"}, {combined, out_bytes, "combined"}};
+        const ByteRange inputs[] = {{q, (size_t)M * weight->K, "q"}, {a_scale, (size_t)M * 4, "a_scale"},
+                                    {weight->w, (size_t)weight->N * weight->K, "w"}, {weight->w_scale, (size_t)weight->N * 4, "w_scale"},
+                                    {residual, out_bytes, "residual"}};
+        const int st = reject_aliasing(outputs, 2, inputs, 5, "w8a8_linear");
+        if (st != W8A8_OK) return st;
+    }
     LinearArgs l{};
     l.q = q; l.a_scale = a_scale; l.M = M; l.K = weight->K; l.count = 1;
     l.w[0] = weight->w; l.ws[0] = weight->w_scale; l.out[0] = y; l.n[0] = weight->N;
@@ -519,6 +549,13 @@ int w8a8_linear_no_alloc(const int8_t *q, const float *a_scale, const int8_t *w,
     REQUIRE(q && a_scale && w && w_scale && y && M > 0 && N > 0 && K > 0 && check_dtype(dtype), W8A8_ERR_BAD_ARG);
     REQUIRE(K % 128 == 0 && aligned16(q) && aligned16(y) && (reinterpret_cast<uintptr_t>(w) & 127u) == 0 && aligned16(w_scale),
             W8A8_ERR_ALIGNMENT);
+    {
+        const ByteRange outputs[] = {{y, (size_t)M * N * elem_bytes(dtype), "y"}};
+        const ByteRange inputs[] = {{q, (size_t)M * K, "q"}, {a_scale, (size_t)M * 4, "a_scale"}, {w, (size_t)N * K, "w"},
+                                    {w_scale, (size_t)N * 4, "w_scale"}};
+        const int st = reject_aliasing(outputs, 1, inputs, 4, "w8a8_linear_no_alloc");
+        if (st != W8A8_OK) return st;
+    }
     if (M > kNoAllocMaxTokens) {
         snprintf(g_err, sizeof g_err, "w8a8_linear_no_alloc: M=%d exceeds the %d tokens its fixed scratch array holds", M,
                  kNoAllocMaxTokens);

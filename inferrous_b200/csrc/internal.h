@@ -92,14 +92,10 @@ struct LinearArgs {
 cudaError_t launch_linear_naive(const LinearArgs &a, cudaStream_t s);
 cudaError_t launch_gemv_dp4a(const LinearArgs &a, cudaStream_t s);   // M <= 4
 cudaError_t launch_gemv_mma(const LinearArgs &a, cudaStream_t s);    // M <= 64
-cudaError_t launch_gemv_rows(const LinearArgs &a, cudaStream_t s);   // M <= 16
-cudaError_t init_gemv_rows();
 // tcgen05 path: one matrix, EPI_PLAIN / EPI_RESIDUAL / EPI_ACC
 cudaError_t launch_gemm_tcgen05(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);
 cudaError_t init_gemm_tcgen05();
 int tcgen05_tile_channels(int M, int N);  // 256, 128 or 64: output channels per tile the launcher will use
-cudaError_t launch_gemm_tcgen05_wide(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);  // 256x256 tiles
-cudaError_t init_gemm_tcgen05_wide();
 cudaError_t launch_gemm_tcgen05_pair(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);  // CTA pairs
 cudaError_t init_gemm_tcgen05_pair();
 cudaError_t make_weight_maps(w8a8_weight *wt);  // TMA descriptors of the [N,K] matrix
@@ -122,6 +118,7 @@ constexpr size_t kSkinnySlotInts = 4 * (size_t)kSkinnyMaxTokens * 32;  // one 12
 cudaError_t init_gemv();
 cudaError_t init_quantize();
 cudaError_t init_forward_glue();
+cudaError_t init_batched_decode();
 
 // Device status word (bounded waits report here instead of trapping).
 uint32_t *device_status_ptr();  // device address of the 2-word status block of the current device

@@ -12,7 +12,7 @@
 // Unlike the reference: Q|K|V are one concatenated matrix (identical channel for channel with per-channel scales); the
 // head is quantized per output channel when the bundle is loaded (tools/prepare.py:79-81) and runs as a W8A8
 // projection with the selection fused (w8a8_linear_argmax); sha256 digests of the manifest are not verified here (the
-// Python reader does), only names, sizes and finiteness.
+// Python reader does), only names, sizes, finiteness and the weight checks of src/model.rs:143-145.
 #pragma once
 
 #include <chrono>
@@ -69,6 +69,20 @@ inline std::vector<float> read_floats(const std::string &dir, const std::string 
     auto v = read_tensor<float>(dir, name, count);
     for (float x : v)
         if (!std::isfinite(x)) throw std::runtime_error(name + ": nonfinite float");
+    return v;
+}
+// An int8 weight matrix and its per-channel scales as Model::load admits them (src/model.rs:143-145): the code -128
+// never occurs in symmetric quantization, and a scale must be positive.
+inline std::vector<int8_t> read_codes(const std::string &dir, const std::string &name, size_t count) {
+    auto v = read_tensor<int8_t>(dir, name, count);
+    for (int8_t x : v)
+        if (x == -128) throw std::runtime_error(name + ": invalid quantized weight");
+    return v;
+}
+inline std::vector<float> read_scales(const std::string &dir, const std::string &name, size_t count) {
+    auto v = read_floats(dir, name, count);
+    for (float x : v)
+        if (!(x > 0.0f)) throw std::runtime_error(name + ": invalid weight scale");
     return v;
 }
 inline float widen(uint16_t b) {
@@ -137,19 +151,19 @@ struct Qwen3Bundle {
             t.knorm = read_floats(dir, p + "knorm", 128);
             for (const char *name : {"q", "k", "v"}) {
                 const size_t n = name[0] == 'q' ? c.q_width() : c.kv_width();
-                const auto w = read_tensor<int8_t>(dir, p + name + ".w", n * H);
-                const auto s = read_floats(dir, p + name + ".scale", n);
+                const auto w = read_codes(dir, p + name + ".w", n * H);
+                const auto s = read_scales(dir, p + name + ".scale", n);
                 t.qkv.insert(t.qkv.end(), w.begin(), w.end());
                 t.qkv_scale.insert(t.qkv_scale.end(), s.begin(), s.end());
             }
-            t.o = read_tensor<int8_t>(dir, p + "o.w", H * c.q_width());
-            t.o_scale = read_floats(dir, p + "o.scale", H);
-            t.gate = read_tensor<int8_t>(dir, p + "gate.w", I * H);
-            t.gate_scale = read_floats(dir, p + "gate.scale", I);
-            t.up = read_tensor<int8_t>(dir, p + "up.w", I * H);
-            t.up_scale = read_floats(dir, p + "up.scale", I);
-            t.down = read_tensor<int8_t>(dir, p + "down.w", H * I);
-            t.down_scale = read_floats(dir, p + "down.scale", H);
+            t.o = read_codes(dir, p + "o.w", H * c.q_width());
+            t.o_scale = read_scales(dir, p + "o.scale", H);
+            t.gate = read_codes(dir, p + "gate.w", I * H);
+            t.gate_scale = read_scales(dir, p + "gate.scale", I);
+            t.up = read_codes(dir, p + "up.w", I * H);
+            t.up_scale = read_scales(dir, p + "up.scale", I);
+            t.down = read_codes(dir, p + "down.w", H * I);
+            t.down_scale = read_scales(dir, p + "down.scale", H);
         }
         return b;
     }

@@ -45,6 +45,41 @@ def test_bundle_tensors_round_trip_and_are_verified(tmp_path):
         Bundle(tmp_path / "b")
 
 
+def test_invalid_weights_are_refused_at_load(tmp_path):
+    """Model::load rejects the code -128 and non-positive scales (src/model.rs:143-145); so do both readers here."""
+    import hashlib
+
+    from inferrous_b200.bundle import Bundle, BundleError
+
+    manifest = write_bundle(tmp_path / "b", seed=5)
+    root = tmp_path / "b"
+
+    def rewrite(name, mutate):
+        path = root / f"{name}.bin"
+        original = path.read_bytes()
+        raw = bytearray(original)
+        mutate(raw)
+        path.write_bytes(bytes(raw))
+        m = json.loads(json.dumps(manifest))
+        m["tensors"][name]["sha256"] = hashlib.sha256(bytes(raw)).hexdigest()  # the digest is right: the VALUE is refused
+        (root / "manifest.json").write_text(json.dumps(m))
+        return path, original
+
+    b = Bundle(root)
+    assert b.weight("layer.0.o", 256, 512)[0].shape == (256, 512)
+    path, original = rewrite("layer.0.o.w", lambda raw: raw.__setitem__(7, 0x80))
+    with pytest.raises(BundleError, match="invalid quantized weight"):
+        Bundle(root).weight("layer.0.o", 256, 512)
+    path.write_bytes(original)
+    for bits in (0.0, -1.0):
+        path, original = rewrite("layer.1.gate.scale", lambda raw: raw.__setitem__(slice(8, 12), np.float32(bits).tobytes()))
+        with pytest.raises(BundleError, match="invalid weight scale"):
+            Bundle(root).weight("layer.1.gate", 512, 256)
+        path.write_bytes(original)
+    (root / "manifest.json").write_text(json.dumps(manifest))
+    assert Bundle(root).weight("layer.1.gate", 512, 256)[1].min() > 0
+
+
 def test_cpp_generation_program_compiles():
     from tests.cpp.build import build
 

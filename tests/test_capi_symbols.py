@@ -73,6 +73,26 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.qwen3_attention(None, 0, 4096, 1, 32, 8, None, None, None, None, 4096, 4096, None, None) == 6
 
 
+def test_overlapping_operands_are_rejected_on_the_host(lib):
+    """Inputs and outputs of a projection never share memory (docs/qwen3-8b-w8a8/safety.md:15).  The check runs on the
+    host before any CUDA call, so it can be exercised here with made-up, suitably aligned addresses through the entry
+    point that takes raw pointers; w8a8_linear / w8a8_linear_ex run the same check with the shapes of the weight handle."""
+    base = 0x7000_0000_0000
+    M, N, K = 17, 256, 512  # one token more than that entry point takes: a call that passes the check stops at the next one
+    q, a, w, ws, y = base, base + (1 << 20), base + (2 << 20), base + (3 << 20), base + (4 << 20)
+    call = lambda q=q, a=a, w=w, ws=ws, y=y, dtype=0: lib.w8a8_linear_no_alloc(q, a, w, ws, M, N, K, y, dtype, None)
+    for kw, names in [(dict(y=q), b"output y overlaps input q"), (dict(y=w + N * K - 16), b"output y overlaps input w"),
+                      (dict(y=ws), b"w_scale"), (dict(y=a - M * N * 2 + 16), b"a_scale"), (dict(y=q + M * K - 16), b"input q")]:
+        assert call(**kw) == 1
+        assert names in lib.w8a8_last_cuda_error()
+    # adjacent ranges do not overlap: the call gets past this check and is refused by the next one (too many tokens,
+    # W8A8_ERR_UNSUPPORTED), so nothing is ever launched with these addresses
+    assert call(y=q + M * K) == 3
+    assert call(y=w - M * N * 2) == 3
+    # the f32 carrier doubles the output's extent
+    assert call(y=w - M * N * 4 + 16, dtype=1) == 1 and call(y=w - M * N * 4, dtype=1) == 3
+
+
 def test_product_does_not_import_the_oracle():
     """The oracle is test infrastructure: nothing under inferrous_b200/ may import, load or link it."""
     needles = ("import oracle", "from oracle", "w8a8_oracle", "oracle/", "oracle.py")

@@ -32,8 +32,9 @@ def random_caches(rng, sequences, capacity, kv_heads):
 
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 @pytest.mark.parametrize("qh,kvh,positions", [
-    (32, 8, [0, 63, 64, 127, 128, 700, 1024, 1025, 2047]),   # one split, exact multiples, emptied trailing splits
-    (8, 2, [5, 4095, 300]),                                  # the longest context: 16 splits of 256 keys
+    (32, 8, [0, 31, 32, 127, 128, 700, 1024, 1025, 2047]),   # one warp, one split, exact multiples, a split of one key
+    (8, 2, [5, 4095, 300]),                                  # the longest context: 32 splits of 128 keys
+    (16, 2, [77, 1500]),                                     # eight query heads per key/value head
     (4, 4, [90, 91]),                                        # one query head per key/value head
     (6, 3, [513, 2]),                                        # two query heads per key/value head
 ])
@@ -71,8 +72,8 @@ def test_attention_batched_matches_the_cpu_restatement(ops, dtype, qh, kvh, posi
 
 
 def test_attention_batched_workspace_counters_only(ops):
-    """The workspace's leading words are arrival counters that every launch leaves at zero; what follows are partial
-    results that the next launch overwrites before it reads them."""
+    """The workspace's leading words are ticket and arrival counters that every launch leaves at zero; what follows are
+    partial results that the next launch overwrites before it reads them."""
     import torch
 
     rng = np.random.default_rng(5)
@@ -84,7 +85,7 @@ def test_attention_batched_workspace_counters_only(ops):
     out = torch.empty((rows, qh * 128), dtype=torch.bfloat16, device="cuda")
     ops.attention_batched(qd, qh, kvh, kc, vc, pos, out, ws)
     first = to_host(out).copy()
-    counters = (rows * qh * 4 + 255) // 256 * 256 // 4
+    counters = 256 // 4 + (rows * qh * 4 + 255) // 256 * 256 // 4  # one 256-byte block of tickets, then the arrival counters
     assert not ws[:counters].any() and ws[counters:].any()
     ws[counters:].fill_(0x7FC00000)  # NaN in every partial result: a launch must not read what it has not written
     ops.attention_batched(qd, qh, kvh, kc, vc, pos, out, ws)
@@ -239,4 +240,24 @@ def test_sequences_decoded_side_by_side_equal_sequences_decoded_alone(batch, cfg
         if r < 3:
             same_as_classic += classic.generate(prompt, steps)[0] == tokens[r]
     assert same_as_classic == 3
+    assert ops.device_status() == (0, 0)
+
+
+def test_attention_batched_more_rows_than_one_launch_takes(ops):
+    """A batch beyond the row limit of one launch is cut into several launches inside the entry point: every row still
+    equals the row computed in a smaller batch."""
+    import torch
+
+    rng = np.random.default_rng(300)
+    rows, qh, kvh, capacity = 300, 4, 2, 256
+    _, _, kc, vc = random_caches(rng, rows, capacity, kvh)
+    qd = to_dev(oracle.bf16(rng.standard_normal((rows, qh * 128)).astype(np.float32)), "bf16")
+    pos = to_dev(rng.integers(0, capacity, rows).astype(np.uint32))
+    out = torch.full((rows, qh * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.attention_batched(qd, qh, kvh, kc, vc, pos, out, ops.attention_batched_workspace(rows, qh, kvh))
+    for a, b in [(0, 150), (150, 300)]:
+        part = torch.full((b - a, qh * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.attention_batched(qd[a:b], qh, kvh, kc[a:b], vc[a:b], pos[a:b], part, ops.attention_batched_workspace(b - a, qh, kvh))
+        assert np.array_equal(to_host(part), to_host(out[a:b]))
+    assert not np.isnan(to_host(out)).any()
     assert ops.device_status() == (0, 0)

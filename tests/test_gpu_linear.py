@@ -12,7 +12,7 @@ from tests.util import bits, empty_act, synth_activations, synth_weights, to_dev
 
 pytestmark = pytest.mark.gpu
 
-NAIVE, DP4A, MMA, TC, SKINNY, ROWS, WIDE, PAIR = 1, 2, 3, 4, 5, 6, 7, 8
+NAIVE, DP4A, MMA, TC, SKINNY, PAIR = 1, 2, 3, 4, 5, 8
 CARRIERS = ["bf16", "f32"]
 
 
@@ -27,11 +27,9 @@ def ops():
 
 
 def variants_for(M):
-    v = [NAIVE, TC, WIDE, PAIR]
+    v = [NAIVE, TC, PAIR]
     if M <= 256:
         v.append(SKINNY)
-    if M <= 16:
-        v.append(ROWS)
     if os.environ.get("W8A8_TEST_SKIP_TCGEN05"):  # bring-up aid: check the SIMT variants alone
         v = [NAIVE]
     if M <= 4:

@@ -63,6 +63,19 @@ def main() -> None:
         expect = total.to(torch.bfloat16)
         fused_exact &= bool(torch.equal(y, expect)) and bool(torch.equal(comb, (res.float() + expect.float()).to(torch.bfloat16)))
 
+    # batched decode under tensor parallelism: ragged sequences side by side; graph replay == eager launches, the fused
+    # exchange == NCCL + residual on this model, and (fused exchange: partial outputs are exact per row and summed in
+    # rank order) every sequence gives the tokens it gives when decoded alone
+    rng = np.random.default_rng(17)
+    prompts = [[int(t) for t in rng.integers(0, config.vocab, n)] for n in (1, 37, 150, 64, 9)]
+    side = Qwen3Runner(shard, group=group, batch=len(prompts))
+    batch_tokens, _ = side.generate_batch(prompts, steps)
+    batch_eager, _ = side.generate_batch(prompts, steps, use_graph=False)
+    batch_nccl, _ = Qwen3Runner(shard, group=group, batch=len(prompts), fused_allreduce=False).generate_batch(prompts, steps)
+    alone = Qwen3Runner(shard, group=group, batch=1)
+    alone._make_batch_buffers()
+    batch_alone = [alone.generate_batch([p], steps)[0][0] for p in prompts]
+
     def prompt_logits(weights, grp):
         runner = Qwen3Runner(weights, unfused=True, group=grp)
         ws = Workspace(weights.config, len(prompt))
@@ -73,9 +86,11 @@ def main() -> None:
 
     logits_tp = prompt_logits(shard, group)
     result = {"rank": rank, "tp": tp, "tokens_tp": tokens_tp, "tokens_tp_eager": tokens_eager, "tokens_nccl": tokens_nccl,
-              "fused_exact": fused_exact}
+              "fused_exact": fused_exact, "batch_tokens": batch_tokens, "batch_eager": batch_eager, "batch_nccl": batch_nccl,
+              "batch_alone": batch_alone}
     if rank == 0:
         tokens_single, _ = Qwen3Runner(full).generate(prompt, steps)
+        result["batch_single_gpu"] = Qwen3Runner(full, batch=len(prompts)).generate_batch(prompts, steps)[0]
         logits_single = prompt_logits(full, None)
         diff = logits_tp.astype(np.float64) - logits_single
         result.update(tokens_single=tokens_single,
