@@ -262,11 +262,18 @@ def run_ours(args):
     hbm_peak, _, peak_kind = measured_peaks()
 
     # ---- resident weights (model state) and per-(M,shape) activation/output buffers ----
-    mats, bufs = {}, {}
-    for i, (name, K, N) in enumerate(SHAPES):
-        k, n = shard(name, K, N, tp)
-        wq, ws = make_weights_device(torch, k, n, seed=1000 + 10 * i + rank)
-        mats[name] = ops.Matrix(wq, ws)
+    # A rank whose shard of the weights is smaller than twice the L2 rotates over several distinct copies of every matrix
+    # (one copy per step, round-robin), so that its passes stream from HBM instead of from the cache.
+    copies = weight_copies(tp)
+    mats_all, bufs = [], {}
+    for c in range(copies):
+        mats_c = {}
+        for i, (name, K, N) in enumerate(SHAPES):
+            k, n = shard(name, K, N, tp)
+            wq, ws = make_weights_device(torch, k, n, seed=1000 + 10 * i + rank + 100 * c)
+            mats_c[name] = ops.Matrix(wq, ws)
+        mats_all.append(mats_c)
+    mats = mats_all[0]
     # Activations and outputs of one step live in two device arenas mirrored by two pinned host arenas, so the
     # end-to-end step moves them with one host->device and one device->host copy.
     def carve(sizes):
@@ -302,7 +309,8 @@ def run_ours(args):
 
     gemv_events = []  # (kernel family, bytes, start, end) per linear launch of the timed region
 
-    def step(record=False, host_io=False, ms=None):
+    def step(record=False, host_io=False, ms=None, copy=0):
+        mats = mats_all[copy]
         if host_io:
             x_all.copy_(hx_all, non_blocking=True)
         for M in (DECODE_M if ms is None else ms):
@@ -335,11 +343,11 @@ def run_ours(args):
         y_span[M] = (lo, y_off[i] + (M * n + 127) // 128 * 128)
     copy_stream = torch.cuda.Stream()
 
-    def step_e2e():
+    def step_e2e(copy=0):
         main = torch.cuda.current_stream()
         x_all.copy_(hx_all, non_blocking=True)
         for M in sorted(DECODE_M, reverse=True):
-            step(ms=[M])
+            step(ms=[M], copy=copy)
             lo, hi = y_span[M]
             ready = torch.cuda.Event()
             ready.record(main)
@@ -364,9 +372,7 @@ def run_ours(args):
             dist.barrier()
         return float(ms.item())
 
-    def capture(fn):
-        """One step as a CUDA graph (the reference replays captured decode graphs, src/gpu.rs:318-328,890).
-        Every launch call of the library is capture-safe; under TP the NCCL all-reduce is captured with it."""
+    def capture_one(fn):
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -379,6 +385,22 @@ def run_ours(args):
             fn()
         return g
 
+    class Rotation:
+        """One step per call, over the weight copies in turn (copy = call number mod copies)."""
+
+        def __init__(self, fns):
+            self.fns, self.turn = fns, 0
+
+        def __call__(self):
+            self.fns[self.turn % len(self.fns)]()
+            self.turn += 1
+
+    def capture(fn):
+        """One step as a CUDA graph per weight copy (the reference replays captured decode graphs, src/gpu.rs:318-328,890).
+        Every launch call of the library is capture-safe; under TP the NCCL all-reduce is captured with it."""
+        graphs = [capture_one(lambda c=c: fn(copy=c)) for c in range(copies)]
+        return graphs, Rotation([g.replay for g in graphs])
+
     if fused is not None:
         # One eager step first: if a wait for another rank's packets ran out (the kernels give up after two seconds and
         # report it), every rank falls back to NCCL together rather than timing a broken exchange.
@@ -388,15 +410,14 @@ def run_ours(args):
         if expired.item() > 0:
             print("bench: a wait in the fused projection + all-reduce expired; using NCCL", file=sys.stderr)
             fused, reduce_kind = None, "nccl"
-    for _ in range(args.warmup):
+    for _ in range(max(args.warmup, copies)):
         step()
     launch_mode = "eager"
-    run_step = step
+    run_step = Rotation([lambda c=c: step(copy=c) for c in range(copies)])
     graph = e2e_graph = None
     if not args.eager:
         try:
-            graph = capture(step)
-            run_step = graph.replay
+            graph, run_step = capture(step)
             launch_mode = "cuda_graph"
             for _ in range(args.warmup):
                 run_step()
@@ -411,7 +432,7 @@ def run_ours(args):
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
 
     # per-launch CUDA events need eager launches: the same steps again, instrumented
-    eager_ms = timed(lambda: step(record=True), args.steps) / args.steps
+    eager_ms = timed(Rotation([lambda c=c: step(record=True, copy=c) for c in range(copies)]), args.steps) / args.steps
 
     # ---- roofline of the dominant kernel family ----
     # Per-launch events (above) bracket one short kernel each and carry several microseconds of event and launch
@@ -462,13 +483,12 @@ def run_ours(args):
                                       "launches": v[2]} for k, v in fam.items() if k != dominant}}
 
     # ---- end to end: host buffers in, host buffers out, through the same calls ----
-    e2e_step = step_e2e
+    e2e_step = Rotation([lambda c=c: step_e2e(copy=c) for c in range(copies)])
     for _ in range(3):
         e2e_step()
     if launch_mode == "cuda_graph":
         try:
-            e2e_graph = capture(e2e_step)
-            e2e_step = e2e_graph.replay
+            e2e_graph, e2e_step = capture(step_e2e)
             for _ in range(3):
                 e2e_step()
         except Exception as exc:
@@ -508,13 +528,9 @@ def run_ours(args):
            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8xint8->int32 (bf16 in/out)",
            "data": "synthetic", "impl": "ours",
-           "config": {"workload": WORKLOAD, "shapes": {n: [K, N] for n, K, N in SHAPES}, "M": DECODE_M,
-                      "parallelism": f"tp{world}" if world > 1 else "single",
-                      "launch": launch_mode + ("" if args.no_pdl else "+programmatic_dependent_launch"),
-                      "all_reduce": reduce_kind, "all_reduce_check": reduce_check,
-                      "l2": f"weights ({sum(shard(n, K, N, tp)[0] * shard(n, K, N, tp)[1] for n, K, N in SHAPES) >> 20} MiB streamed per "
-                            "pass, each matrix revisited only after all the others) exceed the 126 MB L2; no flush",
-                      "bytes_per_step": step_bytes},
+           "config": workload_config(world),
+           "execution": {"launch": launch_mode + ("" if args.no_pdl else "+programmatic_dependent_launch"),
+                         "all_reduce": reduce_kind, "all_reduce_check": reduce_check, "weight_copies": copies},
            "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
     if world == 1 and not args.no_cpu:
         out["cpu_baseline"] = cpu_baseline(torch, mats, bufs, reps=3)
@@ -816,9 +832,41 @@ def cpu_baseline(torch, mats, bufs, reps):
         cpu_step(oracle, host, threads)
     dt = (time.perf_counter() - t) / reps
     nbytes = sum(linear_bytes(M, K, N) + quant_bytes(M, K) for M in DECODE_M for _, K, N in SHAPES)
-    return {"value": round(nbytes / dt / 1e9, 2), "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"{reps} full steps (all 15 quantize+linear pairs) of the same workload, {threads} host threads",
-            "s_per_step": round(dt, 4)}
+    out = {"value": round(nbytes / dt / 1e9, 2), "unit": "GB/s", "cores": threads, "kind": "port",
+           "sample": f"{reps} full steps (all 15 quantize+linear pairs) of the same workload, {threads} host threads",
+           "s_per_step": round(dt, 4)}
+    out["torch_path"] = torch_cpu_path(torch, host)
+    return out
+
+
+def torch_cpu_path(torch, host, budget_s=12.0):
+    """The same path written as the reference's fixture generator writes it (tools/operator_fixtures.py:42-44,54):
+    scale = amax/127, q = round(x/scale).clamp(+-127), out = bf16((q.int() @ w.int().T).float() * a_scale * w_scale), with
+    torch.set_num_threads(8) (:17).  Torch's CPU int32 matmul is slow, so the (M, projection) pairs are timed one by one
+    in the order of the workload until the time budget is spent; the figure is algorithmic bytes over time for the pairs
+    that ran."""
+    before = torch.get_num_threads()
+    torch.set_num_threads(8)
+    done_bytes, spent, ran = 0, 0.0, []
+    try:
+        for M in DECODE_M:
+            for name, K, N in SHAPES:
+                if spent > budget_s:
+                    break
+                x, w, ws = host[(M, name)]
+                xt, wt, wst = torch.from_numpy(x), torch.from_numpy(w).int(), torch.from_numpy(ws)
+                t = time.perf_counter()
+                scale = xt.abs().amax(-1, keepdim=True).clamp(min=1e-8) / 127
+                q = torch.round(xt / scale).clamp(-127, 127).to(torch.int8)
+                out = ((q.int() @ wt.T).float() * scale * wst).bfloat16()
+                spent += time.perf_counter() - t
+                done_bytes += linear_bytes(M, K, N) + quant_bytes(M, K)
+                ran.append(f"{name}@{M}")
+                del out
+    finally:
+        torch.set_num_threads(before)
+    return {"value": round(done_bytes / max(spent, 1e-9) / 1e9, 3), "unit": "GB/s", "cores": 8, "kind": "reference formula in torch (CPU)",
+            "sample": f"{len(ran)} of 15 (M, projection) pairs within {budget_s:.0f} s: " + " ".join(ran), "seconds": round(spent, 2)}
 
 
 def run_reference(args):
@@ -841,12 +889,12 @@ def run_reference(args):
             x[:, rng.choice(K, 8, replace=False)] *= 20
             host[(M, name)] = (oracle.bf16(x), *wh[name])
     t = time.perf_counter()
-    cpu_step(oracle, host, threads)
+    cpu_step(oracle, host, threads)  # the first of the W warm-up steps
     first = time.perf_counter() - t
-    # keep the whole run within a few minutes whatever K and W were asked for
-    args.warmup = max(0, min(args.warmup - 1, int(30 / first)))
+    # W warm-up and K timed steps as asked, unless that would take more than a few minutes on this host
+    args.warmup = max(1, min(args.warmup, int(30 / first)))
     args.steps = max(1, min(args.steps, int(150 / first)))
-    for _ in range(args.warmup):
+    for _ in range(args.warmup - 1):
         cpu_step(oracle, host, threads)
     t = time.perf_counter()
     for _ in range(args.steps):
@@ -859,7 +907,8 @@ def run_reference(args):
                       "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
                       "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
                       "dtype": "int8xint8->int32 (bf16 in/out)", "data": "synthetic",
-                      "config": {"workload": WORKLOAD, "shapes": {n: [K, N] for n, K, N in SHAPES}, "M": DECODE_M},
+                      "config": workload_config(args.gpus),
+                      "execution": {"launch": "host threads", "all_reduce": "none", "all_reduce_check": None, "weight_copies": 1},
                       "cpu_baseline": {"value": v, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
                       "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
@@ -874,9 +923,9 @@ def main():
     ap.add_argument("--peer-allreduce", action="store_true",
                     help="tensor parallel, with --nccl-allreduce: the library's stand-alone one-shot peer-memory all-reduce instead "
                          "of NCCL (measured 3 us per call slower than NCCL at 2 and 4 GPUs)")
-    ap.add_argument("--fused-max-ranks", type=int, default=4,
-                    help="largest tensor-parallel degree that uses the fused exchange by default; it has been run on 2 GPUs (its "
-                         "symmetric-memory set-up also on 4), larger groups use NCCL unless this is raised")
+    ap.add_argument("--fused-max-ranks", type=int, default=8,
+                    help="largest tensor-parallel degree that uses the fused exchange by default (it is checked bit for bit against "
+                         "gathered partial sums before anything is timed; every rank falls back to NCCL together if the check fails)")
     ap.add_argument("--nccl-allreduce", dest="fused_allreduce", action="store_false",
                     help="tensor parallel: projection + NCCL all-reduce for O and down instead of w8a8_linear_allreduce (GEMV "
                          "epilogue pushes tagged packets to every rank, a consumer kernel sums them; the default: 0.286 against "

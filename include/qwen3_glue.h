@@ -84,8 +84,8 @@ int qwen3_prepare_qk_batched(void *qkv, int dtype, int64_t ld, int rows, int q_h
 
 /* out[r, h, :] = bf16(softmax(q[r, h, :] . K_r[0 .. positions[r], h / (q_heads / kv_heads), :] * 128^-0.5) . V_r[...]) with
  * K_r, V_r the caches of sequence r.  One CTA serves the query heads that share a key/value head, and the keys of a row
- * are split over one CTA per 128 keys as a function of positions[r] alone, so a sequence gives the same bits whether it
- * is decoded alone or inside a batch.  `workspace` (16-byte aligned, at least qwen3_attention_batched_workspace() bytes,
+ * are split into units of 512 keys as a function of positions[r] alone, so a sequence gives the same bits whether it
+ * is decoded alone or inside a batch.  The launch shape does not depend on the positions.  `workspace` (16-byte aligned, at least qwen3_attention_batched_workspace() bytes,
  * zero before the first call; the kernel leaves its counters at zero) holds the partial results of the splits; calls
  * that share a workspace must not overlap on the GPU.  `maxima` as in qwen3_attention. */
 size_t qwen3_attention_batched_workspace(int rows, int q_heads, int kv_heads);

@@ -10,10 +10,10 @@
 //   * one CTA serves the GH query heads that share a key/value head (grouped-query attention): every key and value
 //     line is fetched once for the group instead of once per head -- in batched decode the KV cache, not the weights,
 //     is the larger stream (64 sequences of 2 000 keys read 0.55 GB per layer against 0.19 GB of weights);
-//   * the keys of a row are split over one CTA per 128 visible keys (up to 32) whose partial (maximum, total, sums)
-//     the last CTA to arrive combines, so a short and a long sequence in the same batch both spread over the GPU.  The
-//     number of splits is a function of the row's context length alone, never of the batch: a sequence decoded alone
-//     and the same sequence decoded inside a batch produce the same bits;
+//   * the keys of a row are split into units of 512 (up to 8) whose partial (maximum, total, sums) the last CTA to
+//     arrive combines, so a short and a long sequence in the same batch both spread over the GPU.  The units are a
+//     function of the row's context length alone, never of the batch: a sequence decoded alone and the same sequence
+//     decoded inside a batch produce the same bits;
 //   * both products run on the tensor cores (warp-level bf16 MMA, float32 accumulation) with the keys, not the query
 //     rows, on the MMA's 16-row side; the kernel is bound by the stream of keys and values from HBM.
 // float32 sums are reassociated relative to the reference's one-thread-per-key kernel (q, k, v are bf16 values, so every
@@ -35,10 +35,12 @@ constexpr int kHeadDim = 128;
 constexpr int kMaxContext = 4096;     // src/lib.rs:18
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
-constexpr int kSplitKeys = 128;       // keys per CTA: 32 per warp
-constexpr int kMaxSplits = kMaxContext / kSplitKeys;  // 32 CTAs for the longest context
+constexpr int kStepKeys = 32;         // keys a warp stages and multiplies at a time
+constexpr int kWarpKeys = 128;        // consecutive keys per warp and item
+constexpr int kUnitKeys = kWarps * kWarpKeys;         // keys per item: 512
+constexpr int kMaxUnits = kMaxContext / kUnitKeys;    // 8 items for the longest context
 constexpr int kPitch = kHeadDim + 8;  // bf16 elements per staged row: 272 bytes, conflict-free for ldmatrix
-constexpr size_t kSmemBytes = (size_t)2 * kSplitKeys * kPitch * sizeof(uint16_t);  // keys + values: 68 KiB, three CTAs per SM
+constexpr size_t kSmemBytes = (size_t)2 * kWarps * kStepKeys * kPitch * sizeof(uint16_t);  // keys + values: 68 KiB, three CTAs per SM
 constexpr int kRecord = kHeadDim + 4;  // floats per (row, head, split) in the workspace: 128 sums, maximum, total, padding
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -64,19 +66,22 @@ __device__ __forceinline__ uint32_t transpose_8x8(uint32_t a) {
 }
 
 // A fixed number of CTAs (as many as the GPU holds at once, three per SM) of four warps each work through the launch's
-// items -- one item per (row, split of 128 keys, group of GH query heads that share a key/value head), found from the
+// items -- one item per (row, unit of 512 keys, group of GH query heads that share a key/value head), found from the
 // rows' positions by a prefix sum that every CTA computes for itself and handed out through a ticket counter, so rows
 // with short contexts cost nothing and the launch shape never depends on the positions (a captured graph replays for any
-// of them).  Per item every warp is an independent pipeline over 32 keys:
-//   stage    its 32 key rows and 32 value rows go to shared memory with 16-byte asynchronous copies (all of them in flight
-//            at once: 64 KiB per CTA)
+// of them).  Within an item every warp is an independent pipeline over its own 128 consecutive keys, 32 at a time:
+//   stage    32 key rows, then 32 value rows, go to the warp's part of shared memory with 16-byte asynchronous copies;
+//            the next step's keys are requested as soon as the scores of this step are computed and its values as soon
+//            as the second product is done, so copies and arithmetic overlap inside every warp (up to 192 KiB in flight
+//            per SM)
 //   scores   S^T = K . Q^T on mma.sync.m16n8k16 (bf16 x bf16 -> f32): the keys are the MMA's 16 rows, the GH query heads
 //            its 8 columns, so no tensor-core work is spent on absent rows; score = dot * 128^-0.5
-//   softmax  within the warp: maximum over its keys, e = exp(score - maximum) in the reference's ex2.approx form, total
-//   P.V      O^T = V^T . P^T on the same MMA: the value tile is read through ldmatrix.trans, each float32 weight enters
+//   softmax  running maximum and total per head (flash attention): e = exp(score - maximum) in the reference's
+//            ex2.approx form, earlier sums rescaled by exp(old maximum - new maximum)
+//   P.V      O^T += V^T . P^T on the same MMA: the value tile is read through ldmatrix.trans, each float32 weight enters
 //            as hi + lo, two bf16 numbers (hi = bf16(p), lo = bf16(p - hi)), moved from the accumulator layout of the
 //            first product to the operand layout of the second with movmatrix
-//   combine  (maximum, total, sums) of the four warps, then of the row's splits by the last CTA to arrive, with weights
+//   combine  (maximum, total, sums) of the four warps, then of the row's units by the last CTA to arrive, with weights
 //            exp(m - M) -- flash decoding.  No CTA ever waits for another.
 // The association depends on nothing but the row's context length.
 constexpr int kMaxRows = 256;  // rows per launch (the prefix sum over the rows lives in shared memory); the entry point cuts larger batches
@@ -91,18 +96,19 @@ __global__ void __launch_bounds__(kThreads, 3) attention_batched_kernel(const ty
                                                                         uint32_t *tickets, uint32_t *status) {
     extern __shared__ __align__(16) uint16_t tile_smem[];
     typedef uint16_t (*TilePtr)[kPitch];
-    TilePtr ks = reinterpret_cast<TilePtr>(tile_smem);
-    TilePtr vs = ks + kSplitKeys;
+    TilePtr ks = reinterpret_cast<TilePtr>(tile_smem);  // [4 warps][32 keys]
+    TilePtr vs = ks + kWarps * kStepKeys;
     __shared__ float warp_max[kWarps][8], warp_total[kWarps][8];
-    __shared__ float split_weight[8][kMaxSplits], split_den[8];
-    __shared__ int first_split[kMaxRows + 1];  // exclusive prefix sum of the rows' split counts
+    __shared__ float unit_weight[8][kMaxUnits], unit_den[8];
+    __shared__ int first_unit[kMaxRows + 1];  // exclusive prefix sum of the rows' unit counts
+    __shared__ int row_end[kMaxRows];         // visible keys per row
     __shared__ int scan_warp[kWarps];
     __shared__ uint32_t arrived, ticket[2];
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31, g = lane >> 2, tq = lane & 3;
     const int group = q_heads / kv_heads, chunks = group / GH;
     const int groups = kv_heads * chunks;  // head groups per row
 
-    // Work list: row r has ceil((positions[r] + 1) / 128) splits (none if its position lies beyond the cache: the row is
+    // Work list: row r has ceil((positions[r] + 1) / 512) units (none if its position lies beyond the cache: the row is
     // skipped and reported).  The positions were uploaded by the host before the step began, so they do not depend on the
     // preceding kernel and all of this runs before the dependency wait.
     {
@@ -116,8 +122,10 @@ __global__ void __launch_bounds__(kThreads, 3) attention_batched_kernel(const ty
                 const uint32_t end_u = positions[r] + 1u;
                 if (end_u > (uint32_t)capacity) {
                     if (blockIdx.x == 0) record_range_fault(status, end_u);
+                    row_end[r] = 0;
                 } else {
-                    n = ((int)end_u + kSplitKeys - 1) / kSplitKeys;
+                    n = ((int)end_u + kUnitKeys - 1) / kUnitKeys;
+                    row_end[r] = (int)end_u;
                 }
             }
             mine[i] = total;
@@ -136,15 +144,16 @@ __global__ void __launch_bounds__(kThreads, 3) attention_batched_kernel(const ty
 #pragma unroll
         for (int i = 0; i < kPer; ++i) {
             const int r = t * kPer + i;
-            if (r < rows) first_split[r] = base + mine[i];
+            if (r < rows) first_unit[r] = base + mine[i];
         }
-        if (t == kThreads - 1) first_split[rows] = base + total;  // rows beyond `rows` contributed nothing
+        if (t == kThreads - 1) first_unit[rows] = base + total;  // rows beyond `rows` contributed nothing
         __syncthreads();
     }
-    const uint32_t items = (uint32_t)first_split[rows] * (uint32_t)groups;
+    const uint32_t items = (uint32_t)first_unit[rows] * (uint32_t)groups;
     const size_t key_stride = (size_t)kv_heads * kHeadDim;
-    const int r0 = warp * 32;  // this warp's rows of the tile
+    const int r0 = warp * kStepKeys;  // this warp's rows of the two tiles
     float *mine_o = reinterpret_cast<float *>(&ks[r0][0]);  // [GH][128] partial sums, over this warp's key rows once read
+    const int part = lane & 15, half = lane >> 4;
 
     // Items are handed out through a ticket counter (tickets[0]; zero between launches), so a CTA that starts late or
     // runs on a slower SM simply takes fewer; which CTA computes an item has no influence on the result.  The counter
@@ -157,48 +166,44 @@ __global__ void __launch_bounds__(kThreads, 3) attention_batched_kernel(const ty
         const uint32_t item = ticket[turn];
         if (item >= items) break;
         if (t == 0) ticket[turn ^ 1] = atomicAdd(tickets, 1u);  // read after the barrier that ends this item
-        const int js = (int)(item / (uint32_t)groups), kvg = (int)(item % (uint32_t)groups);
+        const int ju = (int)(item / (uint32_t)groups), kvg = (int)(item % (uint32_t)groups);
         int row;
-        {  // the row whose range of splits holds js: the last r with first_split[r] <= js
+        {  // the row whose range of units holds ju: the last r with first_unit[r] <= ju
             int lo = 0, hi = rows;
             while (hi - lo > 1) {
                 const int mid = (lo + hi) >> 1;
-                if (first_split[mid] <= js) lo = mid; else hi = mid;
+                if (first_unit[mid] <= ju) lo = mid; else hi = mid;
             }
             row = lo;
         }
-        const int split = js - first_split[row];
-        const int splits = first_split[row + 1] - first_split[row];
+        const int unit = ju - first_unit[row];
+        const int units = first_unit[row + 1] - first_unit[row];
         const int kv = kvg / chunks, head0 = kv * group + (kvg % chunks) * GH;
-        const int end = (int)positions[row] + 1;
-        const int begin = split * kSplitKeys;
-        const int count = min(kSplitKeys, end - begin);  // 1 .. 128 keys of this item
-        const bool live = r0 < count;
-        const uint16_t *kc = k_cache + (size_t)row * cache_stride + (size_t)kv * kHeadDim;
-        const uint16_t *vc = v_cache + (size_t)row * cache_stride + (size_t)kv * kHeadDim;
+        const int end = row_end[row];
+        const int wbegin = unit * kUnitKeys + warp * kWarpKeys;             // this warp's first key
+        const int wcount = max(0, min(kWarpKeys, end - wbegin));            // and how many it has: 0 .. 128
+        const int nsteps = (wcount + kStepKeys - 1) / kStepKeys;
+        const uint16_t *kc = k_cache + (size_t)row * cache_stride + (size_t)kv * kHeadDim + (size_t)wbegin * key_stride + 8 * part;
+        const uint16_t *vc = v_cache + (size_t)row * cache_stride + (size_t)kv * kHeadDim + (size_t)wbegin * key_stride + 8 * part;
 
-        // 16 chunks of 16 bytes per row and cache: a half-warp copies one row, the warp two rows per step
-        if (live) {
-            const int part = lane & 15;
-            const uint16_t *ksrc = kc + (size_t)(begin + r0 + (lane >> 4)) * key_stride + 8 * part;
-            const uint16_t *vsrc = vc + (size_t)(begin + r0 + (lane >> 4)) * key_stride + 8 * part;
+        // 16 chunks of 16 bytes per row: a half-warp copies one row, the warp two rows per instruction
+        auto stage = [&](TilePtr tile, const uint16_t *src, int step) {
+            const uint16_t *p = src + (size_t)(step * kStepKeys + half) * key_stride;
 #pragma unroll 4
             for (int i = 0; i < 16; ++i) {
-                const int r = r0 + 2 * i + (lane >> 4);
-                if (r < count) {
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&ks[r][8 * part])), "l"(ksrc));
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&vs[r][8 * part])), "l"(vsrc));
-                } else {  // rows past the end: zeros, so that 0 * value stays 0 in the second product
-                    *reinterpret_cast<uint4 *>(&ks[r][8 * part]) = make_uint4(0, 0, 0, 0);
-                    *reinterpret_cast<uint4 *>(&vs[r][8 * part]) = make_uint4(0, 0, 0, 0);
-                }
-                ksrc += 2 * key_stride;
-                vsrc += 2 * key_stride;
+                const int r = 2 * i + half;
+                if (step * kStepKeys + r < wcount)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(&tile[r0 + r][8 * part])), "l"(p));
+                else  // rows past the end: zeros, so that 0 * value stays 0 in the second product
+                    *reinterpret_cast<uint4 *>(&tile[r0 + r][8 * part]) = make_uint4(0, 0, 0, 0);
+                p += 2 * key_stride;
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
-        }
+        };
         float m_w[2] = {-INFINITY, -INFINITY}, l_w[2] = {0.0f, 0.0f};  // this lane's two heads: 2 tq and 2 tq + 1
-        if (live) {
+        if (nsteps > 0) {
+            stage(ks, kc, 0);
+            stage(vs, vc, 0);
             // Q^T as the B operand: lane g holds head g (zeros beyond GH), 16 channels per step
             uint32_t qf[8][2];
             {
@@ -209,87 +214,110 @@ __global__ void __launch_bounds__(kThreads, 3) attention_batched_kernel(const ty
                     qf[s][1] = g < GH ? pack_bf16(T::load(qr + 16 * s + 8), T::load(qr + 16 * s + 9)) : 0u;
                 }
             }
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            __syncwarp();
-
-            // scores of 32 keys x GH heads, transposed: sc[mt] = keys r0 + 16 mt + {g, g + 8} x heads {2 tq, 2 tq + 1}
-            float sc[2][4];
-#pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) sc[mt][i] = 0.0f;
-            const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    uint32_t a[4];
-                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
-                                 : "r"(smem_addr(&ks[r0 + 16 * mt + a_row][16 * s + a_col])));
-                    mma_bf16(sc[mt], a, qf[s][0], qf[s][1]);
-                }
-            }
-            __syncwarp();  // the key rows are read: mine_o may overwrite them
-            // scale, mask, maximum over the warp's keys per head
-#pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int key = r0 + 16 * mt + g + 8 * (i >> 1), head = 2 * tq + (i & 1);
-                    sc[mt][i] = (key < count && head < GH) ? __fmul_rn(sc[mt][i], 0.08838834764831845f) : -INFINITY;
-                    m_w[i & 1] = fmaxf(m_w[i & 1], sc[mt][i]);
-                }
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                m_w[e] = fmaxf(m_w[e], __shfl_xor_sync(0xffffffffu, m_w[e], 4));
-                m_w[e] = fmaxf(m_w[e], __shfl_xor_sync(0xffffffffu, m_w[e], 8));
-                m_w[e] = fmaxf(m_w[e], __shfl_xor_sync(0xffffffffu, m_w[e], 16));
-            }
-            // weights (hi + lo) in the operand layout of the second product, and their totals
-            uint32_t ph[2][2], pl[2][2];
-#pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
-                float hi[4], lo[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float base = m_w[i & 1];
-                    const float p = base == -INFINITY ? 0.0f : exp_approx(__fadd_rn(sc[mt][i], -base));  // a masked score gives 0
-                    l_w[i & 1] = __fadd_rn(l_w[i & 1], p);
-                    hi[i] = bf16_rne(p);
-                    lo[i] = bf16_rne(__fadd_rn(p, -hi[i]));
-                }
-                ph[mt][0] = transpose_8x8(pack_bf16(hi[0], hi[1]));
-                ph[mt][1] = transpose_8x8(pack_bf16(hi[2], hi[3]));
-                pl[mt][0] = transpose_8x8(pack_bf16(lo[0], lo[1]));
-                pl[mt][1] = transpose_8x8(pack_bf16(lo[2], lo[3]));
-            }
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                l_w[e] = __fadd_rn(l_w[e], __shfl_xor_sync(0xffffffffu, l_w[e], 4));
-                l_w[e] = __fadd_rn(l_w[e], __shfl_xor_sync(0xffffffffu, l_w[e], 8));
-                l_w[e] = __fadd_rn(l_w[e], __shfl_xor_sync(0xffffffffu, l_w[e], 16));
-            }
-            // O^T = V^T . P^T: eight tiles of 16 channels, two steps of 16 keys
-            float o[8][4];
+            float o[8][4];  // channels 16 dt + {g, g + 8} x heads {2 tq, 2 tq + 1}, unnormalised
 #pragma unroll
             for (int dt = 0; dt < 8; ++dt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) o[dt][i] = 0.0f;
+            const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1), a_col = 8 * (lane >> 4);
             const int v_row = (lane & 7) + 8 * (lane >> 4), v_col = 8 * ((lane >> 3) & 1);
+
+            for (int step = 0; step < nsteps; ++step) {
+                // copies are committed in the order K0 V0 K1 V1 ...: one group may stay in flight behind the one needed
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+                __syncwarp();
+                // scores of 32 keys x GH heads, transposed: sc[mt] = keys 16 mt + {g, g + 8} x heads {2 tq, 2 tq + 1}
+                float sc[2][4];
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
+                for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-                for (int dt = 0; dt < 8; ++dt) {
-                    uint32_t a[4];
-                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
-                                 : "r"(smem_addr(&vs[r0 + 16 * mt + v_row][16 * dt + v_col])));
-                    mma_bf16(o[dt], a, ph[mt][0], ph[mt][1]);
-                    mma_bf16(o[dt], a, pl[mt][0], pl[mt][1]);
+                    for (int i = 0; i < 4; ++i) sc[mt][i] = 0.0f;
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt) {
+                        uint32_t a[4];
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                                     : "r"(smem_addr(&ks[r0 + 16 * mt + a_row][16 * s + a_col])));
+                        mma_bf16(sc[mt], a, qf[s][0], qf[s][1]);
+                    }
                 }
+                __syncwarp();  // the key rows are read
+                if (step + 1 < nsteps)
+                    stage(ks, kc, step + 1);
+                else
+                    asm volatile("cp.async.commit_group;" ::: "memory");  // keeps the group count in step
+                // scale, mask, running maximum per head
+                float m_new[2] = {m_w[0], m_w[1]};
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int key = step * kStepKeys + 16 * mt + g + 8 * (i >> 1), head = 2 * tq + (i & 1);
+                        sc[mt][i] = (key < wcount && head < GH) ? __fmul_rn(sc[mt][i], 0.08838834764831845f) : -INFINITY;
+                        m_new[i & 1] = fmaxf(m_new[i & 1], sc[mt][i]);
+                    }
+                float corr[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    m_new[e] = fmaxf(m_new[e], __shfl_xor_sync(0xffffffffu, m_new[e], 4));
+                    m_new[e] = fmaxf(m_new[e], __shfl_xor_sync(0xffffffffu, m_new[e], 8));
+                    m_new[e] = fmaxf(m_new[e], __shfl_xor_sync(0xffffffffu, m_new[e], 16));
+                    corr[e] = m_w[e] == -INFINITY ? 0.0f : exp_approx(__fadd_rn(m_w[e], -m_new[e]));  // nothing summed yet: 0
+                    l_w[e] = __fmul_rn(l_w[e], corr[e]);
+                    m_w[e] = m_new[e];
+                }
+#pragma unroll
+                for (int dt = 0; dt < 8; ++dt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o[dt][i] = __fmul_rn(o[dt][i], corr[i & 1]);
+                // weights (hi + lo) in the operand layout of the second product, and their totals (per lane for now)
+                uint32_t ph[2][2], pl[2][2];
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    float hi[4], lo[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float base = m_w[i & 1];
+                        const float p = base == -INFINITY ? 0.0f : exp_approx(__fadd_rn(sc[mt][i], -base));  // a masked score gives 0
+                        l_w[i & 1] = __fadd_rn(l_w[i & 1], p);
+                        hi[i] = bf16_rne(p);
+                        lo[i] = bf16_rne(__fadd_rn(p, -hi[i]));
+                    }
+                    ph[mt][0] = transpose_8x8(pack_bf16(hi[0], hi[1]));
+                    ph[mt][1] = transpose_8x8(pack_bf16(hi[2], hi[3]));
+                    pl[mt][0] = transpose_8x8(pack_bf16(lo[0], lo[1]));
+                    pl[mt][1] = transpose_8x8(pack_bf16(lo[2], lo[3]));
+                }
+                asm volatile("cp.async.wait_group 1;" ::: "memory");  // this step's values (the next keys may be in flight)
+                __syncwarp();
+                // O^T += V^T . P^T: eight tiles of 16 channels, two steps of 16 keys
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+#pragma unroll
+                    for (int dt = 0; dt < 8; ++dt) {
+                        uint32_t a[4];
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                                     : "r"(smem_addr(&vs[r0 + 16 * mt + v_row][16 * dt + v_col])));
+                        mma_bf16(o[dt], a, ph[mt][0], ph[mt][1]);
+                        mma_bf16(o[dt], a, pl[mt][0], pl[mt][1]);
+                    }
+                }
+                __syncwarp();  // the value rows are read
+                if (step + 1 < nsteps)
+                    stage(vs, vc, step + 1);
+                else
+                    asm volatile("cp.async.commit_group;" ::: "memory");
             }
-            // o[dt] = channels 16 dt + {g, g + 8} x heads {2 tq, 2 tq + 1}
+            asm volatile("cp.async.wait_group 0;" ::: "memory");  // only empty groups are left
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {  // the lanes that share a head hold partial totals
+                l_w[e] = __fadd_rn(l_w[e], __shfl_xor_sync(0xffffffffu, l_w[e], 4));
+                l_w[e] = __fadd_rn(l_w[e], __shfl_xor_sync(0xffffffffu, l_w[e], 8));
+                l_w[e] = __fadd_rn(l_w[e], __shfl_xor_sync(0xffffffffu, l_w[e], 16));
+            }
 #pragma unroll
             for (int dt = 0; dt < 8; ++dt)
 #pragma unroll
@@ -321,7 +349,7 @@ __global__ void __launch_bounds__(kThreads, 3) attention_batched_kernel(const ty
                 if (mw != -INFINITY) {  // a warp without keys left nothing behind
                     const float weight = exp_approx(__fadd_rn(mw, -top));
                     den = __fmaf_rn(warp_total[w][h], weight, den);
-                    sum = __fmaf_rn(reinterpret_cast<const float *>(&ks[32 * w][0])[h * kHeadDim + t], weight, sum);
+                    sum = __fmaf_rn(reinterpret_cast<const float *>(&ks[kStepKeys * w][0])[h * kHeadDim + t], weight, sum);
                 }
             }
             sums[h] = sum;
@@ -329,12 +357,12 @@ __global__ void __launch_bounds__(kThreads, 3) attention_batched_kernel(const ty
             dens[h] = den;
         }
         bool finish = true;
-        if (splits > 1) {
-            // leave (sums, maximum, total) of this split; the last split of the row's head group to arrive combines them
-            float *group_records = scratch + ((size_t)row * q_heads + head0) * kMaxSplits * kRecord;
+        if (units > 1) {
+            // leave (sums, maximum, total) of this unit; the last unit of the row's head group to arrive combines them
+            float *group_records = scratch + ((size_t)row * q_heads + head0) * kMaxUnits * kRecord;
 #pragma unroll
             for (int h = 0; h < GH; ++h) {
-                float *mine = group_records + ((size_t)h * kMaxSplits + split) * kRecord;
+                float *mine = group_records + ((size_t)h * kMaxUnits + unit) * kRecord;
                 mine[t] = sums[h];
                 if (t == 0) {
                     mine[kHeadDim] = tops[h];
@@ -347,43 +375,41 @@ __global__ void __launch_bounds__(kThreads, 3) attention_batched_kernel(const ty
                 uint32_t *counter = counters + (size_t)row * groups + kvg;
                 const uint32_t before = atomicAdd(counter, 1u);
                 arrived = before;
-                if (before == (uint32_t)splits - 1u) *counter = 0u;  // zero again for the next launch
+                if (before == (uint32_t)units - 1u) *counter = 0u;  // zero again for the next launch
             }
             __syncthreads();
-            finish = arrived == (uint32_t)splits - 1u;
+            finish = arrived == (uint32_t)units - 1u;
             if (finish) {
                 __threadfence();
-                // weights of the splits: one warp per head, lane = split (at most 32 splits)
+                // weights of the units: one warp per head, lane = unit (at most 8 units)
                 for (int h = warp; h < GH; h += kWarps) {
-                    const float *all = group_records + (size_t)h * kMaxSplits * kRecord;
-                    const float m = lane < splits ? __ldcg(all + lane * kRecord + kHeadDim) : -INFINITY;
-                    const float l = lane < splits ? __ldcg(all + lane * kRecord + kHeadDim + 1) : 0.0f;
+                    const float *all = group_records + (size_t)h * kMaxUnits * kRecord;
+                    const float m = lane < units ? __ldcg(all + lane * kRecord + kHeadDim) : -INFINITY;
+                    const float l = lane < units ? __ldcg(all + lane * kRecord + kHeadDim + 1) : 0.0f;
                     float top = m;
 #pragma unroll
                     for (int d = 16; d > 0; d >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, d));
-                    const float weight = lane < splits ? exp_approx(__fadd_rn(m, -top)) : 0.0f;
+                    const float weight = lane < units ? exp_approx(__fadd_rn(m, -top)) : 0.0f;
                     float den = __fmul_rn(l, weight);
 #pragma unroll
                     for (int d = 16; d > 0; d >>= 1) den = __fadd_rn(den, __shfl_xor_sync(0xffffffffu, den, d));
-                    split_weight[h][lane] = weight;
-                    if (lane == 0) split_den[h] = den;
+                    if (lane < kMaxUnits) unit_weight[h][lane] = weight;
+                    if (lane == 0) unit_den[h] = den;
                 }
                 __syncthreads();
-                // sums over the splits in split order, eight independent loads in flight; thread = channel
+                // sums over the units in unit order, all loads in flight at once; thread = channel
 #pragma unroll
                 for (int h = 0; h < GH; ++h) {
-                    const float *all = group_records + (size_t)h * kMaxSplits * kRecord + t;
+                    const float *all = group_records + (size_t)h * kMaxUnits * kRecord + t;
+                    float v[kMaxUnits];
+#pragma unroll
+                    for (int i = 0; i < kMaxUnits; ++i) v[i] = i < units ? __ldcg(all + i * kRecord) : 0.0f;
                     float sum = 0.0f;
-                    for (int s0 = 0; s0 < splits; s0 += 8) {
-                        float v[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) v[i] = s0 + i < splits ? __ldcg(all + (s0 + i) * kRecord) : 0.0f;
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            if (s0 + i < splits) sum = __fmaf_rn(v[i], split_weight[h][s0 + i], sum);
-                    }
+                    for (int i = 0; i < kMaxUnits; ++i)
+                        if (i < units) sum = __fmaf_rn(v[i], unit_weight[h][i], sum);
                     sums[h] = sum;
-                    dens[h] = split_den[h];
+                    dens[h] = unit_den[h];
                 }
             }
         }
@@ -400,7 +426,7 @@ __global__ void __launch_bounds__(kThreads, 3) attention_batched_kernel(const ty
                 if (lane == 0) atomicMax(maxima + row, row_max);
             }
         }
-        __syncthreads();  // the tile and the per-warp slots are free for the next item; the next ticket has been written
+        __syncthreads();  // the tiles and the per-warp slots are free for the next item; the next ticket has been written
     }
     // every CTA draws exactly one ticket beyond the last item; the CTA that leaves last returns both counters to zero
     if (t == 0) {
@@ -486,7 +512,7 @@ size_t ticket_bytes(int rows) { return ((((size_t)(rows + kMaxRows - 1) / kMaxRo
 size_t counter_bytes(int rows, int q_heads) { return (((size_t)rows * q_heads * sizeof(uint32_t)) + 255) & ~(size_t)255; }
 size_t workspace_bytes(int rows, int q_heads, int kv_heads) {
     (void)kv_heads;
-    return ticket_bytes(rows) + counter_bytes(rows, q_heads) + (size_t)rows * q_heads * kMaxSplits * kRecord * sizeof(float);
+    return ticket_bytes(rows) + counter_bytes(rows, q_heads) + (size_t)rows * q_heads * kMaxUnits * kRecord * sizeof(float);
 }
 
 template <class T, int GH>
@@ -504,7 +530,7 @@ cudaError_t launch_batched(const void *q, int64_t ldq, int rows, int q_heads, in
         if (e != cudaSuccess) return e;
         per_sm = n > 0 ? n : 1;
     }
-    const long long most = (long long)rows * kv_heads * ((q_heads / kv_heads) / GH) * ((capacity + kSplitKeys - 1) / kSplitKeys);
+    const long long most = (long long)rows * kv_heads * ((q_heads / kv_heads) / GH) * ((capacity + kUnitKeys - 1) / kUnitKeys);
     const dim3 grid((unsigned)std::min<long long>(most, (long long)per_sm * sm_count()));
     return launch_kernel(attention_batched_kernel<T, GH>, grid, dim3(kThreads), kSmemBytes, s, (const S *)q, ldq, rows, q_heads, kv_heads, k_cache,
                          v_cache, cache_stride, positions, (S *)out, ldo, capacity, maxima, scratch, counters, tickets, device_status_ptr());
@@ -581,10 +607,10 @@ int qwen3_attention_batched(const void *q, int dtype, int64_t ldq, int rows, int
         uint32_t *mc = maxima ? maxima + r0 : nullptr;
         cudaError_t e = dtype == W8A8_BF16
                             ? launch_batched_any<Bf16>(qc, ldq, n, q_heads, kv_heads, kc, vc, cache_stride, positions + r0, oc, ldo, capacity,
-                                                       mc, counters + (size_t)r0 * q_heads, scratch + (size_t)r0 * q_heads * kMaxSplits * kRecord,
+                                                       mc, counters + (size_t)r0 * q_heads, scratch + (size_t)r0 * q_heads * kMaxUnits * kRecord,
                                                        tickets + 2 * (r0 / kMaxRows), (cudaStream_t)stream)
                             : launch_batched_any<F32>(qc, ldq, n, q_heads, kv_heads, kc, vc, cache_stride, positions + r0, oc, ldo, capacity,
-                                                      mc, counters + (size_t)r0 * q_heads, scratch + (size_t)r0 * q_heads * kMaxSplits * kRecord,
+                                                      mc, counters + (size_t)r0 * q_heads, scratch + (size_t)r0 * q_heads * kMaxUnits * kRecord,
                                                       tickets + 2 * (r0 / kMaxRows), (cudaStream_t)stream);
         if (e != cudaSuccess) return fail_cuda(e, "batched attention launch");
     }

@@ -40,20 +40,24 @@ __device__ __forceinline__ int round_i8(float x) {
 }
 
 // q = round_i8(x / s) with one multiply instead of one IEEE division per element, bit-identical to the
-// division the reference performs (src/kernels.rs:448: round(div(x, s))).
+// division the reference performs (src/kernels.rs:448: round(div(x, s))), and without the two conversion-unit
+// instructions (floor, float -> int) that made the quantizers issue-bound on that unit.
 // inv = rcp.rn(s) is computed once per row.  t = x * inv differs from the true quotient by at most
 // (1 + 2^-24)^2 - 1 < 1.2e-7 relative, i.e. by less than 1.6e-5 for |t| <= 127, and the correctly rounded
 // quotient differs from the true one by at most half an ulp (3.8e-6 below 128).  Two numbers that close
 // round to different integers only if a rounding boundary k + 0.5 lies between or on them, so whenever t is
-// farther than 4e-5 from every k + 0.5 both round alike; otherwise (about one element in 12 000, and for
-// NaN / infinity, whose distance test is false) the exact division decides.  Values beyond +-127 clamp to
-// the same code either way.
+// farther than 4e-5 from every k + 0.5 both round alike; otherwise (about one element in 12 000) the exact
+// division decides.  Values beyond +-127 (infinities included) clamp to the same code either way; NaN gives 0.
+// Rounding: c + 1.5 * 2^23 has an ulp of 1, so the addition rounds c (|c| <= 127) to the nearest even integer
+// and leaves that integer in the low mantissa bits; subtracting the constant again gives it back as a float.
 __device__ __forceinline__ int quant_code(float x, float s, float inv) {
     const float t = __fmul_rn(x, inv);
-    const float a = fabsf(t);
-    const float fr = a - floorf(a);
-    if (fabsf(fr - 0.5f) > 4e-5f) return round_i8(t);
-    return round_i8(__fdiv_rn(x, s));
+    const float c = fminf(fmaxf(t, -127.0f), 127.0f);  // a NaN becomes -127 here and is put right below
+    const float y = __fadd_rn(c, 12582912.0f);
+    const float r = __fadd_rn(y, -12582912.0f);        // rne(c)
+    if (fabsf(__fadd_rn(c, -r)) > 0.49996f) return round_i8(__fdiv_rn(x, s));
+    const int code = __float_as_int(y) - 0x4B400000;
+    return t == t ? code : 0;
 }
 
 // exp(x) as the reference writes it: ex2.approx(x * log2(e)) (src/kernels.rs:21-23).
@@ -169,15 +173,20 @@ __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) { return __reduce_m
 
 // ---- shared by the standalone quantizers and the quantizing GEMV prologue ------------------------------------
 template <int N> __device__ __forceinline__ void store_codes(int8_t *dst, const int (&c)[N]);
+// the low bytes of four ints as one word (three byte permutes)
+__device__ __forceinline__ uint32_t pack_codes4(int c0, int c1, int c2, int c3) {
+    const uint32_t lo = __byte_perm((uint32_t)c0, (uint32_t)c1, 0x0040);  // bytes: c0.0 c1.0 . .
+    const uint32_t hi = __byte_perm((uint32_t)c2, (uint32_t)c3, 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
+}
 template <> __device__ __forceinline__ void store_codes<8>(int8_t *dst, const int (&c)[8]) {
     uint2 p;
-    p.x = (c[0] & 0xff) | ((c[1] & 0xff) << 8) | ((c[2] & 0xff) << 16) | ((uint32_t)c[3] << 24);
-    p.y = (c[4] & 0xff) | ((c[5] & 0xff) << 8) | ((c[6] & 0xff) << 16) | ((uint32_t)c[7] << 24);
+    p.x = pack_codes4(c[0], c[1], c[2], c[3]);
+    p.y = pack_codes4(c[4], c[5], c[6], c[7]);
     *reinterpret_cast<uint2 *>(dst) = p;
 }
 template <> __device__ __forceinline__ void store_codes<4>(int8_t *dst, const int (&c)[4]) {
-    *reinterpret_cast<uint32_t *>(dst) =
-        (c[0] & 0xff) | ((c[1] & 0xff) << 8) | ((c[2] & 0xff) << 16) | ((uint32_t)c[3] << 24);
+    *reinterpret_cast<uint32_t *>(dst) = pack_codes4(c[0], c[1], c[2], c[3]);
 }
 
 // Block-wide maximum of non-negative floats (compared as unsigned bit patterns); up to 32 warps.

@@ -8,12 +8,15 @@
 //   swiglu              src/kernels.rs:2172-2190 act = bf16((g/(1+exp(-g)))*u) (+ absmax publish)
 //   residual            src/kernels.rs:2163-2170 bf16(a+b)
 //
-// Design here: one 256-thread CTA per token row, 128-bit global loads, the row parked in
-// shared memory as f32 between the passes (so the row is read from HBM exactly once),
-// warp-level redux for the absmax, a multiply with an exact-division fallback near rounding ties
-// (quant_code, bit-identical to the reference's per-element division), 4/8 int8 codes packed per store.  The sum of squares follows the reference's fixed tree (256 strided partials, then
-// distances 128..1) so that the bf16 norm row can match the reference bit for bit wherever
-// rsqrt.approx does.
+// Design here: one CTA per token row (256 or 512 threads; 1024 for a few rows), 128-bit global loads, the row kept
+// in registers between the absmax pass and the coding pass (so it is read from HBM exactly once), warp-level
+// redux for the absmax, a multiply with an exact-division fallback near rounding ties (quant_code,
+// bit-identical to the reference's per-element division, no conversion-unit instructions), 4/8 int8 codes
+// packed per store.  The sum of squares follows the reference's fixed tree (256 strided partials over a
+// swizzled shared-memory copy of x, then distances 128..1) so that the bf16 norm row can match the reference
+// bit for bit wherever rsqrt.approx does.  At thousands of rows these kernels are bound by instruction issue,
+// not by HBM: requesting the next row ahead of time changed nothing, and the counters show two thirds of the
+// cycles issuing with no pipe above 55 %.
 #include "common.cuh"
 #include "internal.h"
 
@@ -103,9 +106,20 @@ __global__ void __launch_bounds__(THREADS) quantize_rows_reg_kernel(const QuantD
             __syncthreads();
             if (tid < 256) {  // 256 strided partial sums, each added in index order (src/kernels.rs:508-519)
                 float s = 0.0f;
-                for (int j = tid; j < K; j += 256) {
-                    const float x = row[swz(j)];
-                    s = __fadd_rn(s, __fmul_rn(x, x));
+                constexpr int kFull = RV * THREADS * V;  // the widest row of this instance
+                if (K == kFull) {
+                    // all loads first, then the chain of additions: swz(tid + 256 i) = swz(tid) + 256 i
+                    const float *mine = row + swz(tid);
+                    float x[kFull / 256];
+#pragma unroll
+                    for (int i = 0; i < kFull / 256; ++i) x[i] = mine[256 * i];
+#pragma unroll
+                    for (int i = 0; i < kFull / 256; ++i) s = __fadd_rn(s, __fmul_rn(x[i], x[i]));
+                } else {
+                    for (int j = tid; j < K; j += 256) {
+                        const float x = row[swz(j)];
+                        s = __fadd_rn(s, __fmul_rn(x, x));
+                    }
                 }
                 red[tid] = s;
             }

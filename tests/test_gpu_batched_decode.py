@@ -32,8 +32,8 @@ def random_caches(rng, sequences, capacity, kv_heads):
 
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 @pytest.mark.parametrize("qh,kvh,positions", [
-    (32, 8, [0, 31, 32, 127, 128, 700, 1024, 1025, 2047]),   # one warp, one split, exact multiples, a split of one key
-    (8, 2, [5, 4095, 300]),                                  # the longest context: 32 splits of 128 keys
+    (32, 8, [0, 31, 32, 127, 128, 511, 512, 700, 1024, 1025, 2047]),   # one step, one warp, one unit, exact multiples, a unit of one key
+    (8, 2, [5, 4095, 300]),                                  # the longest context: 8 units of 512 keys
     (16, 2, [77, 1500]),                                     # eight query heads per key/value head
     (4, 4, [90, 91]),                                        # one query head per key/value head
     (6, 3, [513, 2]),                                        # two query heads per key/value head
@@ -78,9 +78,9 @@ def test_attention_batched_workspace_counters_only(ops):
 
     rng = np.random.default_rng(5)
     rows, qh, kvh = 3, 8, 2
-    _, _, kc, vc = random_caches(rng, rows, 512, kvh)
+    _, _, kc, vc = random_caches(rng, rows, 2048, kvh)
     qd = to_dev(oracle.bf16(rng.standard_normal((rows, qh * 128)).astype(np.float32)), "bf16")
-    pos = to_dev(np.array([400, 70, 3], np.uint32))
+    pos = to_dev(np.array([1400, 70, 3], np.uint32))  # the first row has three units, whose partial results meet in the workspace
     ws = ops.attention_batched_workspace(rows, qh, kvh)
     out = torch.empty((rows, qh * 128), dtype=torch.bfloat16, device="cuda")
     ops.attention_batched(qd, qh, kvh, kc, vc, pos, out, ws)
