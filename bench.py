@@ -506,6 +506,7 @@ def run_ours(args):
     if world == 1 and not args.no_extra:
         extra["per_shape"] = per_shape_table(torch, ops, mats, bufs, hbm_peak, args.variant)
         extra["prefill"] = prefill_table(torch, ops, mats, args.prefill_variant)
+        extra["roofline_prefill"] = prefill_roofline(extra["prefill"], hbm_peak)
         if not args.shapes:
             extra["quantizers"] = quantizer_table(torch, ops, hbm_peak)
             extra["decode_fused_kernels"] = decode_fused_table(torch, ops, hbm_peak)
@@ -595,6 +596,40 @@ def prefill_table(torch, ops, mats, variant=0):
             del x, q, s, y
     del flush
     return rows
+
+
+INT8_NOMINAL_TOPS = 4500.0  # dense INT8 tensor peak of a B200 (no measured INT8 figure is available)
+
+
+def prefill_roofline(rows, hbm_peak):
+    """The tensor-core regime beside the headline's HBM roofline: per (M, projection) the time against
+    max(ops / INT8 peak, algorithmic bytes / HBM peak), and which of the two terms binds.  At 129 rows every
+    projection is bound by the one pass over its weights (about 240 ops per byte against a ridge of 560 or more); from
+    512 rows up by the tensor cores.  Peaks: 4500 TOPS nominal dense INT8, and for comparison twice the measured bf16
+    cuBLAS burst; the HBM peak is the measured copy rate."""
+    _, bf16_tflops, kind = measured_peaks()
+    shapes = {n: (K, N) for n, K, N in SHAPES}
+    per_shape, best = [], None
+    for r in rows:
+        K, N = shapes[r["shape"]]
+        M, us = r["M"], r["us"]
+        ops_total = 2.0 * M * N * K
+        t_tensor = ops_total / (INT8_NOMINAL_TOPS * 1e12) * 1e6
+        t_hbm = linear_bytes(M, K, N) / (hbm_peak * 1e9) * 1e6
+        bound = "tensor" if t_tensor >= t_hbm else "hbm"
+        row = {"shape": r["shape"], "M": M, "us": us, "TOPS": r["TOPS"], "GB/s": r["GB/s"], "bound": bound,
+               "floor_us": round(max(t_tensor, t_hbm), 2), "frac": round(max(t_tensor, t_hbm) / us, 3),
+               "frac_of_2x_measured_bf16": round(r["TOPS"] / (2 * bf16_tflops), 3) if bf16_tflops else None}
+        per_shape.append(row)
+        if bound == "tensor" and (best is None or ops_total > best[0]):
+            best = (ops_total, row)
+    top = best[1] if best else None
+    return {"bound": "tensor", "kernel": "gemm_tcgen05_pair (tcgen05.mma.cta_group::2.kind::i8)",
+            "achieved": top and top["TOPS"], "peak": INT8_NOMINAL_TOPS, "peak_kind": "nominal dense INT8", "unit": "TOPS",
+            "frac": top and round(top["TOPS"] / INT8_NOMINAL_TOPS, 4), "shape": top and f'{top["shape"]} at M={top["M"]}',
+            "twice_measured_bf16_tflops": round(2 * bf16_tflops, 1), "bf16_peak_kind": kind,
+            "timing": "median of 5 launches, CUDA events, L2 displaced by a 256 MB read before every launch",
+            "per_shape": per_shape}
 
 
 def quantizer_table(torch, ops, hbm_peak):
@@ -745,20 +780,37 @@ def config4_table(torch, weights, config, hbm_peak, rank, world, group, fused_al
     # a sequence must be able to grow by the decode steps that are timed: the longest contexts start that many tokens short
     prompt_lens = [min(n, full.context - total_steps - 1) for n in contexts]
     prompts = [[int(t) for t in rng.integers(0, full.vocab, n)] for n in prompt_lens]
-    runner = Qwen3Runner(weights, group=group, fused_allreduce=fused_allreduce, batch=sequences)
-    runner.generate_batch(prompts, 2)  # captures the step graph; also the first check of the exchange at 64 rows
-    if world > 1 and fused_allreduce:
-        from inferrous_b200 import ops as _ops
-        expired = torch.tensor([float(_ops.device_status()[0] != 0)], device="cuda")
-        dist.all_reduce(expired, op=dist.ReduceOp.MAX, group=group)
-        if expired.item() > 0:
-            fused_allreduce = False
-            runner = Qwen3Runner(weights, group=group, fused_allreduce=False, batch=sequences)
-    tokens, seconds = runner.generate_batch(prompts, 1 + total_steps)
+    def run(**kw):
+        runner = Qwen3Runner(weights, group=group, batch=sequences, **kw)
+        runner.generate_batch(prompts, 2)  # captures the step graph; also the first check of the exchange at 64 rows
+        ok = True
+        if world > 1 and kw.get("fused_allreduce", True):
+            from inferrous_b200 import ops as _ops
+            expired = torch.tensor([float(_ops.device_status()[0] != 0)], device="cuda")
+            dist.all_reduce(expired, op=dist.ReduceOp.MAX, group=group)
+            ok = expired.item() == 0
+        toks, secs = runner.generate_batch(prompts, 1 + total_steps)
+        if world > 1:
+            slowest = torch.tensor(secs, dtype=torch.float64, device="cuda")
+            dist.all_reduce(slowest, op=dist.ReduceOp.MAX, group=group)
+            secs = slowest.tolist()
+        del runner
+        torch.cuda.empty_cache()
+        return ok, toks, secs
+
+    # Under tensor parallelism the sum after O and down is timed both ways at 64 rows: fused into the projection (tagged
+    # packets to every rank) and as projection + NCCL all-reduce + residual kernel; the step reports the faster one.
+    exchange_ms = {}
+    ok, tokens, seconds = run(fused_allreduce=False) if world > 1 else run()
+    exchange = "NCCL all-reduce" if world > 1 else "single GPU"
     if world > 1:
-        slowest = torch.tensor(seconds, dtype=torch.float64, device="cuda")
-        dist.all_reduce(slowest, op=dist.ReduceOp.MAX, group=group)
-        seconds = slowest.tolist()
+        exchange_ms["nccl"] = round(float(np.median(seconds[1 + warm:])) * 1e3, 4)
+        if fused_allreduce:
+            ok_f, tokens_f, seconds_f = run(fused_allreduce=True, peer_rows_times_ranks=1 << 30)
+            if ok_f:
+                exchange_ms["fused_packets"] = round(float(np.median(seconds_f[1 + warm:])) * 1e3, 4)
+                if exchange_ms["fused_packets"] < exchange_ms["nccl"]:
+                    tokens, seconds, exchange = tokens_f, seconds_f, "fused into the O / down projections over peer memory"
     decode = seconds[1 + warm:]
     median = float(np.median(decode))
     # keys visible to step s of the timed region: prompt + warm + s + 1 per sequence (the new token's own key included)
@@ -771,9 +823,8 @@ def config4_table(torch, weights, config, hbm_peak, rank, world, group, fused_al
               "tok_s": round(sequences * len(decode) / sum(decode), 1),
               "bytes_per_step": step_bytes, "kv_bytes_per_step": kv_bytes,
               "GB/s": round(step_bytes / median / 1e9, 1), "frac_hbm": round(step_bytes / median / 1e9 / (hbm_peak * world), 3),
-              "distinct_first_tokens": len({t[0] for t in tokens})}
-    del runner
-    torch.cuda.empty_cache()
+              "distinct_first_tokens": len({t[0] for t in tokens}), "all_reduce": exchange,
+              "decode_ms_per_step_by_exchange": exchange_ms or None}
 
     # (ii) one prefill of 4096 tokens, every position of the context
     runner = Qwen3Runner(weights, group=group, fused_allreduce=fused_allreduce)
@@ -802,7 +853,6 @@ def config4_table(torch, weights, config, hbm_peak, rank, world, group, fused_al
     torch.cuda.empty_cache()
     return {"workload": "configs[4]: 64 ragged sequences decoded side by side; one 4096-token prefill",
             "parallelism": f"tp{world}" if world > 1 else "single",
-            "all_reduce": ("fused into the O / down projections over peer memory" if fused_allreduce else "NCCL all-reduce") if world > 1 else "single GPU",
             "ragged_decode": ragged, "prefill_4096": prefill}
 
 

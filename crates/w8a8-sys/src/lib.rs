@@ -83,6 +83,7 @@ extern "C" {
     pub fn qwen3_attention_batched_workspace(rows: c_int, q_heads: c_int, kv_heads: c_int) -> usize;
     pub fn qwen3_attention_batched(q: *const c_void, dtype: c_int, ldq: i64, rows: c_int, q_heads: c_int, kv_heads: c_int, k_cache: *const u16, v_cache: *const u16, cache_stride: i64, positions: *const u32, out: *mut c_void, ldo: i64, capacity: c_int, maxima: *mut u32, workspace: *mut c_void, workspace_size: usize, stream: *mut c_void) -> c_int;
     pub fn qwen3_select_token(logits: *const c_void, dtype: c_int, rows: c_int, n: c_int, ld: i64, token: *mut u32, value: *mut f32, stream: *mut c_void) -> c_int;
+    pub fn qwen3_head_bf16(x: *const c_void, dtype: c_int, w: *const u16, vocab: c_int, hidden: c_int, logits: *mut c_void, token: *mut u32, value: *mut f32, stream: *mut c_void) -> c_int;
     pub fn qwen3_merge_candidates(candidates: *const u32, parts: c_int, rows: c_int, part_width: c_int, token: *mut u32, stream: *mut c_void) -> c_int;
     pub fn qwen3_attention_use_tensor_cores(enabled: c_int) -> c_int;
 }

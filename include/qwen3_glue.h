@@ -98,6 +98,18 @@ int qwen3_attention_batched(const void *q, int dtype, int64_t ldq, int rows, int
  * finite.  `value` (optional) receives the winning logit. */
 int qwen3_select_token(const void *logits, int dtype, int rows, int n, int64_t ld, uint32_t *token, float *value, void *stream);
 
+/* The reference's own output head, `head` / `head_packed` (src/kernels.rs:2233-2373; launched at src/gpu.rs:801-809) with
+ * `select_token` (src/kernels.rs:2191-2231; :811) fused in: logit[n] = bf16(sum_k x[k] * w[n, k]) for ONE row x of `hidden`
+ * values (the final norm of the last position) against bf16 weights w [vocab, hidden] (bit patterns; the checkpoint keeps
+ * the head unquantized, tools/prepare.py:99), the float32 sum taken in the reference's order -- lane-strided columns, then a
+ * shuffle-down tree -- so the logits are bit-identical to the reference kernel's.  `logits` (optional, [vocab] in the
+ * carrier `dtype`) receives them; `token` (optional) the greedy selection (largest value, lowest index among equals,
+ * 0xffffffff if a logit is not finite) and `value` its logit; at least one of `logits` and `token` is required.
+ * vocab <= 262144.  Calls that select a token share one per-device candidate buffer with w8a8_linear_argmax: keep them
+ * in order. */
+int qwen3_head_bf16(const void *x, int dtype, const uint16_t *w, int vocab, int hidden, void *logits, uint32_t *token,
+                    float *value, void *stream);
+
 /* Vocabulary split over `parts` ranks (no counterpart in the reference, which is single-GPU): candidates is
  * [parts][2][rows] = per part, `rows` tokens within the part and then the float32 bits of their logits (the `token` and
  * `value` outputs of w8a8_linear_argmax or qwen3_select_token side by side), gathered from the ranks in rank order;

@@ -13,10 +13,11 @@ Every tensor's shape, dtype and sha256 are checked against the manifest, as the 
 loader, which accepts the Qwen3-8B dimensions only, the dimensions are taken from the manifest's `config` (head width
 128 and the operator set are still required), so that small bundles can be used in tests.
 
-What this loader does beyond copying: Q, K, V (and gate, up) are concatenated along the output dimension, the gains
-of the hidden-width norms are converted to the activation dtype (they are bf16 values in the checkpoint), and the bf16
-head is quantized per output channel with the formula the bundle's other matrices were quantized with
-(tools/prepare.py:79-81), because the forward pass here runs a W8A8 head.
+What this loader does beyond copying: Q, K, V (and gate, up) are concatenated along the output dimension and the gains
+of the hidden-width norms are converted to the activation dtype (they are bf16 values in the checkpoint).  The head stays
+bf16, as the reference runs it (`head="bf16"`, the default); `head="w8a8"` instead quantizes it per output channel with
+the formula the bundle's other matrices were quantized with (tools/prepare.py:79-81) -- the benchmark's W8A8 lm_head,
+whose logits differ from the reference's.
 """
 from __future__ import annotations
 
@@ -94,7 +95,9 @@ def quantize_rows(w: torch.Tensor):
     return q, scale.flatten().contiguous()
 
 
-def load_bundle(path, device="cuda", verify_hashes: bool = True) -> Qwen3Weights:
+def load_bundle(path, device="cuda", verify_hashes: bool = True, head: str = "bf16") -> Qwen3Weights:
+    if head not in ("bf16", "w8a8", "both"):
+        raise ValueError("head must be 'bf16', 'w8a8' or 'both'")
     b = Bundle(path, verify_hashes)
     c = b.config
     act = torch.bfloat16
@@ -124,7 +127,9 @@ def load_bundle(path, device="cuda", verify_hashes: bool = True) -> Qwen3Weights
         layers.append(Layer(c, dev(gain("norm1", c.hidden), act), qkv, qkv_s, dev(gain("qnorm", 128)), dev(gain("knorm", 128)),
                             o, o_s, dev(gain("norm2", c.hidden), act), gate_up, gate_up_s, down, down_s))
     embedding = bf16(b.tensor("embedding", "<u2", (c.vocab, c.hidden)))
-    head, head_s = quantize_rows(bf16(b.tensor("head", "<u2", (c.vocab, c.hidden))))
-    weights = Qwen3Weights(c, embedding, layers, dev(b.tensor("final_gain", "<f4", (c.hidden,)), act), head, head_s, device)
+    head_bits = bf16(b.tensor("head", "<u2", (c.vocab, c.hidden)))
+    head_q, head_s = quantize_rows(head_bits) if head in ("w8a8", "both") else (None, None)
+    weights = Qwen3Weights(c, embedding, layers, dev(b.tensor("final_gain", "<f4", (c.hidden,)), act), head_q, head_s, device,
+                           head_bf16=head_bits.contiguous() if head in ("bf16", "both") else None)
     weights.rope = dev(b.tensor("rope", "<f4", (c.context, 128)))  # the bundle's table, not a recomputed one
     return weights

@@ -50,6 +50,7 @@ SIGNATURES = {
     "qwen3_prepare_qk_batched": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _vp]),
     "qwen3_attention_batched_workspace": (_sz, [_i, _i, _i]),
     "qwen3_attention_batched": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _i64, _vp, _vp, _i64, _i, _vp, _vp, _sz, _vp]),
+    "qwen3_head_bf16": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp]),
     "qwen3_select_token": (_i, [_vp, _i, _i, _i, _i64, _vp, _vp, _vp]),
     "qwen3_merge_candidates": (_i, [_vp, _i, _i, _i, _vp, _vp]),
     "qwen3_attention_use_tensor_cores": (_i, [_i]),

@@ -193,6 +193,7 @@ int w8a8_init(int device) {
     CUDA_OK(init_gemm_skinny(), "init_gemm_skinny");
     CUDA_OK(init_forward_glue(), "init_forward_glue");
     CUDA_OK(init_batched_decode(), "init_batched_decode");
+    CUDA_OK(init_head_bf16(), "init_head_bf16");
     d.ready = true;
     return W8A8_OK;
 }

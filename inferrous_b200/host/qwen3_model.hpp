@@ -10,8 +10,9 @@
 // Like the reference: f32 activation buffers holding bf16 values, one stream, caller-visible errors instead of traps,
 // {token, position} uploaded and the selected token read back every step.
 // Unlike the reference: Q|K|V are one concatenated matrix (identical channel for channel with per-channel scales); the
-// head is quantized per output channel when the bundle is loaded (tools/prepare.py:79-81) and runs as a W8A8
-// projection with the selection fused (w8a8_linear_argmax); sha256 digests of the manifest are not verified here (the
+// head runs as the reference's bf16 head with the selection fused (qwen3_head_bf16; logits bit-identical to `head`,
+// src/kernels.rs:2233-2257) or, on request (HeadKind::W8A8), quantized per output channel when the bundle is loaded
+// (tools/prepare.py:79-81) as a W8A8 projection (w8a8_linear_argmax); sha256 digests of the manifest are not verified here (the
 // Python reader does), only names, sizes, finiteness and the weight checks of src/model.rs:143-145.
 #pragma once
 
@@ -93,6 +94,8 @@ inline float widen(uint16_t b) {
 }
 }  // namespace detail
 
+enum class HeadKind { Bf16, W8A8 };
+
 // Host copy of a bundle (src/model.rs `Model`, without the tokenizer).
 struct Qwen3Bundle {
     struct LayerTensors {
@@ -102,11 +105,12 @@ struct Qwen3Bundle {
     };
     Qwen3Config config;
     std::vector<uint16_t> embedding;
-    std::vector<int8_t> head;
+    std::vector<uint16_t> head_bf16;  // HeadKind::Bf16: the checkpoint's head as it is
+    std::vector<int8_t> head;         // HeadKind::W8A8: its per-channel int8 quantization
     std::vector<float> head_scale, final_gain, rope;
     std::vector<LayerTensors> layers;
 
-    static Qwen3Bundle load(const std::string &dir) {
+    static Qwen3Bundle load(const std::string &dir, HeadKind head_kind = HeadKind::Bf16) {
         using namespace detail;
         const std::string manifest = slurp(dir + "/manifest.json");
         if (json_uint(manifest, "format_version") != 1) throw std::runtime_error("unsupported bundle format version");
@@ -124,8 +128,10 @@ struct Qwen3Bundle {
         b.embedding = read_tensor<uint16_t>(dir, "embedding", V * H);
         b.final_gain = read_floats(dir, "final_gain", H);
         b.rope = read_floats(dir, "rope", (size_t)c.context * 128);
-        // W8A8 head: per-output-channel symmetric int8 of the bf16 head (the formula of tools/prepare.py:79-81)
-        {
+        if (head_kind == HeadKind::Bf16) {
+            b.head_bf16 = read_tensor<uint16_t>(dir, "head", V * H);
+        } else {
+            // W8A8 head: per-output-channel symmetric int8 of the bf16 head (the formula of tools/prepare.py:79-81)
             const auto head = read_tensor<uint16_t>(dir, "head", V * H);
             b.head.resize(V * H);
             b.head_scale.resize(V);
@@ -192,8 +198,12 @@ class Qwen3Model {
     explicit Qwen3Model(const Qwen3Bundle &b, int device = 0)
         : c_(b.config), gpu_(device), embedding_(DeviceBuffer<uint16_t>::from_host(b.embedding)),
           final_gain_(Buffer::from_host(b.final_gain)), rope_(Buffer::from_host(b.rope)),
-          head_(b.head, b.head_scale, b.config.vocab, b.config.hidden), control_(DeviceBuffer<uint32_t>::zeroed(2)),
-          next_(DeviceBuffer<uint32_t>::zeroed(1)), head_q_(b.config.hidden), head_scale_(1), decode_(b.config, 1) {
+          control_(DeviceBuffer<uint32_t>::zeroed(2)), next_(DeviceBuffer<uint32_t>::zeroed(1)), head_q_(b.config.hidden),
+          head_scale_(1), head_x_(b.config.hidden), decode_(b.config, 1) {
+        if (!b.head_bf16.empty())
+            head_bf16_ = DeviceBuffer<uint16_t>::from_host(b.head_bf16);
+        else
+            head_ = std::make_unique<Matrix>(b.head, b.head_scale, b.config.vocab, b.config.hidden);
         for (const auto &t : b.layers) {
             auto l = std::make_unique<Layer>(t, c_);
             l->k_cache = DeviceBuffer<uint16_t>::zeroed((size_t)c_.context * c_.kv_width());
@@ -242,10 +252,15 @@ class Qwen3Model {
                    "down projection");
         }
         const float *last = ws.hidden.ptr() + (size_t)(rows - 1) * H;
-        ensure(w8a8_rmsnorm_quantize(last, final_gain_.ptr(), W8A8_F32, c_.eps, 1, H, H, head_q_.ptr(), head_scale_.ptr(), nullptr,
-                                     nullptr, s),
+        const bool bf16_head = head_ == nullptr;
+        // the final norm; with the bf16 head its output row is what the head multiplies (`norm`, src/gpu.rs:798)
+        ensure(w8a8_rmsnorm_quantize(last, final_gain_.ptr(), W8A8_F32, c_.eps, 1, H, H, head_q_.ptr(), head_scale_.ptr(),
+                                     bf16_head ? head_x_.ptr() : nullptr, nullptr, s),
                "final norm");
-        ensure(w8a8_linear_argmax(head_q_.ptr(), head_scale_.ptr(), head_.handle, 1, next_.ptr(), nullptr, s), "head");
+        if (bf16_head)
+            ensure(qwen3_head_bf16(head_x_.ptr(), W8A8_F32, head_bf16_.ptr(), c_.vocab, H, nullptr, next_.ptr(), nullptr, s), "head");
+        else
+            ensure(w8a8_linear_argmax(head_q_.ptr(), head_scale_.ptr(), head_->handle, 1, next_.ptr(), nullptr, s), "head");
     }
 
     Generation generate(const std::vector<uint32_t> &prompt, int max_tokens, bool use_graph = true) {
@@ -320,11 +335,12 @@ class Qwen3Model {
     GpuLinear gpu_;
     DeviceBuffer<uint16_t> embedding_;
     Buffer final_gain_, rope_;
-    Matrix head_;
+    std::unique_ptr<Matrix> head_;        // W8A8 head, or
+    DeviceBuffer<uint16_t> head_bf16_;    // the reference's bf16 head
     std::vector<std::unique_ptr<Layer>> layers_;
     DeviceBuffer<uint32_t> control_, next_;
     DeviceBuffer<int8_t> head_q_;
-    Buffer head_scale_;
+    Buffer head_scale_, head_x_;
     Qwen3Workspace decode_;
     cudaGraph_t graph_ = nullptr;
     cudaGraphExec_t exec_ = nullptr;

@@ -326,3 +326,14 @@ def merge_candidates(candidates: torch.Tensor, part_width: int, token: torch.Ten
     parts, _, rows = candidates.shape
     capi.check(capi.load().qwen3_merge_candidates(_ptr(candidates), parts, rows, part_width, _ptr(token), _stream()),
                "qwen3_merge_candidates")
+
+
+def head_bf16(x: torch.Tensor, w: torch.Tensor, logits: torch.Tensor | None = None, token: torch.Tensor | None = None,
+              value: torch.Tensor | None = None) -> None:
+    """Kernels `head` / `head_packed` + `select_token` (src/kernels.rs:2233-2373, :2191-2231; src/gpu.rs:801-811): the
+    reference's bf16 head on one row `x` ([1, hidden] or [hidden]) against `w` ([vocab, hidden] torch.bfloat16), logits
+    bit-identical to the reference's summation order; `token` receives the greedy selection."""
+    vocab, hidden = w.shape
+    assert w.dtype == torch.bfloat16 and w.is_contiguous() and x.numel() == hidden
+    capi.check(capi.load().qwen3_head_bf16(_ptr(x), _dtype_code(x), _ptr(w), vocab, hidden, _ptr(logits), _ptr(token), _ptr(value),
+                                           _stream()), "qwen3_head_bf16")

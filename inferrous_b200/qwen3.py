@@ -12,8 +12,9 @@ and reads the selected token back every step (src/gpu.rs:876-906).
 Differences from the reference host, all outside the linear-layer arithmetic:
   * Q, K and V (and gate, up) are stored as one concatenated matrix each; with per-output-channel scales the
     concatenated projection equals the separate ones channel for channel.
-  * The head is a W8A8 matrix like the body (the reference keeps a packed bf16 head, src/gpu.rs:801-809); the final
-    norm is therefore fused with a quantizer and the selection with the projection.
+  * Two output heads: the reference's bf16 head (Qwen3Weights.head_bf16; what a loaded bundle uses, logits bit-identical
+    to the reference's `head` kernel, src/gpu.rs:801-809) and a W8A8 head like the body (the benchmark's lm_head shape;
+    the final norm is then fused with a quantizer).  Either way the greedy selection is fused into the head kernel.
   * Activations are stored as bf16 (the reference stores the same values in f32 buffers).
 """
 from __future__ import annotations
@@ -83,12 +84,18 @@ class Layer:
 
 
 class Qwen3Weights:
-    def __init__(self, config: Qwen3Config, embedding, layers, final_gain, head, head_scale, device):
+    def __init__(self, config: Qwen3Config, embedding, layers, final_gain, head, head_scale, device, head_bf16=None):
+        """`head`, `head_scale`: the W8A8 output head (int8 [vocab, hidden] + channel scales).  `head_bf16` ([vocab, hidden]
+        torch.bfloat16): the reference's own unquantized head (src/gpu.rs:801-809); when given, generation uses it
+        (ops.head_bf16, logits bit-identical to the reference's kernel) and the W8A8 head may be None."""
         self.config = config
         self.embedding = embedding
         self.layers = layers
         self.final_gain = final_gain
-        self.head = ops.Matrix(head, head_scale)
+        self.head = ops.Matrix(head, head_scale) if head is not None else None
+        self.head_bf16 = head_bf16
+        if self.head is None and head_bf16 is None:
+            raise ValueError("a model needs an output head")
         self.rope = rope_table(config).to(device)
         self.tp, self.rank = 1, 0          # tensor-parallel degree and this process's rank (see shard())
         self.full_config = config          # the unsharded model
@@ -114,8 +121,11 @@ class Qwen3Weights:
             down = l.down.w[:, rank * il:(rank + 1) * il].contiguous()
             layers.append(Layer(local, l.norm1, qkv, qkv_s, l.qnorm, l.knorm, o, l.o.scale, l.norm2, gu, gu_s, down, l.down.scale))
         vl = c.vocab // tp
-        out = Qwen3Weights(local, self.embedding, layers, self.final_gain, self.head.w[rank * vl:(rank + 1) * vl].contiguous(),
-                           self.head.scale[rank * vl:(rank + 1) * vl].contiguous(), self.embedding.device)
+        rows = slice(rank * vl, (rank + 1) * vl)
+        out = Qwen3Weights(local, self.embedding, layers, self.final_gain,
+                           self.head.w[rows].contiguous() if self.head is not None else None,
+                           self.head.scale[rows].contiguous() if self.head is not None else None, self.embedding.device,
+                           head_bf16=self.head_bf16[rows].contiguous() if self.head_bf16 is not None else None)
         out.rope = self.rope
         out.tp, out.rank, out.full_config = tp, rank, c
         return out
@@ -199,7 +209,8 @@ class Qwen3Runner:
 
     def __init__(self, weights: Qwen3Weights, unfused: bool = False, device="cuda", fold_quantizers: str = "none",
                  prefetch_rows: int = 0, prefetch_down_at: str = "quant", prefetch_o: bool = False, group=None,
-                 fused_allreduce: bool = True, fold_attention_quantizer: bool = False, batch: int = 1):
+                 fused_allreduce: bool = True, fold_attention_quantizer: bool = False, batch: int = 1,
+                 peer_rows_times_ranks: int = 128):
         ops.init()
         if batch < 1:
             raise ValueError("batch must be at least 1")
@@ -209,6 +220,10 @@ class Qwen3Runner:
         # token against 2.47 with the separate quantizer launch, whose latency programmatic launch already hides.
         self.fold_attention_quantizer = fold_attention_quantizer
         # Tensor parallel decode: O and down with the all-reduce fused in (tp.PeerLinear) instead of NCCL + `residual`.
+        # The fused exchange sends every partial output to every rank as an 8-byte packet: rows * 4096 * 8 bytes * (ranks - 1)
+        # per rank and call.  That beats NCCL's latency for decode-sized launches, but at 64 rows on 8 ranks it is 14.7 MB
+        # per call against 0.5 MB of bf16 partials, so beyond rows * ranks = 128 the projection is followed by NCCL instead.
+        self.peer_rows_times_ranks = peer_rows_times_ranks
         self.peer = None
         if weights.tp > 1 and fused_allreduce and not unfused:
             from .tp import PeerLinear
@@ -235,9 +250,11 @@ class Qwen3Runner:
         self.decode = Workspace(c, 1, device, wide_gate_up=unfused)
         self.head_q = torch.empty(1, c.hidden, dtype=torch.int8, device=device)
         self.head_scale = torch.empty(1, dtype=torch.float32, device=device)
+        self.head_x = torch.empty(1, c.hidden, dtype=torch.bfloat16, device=device)  # final norm row (bf16 head)
+        self.head_rows = weights.head_bf16.shape[0] if weights.head_bf16 is not None else weights.head.n  # this rank's vocabulary rows
         self.logits = torch.empty(1, weights.full_config.vocab, dtype=torch.bfloat16, device=device) if unfused else None
         if weights.tp > 1:
-            self.local_logits = torch.empty(1, weights.head.n, dtype=torch.bfloat16, device=device) if unfused else None
+            self.local_logits = torch.empty(1, self.head_rows, dtype=torch.bfloat16, device=device) if unfused else None
             self.local_best = torch.zeros(2, dtype=torch.int32, device=device)         # {token within the shard, value bits}
             self.all_best = torch.zeros(weights.tp, 2, dtype=torch.int32, device=device)
         self.graph = None
@@ -260,6 +277,8 @@ class Qwen3Runner:
         self.attention_ws = ops.attention_batched_workspace(rows, c.q_heads, c.kv_heads, device)
         self.batch_head_q = torch.empty(rows, c.hidden, dtype=torch.int8, device=device)
         self.batch_head_scale = torch.empty(rows, dtype=torch.float32, device=device)
+        if w.head is None:
+            raise ValueError("batched decode needs the W8A8 head (the bf16 head kernel serves one row per launch)")
         stored = self.unfused or rows > 16  # the fused head + selection kernel takes at most 16 rows
         self.batch_logits = torch.empty(rows, w.head.n, dtype=torch.bfloat16, device=device) if stored else None
         if w.tp > 1:
@@ -352,7 +371,8 @@ class Qwen3Runner:
         if self.w.tp == 1:
             ops.linear_residual(q, ws.scales, matrix, None, residual_in, combined, variant)
             return
-        if self.peer is not None and ws.rows * matrix.n <= self.peer.slot and ws.rows <= self.PEER_MAX_ROWS:
+        if (self.peer is not None and ws.rows * matrix.n <= self.peer.slot and ws.rows <= self.PEER_MAX_ROWS
+                and ws.rows * self.w.tp <= self.peer_rows_times_ranks):
             self.peer.linear_residual(q, ws.scales, matrix, None, residual_in, combined)
             return
         import torch.distributed as dist
@@ -391,9 +411,15 @@ class Qwen3Runner:
         rows = ws.rows
         variant = capi.VARIANT_NAIVE if self.unfused else capi.VARIANT_AUTO
         last = ws.hidden[rows - 1:rows]
-        ops.norm_quantize(last, w.final_gain, None, self.head_q, self.head_scale, None, c.eps)
+        bf16_head = w.head_bf16 is not None
+        # the final norm; with a bf16 head its output row is what the head multiplies (the reference's `norm`, src/gpu.rs:798)
+        ops.norm_quantize(last, w.final_gain, self.head_x if bf16_head else None, self.head_q, self.head_scale, None, c.eps)
         if w.tp == 1:
-            if self.unfused:
+            if bf16_head and self.unfused:
+                ops.head_bf16(self.head_x, w.head_bf16, logits=self.logits)
+            elif bf16_head:
+                ops.head_bf16(self.head_x, w.head_bf16, token=self.next)
+            elif self.unfused:
                 ops.linear_quantized(self.head_q, self.head_scale, w.head, self.logits, variant)
             else:
                 ops.linear_argmax(self.head_q, self.head_scale, w.head, self.next)
@@ -402,13 +428,19 @@ class Qwen3Runner:
         import torch.distributed as dist
 
         if self.unfused:
-            ops.linear_quantized(self.head_q, self.head_scale, w.head, self.local_logits, variant)
+            if bf16_head:
+                ops.head_bf16(self.head_x, w.head_bf16, logits=self.local_logits)
+            else:
+                ops.linear_quantized(self.head_q, self.head_scale, w.head, self.local_logits, variant)
             dist.all_gather_into_tensor(self.logits.view(-1), self.local_logits.view(-1), group=self.group)
             return
-        ops.linear_argmax(self.head_q, self.head_scale, w.head, self.local_best[0:1], self.local_best[1:2].view(torch.float32))
+        if bf16_head:
+            ops.head_bf16(self.head_x, w.head_bf16, token=self.local_best[0:1], value=self.local_best[1:2].view(torch.float32))
+        else:
+            ops.linear_argmax(self.head_q, self.head_scale, w.head, self.local_best[0:1], self.local_best[1:2].view(torch.float32))
         dist.all_gather_into_tensor(self.all_best.view(-1), self.local_best, group=self.group)
         # device-side selection over the ranks' candidates (no host synchronisation: this runs inside the captured step)
-        ops.merge_candidates(self.all_best.view(w.tp, 2, 1), w.head.n, self.next)
+        ops.merge_candidates(self.all_best.view(w.tp, 2, 1), self.head_rows, self.next)
 
     def _head_rows(self, ws: Workspace) -> None:
         """Final norm, head projection and greedy selection for every row (batched decode): next_tokens[r]."""

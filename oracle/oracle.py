@@ -236,6 +236,26 @@ def head_norm_rope(x, gain, table, position: int, eps: float = 1e-6, inv_ulps: i
     return rope(head_norm(x, gain, eps, inv_ulps), table, position)
 
 
+def head(x, w_bits):
+    """The reference's bf16 output head, `head` (src/kernels.rs:2233-2257; `head_packed` :2259-2373 gives the same bits):
+    logit[n] = bf16(sum_k x[k] * w[n, k]) with the float32 sum in the kernel's order -- lane L of a warp adds the
+    products of columns L, L + 32, L + 64, ... in that order, then the 32 partial sums meet in a shuffle-down tree of
+    distances 16, 8, 4, 2, 1.  x: [K] float32 (bf16 values), K a multiple of 32; w_bits: [N, K] bf16 bit patterns."""
+    x = _f32(x).reshape(-1)
+    w = from_bf16_bits(np.asarray(w_bits, np.uint16))
+    n, k = w.shape
+    assert k == x.size and k % 32 == 0
+    prod = (w * x[None, :]).reshape(n, k // 32, 32)   # [row, step, lane]; one float32 rounding per product
+    s = np.zeros((n, 32), np.float32)
+    for step in range(k // 32):
+        s = s + prod[:, step, :]
+    d = 16
+    while d > 0:
+        s[:, :d] = s[:, :d] + s[:, d:2 * d]
+        d //= 2
+    return bf16(s[:, 0])
+
+
 def attention(q, k_bits, v_bits, position: int):
     """src/kernels.rs:1490-1658.  q: [rows, q_heads, 128] float32 (bf16 values); k_bits, v_bits: [keys, kv_heads, 128]
     bf16 bit patterns with keys >= position + rows.  Row r sees keys 0 .. position + r.  Summation orders follow the

@@ -1,5 +1,6 @@
 // Greedy generation through the C++ host harness (inferrous_b200/host/qwen3_model.hpp) from an on-disk bundle.
-// usage: generate <bundle dir> <max tokens> <use graph 0|1> <prompt id>...
+// usage: generate <bundle dir> <max tokens> <use graph 0|1> <prompt id>...      (W8A8_HEAD=w8a8 in the environment
+//        runs the head as a W8A8 projection instead of the reference's bf16 head)
 // Prints one line "tokens: t0 t1 ..." and exits 0; any failure is a message on stderr and exit code 1.
 #include <cstdio>
 #include <cstdlib>
@@ -12,7 +13,9 @@ int main(int argc, char **argv) {
         return 1;
     }
     try {
-        const w8a8::Qwen3Bundle bundle = w8a8::Qwen3Bundle::load(argv[1]);
+        const char *head = getenv("W8A8_HEAD");
+        const bool w8a8_head = head && std::string(head) == "w8a8";
+        const w8a8::Qwen3Bundle bundle = w8a8::Qwen3Bundle::load(argv[1], w8a8_head ? w8a8::HeadKind::W8A8 : w8a8::HeadKind::Bf16);
         const int max_tokens = atoi(argv[2]);
         const bool use_graph = atoi(argv[3]) != 0;
         std::vector<uint32_t> prompt;

@@ -3,11 +3,10 @@
 Runs the reference repository's `crates/inferrous-qwen3/tools/operator_fixtures.py`
 UNMODIFIED (PyTorch CPU, seed 824, 8 threads) into a scratch directory and keeps
 the cases that exercise the W8A8 linear-layer path (`norm`, `quantize`, `linear`,
-`swiglu`, `residual`) and the operators around it (`rope`, `attention`, `embedding`).
+`swiglu`, `residual`) and the operators around it (`rope`, `attention`, `embedding`, `head`).
 To keep the committed files small, the rope case's 2 MB table (4096 positions) is cut
 to the rows the case reads (tensor `table_rows`, first row = `position`), and the
-attention case at position 4095 (16 MB of keys and values) and the bf16 `head` case
-(not on this path) are dropped.  File format is the reference's:
+attention case at position 4095 (16 MB of keys and values) is dropped.  File format is the reference's:
 raw little-endian tensors + `manifest.json` with shape and sha256 per tensor
 (operator_fixtures.py:23-34,83).
 
@@ -26,7 +25,7 @@ import hashlib
 
 import numpy as np
 
-KEEP = {"norm", "quantize", "linear", "swiglu", "residual", "rope", "attention", "embedding"}
+KEEP = {"norm", "quantize", "linear", "swiglu", "residual", "rope", "attention", "embedding", "head"}
 MAX_ATTENTION_POSITION = 1024
 
 

@@ -18,7 +18,8 @@ def export(weights) -> dict:
         embedding=oracle.bf16_bits(to_host(weights.embedding)),
         rope=weights.rope.cpu().numpy(),
         final_gain=to_host(weights.final_gain),
-        head=m(weights.head),
+        head=m(weights.head) if weights.head is not None else None,
+        head_bf16=oracle.bf16_bits(to_host(weights.head_bf16)) if weights.head_bf16 is not None else None,
         layers=[dict(norm1=to_host(l.norm1), norm2=to_host(l.norm2), qnorm=l.qnorm.cpu().numpy(), knorm=l.knorm.cpu().numpy(),
                      qkv=m(l.qkv), o=m(l.o), gate_up=m(l.gate_up), down=m(l.down)) for l in weights.layers],
     )
@@ -53,7 +54,10 @@ class OracleModel:
             gu = self.project(oracle.rmsnorm(residual, layer["norm2"], c.eps), layer["gate_up"])
             act = np.stack([oracle.swiglu(gu[r, :c.intermediate], gu[r, c.intermediate:])[0] for r in range(rows)])
             hidden = self.project(act, layer["down"], residual=residual)[1]
-        logits = self.project(oracle.rmsnorm(hidden[-1:], p["final_gain"], c.eps), p["head"])
+        last = oracle.rmsnorm(hidden[-1:], p["final_gain"], c.eps)
+        if p.get("head_bf16") is not None:  # the reference's own head: bf16 weights, its summation order
+            return hidden, oracle.head(last[0], p["head_bf16"])
+        logits = self.project(last, p["head"])
         return hidden, logits[0]
 
     def generate(self, prompt_ids, max_tokens: int):

@@ -99,15 +99,41 @@ def test_generation_from_a_bundle_python_cpp_and_cpu_agree(tmp_path, prompt_len,
     from tests.cpp.build import build
     from tests.qwen3_oracle import OracleModel, export
 
+    import os
+
     write_bundle(tmp_path / "b", seed=11, **shape)
-    weights = load_bundle(tmp_path / "b")
     rng = np.random.default_rng(1)
-    prompt = [int(t) for t in rng.integers(0, weights.config.vocab, prompt_len)]
-    tokens, _ = Qwen3Runner(weights).generate(prompt, steps)
-    for use_graph in (1, 0):
-        r = subprocess.run([str(build("generate")), str(tmp_path / "b"), str(steps), str(use_graph), *map(str, prompt)],
-                           capture_output=True, text=True, timeout=600)
-        assert r.returncode == 0, r.stdout + r.stderr
-        assert [int(t) for t in r.stdout.split("tokens:")[1].split()] == tokens
-    if prompt_len <= 16:
-        assert OracleModel(export(weights)).generate(prompt, steps) == tokens
+    for head in ("bf16", "w8a8"):  # the reference's head (the default of both hosts) and the W8A8 head
+        weights = load_bundle(tmp_path / "b", head=head)
+        prompt = [int(t) for t in rng.integers(0, weights.config.vocab, prompt_len)]
+        tokens, _ = Qwen3Runner(weights).generate(prompt, steps)
+        for use_graph in (1, 0):
+            r = subprocess.run([str(build("generate")), str(tmp_path / "b"), str(steps), str(use_graph), *map(str, prompt)],
+                               capture_output=True, text=True, timeout=600, env=dict(os.environ, W8A8_HEAD=head))
+            assert r.returncode == 0, r.stdout + r.stderr
+            assert [int(t) for t in r.stdout.split("tokens:")[1].split()] == tokens
+        if prompt_len <= 16:
+            assert OracleModel(export(weights)).generate(prompt, steps) == tokens
+
+
+@pytest.mark.gpu
+def test_generation_from_a_bundle_with_the_reference_head(tmp_path):
+    """A bundle loads with its bf16 head by default, as the reference runs it (src/gpu.rs:801-811): tokens equal the CPU
+    restatement's (bf16 head in the reference's summation order), fused selection equals stored logits + selection, and
+    the W8A8 head remains available as an option."""
+    from inferrous_b200.bundle import load_bundle
+    from inferrous_b200.qwen3 import Qwen3Runner
+    from tests.qwen3_oracle import OracleModel, export
+
+    write_bundle(tmp_path / "b", seed=13)
+    weights = load_bundle(tmp_path / "b")
+    assert weights.head is None and weights.head_bf16 is not None
+    prompt = [5, 17, 600, 3]
+    tokens, _ = Qwen3Runner(weights).generate(prompt, 8)
+    assert OracleModel(export(weights)).generate(prompt, 8) == tokens
+    assert Qwen3Runner(weights, unfused=True).generate(prompt, 8)[0] == tokens
+    assert Qwen3Runner(weights).generate(prompt, 8, use_graph=False)[0] == tokens
+    both = load_bundle(tmp_path / "b", head="both")
+    assert both.head is not None and Qwen3Runner(both).generate(prompt, 8)[0] == tokens  # the bf16 head wins when both exist
+    with pytest.raises(ValueError):
+        load_bundle(tmp_path / "b", head="fp8")

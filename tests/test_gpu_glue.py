@@ -307,3 +307,69 @@ def test_attention_with_folded_quantizer_refuses_many_rows(ops):
         ops.attention_quantize(qd, Q_HEADS, KV_HEADS, kc, kc, control(0, 0), out, torch.zeros(rows, Q_HEADS * 128, dtype=torch.int8, device="cuda"),
                                torch.zeros(rows, device="cuda"))
     assert e.value.status == 3
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_head_bf16_fixture_and_reference_order(ops, fixtures, dtype):
+    """The reference's `head` fixture (x [3, 4096], w [33, 4096] bf16): the last row's logits inside the reference's gate
+    for this operator (its expected values come from a Torch matmul, src/conformance.rs:611-674), and bit-identical to
+    the CPU restatement of the kernel's own summation order (src/kernels.rs:2233-2257); the fused selection agrees."""
+    import torch
+
+    from tests.util import gate
+
+    (case,) = fixtures.cases("head")
+    x = fixtures.tensor(case, "x")
+    w_bits = np.frombuffer((fixtures.root / case["tensors"]["w"]["file"]).read_bytes(), np.uint16).reshape(case["tensors"]["w"]["shape"])
+    expected = fixtures.tensor(case, "out").reshape(-1)
+    w = to_dev(w_bits.view(np.int16).copy()).view(torch.bfloat16)
+    td = torch.bfloat16 if dtype == "bf16" else torch.float32
+    logits = torch.full((w.shape[0],), float("nan"), dtype=td, device="cuda")
+    token = torch.zeros(1, dtype=torch.int32, device="cuda")
+    value = torch.zeros(1, dtype=torch.float32, device="cuda")
+    ops.head_bf16(to_dev(x[-1:], dtype), w, logits, token, value)
+    got = to_host(logits)
+    gate(got, expected)
+    cpu = oracle.head(x[-1], w_bits)
+    assert np.array_equal(got.view(np.uint32), cpu.view(np.uint32))
+    assert int(token[0]) == int(np.argmax(cpu)) and float(value[0]) == float(cpu.max())
+    assert ops.device_status() == (0, 0)
+
+
+@pytest.mark.parametrize("vocab,hidden", [(1000, 4096), (151936, 4096), (17, 256), (640, 1024)])
+def test_head_bf16_shapes_ties_and_bad_rows(ops, vocab, hidden):
+    """Ragged vocabulary sizes (a last CTA with fewer than 16 rows), the full Qwen3 vocabulary, other widths: logits bit-identical
+    to the CPU restatement; equal maxima go to the lowest index; an infinite logit gives 0xffffffff."""
+    import torch
+
+    rng = np.random.default_rng(vocab)
+    x = oracle.bf16(rng.standard_normal(hidden).astype(np.float32))
+    w = oracle.bf16((rng.standard_normal((vocab, hidden)) * 0.05).astype(np.float32))
+    w[vocab // 2] = w[vocab // 3]  # two identical rows: identical logits
+    w_bits = oracle.bf16_bits(w)
+    wd = to_dev(w_bits.view(np.int16)).view(torch.bfloat16)
+    logits = torch.full((vocab,), float("nan"), dtype=torch.bfloat16, device="cuda")
+    token = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.head_bf16(to_dev(x.reshape(1, -1), "bf16"), wd, logits, token)
+    rows = slice(None) if vocab <= 2000 else rng.choice(vocab, 2000, replace=False)
+    cpu = oracle.head(x, w_bits[rows])
+    got = to_host(logits)
+    assert np.array_equal(got[rows].view(np.uint32), cpu.view(np.uint32))
+    assert int(token[0]) == int(np.flatnonzero(got == got.max())[0])
+    # make the tied rows the maximum: the lower index wins
+    big = x.copy()
+    w2 = w.copy()
+    w2[vocab // 2] = w2[vocab // 3] = oracle.bf16(np.sign(x) * 0.5)
+    wd2 = to_dev(oracle.bf16_bits(w2).view(np.int16)).view(torch.bfloat16)
+    only_token = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.head_bf16(to_dev(big.reshape(1, -1), "bf16"), wd2, None, only_token)
+    assert int(only_token[0]) == vocab // 3
+    # a logit that overflows to infinity marks the row of activations as bad (a NaN sum, by contrast, becomes -0.0 in
+    # the reference's bf16 rounding, which has no NaN case: src/kernels.rs:12-15)
+    x[0] = float(oracle.bf16(np.array([3e38], np.float32))[0])
+    w3 = w.copy()
+    w3[5, 0] = x[0]
+    wd3 = to_dev(oracle.bf16_bits(w3).view(np.int16)).view(torch.bfloat16)
+    ops.head_bf16(to_dev(x.reshape(1, -1), "f32"), wd3, None, only_token)
+    assert int(only_token[0]) & 0xFFFFFFFF == 0xFFFFFFFF
+    assert ops.device_status() == (0, 0)

@@ -189,3 +189,17 @@ def test_head_norm_is_the_fixture_pinned_norm_at_width_128(fixtures):
     assert np.array_equal(oracle.head_norm(y, g), oracle.rmsnorm(y.reshape(-1, 128), g).reshape(y.shape))
     moved = oracle.head_norm(y, g, inv_ulps=2)
     assert 0 < (moved != oracle.head_norm(y, g)).mean() < 0.02
+
+
+def test_head_restatement_against_the_reference_fixture(fixtures):
+    """`head` (src/kernels.rs:2233-2257) restated with the kernel's summation order: inside the reference's gate for the
+    operator against its Torch-generated fixture (src/conformance.rs:611-674; in fact equal on all 33 logits)."""
+    from tests.util import gate
+
+    (case,) = fixtures.cases("head")
+    x = fixtures.tensor(case, "x")
+    w_bits = np.frombuffer((fixtures.root / case["tensors"]["w"]["file"]).read_bytes(), np.uint16).reshape(case["tensors"]["w"]["shape"])
+    expected = fixtures.tensor(case, "out").reshape(-1)
+    got = oracle.head(x[-1], w_bits)
+    gate(got, expected)
+    assert np.array_equal(got, oracle.bf16(got))  # logits are bf16 values
