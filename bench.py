@@ -47,7 +47,7 @@ NCU_TRAFFIC_RATIO = {"gemv_mma": 1.025, "gemv_dp4a": 1.035, "gemm_skinny": 1.003
 
 def kernel_family(M, weight_bytes, K, forced=0):
     """Which kernel w8a8_linear picks (mirrors pick_variant in inferrous_b200/csrc/capi.cu)."""
-    names = {1: "naive_linear", 2: "gemv_dp4a", 3: "gemv_mma", 4: "gemm_tcgen05", 5: "gemm_skinny", 8: "gemm_tcgen05_pair"}
+    names = {1: "naive_linear", 2: "gemv_dp4a", 3: "gemv_mma", 4: "gemm_tcgen05", 5: "gemm_skinny", 8: "gemm_tcgen05_pair", 9: "gemm_cluster"}
     if forced:
         return names[forced]
     if M <= 1:
@@ -57,9 +57,11 @@ def kernel_family(M, weight_bytes, K, forced=0):
     if M <= 16:
         return "gemm_skinny" if weight_bytes >= (256 << 20) else "gemv_mma"
     if M <= 64:
-        return "gemm_skinny" if weight_bytes >= (48 << 20) else "gemv_mma"
+        return "gemm_skinny" if weight_bytes >= (64 << 20) else "gemm_cluster"
     if M <= 128:
-        return "gemm_skinny" if weight_bytes >= (256 << 20) else "gemm_tcgen05"
+        if weight_bytes >= (256 << 20):
+            return "gemm_skinny"
+        return "gemm_cluster" if K >= 8192 and weight_bytes < (64 << 20) else "gemm_tcgen05"
     return "gemm_tcgen05_pair"
 
 

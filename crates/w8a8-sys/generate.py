@@ -73,6 +73,7 @@ pub const W8A8_VARIANT_GEMV_MMA: c_int = 3;
 pub const W8A8_VARIANT_GEMM_TCGEN05: c_int = 4;
 pub const W8A8_VARIANT_GEMM_SKINNY: c_int = 5;
 pub const W8A8_VARIANT_GEMM_TCGEN05_PAIR: c_int = 8;
+pub const W8A8_VARIANT_GEMM_CLUSTER: c_int = 9;
 
 pub const W8A8_SOURCE_WITH_MAX: c_int = 1;
 pub const W8A8_SOURCE_RMSNORM: c_int = 2;

@@ -10,7 +10,8 @@ OK = 0
 BF16, F32 = 0, 1
 SOURCE_WITH_MAX, SOURCE_RMSNORM = 1, 2
 VARIANT_AUTO, VARIANT_NAIVE, VARIANT_GEMV_DP4A, VARIANT_GEMV_MMA, VARIANT_GEMM_TCGEN05, VARIANT_GEMM_SKINNY = range(6)
-VARIANT_GEMM_TCGEN05_PAIR = 8  # 6 and 7 were kernels that lost to the others everywhere and are gone
+VARIANT_GEMM_TCGEN05_PAIR = 8
+VARIANT_GEMM_CLUSTER = 9  # 6 and 7 were kernels that lost to the others everywhere and are gone
 
 _vp, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 

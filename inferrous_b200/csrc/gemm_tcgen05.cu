@@ -292,6 +292,8 @@ cudaError_t make_weight_maps(w8a8_weight *wt) {
     if (e != cudaSuccess) return e;
     e = encode_map_impl(&wt->map_rows128, wt->w, wt->N, wt->K, 128);
     if (e != cudaSuccess) return e;
+    e = encode_map_impl(&wt->map_rows96, wt->w, wt->N, wt->K, 96);
+    if (e != cudaSuccess) return e;
     e = encode_map_impl(&wt->map_rows64, wt->w, wt->N, wt->K, 64);
     if (e != cudaSuccess) return e;
     wt->has_maps = true;

@@ -20,17 +20,25 @@
 #include "internal.h"
 #include "ptx.cuh"
 
+#include <cstdlib>
+
 namespace w8a8 {
 namespace {
 
-constexpr int TILE_M = 256, TILE_N = 256;
+constexpr int TILE_M = 256;
 constexpr int BLOCK_K = 128, UMMA_K = 32;
-constexpr int STAGES = 6;
-constexpr int HALF_BYTES = 128 * BLOCK_K;       // one 128-row box
-constexpr int STAGE_BYTES = 2 * HALF_BYTES;     // this CTA's A half + B half
+constexpr int HALF_BYTES = 128 * BLOCK_K;       // this CTA's half of the token rows: one 128-row box
 constexpr int TMEM_COLS = 512;
 constexpr int kThreads = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+// Output channels per tile: 256, 192 or 128 (each CTA stages half of them).  The narrower tiles exist for the shapes
+// whose 256-channel tiles leave the last wave over the 74 CTA pairs mostly empty (Q|K|V at 4096 tokens: 384 tiles = 5.2
+// waves; with 192 channels 512 tiles = 6.9 waves).
+template <int BN> struct PairTile {
+    static constexpr int kHalfB = (BN / 2) * BLOCK_K;                 // this CTA's half of the weight rows
+    static constexpr int kStageBytes = HALF_BYTES + kHalfB;
+    static constexpr int kStages = (196 * 1024) / kStageBytes;        // 6, 7, 8
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -82,9 +90,10 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
                  : "memory");
 }
 
-template <class T, int EPI>
+template <class T, int EPI, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmDev p) {
+    constexpr int TILE_N = BN, STAGES = PairTile<BN>::kStages, STAGE_BYTES = PairTile<BN>::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -145,7 +154,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
                     const uint32_t dst = tiles + stage * STAGE_BYTES;
                     tma_load_2d_pair(dst, &map_a, kb * BLOCK_K, m_blk * TILE_M + (int)rank * 128, leader_full);
-                    tma_load_2d_pair(dst + HALF_BYTES, &map_b, kb * BLOCK_K, n_blk * TILE_N + (int)rank * 128, leader_full);
+                    tma_load_2d_pair(dst + HALF_BYTES, &map_b, kb * BLOCK_K, n_blk * TILE_N + (int)rank * (TILE_N / 2), leader_full);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -225,35 +234,60 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
 }
 
-template <class T, int EPI> cudaError_t launch_inst(const CUtensorMap &ma, const CUtensorMap &mb, const GemmDev &d, cudaStream_t s) {
-    const int tiles = ((d.M + TILE_M - 1) / TILE_M) * ((d.N + TILE_N - 1) / TILE_N);
+template <class T, int EPI, int BN> cudaError_t launch_inst(const CUtensorMap &ma, const CUtensorMap &mb, const GemmDev &d, cudaStream_t s) {
+    const int tiles = ((d.M + TILE_M - 1) / TILE_M) * ((d.N + BN - 1) / BN);
     int pairs = sm_count() / 2;
     if (tiles < pairs) pairs = tiles;
-    return launch_kernel(gemm_tcgen05_pair_kernel<T, EPI>, dim3(2 * pairs), dim3(kThreads), (size_t)SMEM_BYTES, s, ma, mb, d);
+    return launch_kernel(gemm_tcgen05_pair_kernel<T, EPI, BN>, dim3(2 * pairs), dim3(kThreads), (size_t)PairTile<BN>::kSmemBytes, s, ma, mb, d);
 }
-template <class T> cudaError_t launch_epi(int epi, const CUtensorMap &ma, const CUtensorMap &mb, const GemmDev &d, cudaStream_t s) {
+template <class T, int BN> cudaError_t launch_epi(int epi, const CUtensorMap &ma, const CUtensorMap &mb, const GemmDev &d, cudaStream_t s) {
     switch (epi) {
-        case EPI_PLAIN: return launch_inst<T, EPI_PLAIN>(ma, mb, d, s);
-        case EPI_RESIDUAL: return launch_inst<T, EPI_RESIDUAL>(ma, mb, d, s);
-        case EPI_ACC: return launch_inst<T, EPI_ACC>(ma, mb, d, s);
+        case EPI_PLAIN: return launch_inst<T, EPI_PLAIN, BN>(ma, mb, d, s);
+        case EPI_RESIDUAL: return launch_inst<T, EPI_RESIDUAL, BN>(ma, mb, d, s);
+        case EPI_ACC: return launch_inst<T, EPI_ACC, BN>(ma, mb, d, s);
         default: return cudaErrorInvalidValue;
     }
 }
-template <class T, int EPI> cudaError_t set_attr() {
-    return cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<T, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+template <class T, int BN> cudaError_t set_attrs() {
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<T, EPI_PLAIN, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairTile<BN>::kSmemBytes))) return e;
+    if ((e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<T, EPI_RESIDUAL, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairTile<BN>::kSmemBytes))) return e;
+    return cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<T, EPI_ACC, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairTile<BN>::kSmemBytes);
+}
+
+// Channels per tile: the width with the least (waves over the CTA pairs) x (time of one tile, measured to go as
+// BN + 64: a 192-channel tile takes 0.80 of a 256-channel one); the wider one on a tie.  Measured at 4096 tokens:
+// Q|K|V 96.1 -> 90.1 us with 192 channels (6 -> 7 waves of smaller tiles); O, down, gate|up stay at 256; 128-channel
+// tiles lost everywhere (their K loop is bound by the token rows staged per block) and exist for tests.
+int pair_tile_channels(int M, int N) {
+    if (const char *force = getenv("W8A8_PAIR_BN")) {
+        const int bn = atoi(force);
+        if (bn == 256 || bn == 192 || bn == 128) return bn;
+    }
+    const long long pairs = sm_count() / 2, m_tiles = (M + TILE_M - 1) / TILE_M;
+    int best = 256;
+    long long best_cost = -1;
+    for (int bn : {256, 192}) {
+        const long long tiles = m_tiles * ((N + bn - 1) / bn);
+        const long long cost = ((tiles + pairs - 1) / pairs) * (bn + 64);
+        if (best_cost < 0 || cost < best_cost) {
+            best = bn;
+            best_cost = cost;
+        }
+    }
+    return best;
 }
 
 }  // namespace
 
 cudaError_t init_gemm_tcgen05_pair() {
     cudaError_t e;
-    if ((e = set_attr<Bf16, EPI_PLAIN>()) != cudaSuccess) return e;
-    if ((e = set_attr<Bf16, EPI_RESIDUAL>()) != cudaSuccess) return e;
-    if ((e = set_attr<Bf16, EPI_ACC>()) != cudaSuccess) return e;
-    if ((e = set_attr<F32, EPI_PLAIN>()) != cudaSuccess) return e;
-    if ((e = set_attr<F32, EPI_RESIDUAL>()) != cudaSuccess) return e;
-    if ((e = set_attr<F32, EPI_ACC>()) != cudaSuccess) return e;
-    return cudaSuccess;
+    if ((e = set_attrs<Bf16, 256>()) != cudaSuccess) return e;
+    if ((e = set_attrs<Bf16, 192>()) != cudaSuccess) return e;
+    if ((e = set_attrs<Bf16, 128>()) != cudaSuccess) return e;
+    if ((e = set_attrs<F32, 256>()) != cudaSuccess) return e;
+    if ((e = set_attrs<F32, 192>()) != cudaSuccess) return e;
+    return set_attrs<F32, 128>();
 }
 
 cudaError_t launch_gemm_tcgen05_pair(const LinearArgs &l, const w8a8_weight *wt, cudaStream_t s) {
@@ -265,8 +299,17 @@ cudaError_t launch_gemm_tcgen05_pair(const LinearArgs &l, const w8a8_weight *wt,
     d.a_scale = l.a_scale; d.w_scale = wt->w_scale; d.M = l.M; d.N = wt->N; d.K = l.K;
     d.y = l.out[0]; d.residual = l.residual; d.combined = l.combined; d.acc = l.acc;
     d.status = device_status_ptr();
-    return l.dtype == 0 ? launch_epi<Bf16>(l.epilogue, map_a, wt->map_rows128, d, s)
-                        : launch_epi<F32>(l.epilogue, map_a, wt->map_rows128, d, s);
+    switch (pair_tile_channels(l.M, wt->N)) {
+        case 192:
+            return l.dtype == 0 ? launch_epi<Bf16, 192>(l.epilogue, map_a, wt->map_rows96, d, s)
+                                : launch_epi<F32, 192>(l.epilogue, map_a, wt->map_rows96, d, s);
+        case 128:
+            return l.dtype == 0 ? launch_epi<Bf16, 128>(l.epilogue, map_a, wt->map_rows64, d, s)
+                                : launch_epi<F32, 128>(l.epilogue, map_a, wt->map_rows64, d, s);
+        default:
+            return l.dtype == 0 ? launch_epi<Bf16, 256>(l.epilogue, map_a, wt->map_rows128, d, s)
+                                : launch_epi<F32, 256>(l.epilogue, map_a, wt->map_rows128, d, s);
+    }
 }
 
 }  // namespace w8a8

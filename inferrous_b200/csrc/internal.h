@@ -12,6 +12,7 @@ struct w8a8_weight {
     int N, K;
     CUtensorMap map_rows256;  // [N,K] uint8, box 128 bytes x 256 rows, SWIZZLE_128B
     CUtensorMap map_rows128;  // same with a 128-row box
+    CUtensorMap map_rows96;   // same with a 96-row box
     CUtensorMap map_rows64;   // same with a 64-row box
     bool has_maps;
 };
@@ -101,6 +102,10 @@ cudaError_t init_gemm_tcgen05_pair();
 cudaError_t make_weight_maps(w8a8_weight *wt);  // TMA descriptors of the [N,K] matrix
 // [rows,K] int8 row-major -> tiled map with a box of 128 bytes of K x box_rows rows, 128-byte swizzle, zero fill.
 cudaError_t encode_tile_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows);
+// 9..128 tokens, small and mid-sized matrices: K split over a thread-block cluster, partial sums through distributed shared memory
+cudaError_t launch_gemm_cluster(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);
+cudaError_t init_gemm_cluster();
+constexpr int kClusterMaxTokens = 128;
 // few-token tensor-core path (weights on the MMA's M side, stream-K over output tiles x K blocks)
 cudaError_t launch_gemm_skinny(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);
 cudaError_t init_gemm_skinny();

@@ -12,7 +12,7 @@ from tests.util import bits, empty_act, synth_activations, synth_weights, to_dev
 
 pytestmark = pytest.mark.gpu
 
-NAIVE, DP4A, MMA, TC, SKINNY, PAIR = 1, 2, 3, 4, 5, 8
+NAIVE, DP4A, MMA, TC, SKINNY, PAIR, CLUSTER = 1, 2, 3, 4, 5, 8, 9
 CARRIERS = ["bf16", "f32"]
 
 
@@ -30,6 +30,8 @@ def variants_for(M):
     v = [NAIVE, TC, PAIR]
     if M <= 256:
         v.append(SKINNY)
+    if M <= 128:
+        v.append(CLUSTER)
     if os.environ.get("W8A8_TEST_SKIP_TCGEN05"):  # bring-up aid: check the SIMT variants alone
         v = [NAIVE]
     if M <= 4:
@@ -442,4 +444,24 @@ def test_fused_allreduce_with_one_rank_is_linear_residual(ops, M):
         assert torch.equal(y.view(torch.int16), y_ref.view(torch.int16)), call
         assert torch.equal(comb.view(torch.int16), c_ref.view(torch.int16)), call
     assert int(seq[0]) == 5
+    check_status(ops)
+
+
+@pytest.mark.parametrize("bn", [256, 192, 128])
+def test_pair_kernel_every_tile_width_exact(ops, bn, monkeypatch):
+    """The CTA-pair kernel with 256, 192 and 128 output channels per tile (W8A8_PAIR_BN forces a width): partial tiles in
+    both directions, residual epilogue, raw accumulators -- all equal to the one-thread-per-output kernel."""
+    monkeypatch.setenv("W8A8_PAIR_BN", str(bn))
+    rng = np.random.default_rng(bn)
+    for M, K, N in [(300, 512, 1000), (129, 4096, 200), (512, 1024, 768)]:
+        q = rng.integers(-127, 128, (M, K), dtype=np.int8)
+        w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+        asc = (rng.random(M, dtype=np.float32) / 64).astype(np.float32)
+        ws = (rng.random(N, dtype=np.float32) / 64).astype(np.float32)
+        res = oracle.bf16(rng.standard_normal((M, N)).astype(np.float32))
+        mat = make_matrix(ops, w, ws)
+        y, comb = run_linear(ops, mat, q, asc, "bf16", PAIR, residual=res)
+        y0, comb0 = run_linear(ops, mat, q, asc, "bf16", NAIVE, residual=res)
+        assert np.array_equal(bits(y), bits(y0)) and np.array_equal(bits(comb), bits(comb0))
+        assert np.array_equal(run_acc(ops, mat, q, PAIR), run_acc(ops, mat, q, NAIVE))
     check_status(ops)
