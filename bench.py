@@ -62,6 +62,8 @@ def kernel_family(M, weight_bytes, K, forced=0):
         if weight_bytes >= (256 << 20):
             return "gemm_skinny"
         return "gemm_cluster" if K >= 8192 and weight_bytes < (64 << 20) else "gemm_tcgen05"
+    if M <= 256 and K >= 8192 and weight_bytes < (64 << 20):
+        return "gemm_cluster"
     return "gemm_tcgen05_pair"
 
 
@@ -576,6 +578,13 @@ def per_shape_table(torch, ops, mats, bufs, hbm_peak, variant=0):
             us = time_launch(torch, lambda: ops.linear_quantized(b["q"], b["s"], mats[name], b["y"], variant), 20, flush)
             gbs = linear_bytes(M, K, N) / us / 1e3
             rows.append({"shape": name, "M": M, "us": round(us, 2), "GB/s": round(gbs, 1), "frac_hbm": round(gbs / hbm_peak, 3)})
+    # the allocation-free entry point (raw weight pointers, scratch in a fixed device array) on the O projection
+    if 16 in DECODE_M and "o" in mats:
+        b, m = bufs[(16, "o")], mats["o"]
+        us = time_launch(torch, lambda: ops.linear_no_alloc(b["q"], b["s"], m.w, m.scale, b["y"]), 20, flush)
+        gbs = linear_bytes(16, m.k, m.n) / us / 1e3
+        rows.append({"shape": "o via w8a8_linear_no_alloc", "M": 16, "us": round(us, 2), "GB/s": round(gbs, 1),
+                     "frac_hbm": round(gbs / hbm_peak, 3)})
     del flush
     return rows
 
@@ -638,7 +647,7 @@ def quantizer_table(torch, ops, hbm_peak):
     """The activation quantizers of configs[2]: fused with RMSNorm (QKV / gate_up input, K=4096) and with SwiGLU
     (down input, [M,24576] -> [M,12288]); HBM-bound.  Bytes: 2MK in + MK out + 4M (+2K gamma); SwiGLU reads 4MI.
     Timed as 8 back-to-back launches over rotating buffer sets that together exceed the L2 (single launches of a
-    few microseconds are below what a CUDA-event pair resolves)."""
+    few microseconds are below what a CUDA-event pair resolves), replayed as one CUDA graph."""
     rows = []
     K, I = 4096, 12288
     for M in DECODE_M + PREFILL_M:
@@ -657,13 +666,23 @@ def quantizer_table(torch, ops, hbm_peak):
             for i in range(sets):
                 fn(i)
             torch.cuda.synchronize()
+            # the eight launches are replayed as one CUDA graph, so that what is timed is the kernels, not the cost of
+            # eight host calls (a few microseconds each, more than a quantizer launch of a few rows takes)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for r in range(reps):
+                    fn(r % sets)
+            graph.replay()
+            torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for r in range(reps):
-                fn(r % sets)
+            graph.replay()
             e1.record()
             e1.synchronize()
             us = e0.elapsed_time(e1) * 1e3 / reps
+            del graph
             rows.append({"kernel": name, "M": M, "us": round(us, 2), "GB/s": round(nbytes / us / 1e3, 1),
                          "frac_hbm": round(nbytes / us / 1e3 / hbm_peak, 3), "buffer_sets": sets})
         del xs, gus, q4, q12

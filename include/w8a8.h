@@ -56,7 +56,7 @@ typedef enum {
     W8A8_VARIANT_GEMM_SKINNY = 5,  /* M <= 256: tcgen05 with the weights on the MMA's M side, stream-K split */
     /* 6 and 7 named two kernels that lost to the others on every shape and were removed; the values stay unused */
     W8A8_VARIANT_GEMM_TCGEN05_PAIR = 8, /* any M: 256x256 tiles over CTA pairs (tcgen05.mma.cta_group::2) */
-    W8A8_VARIANT_GEMM_CLUSTER = 9       /* M <= 128: tcgen05, weights on the MMA's M side, K split over a thread-block
+    W8A8_VARIANT_GEMM_CLUSTER = 9       /* M <= 256: tcgen05, weights on the MMA's M side, K split over a thread-block
                                            cluster with the partial sums reduced through distributed shared memory */
 } w8a8_variant_t;
 

@@ -361,11 +361,14 @@ static int pick_variant(int M, int epilogue, bool single_matrix, long long weigh
         // long K, few channels (down): 23.6 us against 33.7 with 128-channel tiles on 32 SMs
         return (K >= 8192 && weight_bytes < (64ll << 20)) ? W8A8_VARIANT_GEMM_CLUSTER : W8A8_VARIANT_GEMM_TCGEN05;
     }
+    // the same matrices up to 256 tokens: 24.6 / 28.7 / 32.8 us at 129 / 200 / 256 tokens against 34.8
+    if (M <= kClusterMaxTokens && K >= 8192 && weight_bytes < (64ll << 20)) return W8A8_VARIANT_GEMM_CLUSTER;
     // 256x256 tiles over CTA pairs: 5-16 % faster than 128x256 tiles from 129 tokens up, as long as there are tiles
     // for most of the 74 pairs; otherwise (O, down, Q|K|V at a few hundred tokens) the single-CTA kernel, which then
     // narrows its tiles to 128 or 64 channels to put the matrix on more SMs.
     const long long N = weight_bytes / K;
-    const long long pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    const int bn = pair_tile_channels(M, (int)N);
+    const long long pair_tiles = ((M + 255) / 256) * ((N + bn - 1) / bn);
     if (pair_tiles * 4 < (long long)(sm_count() / 2) * 3) return W8A8_VARIANT_GEMM_TCGEN05;
     // Token counts just above a multiple of 256 (300 -> 512 padded rows against 384): the 128-row tiles do a quarter
     // less work, which outweighs the pair kernel's advantage per tile.

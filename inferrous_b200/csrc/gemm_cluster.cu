@@ -1,4 +1,4 @@
-// W8A8 projection for 9..128 tokens against the small and mid-sized matrices (Q|K|V, O, down: 16-50 MB), where the
+// W8A8 projection for 9..256 tokens against the small and mid-sized matrices (Q|K|V, O, down: 16-50 MB), where the
 // product is bound by one pass over the int8 weights and by fixed latencies, and where a tile per SM would leave most
 // of the GPU idle (N = 4096 is 32 tiles of 128 channels).
 //
@@ -32,7 +32,7 @@ constexpr int UMMA_K = 32;
 constexpr int A_BYTES = TILE_N * BLOCK_K;
 constexpr int kThreads = 192;
 constexpr int kSmemBudget = 200 * 1024;
-constexpr int kMaxTokens = 128;
+constexpr int kMaxTokens = 256;
 
 struct ClusterDev {
     const float *a_scale;
@@ -102,7 +102,7 @@ gemm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int tile = blockIdx.x / split;
     const int blocks = p.K / BLOCK_K;
     const int kb_begin = (int)((long long)rank * blocks / split), kb_end = (int)((long long)(rank + 1) * blocks / split);
-    const int tmem_cols = p.ntok <= 32 ? 32 : (p.ntok <= 64 ? 64 : 128);
+    const int tmem_cols = p.ntok <= 32 ? 32 : (p.ntok <= 64 ? 64 : (p.ntok <= 128 ? 128 : 256));
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
@@ -313,6 +313,8 @@ cudaError_t launch_gemm_cluster(const LinearArgs &l, const w8a8_weight *wt, cuda
     const int stage_bytes = A_BYTES + ntok * BLOCK_K;
     const int share = (l.K / BLOCK_K + d.split - 1) / d.split;  // K blocks of the busiest CTA
     d.stages = std::max(2, std::min(std::min(8, share), (kSmemBudget - 1024) / stage_bytes));
+    // the partial tile ([ntok][128] int32) is spilled on top of the ring: the ring must be at least that large
+    d.stages = std::max(d.stages, (ntok * TILE_N * 4 + stage_bytes - 1) / stage_bytes);
     d.y = l.out[0]; d.residual = l.residual; d.combined = l.combined; d.acc = l.acc;
     d.status = device_status_ptr();
     const int grid = ((wt->N + TILE_N - 1) / TILE_N) * d.split;

@@ -259,6 +259,8 @@ template <class T, int BN> cudaError_t set_attrs() {
 // BN + 64: a 192-channel tile takes 0.80 of a 256-channel one); the wider one on a tie.  Measured at 4096 tokens:
 // Q|K|V 96.1 -> 90.1 us with 192 channels (6 -> 7 waves of smaller tiles); O, down, gate|up stay at 256; 128-channel
 // tiles lost everywhere (their K loop is bound by the token rows staged per block) and exist for tests.
+}  // namespace
+
 int pair_tile_channels(int M, int N) {
     if (const char *force = getenv("W8A8_PAIR_BN")) {
         const int bn = atoi(force);
@@ -277,8 +279,6 @@ int pair_tile_channels(int M, int N) {
     }
     return best;
 }
-
-}  // namespace
 
 cudaError_t init_gemm_tcgen05_pair() {
     cudaError_t e;

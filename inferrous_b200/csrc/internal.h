@@ -99,13 +99,14 @@ cudaError_t init_gemm_tcgen05();
 int tcgen05_tile_channels(int M, int N);  // 256, 128 or 64: output channels per tile the launcher will use
 cudaError_t launch_gemm_tcgen05_pair(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);  // CTA pairs
 cudaError_t init_gemm_tcgen05_pair();
+int pair_tile_channels(int M, int N);  // 256 or 192: output channels per tile the CTA-pair launcher will use
 cudaError_t make_weight_maps(w8a8_weight *wt);  // TMA descriptors of the [N,K] matrix
 // [rows,K] int8 row-major -> tiled map with a box of 128 bytes of K x box_rows rows, 128-byte swizzle, zero fill.
 cudaError_t encode_tile_map(CUtensorMap *map, const void *base, int rows, int K, int box_rows);
 // 9..128 tokens, small and mid-sized matrices: K split over a thread-block cluster, partial sums through distributed shared memory
 cudaError_t launch_gemm_cluster(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);
 cudaError_t init_gemm_cluster();
-constexpr int kClusterMaxTokens = 128;
+constexpr int kClusterMaxTokens = 256;
 // few-token tensor-core path (weights on the MMA's M side, stream-K over output tiles x K blocks)
 cudaError_t launch_gemm_skinny(const LinearArgs &a, const w8a8_weight *wt, cudaStream_t s);
 cudaError_t init_gemm_skinny();

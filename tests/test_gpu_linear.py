@@ -30,7 +30,7 @@ def variants_for(M):
     v = [NAIVE, TC, PAIR]
     if M <= 256:
         v.append(SKINNY)
-    if M <= 128:
+    if M <= 256:
         v.append(CLUSTER)
     if os.environ.get("W8A8_TEST_SKIP_TCGEN05"):  # bring-up aid: check the SIMT variants alone
         v = [NAIVE]
