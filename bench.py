@@ -767,11 +767,24 @@ def model_generation_table(torch, hbm_peak, rank=0, world=1, group=None, fused_a
                      "weight_GB/s": round(config.weight_bytes() / median / 1e9, 1),
                      "frac_hbm": round(config.weight_bytes() / median / 1e9 / (hbm_peak * world), 3),
                      "reference_tok_s_rtx_pro_6000": published.get(prompt_len) if generated == 32 else None})
+    resident = getattr(runner, "plan", None) is not None
     del runner
     torch.cuda.empty_cache()
     table = {"model": "Qwen3-8B architecture, random-init W8A8 weights (body and head int8), batch 1, greedy",
              "parallelism": f"tp{world}" if world > 1 else "single", "all_reduce": exchange,
+             "decode_step": ("one resident cooperative kernel for all layers (qwen3_decode_layers) + head" if resident
+                             else "one launch per operator, CUDA graph with programmatic edges"),
              "weight_bytes_per_token": config.weight_bytes(), "runs": rows}
+    if resident:  # the same step as one launch per operator, for comparison
+        other = Qwen3Runner(weights, resident=False)
+        prompt = [int(t) for t in np.random.default_rng(0).integers(0, config.vocab, 129)]
+        other.generate(prompt, 32)
+        _, seconds = other.generate(prompt, 32)
+        median = float(np.median(seconds[1:]))
+        table["separate_launches"] = {"prompt": 129, "generated": 32, "decode_ms_per_token_median": round(median * 1e3, 4),
+                                      "decode_tok_s": round(len(seconds[1:]) / sum(seconds[1:]), 1)}
+        del other
+        torch.cuda.empty_cache()
     try:
         table["config4"] = config4_table(torch, weights, config, hbm_peak, rank, world, group,
                                          fused_allreduce and not exchange.startswith("NCCL"))

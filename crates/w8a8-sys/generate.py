@@ -11,7 +11,25 @@ TYPES = {
  'const uint16_t *': '*const u16', 'uint16_t *': '*mut u16', 'int32_t *': '*mut i32', 'int *': '*mut c_int',
  'w8a8_weight_t': '*mut W8a8Weight', 'w8a8_weight_t *': '*mut *mut W8a8Weight', 'const w8a8_weight_t *': '*const *mut W8a8Weight',
  'void *const *': '*const *mut c_void', 'uint32_t *const *': '*const *mut u32', 'const char *': '*const c_char',
+ 'const qwen3_layer_desc *': '*const Qwen3LayerDesc', 'qwen3_decode_plan_t': '*mut Qwen3DecodePlan',
+ 'qwen3_decode_plan_t *': '*mut *mut Qwen3DecodePlan', 'const struct w8a8_weight *': '*const W8a8Weight',
 }
+def struct_fields(h, name):
+    """Fields of `typedef struct name {...} name;` as (field, rust type), one per declarator."""
+    text = re.sub(r"/\*.*?\*/", "", (ROOT/h).read_text(), flags=re.S)
+    body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (name, name), text, flags=re.S).group(1)
+    out = []
+    for decl in body.split(';'):
+        decl = ' '.join(decl.split())
+        if not decl:
+            continue
+        first, *rest = [d.strip() for d in decl.split(',')]
+        m = re.match(r"(.*?)(\w+)$", first)
+        ty = m.group(1).strip()
+        out.append((m.group(2), TYPES[ty]))
+        for more in rest:  # `*name`: the pointer belongs to the declarator
+            out.append((more.lstrip('* '), TYPES[ty]))
+    return out
 def parse(h):
     text = re.sub(r"/\*.*?\*/", "", (ROOT/h).read_text(), flags=re.S)
     text = re.sub(r"#.*", "", text)
@@ -32,6 +50,7 @@ for h, title in [('include/w8a8.h', 'the W8A8 linear-layer path'), ('include/qwe
         rs = ', '.join(f"{n}: {t}" for n, t in map(arg, args))
         lines.append(f"    pub fn {name}({rs}) -> {TYPES.get(ret, 'c_int') if ret != 'int' else 'c_int'};")
 body = '\n'.join(lines)
+layer_fields = '\n'.join(f"    pub {n}: {t}," for n, t in struct_fields('include/qwen3_glue.h', 'qwen3_layer_desc'))
 src = f'''//! Raw bindings to `libw8a8.so`, the sm_100a (B200) implementation of the W8A8 linear-layer path of
 //! inferrous-qwen3: one `extern "C"` declaration per function of `include/w8a8.h` and `include/qwen3_glue.h`,
 //! plus the status codes and enums of those headers.  The host keeps its own buffers, stream and graphs
@@ -52,6 +71,18 @@ use std::os::raw::{{c_char, c_int, c_void}};
 #[repr(C)]
 pub struct W8a8Weight {{
     _private: [u8; 0],
+}}
+
+/// Opaque plan of the resident decode kernel (`qwen3_decode_plan_t`).
+#[repr(C)]
+pub struct Qwen3DecodePlan {{
+    _private: [u8; 0],
+}}
+
+/// One decoder layer as `qwen3_decode_plan_create` takes it (`qwen3_layer_desc`).
+#[repr(C)]
+pub struct Qwen3LayerDesc {{
+{layer_fields}
 }}
 
 pub const W8A8_OK: c_int = 0;

@@ -20,6 +20,28 @@ pub struct W8a8Weight {
     _private: [u8; 0],
 }
 
+/// Opaque plan of the resident decode kernel (`qwen3_decode_plan_t`).
+#[repr(C)]
+pub struct Qwen3DecodePlan {
+    _private: [u8; 0],
+}
+
+/// One decoder layer as `qwen3_decode_plan_create` takes it (`qwen3_layer_desc`).
+#[repr(C)]
+pub struct Qwen3LayerDesc {
+    pub norm1: *const c_void,
+    pub qkv: *const W8a8Weight,
+    pub q_gain: *const f32,
+    pub k_gain: *const f32,
+    pub o: *const W8a8Weight,
+    pub norm2: *const c_void,
+    pub gate: *const W8a8Weight,
+    pub up: *const W8a8Weight,
+    pub down: *const W8a8Weight,
+    pub k_cache: *mut u16,
+    pub v_cache: *mut u16,
+}
+
 pub const W8A8_OK: c_int = 0;
 pub const W8A8_ERR_BAD_ARG: c_int = 1;
 pub const W8A8_ERR_ALIGNMENT: c_int = 2;
@@ -86,6 +108,9 @@ extern "C" {
     pub fn qwen3_select_token(logits: *const c_void, dtype: c_int, rows: c_int, n: c_int, ld: i64, token: *mut u32, value: *mut f32, stream: *mut c_void) -> c_int;
     pub fn qwen3_head_bf16(x: *const c_void, dtype: c_int, w: *const u16, vocab: c_int, hidden: c_int, logits: *mut c_void, token: *mut u32, value: *mut f32, stream: *mut c_void) -> c_int;
     pub fn qwen3_merge_candidates(candidates: *const u32, parts: c_int, rows: c_int, part_width: c_int, token: *mut u32, stream: *mut c_void) -> c_int;
+    pub fn qwen3_decode_plan_create(layers: *const Qwen3LayerDesc, n_layers: c_int, hidden: c_int, q_heads: c_int, kv_heads: c_int, intermediate: c_int, capacity: c_int, eps: f32, rope_table: *const f32, dtype: c_int, plan: *mut *mut Qwen3DecodePlan) -> c_int;
+    pub fn qwen3_decode_plan_destroy(plan: *mut Qwen3DecodePlan) -> c_int;
+    pub fn qwen3_decode_layers(plan: *mut Qwen3DecodePlan, hidden: *mut c_void, control: *const u32, stream: *mut c_void) -> c_int;
     pub fn qwen3_attention_use_tensor_cores(enabled: c_int) -> c_int;
 }
 

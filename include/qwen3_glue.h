@@ -117,6 +117,47 @@ int qwen3_head_bf16(const void *x, int dtype, const uint16_t *w, int vocab, int 
  * id), or 0xffffffff if any part reported 0xffffffff or a non-finite value. */
 int qwen3_merge_candidates(const uint32_t *candidates, int parts, int rows, int part_width, uint32_t *token, void *stream);
 
+/* ---- One decode step of the whole decoder stack as a single resident kernel ------------------------------------
+ * No counterpart in the reference as an interface: it runs its decode step as a captured graph of one launch per
+ * operator with programmatic edges and next-weight prefetch CTAs (src/graph.rs:63-127, src/gpu.rs:318-328,
+ * src/kernels.rs:173-237), which is what the launch-per-operator path of this library restates.  This entry point runs
+ * the same operators, for ONE row of one sequence, inside one cooperative kernel with one CTA per SM: for every layer
+ * norm_quantize -> Q|K|V projection -> prepare_qk -> attention -> quantize -> O projection + residual -> norm_quantize ->
+ * gate|up projection + SwiGLU -> quantize -> down projection + residual, separated by grid-wide barriers instead of
+ * kernel boundaries, each CTA quantizing the activation row for itself and requesting its share of the next matrix from
+ * L2 before it waits.  The result (hidden row, KV-cache entries) is bit-identical to the separate calls
+ * w8a8_rmsnorm_quantize / w8a8_linear / qwen3_prepare_qk / qwen3_attention / w8a8_quantize / w8a8_linear (residual) /
+ * w8a8_linear_gate_up_swiglu / w8a8_quantize with the same inputs.
+ *
+ * A plan holds device copies of the layer table and the step's work buffers; creating it allocates, running it does not.
+ * The weights, gains, caches and the rotary table named by the plan must stay alive and in place until it is destroyed.
+ * Limits: hidden, q_heads * 128 and intermediate at most 12288 and multiples of 16; capacity <= 4096; the device must
+ * support cooperative launches (W8A8_ERR_UNSUPPORTED otherwise: use the separate calls). */
+struct w8a8_weight;
+typedef struct qwen3_decode_plan *qwen3_decode_plan_t;
+typedef struct qwen3_layer_desc {
+    const void *norm1;                 /* [hidden] RMSNorm gain in front of Q|K|V, in the carrier `dtype` */
+    const struct w8a8_weight *qkv;     /* [(q_heads + 2 kv_heads) * 128, hidden]: query heads, key heads, value heads */
+    const float *q_gain, *k_gain;      /* [128] head-norm gains */
+    const struct w8a8_weight *o;       /* [hidden, q_heads * 128] */
+    const void *norm2;                 /* [hidden] RMSNorm gain in front of gate / up */
+    const struct w8a8_weight *gate;    /* [intermediate, hidden] */
+    const struct w8a8_weight *up;      /* [intermediate, hidden] */
+    const struct w8a8_weight *down;    /* [hidden, intermediate] */
+    uint16_t *k_cache, *v_cache;       /* [capacity][kv_heads][128] bf16, as for qwen3_prepare_qk */
+} qwen3_layer_desc;
+
+int qwen3_decode_plan_create(const qwen3_layer_desc *layers, int n_layers, int hidden, int q_heads, int kv_heads, int intermediate,
+                             int capacity, float eps, const float *rope_table, int dtype, qwen3_decode_plan_t *plan);
+int qwen3_decode_plan_destroy(qwen3_decode_plan_t plan);
+
+/* hidden: [hidden] in the plan's carrier, the embedding row of the token on entry and the last layer's output on return.
+ * control[1] is the token's position (read on the device, as in qwen3_prepare_qk); the step appends that position's key
+ * and value to every layer's caches.  Queues one 8-byte memset and one kernel on `stream`; capturable.  Two steps of one
+ * plan must not overlap on the device.  A grid-wide wait that runs out (about two seconds) ends the kernel early, leaves
+ * `hidden` undefined and code 7 in the device status word (w8a8_device_status). */
+int qwen3_decode_layers(qwen3_decode_plan_t plan, void *hidden, const uint32_t *control, void *stream);
+
 /* Launches of 32 rows or more (prefill) run both attention products on the tensor cores (bf16 warp-level MMA, float32
  * accumulation, softmax weights carried as two bf16 parts); 0 keeps them on the CUDA-core kernel that shorter launches
  * use, for comparison.  Process-wide; default 1. */

@@ -17,7 +17,7 @@ CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB = LIB_DIR / "libw8a8.so"
 OBJ_DIR = PKG / "lib" / "obj"
-SOURCES = ["capi.cu", "quantize.cu", "naive.cu", "gemv.cu", "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "gemm_skinny.cu", "gemm_cluster.cu", "tp_allreduce.cu", "forward_glue.cu", "batched_decode.cu", "head_bf16.cu"]
+SOURCES = ["capi.cu", "quantize.cu", "naive.cu", "gemv.cu", "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "gemm_skinny.cu", "gemm_cluster.cu", "tp_allreduce.cu", "forward_glue.cu", "batched_decode.cu", "head_bf16.cu", "decode_layers.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -54,10 +54,19 @@ SIGNATURES = {
     "qwen3_head_bf16": (_i, [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp]),
     "qwen3_select_token": (_i, [_vp, _i, _i, _i, _i64, _vp, _vp, _vp]),
     "qwen3_merge_candidates": (_i, [_vp, _i, _i, _i, _vp, _vp]),
+    "qwen3_decode_plan_create": (_i, [_vp, _i, _i, _i, _i, _i, _i, _f, _vp, _i, C.POINTER(_vp)]),
+    "qwen3_decode_plan_destroy": (_i, [_vp]),
+    "qwen3_decode_layers": (_i, [_vp, _vp, _vp, _vp]),
     "qwen3_attention_use_tensor_cores": (_i, [_i]),
     "qwen3_attention_quantize": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp]),
     "qwen3_attention": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _i, _vp, _vp]),
 }
+
+
+class LayerDesc(C.Structure):
+    """qwen3_layer_desc (include/qwen3_glue.h)."""
+    _fields_ = [("norm1", _vp), ("qkv", _vp), ("q_gain", _vp), ("k_gain", _vp), ("o", _vp), ("norm2", _vp), ("gate", _vp),
+                ("up", _vp), ("down", _vp), ("k_cache", _vp), ("v_cache", _vp)]
 
 
 class W8A8Error(RuntimeError):

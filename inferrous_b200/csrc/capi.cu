@@ -197,6 +197,7 @@ int w8a8_init(int device) {
     CUDA_OK(init_forward_glue(), "init_forward_glue");
     CUDA_OK(init_batched_decode(), "init_batched_decode");
     CUDA_OK(init_head_bf16(), "init_head_bf16");
+    CUDA_OK(init_decode_layers(), "init_decode_layers");
     d.ready = true;
     return W8A8_OK;
 }

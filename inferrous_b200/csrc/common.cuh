@@ -20,6 +20,7 @@ enum DeviceWait : uint32_t {
     WAIT_ACC_EMPTY = 4,   // MMA waited for the epilogue to drain an accumulator
     WAIT_PEER = 5,        // tensor-parallel all-reduce waited for another rank's partial outputs
     FAULT_CACHE_RANGE = 6,  // not a wait: a token id or cache position read from device memory was out of range; the access was skipped
+    WAIT_GRID = 7,        // a CTA of the resident decode kernel waited for the others at a grid-wide barrier
 };
 
 __device__ __forceinline__ float bf16_rne(float x) {

@@ -1,0 +1,694 @@
+// One decode step of a Qwen3 decoder stack (one token, one sequence) as ONE resident kernel: every layer's
+// RMSNorm + quantize -> Q|K|V -> head norm + rotary + cache append -> attention -> quantize -> O + residual ->
+// RMSNorm + quantize -> gate|up + SwiGLU -> quantize -> down + residual, with grid-wide barriers between the
+// steps that depend on each other instead of kernel boundaries.
+//
+// Why: launched as separate kernels a step is ten dependent launches per layer, and at one token each of them is
+// shorter than the latency of the dependency itself (the reference's answer to the same problem is its captured
+// graph with programmatic edges and next-weight prefetch CTAs, src/graph.rs:63-127, src/kernels.rs:173-237).  Here
+// one CTA per SM stays resident for the whole stack:
+//   * the activation quantizers run as a prologue of the projection that consumes them, once per SM (not once per
+//     launch-sized CTA), while that CTA's first weight lines are already on their way;
+//   * before a CTA arrives at a barrier it asks L2 for the first part of its share of the NEXT matrix (weights are
+//     immutable), and inside a projection every warp keeps such requests a fixed distance ahead of its loads, so
+//     the HBM stream does not stop at a barrier;
+//   * head norm + rotary embedding are done by the attention units themselves (each recomputes its query head and,
+//     where its key range holds the newest position, that key), which removes one dependent step per layer.
+// Arithmetic: exactly that of the separate kernels (quantize.cu, gemv.cu, forward_glue.cu), so a step gives the
+// same bits as the launch-per-operator path: int32 sums are exact, every float operation is element-wise or follows
+// the same fixed association, and attention is the shared device function of attention_unit.cuh.
+//
+// Every wait is bounded (about two seconds): on expiry the waiter raises the abort word, records WAIT_GRID in the
+// device status word, and every CTA leaves at its next barrier.  The kernel is launched cooperatively, so either all
+// of its CTAs are resident or the launch fails; it never waits for a CTA that cannot run.
+#include "../../include/qwen3_glue.h"
+#include "../../include/w8a8.h"
+#include "attention_unit.cuh"
+#include "common.cuh"
+#include "internal.h"
+#include "ptx.cuh"
+
+#include <cstdlib>
+#include <new>
+#include <vector>
+
+struct qwen3_decode_plan;
+
+namespace w8a8 {
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kGroupWarps = 8;              // a group of eight warps covers 4096 bytes of a weight row per load round
+constexpr int kGroupBytes = kGroupWarps * 32 * 16;
+constexpr int kMaxRounds = 3;               // K <= 12288
+constexpr int kMaxK = kMaxRounds * kGroupBytes;
+constexpr int kMaxCtaRows = 256;            // weight rows one CTA may own in a projection
+constexpr int kHeadDim = kUnitHeadDim;
+
+struct LayerDev {
+    const void *norm1, *norm2;      // RMSNorm gains, carrier storage type
+    const float *q_gain, *k_gain;   // head-norm gains
+    const int8_t *qkv, *o, *gate, *up, *down;
+    const float *qkv_s, *o_s, *gate_s, *up_s, *down_s;
+    uint16_t *k_cache, *v_cache;    // [capacity][kv_heads][128] bf16
+};
+
+struct StepDev {
+    const LayerDev *layers;
+    int n_layers, hidden, q_heads, kv_heads, inter, capacity, splits;
+    float eps;
+    const float *rope;          // [capacity][128]: cos 0..63, sin 0..63
+    const uint32_t *control;    // {token, position}
+    void *hidden_io;            // [hidden]: embedding row in, last layer's output out
+    void *residual;             // [hidden]
+    void *qkv;                  // [(q_heads + 2 kv_heads) * 128]
+    void *attn;                 // [q_heads * 128]
+    void *act;                  // [inter]
+    float *scratch;             // attention: per (head, split) records
+    uint32_t *counters;         // attention: per head arrival counters (zero between launches)
+    uint32_t *sync;             // {arrivals, abort}: zeroed by the host before every launch
+    uint32_t *status;
+    int ahead_bytes;            // per CTA: bytes of the next matrix requested from L2 before a barrier
+    int ahead_rows;             // inside a projection: L2 requests run this many row batches ahead of the loads
+};
+
+// ---- loads of values another CTA wrote during this kernel: from L2, never from this SM's L1 ----------------
+template <class T> __device__ __forceinline__ void load_vec_cg(const typename T::storage *p, float (&v)[T::kVec]) {
+    const uint4 r = __ldcg(reinterpret_cast<const uint4 *>(p));
+    Vec<T>::unpack(r, v);
+}
+template <class T> __device__ __forceinline__ float load_one_cg(const typename T::storage *p);
+template <> __device__ __forceinline__ float load_one_cg<Bf16>(const uint16_t *p) { return bf16_to_f32(__ldcg(p)); }
+template <> __device__ __forceinline__ float load_one_cg<F32>(const float *p) { return __ldcg(p); }
+
+// ---- grid-wide barrier ---------------------------------------------------------------------------------------
+// sync[0] counts arrivals since the launch (the host zeroes it), so the n-th barrier is passed when it reaches
+// n * gridDim.x.  Returns false when the wait was abandoned; the caller leaves the kernel.
+__device__ __forceinline__ bool grid_barrier(const StepDev &a, uint32_t &passed, uint32_t *ok_smem) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        passed += 1;
+        const uint32_t target = passed * gridDim.x;
+        __threadfence();
+        atomicAdd(a.sync, 1u);
+        uint32_t good = 1;
+        unsigned long long t0 = 0;
+        for (uint32_t spin = 1;; ++spin) {
+            uint32_t seen;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(a.sync) : "memory");
+            if (seen >= target) break;
+            if ((spin & 63u) == 0) {
+                uint32_t stop;
+                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(stop) : "l"(a.sync + 1) : "memory");
+                if (stop) { good = 0; break; }
+                const unsigned long long now = global_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > kWaitLimitNs) {
+                    atomicExch(a.sync + 1, 1u);
+                    if (a.status && atomicCAS(a.status, 0u, (uint32_t)WAIT_GRID) == 0u) a.status[1] = blockIdx.x;
+                    good = 0;
+                    break;
+                }
+            }
+        }
+        *ok_smem = good;
+    }
+    __syncthreads();
+    return *ok_smem != 0;
+}
+
+// This CTA's rows [r0, r1) of an N-row matrix.
+__device__ __forceinline__ void cta_rows(int N, int &r0, int &r1) {
+    r0 = (int)(((long long)N * blockIdx.x) / gridDim.x);
+    r1 = (int)(((long long)N * (blockIdx.x + 1)) / gridDim.x);
+}
+
+// Ask L2 for the first `limit` bytes of rows [r0, r1) of a [N][K] matrix (whole 128-byte lines inside the range).
+__device__ __forceinline__ void request_rows(const int8_t *w, int K, int r0, int r1, int limit) {
+    if (r1 <= r0) return;
+    const unsigned long long base = reinterpret_cast<unsigned long long>(w) + (unsigned long long)r0 * K;
+    unsigned long long bytes = (unsigned long long)(r1 - r0) * K;
+    if (bytes > (unsigned long long)limit) bytes = (unsigned long long)limit;
+    const unsigned long long begin = (base + 127ull) & ~127ull, end = (base + bytes) & ~127ull;
+    for (unsigned long long p = begin + 128ull * threadIdx.x; p < end; p += 128ull * kThreads)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+// ---- quantizing prologues: the unquantized row -> int8 codes in shared memory, returns the scale --------------
+struct PrologueShared {
+    float red[256];
+    uint32_t slots[32];
+};
+
+// quantize (src/kernels.rs:415-452): m = max(1e-8, max|x|) ignoring NaN; s = m / 127; q = rne(clamp(x / s))
+template <class T>
+__device__ __forceinline__ float prologue_plain(const typename T::storage *x, int K, int8_t *sq, float *row, PrologueShared &ps, int tid) {
+    constexpr int V = T::kVec;
+    float m = 1e-8f;
+    for (int j = tid * V; j < K; j += kThreads * V) {
+        float v[V];
+        load_vec_cg<T>(x + j, v);
+#pragma unroll
+        for (int i = 0; i < V; ++i) m = fmaxf(m, fabsf(v[i]));  // fmaxf drops a NaN operand
+#pragma unroll
+        for (int i = 0; i < V; i += 4) *reinterpret_cast<float4 *>(row + j + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    }
+    const float s = __fdiv_rn(block_max(m, ps.slots, tid), 127.0f);
+    const float inv = __frcp_rn(s);
+    for (int j = tid * V; j < K; j += kThreads * V) {  // each thread re-reads exactly the elements it parked
+        int c[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) c[i] = quant_code(row[j + i], s, inv);
+        store_codes<V>(sq + j, c);
+    }
+    return s;
+}
+
+// norm_quantize (src/kernels.rs:479-576): the reference's summation tree (256 strided partial sums, distances
+// 128..1), y = bf16((x * rsqrt(mean + eps)) * gain), m = max(1e-8, max|y|), s = m / 127
+template <class T>
+__device__ __forceinline__ float prologue_rmsnorm(const typename T::storage *x, const typename T::storage *gain, float eps, int K,
+                                                  int8_t *sq, float *row, PrologueShared &ps, int tid) {
+    constexpr int V = T::kVec;
+    for (int j = tid * V; j < K; j += kThreads * V) {
+        float v[V];
+        load_vec_cg<T>(x + j, v);
+#pragma unroll
+        for (int i = 0; i < V; i += 4) *reinterpret_cast<float4 *>(row + j + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    }
+    __syncthreads();
+    if (tid < 256) {
+        float p = 0.0f;
+        for (int j = tid; j < K; j += 256) p = __fadd_rn(p, __fmul_rn(row[j], row[j]));
+        ps.red[tid] = p;
+    }
+    __syncthreads();
+    if (tid < 32) {
+        const float *red = ps.red;
+        float t = __fadd_rn(__fadd_rn(__fadd_rn(red[tid], red[tid + 128]), __fadd_rn(red[tid + 64], red[tid + 192])),
+                            __fadd_rn(__fadd_rn(red[tid + 32], red[tid + 160]), __fadd_rn(red[tid + 96], red[tid + 224])));
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) t = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, d));
+        if (tid == 0) ps.red[0] = t;
+    }
+    __syncthreads();
+    const float inv_norm = rsqrt_approx(__fadd_rn(__fdiv_rn(ps.red[0], (float)K), eps));
+    float m = 1e-8f;
+    for (int j = tid * V; j < K; j += kThreads * V) {
+        float g[V];
+        Vec<T>::load(gain + j, g);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const float y = bf16_rne(__fmul_rn(__fmul_rn(row[j + i], inv_norm), g[i]));
+            m = fmaxf(m, fabsf(y));
+            row[j + i] = y;
+        }
+    }
+    const float s = __fdiv_rn(block_max(m, ps.slots, tid), 127.0f);
+    const float inv = __frcp_rn(s);
+    for (int j = tid * V; j < K; j += kThreads * V) {
+        int c[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) c[i] = quant_code(row[j + i], s, inv);
+        store_codes<V>(sq + j, c);
+    }
+    return s;
+}
+
+// ---- one projection, this CTA's share ------------------------------------------------------------------------
+// The CTA owns the weight rows [r0, r1) (row pairs (gate c, up c) for the SwiGLU form).  Its sixteen warps form two
+// groups of eight; a group takes every other row and spreads the row's K bytes over its 256 lanes, 16 bytes each per
+// round of 4096 bytes, so the lane's slice of the activation codes stays in registers for the whole projection.
+// Per row and warp: J loads, 4 J dp4a, one warp-wide integer add; the eight partial sums of a row meet in shared
+// memory and one thread per row finishes it (exact: int32).
+enum { PRJ_PLAIN = 0, PRJ_RESIDUAL = 1, PRJ_SWIGLU = 2 };
+
+__device__ __forceinline__ int dp4a_16(const uint4 &w, const uint4 &x, int acc) {
+    acc = __dp4a((int)w.x, (int)x.x, acc);
+    acc = __dp4a((int)w.y, (int)x.y, acc);
+    acc = __dp4a((int)w.z, (int)x.z, acc);
+    acc = __dp4a((int)w.w, (int)x.w, acc);
+    return acc;
+}
+
+template <class T, int EPI, int J>
+__device__ void project(const StepDev &a, const int8_t *__restrict__ w0, const int8_t *__restrict__ w1,
+                        const float *__restrict__ ws0, const float *__restrict__ ws1, int N, int K, float a_scale,
+                        const int8_t *sq, int *red, const typename T::storage *residual, typename T::storage *out, int tid) {
+    constexpr int R = (EPI == PRJ_SWIGLU) ? 2 : 1;
+    constexpr int U = (R * J == 1) ? 8 : (R * J == 2) ? 4 : (R * J == 3) ? 3 : (R * J == 4) ? 2 : 1;  // row units per batch
+    const int lane = tid & 31, warp = tid >> 5;
+    const int g = warp / kGroupWarps, slot = warp % kGroupWarps;
+    int r0, r1;
+    cta_rows(N, r0, r1);
+    const int units = r1 - r0;
+    const int mine = (units - g + 1) / 2;  // this group's units: local index g, g + 2, ...
+
+    // what the finishing thread of a row needs, requested now so that the end of the projection waits on registers
+    float pre_s0 = 0.0f, pre_s1 = 0.0f, pre_res = 0.0f;
+    if (tid < units) {
+        pre_s0 = ws0[r0 + tid];
+        if (EPI == PRJ_SWIGLU) pre_s1 = ws1[r0 + tid];
+        if (EPI == PRJ_RESIDUAL) pre_res = load_one_cg<T>(residual + r0 + tid);
+    }
+
+    int off[J];
+    bool valid[J];
+    uint4 av[J];
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+        off[j] = j * kGroupBytes + slot * 512 + lane * 16;
+        valid[j] = off[j] < K;
+        av[j] = valid[j] ? *reinterpret_cast<const uint4 *>(sq + off[j]) : make_uint4(0, 0, 0, 0);
+    }
+
+    uint4 wv[U][R][J];
+    auto issue = [&](int first) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = first + u;
+            const bool live = idx < mine;
+            const long long row = (long long)(r0 + g + 2 * idx) * K;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int8_t *wr = (r == 0 ? w0 : w1) + row;
+#pragma unroll
+                for (int j = 0; j < J; ++j) wv[u][r][j] = (live && valid[j]) ? ld_stream_16(wr + off[j]) : make_uint4(0, 0, 0, 0);
+            }
+            // L2 requests a fixed number of batches ahead of the loads (one lane per 128-byte line)
+            const int far = idx + a.ahead_rows * U;
+            if (a.ahead_rows > 0 && far < mine && (lane & 7) == 0) {
+                const long long frow = (long long)(r0 + g + 2 * far) * K;
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+#pragma unroll
+                    for (int j = 0; j < J; ++j)
+                        if (valid[j]) asm volatile("prefetch.global.L2 [%0];" ::"l"((r == 0 ? w0 : w1) + frow + off[j]));
+            }
+        }
+    };
+    issue(0);
+    for (int first = 0; first < mine; first += U) {
+        int acc[U][R];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                int s = 0;
+#pragma unroll
+                for (int j = 0; j < J; ++j) s = dp4a_16(wv[u][r][j], av[j], s);
+                acc[u][r] = s;
+            }
+        if (first + U < mine) issue(first + U);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int total = warp_sum_i32(acc[u][r]);
+                const int idx = first + u;
+                if (lane == 0 && idx < mine) red[((g + 2 * idx) * R + r) * kGroupWarps + slot] = total;
+            }
+    }
+    __syncthreads();
+    if (tid < units) {
+        int sum[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int4 lo = *reinterpret_cast<const int4 *>(red + (tid * R + r) * kGroupWarps);
+            const int4 hi = *reinterpret_cast<const int4 *>(red + (tid * R + r) * kGroupWarps + 4);
+            sum[r] = lo.x + lo.y + lo.z + lo.w + hi.x + hi.y + hi.z + hi.w;
+        }
+        const int c = r0 + tid;
+        if (EPI == PRJ_SWIGLU) {
+            const float gv = dequant(sum[0], a_scale, pre_s0);
+            const float uv = dequant(sum[R - 1], a_scale, pre_s1);
+            T::store(out + c, swiglu_value(gv, uv));
+        } else if (EPI == PRJ_RESIDUAL) {
+            T::store(out + c, bf16_rne(__fadd_rn(pre_res, dequant(sum[0], a_scale, pre_s0))));
+        } else {
+            T::store(out + c, dequant(sum[0], a_scale, pre_s0));
+        }
+    }
+}
+
+template <class T, int EPI>
+__device__ __forceinline__ void project_any(const StepDev &a, const int8_t *w0, const int8_t *w1, const float *ws0, const float *ws1,
+                                            int N, int K, float a_scale, const int8_t *sq, int *red,
+                                            const typename T::storage *residual, typename T::storage *out, int tid) {
+    if (K <= kGroupBytes) project<T, EPI, 1>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid);
+    else if (K <= 2 * kGroupBytes) project<T, EPI, 2>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid);
+    else project<T, EPI, 3>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid);
+}
+
+// ---- attention: two units side by side per CTA ------------------------------------------------------------------
+// Head RMSNorm + rotary embedding of one 128-wide head by one warp (prepare_qk, src/kernels.rs:1350-1443): lane l
+// holds elements l, l+32, l+64, l+96, so the first tree level ((p[t] + p[t+64]) + (p[t+32] + p[t+96]) for t < 32) and
+// the rotary pairs (t, t+64) are lane-local.
+template <class T>
+__device__ __forceinline__ void head_norm_rope(const typename T::storage *x, const float *gain, const float *trow, int lane,
+                                               float (&r)[4]) {
+    float v[4], g[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[i] = load_one_cg<T>(x + lane + 32 * i);
+        g[i] = gain[lane + 32 * i];
+    }
+    const float c0 = trow[lane], c1 = trow[lane + 32], s0 = trow[lane + 64], s1 = trow[lane + 96];
+    float sum = __fadd_rn(__fadd_rn(__fmul_rn(v[0], v[0]), __fmul_rn(v[2], v[2])),
+                          __fadd_rn(__fmul_rn(v[1], v[1]), __fmul_rn(v[3], v[3])));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum = __fadd_rn(sum, __shfl_down_sync(0xffffffffu, sum, d));
+    sum = __shfl_sync(0xffffffffu, sum, 0);
+    const float inv = rsqrt_approx(__fadd_rn(__fdiv_rn(sum, 128.0f), 1e-6f));
+    float n[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) n[i] = bf16_rne(__fmul_rn(__fmul_rn(v[i], inv), g[i]));
+    r[0] = bf16_rne(__fadd_rn(__fmul_rn(n[0], c0), -__fmul_rn(n[2], s0)));
+    r[2] = bf16_rne(__fadd_rn(__fmul_rn(n[2], c0), __fmul_rn(n[0], s0)));
+    r[1] = bf16_rne(__fadd_rn(__fmul_rn(n[1], c1), -__fmul_rn(n[3], s1)));
+    r[3] = bf16_rne(__fadd_rn(__fmul_rn(n[3], c1), __fmul_rn(n[1], s1)));
+}
+
+// Unit u of the step: split-major, so that the splits a short context leaves unused are the last units.
+__device__ __forceinline__ void unit_of(const StepDev &a, int u, int &head, int &split) {
+    split = u / a.q_heads;
+    head = u % a.q_heads;
+}
+
+// Before the barrier in front of the attention step: ask L2 for the cache lines of this half-CTA's first unit.
+__device__ __forceinline__ void request_cache(const StepDev &a, const LayerDev &L, int end, int tid) {
+    const int half = tid >> 8, t = tid & 255;
+    const int u = blockIdx.x * 2 + half;
+    if (u >= a.q_heads * a.splits) return;
+    int head, split, splits, begin, stop;
+    unit_of(a, u, head, split);
+    unit_range(end, a.splits, split, splits, begin, stop);
+    if (split >= splits) return;
+    const int kv = head / (a.q_heads / a.kv_heads);
+    const size_t stride_bytes = (size_t)a.kv_heads * kHeadDim * sizeof(uint16_t);
+    const char *kline = reinterpret_cast<const char *>(L.k_cache) + (size_t)kv * kHeadDim * sizeof(uint16_t);
+    const char *vline = reinterpret_cast<const char *>(L.v_cache) + (size_t)kv * kHeadDim * sizeof(uint16_t);
+    for (int i = t; i < 2 * (stop - begin); i += 256) {  // two 128-byte lines per key and per cache
+        const size_t off = (size_t)(begin + (i >> 1)) * stride_bytes + (size_t)(i & 1) * 128;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(kline + off));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(vline + off));
+    }
+}
+
+template <class T>
+__device__ void attention_phase(const StepDev &a, const LayerDev &L, UnitShared *both, int end, int tid) {
+    typedef typename T::storage S;
+    const int half = tid >> 8, t = tid & 255, warp = t >> 5, lane = t & 31;
+    UnitShared &sh = both[half];
+    const SyncNamed sync{1 + half};
+    const int group = a.q_heads / a.kv_heads;
+    const size_t key_stride = (size_t)a.kv_heads * kHeadDim;
+    const S *qkv = static_cast<const S *>(a.qkv);
+    const float *trow = a.rope + (size_t)(end - 1) * kHeadDim;
+    for (int u = blockIdx.x * 2 + half; u < a.q_heads * a.splits; u += 2 * gridDim.x) {
+        int head, split, splits, begin, stop;
+        unit_of(a, u, head, split);
+        unit_range(end, a.splits, split, splits, begin, stop);
+        if (split >= splits) continue;  // the same for all 256 threads
+        const int kv = head / group;
+        const bool holds_newest = begin <= end - 1 && end - 1 < stop;
+        if (warp == 0) {
+            float r[4];
+            head_norm_rope<T>(qkv + (size_t)head * kHeadDim, L.q_gain, trow, lane, r);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sh.query[lane + 32 * i] = r[i];
+        } else if (warp == 1 && holds_newest) {
+            // the newest key and value are not in the cache yet: this unit makes its own copy, and the first query
+            // head of the group also appends them to the cache (cache, src/kernels.rs:1470-1488)
+            float r[4];
+            head_norm_rope<T>(qkv + (size_t)(a.q_heads + kv) * kHeadDim, L.k_gain, trow, lane, r);
+            const S *vx = qkv + (size_t)(a.q_heads + a.kv_heads + kv) * kHeadDim;
+            const size_t at = ((size_t)(end - 1) * a.kv_heads + kv) * kHeadDim;
+            const bool append = head % group == 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint16_t kb = (uint16_t)(__float_as_uint(r[i]) >> 16);
+                const uint16_t vb = (uint16_t)(__float_as_uint(load_one_cg<T>(vx + lane + 32 * i)) >> 16);
+                sh.fresh_k[lane + 32 * i] = kb;
+                sh.fresh_v[lane + 32 * i] = vb;
+                if (append) {
+                    L.k_cache[at + lane + 32 * i] = kb;
+                    L.v_cache[at + lane + 32 * i] = vb;
+                }
+            }
+        }
+        sync();
+        attention_unit<T, true>(sh, sync, t, L.k_cache + (size_t)kv * kHeadDim, L.v_cache + (size_t)kv * kHeadDim, key_stride, end,
+                                splits, split, begin, stop, a.splits, head, a.scratch, a.counters,
+                                static_cast<S *>(a.attn) + (size_t)head * kHeadDim, nullptr);
+        sync();  // sh is reused by this half's next unit
+    }
+}
+
+// ---- the step -------------------------------------------------------------------------------------------------
+struct StepShared {
+    int8_t codes[kMaxK];                       // the quantized activation row of the current projection
+    int red[kMaxCtaRows * kGroupWarps];        // per weight row: the eight partial sums of its group
+    PrologueShared ps;
+    uint32_t ok;
+    uint32_t pad[3];
+    union {
+        float row[kMaxK];                      // prologues: the unquantized / normalised row
+        UnitShared units[2];                   // attention
+    };
+};
+
+template <class T>
+__global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const StepDev a) {
+    typedef typename T::storage S;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    StepShared &sh = *reinterpret_cast<StepShared *>(smem_raw);
+    const int tid = threadIdx.x;
+    const uint32_t pos = a.control[1];
+    if (pos >= (uint32_t)a.capacity) {  // every CTA takes this branch: nobody waits for anybody
+        if (blockIdx.x == 0 && tid == 0 && a.status && atomicCAS(a.status, 0u, (uint32_t)FAULT_CACHE_RANGE) == 0u) a.status[1] = pos;
+        return;
+    }
+    const int end = (int)pos + 1;
+    const int q_width = a.q_heads * kHeadDim, qkv_width = (a.q_heads + 2 * a.kv_heads) * kHeadDim;
+    S *hidden = static_cast<S *>(a.hidden_io), *residual = static_cast<S *>(a.residual);
+    uint32_t passed = 0;
+    int r0, r1;
+    for (int l = 0; l < a.n_layers; ++l) {
+        const LayerDev L = a.layers[l];
+        // norm1 + quantize -> Q|K|V
+        float s = prologue_rmsnorm<T>(hidden, static_cast<const S *>(L.norm1), a.eps, a.hidden, sh.codes, sh.row, sh.ps, tid);
+        __syncthreads();
+        project_any<T, PRJ_PLAIN>(a, L.qkv, nullptr, L.qkv_s, nullptr, qkv_width, a.hidden, s, sh.codes, sh.red, nullptr,
+                                  static_cast<S *>(a.qkv), tid);
+        cta_rows(a.hidden, r0, r1);
+        request_rows(L.o, q_width, r0, r1, 1 << 30);  // attention leaves HBM idle: the whole share of O
+        request_cache(a, L, end, tid);
+        if (!grid_barrier(a, passed, &sh.ok)) return;
+
+        attention_phase<T>(a, L, sh.units, end, tid);
+        cta_rows(a.inter, r0, r1);
+        request_rows(L.gate, a.hidden, r0, r1, a.ahead_bytes);
+        request_rows(L.up, a.hidden, r0, r1, a.ahead_bytes);
+        if (!grid_barrier(a, passed, &sh.ok)) return;
+
+        // quantize(attention row) -> O + residual
+        s = prologue_plain<T>(static_cast<const S *>(a.attn), q_width, sh.codes, sh.row, sh.ps, tid);
+        __syncthreads();
+        project_any<T, PRJ_RESIDUAL>(a, L.o, nullptr, L.o_s, nullptr, a.hidden, q_width, s, sh.codes, sh.red, hidden, residual, tid);
+        if (!grid_barrier(a, passed, &sh.ok)) return;
+
+        // norm2 + quantize -> gate|up + SwiGLU
+        s = prologue_rmsnorm<T>(residual, static_cast<const S *>(L.norm2), a.eps, a.hidden, sh.codes, sh.row, sh.ps, tid);
+        __syncthreads();
+        project_any<T, PRJ_SWIGLU>(a, L.gate, L.up, L.gate_s, L.up_s, a.inter, a.hidden, s, sh.codes, sh.red, nullptr,
+                                   static_cast<S *>(a.act), tid);
+        cta_rows(a.hidden, r0, r1);
+        request_rows(L.down, a.inter, r0, r1, a.ahead_bytes);
+        if (!grid_barrier(a, passed, &sh.ok)) return;
+
+        // quantize(act) -> down + residual
+        s = prologue_plain<T>(static_cast<const S *>(a.act), a.inter, sh.codes, sh.row, sh.ps, tid);
+        __syncthreads();
+        project_any<T, PRJ_RESIDUAL>(a, L.down, nullptr, L.down_s, nullptr, a.hidden, a.inter, s, sh.codes, sh.red, residual, hidden, tid);
+        if (l + 1 < a.n_layers) {
+            cta_rows(qkv_width, r0, r1);
+            request_rows(a.layers[l + 1].qkv, a.hidden, r0, r1, a.ahead_bytes);
+            if (!grid_barrier(a, passed, &sh.ok)) return;
+        }
+    }
+}
+
+}  // namespace
+}  // namespace w8a8
+
+using namespace w8a8;
+
+struct qwen3_decode_plan {
+    uint32_t magic;
+    int device, dtype, grid;
+    StepDev dev;          // kernel argument; `layers` and the work buffers are device allocations owned by the plan
+    void *layers_dev;
+    void *work;           // residual | qkv | attention | act | scratch | {barrier words, attention counters}, one allocation
+    size_t clear_bytes;   // barrier words + counters: zeroed in stream order before every step
+};
+
+namespace {
+
+constexpr uint32_t kPlanMagic = 0x51334450u;  // "Q3DP"
+
+bool valid_plan(const qwen3_decode_plan *p) { return p && p->magic == kPlanMagic; }
+bool valid_matrix(const w8a8_weight *w) { return w && w->magic == kWeightMagic; }
+size_t round_up(size_t n, size_t to) { return (n + to - 1) / to * to; }
+
+int env_int(const char *name, int fallback) {
+    const char *v = std::getenv(name);
+    return v && *v ? std::atoi(v) : fallback;
+}
+
+}  // namespace
+
+#define REQUIRE(cond, code)         \
+    do {                            \
+        if (!(cond)) return (code); \
+    } while (0)
+
+namespace w8a8 {
+cudaError_t init_decode_layers() {
+    const int smem = (int)sizeof(StepShared);
+    cudaError_t e = cudaFuncSetAttribute(decode_layers_kernel<Bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_kernel<F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    return e;
+}
+}  // namespace w8a8
+
+extern "C" {
+
+int qwen3_decode_plan_create(const qwen3_layer_desc *layers, int n_layers, int hidden, int q_heads, int kv_heads, int intermediate,
+                             int capacity, float eps, const float *rope_table, int dtype, qwen3_decode_plan_t *plan_out) {
+    REQUIRE(device_status_ptr(), W8A8_ERR_NOT_INITIALIZED);
+    REQUIRE(layers && plan_out && rope_table && n_layers > 0, W8A8_ERR_BAD_ARG);
+    REQUIRE(dtype == W8A8_BF16 || dtype == W8A8_F32, W8A8_ERR_BAD_ARG);
+    REQUIRE(hidden > 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && intermediate > 0, W8A8_ERR_BAD_ARG);
+    REQUIRE(capacity > 0 && capacity <= kUnitMaxContext, W8A8_ERR_BAD_ARG);
+    const int q_width = q_heads * kHeadDim, qkv_width = (q_heads + 2 * kv_heads) * kHeadDim;
+    // every row a lane slice of 16 bytes, every vector of the carrier whole, at most three rounds of 4096 bytes
+    REQUIRE(hidden % 16 == 0 && intermediate % 16 == 0, W8A8_ERR_UNSUPPORTED);
+    REQUIRE(hidden <= kMaxK && q_width <= kMaxK && intermediate <= kMaxK, W8A8_ERR_UNSUPPORTED);
+    REQUIRE(q_heads <= kAttnSplitMaxUnits, W8A8_ERR_UNSUPPORTED);
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return fail_cuda(cudaGetLastError(), "cudaGetDevice");
+    int cooperative = 0;
+    cudaDeviceGetAttribute(&cooperative, cudaDevAttrCooperativeLaunch, device);
+    REQUIRE(cooperative, W8A8_ERR_UNSUPPORTED);
+    int per_sm = 0;
+    cudaError_t e = dtype == W8A8_BF16
+                        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_layers_kernel<Bf16>, kThreads, sizeof(StepShared))
+                        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_layers_kernel<F32>, kThreads, sizeof(StepShared));
+    if (e != cudaSuccess) return fail_cuda(e, "occupancy of the decode kernel");
+    REQUIRE(per_sm >= 1, W8A8_ERR_UNSUPPORTED);
+    int grid = sm_count();  // one CTA per SM
+    const int forced = env_int("W8A8_DECODE_CTAS", 0);
+    if (forced > 0 && forced < grid) grid = forced;
+    // rows one CTA owns in the widest projection (row pairs count twice)
+    const int widest = std::max(std::max(qkv_width, hidden), 2 * intermediate);
+    REQUIRE((widest + grid - 1) / grid + 1 <= kMaxCtaRows, W8A8_ERR_UNSUPPORTED);
+
+    std::vector<LayerDev> table((size_t)n_layers);
+    for (int l = 0; l < n_layers; ++l) {
+        const qwen3_layer_desc &d = layers[l];
+        REQUIRE(valid_matrix(d.qkv) && valid_matrix(d.o) && valid_matrix(d.gate) && valid_matrix(d.up) && valid_matrix(d.down),
+                W8A8_ERR_BAD_ARG);
+        REQUIRE(d.norm1 && d.norm2 && d.q_gain && d.k_gain && d.k_cache && d.v_cache, W8A8_ERR_BAD_ARG);
+        REQUIRE(d.qkv->N == qkv_width && d.qkv->K == hidden && d.o->N == hidden && d.o->K == q_width, W8A8_ERR_BAD_ARG);
+        REQUIRE(d.gate->N == intermediate && d.gate->K == hidden && d.up->N == intermediate && d.up->K == hidden, W8A8_ERR_BAD_ARG);
+        REQUIRE(d.down->N == hidden && d.down->K == intermediate, W8A8_ERR_BAD_ARG);
+        REQUIRE((reinterpret_cast<uintptr_t>(d.norm1) & 15u) == 0 && (reinterpret_cast<uintptr_t>(d.norm2) & 15u) == 0 &&
+                    (reinterpret_cast<uintptr_t>(d.k_cache) & 15u) == 0 && (reinterpret_cast<uintptr_t>(d.v_cache) & 15u) == 0,
+                W8A8_ERR_ALIGNMENT);
+        LayerDev &t = table[(size_t)l];
+        t.norm1 = d.norm1; t.norm2 = d.norm2; t.q_gain = d.q_gain; t.k_gain = d.k_gain;
+        t.qkv = d.qkv->w; t.qkv_s = d.qkv->w_scale;
+        t.o = d.o->w; t.o_s = d.o->w_scale;
+        t.gate = d.gate->w; t.gate_s = d.gate->w_scale;
+        t.up = d.up->w; t.up_s = d.up->w_scale;
+        t.down = d.down->w; t.down_s = d.down->w_scale;
+        t.k_cache = d.k_cache; t.v_cache = d.v_cache;
+    }
+
+    qwen3_decode_plan *p = new (std::nothrow) qwen3_decode_plan();
+    REQUIRE(p, W8A8_ERR_CUDA);
+    p->device = device; p->dtype = dtype; p->grid = grid;
+    const size_t el = dtype == W8A8_BF16 ? 2 : 4;
+    // the same split count qwen3_attention launches for one row (forward_glue.cu), so that both give the same bits
+    const int splits = std::min(kAttnMaxSplits, (2 * sm_count() + q_heads - 1) / q_heads);
+    const size_t b_hidden = round_up((size_t)hidden * el, 256), b_qkv = round_up((size_t)qkv_width * el, 256);
+    const size_t b_attn = round_up((size_t)q_width * el, 256), b_act = round_up((size_t)intermediate * el, 256);
+    const size_t b_scratch = round_up((size_t)q_heads * splits * kUnitRecord * sizeof(float), 256);
+    p->clear_bytes = round_up(16 + (size_t)q_heads * sizeof(uint32_t), 16);  // barrier words, then the attention counters
+    const size_t total = b_hidden + b_qkv + b_attn + b_act + b_scratch + round_up(p->clear_bytes, 256);
+    e = cudaMalloc(&p->work, total);
+    if (e == cudaSuccess) e = cudaMemset(p->work, 0, total);
+    if (e == cudaSuccess) e = cudaMalloc(&p->layers_dev, table.size() * sizeof(LayerDev));
+    if (e == cudaSuccess) e = cudaMemcpy(p->layers_dev, table.data(), table.size() * sizeof(LayerDev), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        cudaFree(p->work);
+        cudaFree(p->layers_dev);
+        delete p;
+        return fail_cuda(e, "decode plan allocation");
+    }
+    char *at = static_cast<char *>(p->work);
+    StepDev &s = p->dev;
+    s.layers = static_cast<const LayerDev *>(p->layers_dev);
+    s.n_layers = n_layers; s.hidden = hidden; s.q_heads = q_heads; s.kv_heads = kv_heads; s.inter = intermediate;
+    s.capacity = capacity; s.splits = splits; s.eps = eps; s.rope = rope_table; s.control = nullptr; s.hidden_io = nullptr;
+    s.residual = at; at += b_hidden;
+    s.qkv = at; at += b_qkv;
+    s.attn = at; at += b_attn;
+    s.act = at; at += b_act;
+    s.scratch = reinterpret_cast<float *>(at); at += b_scratch;
+    s.sync = reinterpret_cast<uint32_t *>(at);
+    s.counters = s.sync + 4;
+    s.status = device_status_ptr();
+    s.ahead_bytes = env_int("W8A8_DECODE_AHEAD_KB", 128) * 1024;
+    s.ahead_rows = env_int("W8A8_DECODE_AHEAD_BATCHES", 2);
+    p->magic = kPlanMagic;
+    *plan_out = p;
+    return W8A8_OK;
+}
+
+int qwen3_decode_plan_destroy(qwen3_decode_plan_t plan) {
+    if (!plan) return W8A8_OK;
+    REQUIRE(valid_plan(plan), W8A8_ERR_BAD_ARG);
+    plan->magic = 0;
+    cudaFree(plan->work);
+    cudaFree(plan->layers_dev);
+    delete plan;
+    return W8A8_OK;
+}
+
+int qwen3_decode_layers(qwen3_decode_plan_t plan, void *hidden, const uint32_t *control, void *stream) {
+    REQUIRE(valid_plan(plan) && hidden && control, W8A8_ERR_BAD_ARG);
+    REQUIRE((reinterpret_cast<uintptr_t>(hidden) & 15u) == 0, W8A8_ERR_ALIGNMENT);
+    cudaStream_t s = (cudaStream_t)stream;
+    StepDev args = plan->dev;
+    args.hidden_io = hidden;
+    args.control = control;
+    cudaError_t e = cudaMemsetAsync(args.sync, 0, plan->clear_bytes, s);
+    if (e != cudaSuccess) return fail_cuda(e, "decode barrier reset");
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)plan->grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = sizeof(StepShared);
+    cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeCooperative;
+    attr.val.cooperative = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = plan->dtype == W8A8_BF16 ? cudaLaunchKernelEx(&cfg, decode_layers_kernel<Bf16>, args)
+                                 : cudaLaunchKernelEx(&cfg, decode_layers_kernel<F32>, args);
+    return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "decode step launch");
+}
+
+}  // extern "C"

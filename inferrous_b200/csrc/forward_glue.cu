@@ -11,6 +11,7 @@
 // keeps its keys channel-major; the layout is private to these two kernels).
 #include "../../include/qwen3_glue.h"
 #include "../../include/w8a8.h"
+#include "attention_unit.cuh"
 #include "common.cuh"
 #include "internal.h"
 
@@ -132,32 +133,15 @@ __global__ void __launch_bounds__(128) prepare_qk_kernel(typename T::storage *__
 // One CTA of 256 threads per (row, query head, key split).  A split owns a contiguous range of the visible keys;
 // with one split the CTA writes the output row itself, otherwise it leaves (maximum, total, unnormalised sums)
 // in scratch memory and the last split to arrive combines them (flash-decoding), so that a single decode row
-// still spreads over the whole GPU.
-//   scores   eight lanes per key (16 channels each, summed in order, then a three-step butterfly), four keys per
-//            warp and sweep; score = dot * 128^-0.5, as the reference scales it
-//   softmax  e = exp(score - maximum) with the reference's ex2.approx form; total = sum of e
-//   P.V      sixteen key slices (key j belongs to slice j % 16) x sixteen lanes of 8 channels, each slice summed
-//            in increasing j, the sixteen partial sums added in slice order; one RN division by the total at the end
-//   combine  maximum M over the splits, weights exp(m_s - M), sums and totals added in split order, one division
+// still spreads over the whole GPU.  The arithmetic of a unit and its association are in attention_unit.cuh.
 // The sums are reassociated relative to the reference's one-thread-per-key / one-thread-per-channel kernel (strict
 // key and channel order, each weight divided by the total before the P.V sum, src/kernels.rs:1608-1616); the
 // association here is fixed by the launch shape and the number of visible keys, so the result depends on nothing
 // but the inputs and the launched split count.
-constexpr int kAttnThreads = 256;
-constexpr int kAttnSlices = 16;
-constexpr int kAttnRecord = kHeadDim + 4;  // floats per (unit, split) in scratch: 128 sums, maximum, total, padding
-constexpr int kAttnKeysPerSplit = 64;      // a split is not worth its combine step for fewer keys
+constexpr int kAttnThreads = kUnitThreads;
+constexpr int kAttnSlices = kUnitSlices;
 
-__device__ __forceinline__ float dot16(const float (&qv)[16], const uint4 a, const uint4 b) {
-    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    float s = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        s = __fadd_rn(s, __fmul_rn(qv[2 * i], __uint_as_float(w[i] << 16)));
-        s = __fadd_rn(s, __fmul_rn(qv[2 * i + 1], __uint_as_float(w[i] & 0xffff0000u)));
-    }
-    return s;
-}
+__device__ __forceinline__ float dot16(const float (&qv)[16], const uint4 a, const uint4 b) { return unit_dot16(qv, a, b); }
 
 template <class T>
 __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename T::storage *__restrict__ q, int64_t ldq, int q_heads,
@@ -174,11 +158,9 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
         if (blockIdx.y == 0) prefetch_ranges(hint, blockIdx.x - units, gridDim.x - units);
         return;
     }
-    __shared__ float scores[kMaxContext];
-    __shared__ float query[kHeadDim];
-    __shared__ float reduce[kAttnThreads / 32];
-    __shared__ float partial[kAttnSlices][kHeadDim];
-    __shared__ uint32_t arrived;
+    __shared__ __align__(16) UnitShared sh;
+    float *reduce = sh.reduce;
+    uint32_t &arrived = sh.arrived;
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int unit = blockIdx.x, split = blockIdx.y;
     const int row = unit / q_heads, head = unit % q_heads;
@@ -193,11 +175,9 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
     }
     const int end = (int)end_u;
     // Splits in use: one per kAttnKeysPerSplit visible keys, at most the launched number; the rest leave at once.
-    const int splits = min((int)gridDim.y, (end + kAttnKeysPerSplit - 1) / kAttnKeysPerSplit);
+    int splits, begin, stop;
+    unit_range(end, (int)gridDim.y, split, splits, begin, stop);
     if (split >= splits) return;
-    // this split's keys: [begin, stop), ranges of a multiple of 32 keys
-    const int chunk = (((end + splits - 1) / splits) + 31) & ~31;
-    const int begin = min(end, split * chunk), stop = min(end, begin + chunk);
     const int count = stop - begin;
     {
         const size_t stride_bytes = (size_t)kv_heads * kHeadDim * sizeof(uint16_t);
@@ -210,122 +190,14 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const typename 
         }
     }
     dependency_wait();
-    if (t < kHeadDim) query[t] = T::load(q + (size_t)row * ldq + (size_t)head * kHeadDim + t);
+    if (t < kHeadDim) sh.query[t] = T::load(q + (size_t)row * ldq + (size_t)head * kHeadDim + t);
     __syncthreads();
 
-    // scores
-    const int sub = lane & 7, group = lane >> 3;
-    float qv[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) qv[i] = query[16 * sub + i];
     const size_t key_stride = (size_t)kv_heads * kHeadDim;
-    const uint16_t *kbase = k_cache + (size_t)begin * key_stride + (size_t)kv * kHeadDim + 16 * sub;
-    float maximum = -INFINITY;
-#pragma unroll 2
-    for (int j0 = warp * 4; j0 < count; j0 += (kAttnThreads / 32) * 4) {
-        const int j = j0 + group;
-        float s = 0.0f;
-        if (j < count) {
-            const uint4 *kr = reinterpret_cast<const uint4 *>(kbase + (size_t)j * key_stride);
-            s = dot16(qv, kr[0], kr[1]);
-        }
-        s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 4));
-        s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 2));
-        s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
-        s = __fmul_rn(s, 0.08838834764831845f);
-        if (j < count) {
-            maximum = fmaxf(maximum, s);
-            if (sub == 0) scores[j] = s;
-        }
-    }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, d));
-    if (lane == 0) reduce[warp] = maximum;
-    __syncthreads();
-    maximum = reduce[0];
-#pragma unroll
-    for (int i = 1; i < kAttnThreads / 32; ++i) maximum = fmaxf(maximum, reduce[i]);
-    __syncthreads();
-
-    // softmax numerators and their total (an empty split has maximum -inf and total 0)
-    float total = 0.0f;
-    for (int j = t; j < count; j += kAttnThreads) {
-        const float e = exp_approx(__fadd_rn(scores[j], -maximum));
-        scores[j] = e;
-        total = __fadd_rn(total, e);
-    }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) total = __fadd_rn(total, __shfl_xor_sync(0xffffffffu, total, d));
-    if (lane == 0) reduce[warp] = total;
-    __syncthreads();
-    total = reduce[0];
-#pragma unroll
-    for (int i = 1; i < kAttnThreads / 32; ++i) total = __fadd_rn(total, reduce[i]);
-
-    // P.V, unnormalised
-    const int slice = t >> 4, cg = t & 15;
-    const uint16_t *vbase = v_cache + (size_t)begin * key_stride + (size_t)kv * kHeadDim + 8 * cg;
-    float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll 4
-    for (int j = slice; j < count; j += kAttnSlices) {
-        const uint4 v = *reinterpret_cast<const uint4 *>(vbase + (size_t)j * key_stride);
-        const float p = scores[j];
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(p, __uint_as_float(w[i] << 16)));
-            acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(p, __uint_as_float(w[i] & 0xffff0000u)));
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) partial[slice][8 * cg + i] = acc[i];
-    __syncthreads();
-    float sum = 0.0f;
-    if (t < kHeadDim) {
-        sum = partial[0][t];
-#pragma unroll
-        for (int i = 1; i < kAttnSlices; ++i) sum = __fadd_rn(sum, partial[i][t]);
-    }
-
-    if (splits > 1) {
-        float *mine = scratch + ((size_t)unit * gridDim.y + split) * kAttnRecord;
-        if (t < kHeadDim) mine[t] = sum;
-        if (t == 0) {
-            mine[kHeadDim] = maximum;
-            mine[kHeadDim + 1] = total;
-        }
-        __threadfence();
-        __syncthreads();
-        if (t == 0) {
-            const uint32_t before = atomicAdd(counters + unit, 1u);
-            arrived = before;
-            if (before == (uint32_t)splits - 1u) counters[unit] = 0u;  // the counter is zero again for the next launch
-        }
-        __syncthreads();
-        if (arrived != (uint32_t)splits - 1u) return;
-        __threadfence();
-        if (t < kHeadDim) {
-            const float *all = scratch + (size_t)unit * gridDim.y * kAttnRecord;
-            float top = -INFINITY;
-            for (int s = 0; s < splits; ++s) top = fmaxf(top, __ldcg(all + s * kAttnRecord + kHeadDim));
-            sum = 0.0f;
-            total = 0.0f;
-            for (int s = 0; s < splits; ++s) {
-                const float *rec = all + s * kAttnRecord;
-                const float weight = exp_approx(__fadd_rn(__ldcg(rec + kHeadDim), -top));  // 0 for an empty split
-                total = __fadd_rn(total, __fmul_rn(__ldcg(rec + kHeadDim + 1), weight));
-                sum = __fadd_rn(sum, __fmul_rn(__ldcg(rec + t), weight));
-            }
-        }
-    }
-    if (t < kHeadDim) {
-        const float o = bf16_rne(__fdiv_rn(sum, total));
-        T::store(out + (size_t)row * ldo + (size_t)head * kHeadDim + t, o);
-        if (maxima) {  // max |out| of the row, for a quantizer that takes its maximum from the producer
-            const uint32_t m = warp_max_u32(absmax_key(o));
-            if (lane == 0) atomicMax(maxima + row, m);
-        }
-    }
+    const bool wrote = attention_unit<T, false>(sh, SyncCta{}, t, k_cache + (size_t)kv * kHeadDim, v_cache + (size_t)kv * kHeadDim,
+                                                key_stride, end, splits, split, begin, stop, (int)gridDim.y, unit, scratch, counters,
+                                                out + (size_t)row * ldo + (size_t)head * kHeadDim, maxima ? maxima + row : nullptr);
+    if (!wrote) return;
     if (q_out == nullptr) return;
 
     // Quantizer of the finished row, folded in: the head that completes a row (per-row arrival counter, zero between

@@ -126,6 +126,7 @@ cudaError_t init_quantize();
 cudaError_t init_forward_glue();
 cudaError_t init_batched_decode();
 cudaError_t init_head_bf16();
+cudaError_t init_decode_layers();
 
 // Device status word (bounded waits report here instead of trapping).
 uint32_t *device_status_ptr();  // device address of the 2-word status block of the current device

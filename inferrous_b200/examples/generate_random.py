@@ -21,6 +21,7 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=32, help="tokens to generate")
     ap.add_argument("--eager", action="store_true", help="launch every decode step eagerly instead of replaying the graph")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--separate", action="store_true", help="one launch per operator instead of the resident decode kernel")
     ap.add_argument("--batch", type=int, default=0, help="decode this many sequences side by side (batched decode)")
     ap.add_argument("--contexts", default="128,4000", help="with --batch: range of the prompt lengths, LO,HI")
     args = ap.parse_args()
@@ -38,7 +39,7 @@ def main() -> None:
         tokens, seconds = runner.generate_batch(prompts, args.tokens, use_graph=not args.eager)
         print("first sequence's tokens:", " ".join(map(str, tokens[0])))
     else:
-        runner = Qwen3Runner(Qwen3Weights.random(config, seed=args.seed))
+        runner = Qwen3Runner(Qwen3Weights.random(config, seed=args.seed), resident=not args.separate)
         prompt = [int(t) for t in rng.integers(0, config.vocab, args.prompt)]
         tokens, seconds = runner.generate(prompt, args.tokens, use_graph=not args.eager)
         print("tokens:", " ".join(map(str, tokens)))

@@ -19,6 +19,7 @@
 #include <chrono>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <fstream>
 #include <memory>
@@ -210,11 +211,15 @@ class Qwen3Model {
             l->v_cache = DeviceBuffer<uint16_t>::zeroed((size_t)c_.context * c_.kv_width());
             layers_.push_back(std::move(l));
         }
+        make_plan();
     }
     ~Qwen3Model() {
         if (exec_) cudaGraphExecDestroy(exec_);
         if (graph_) cudaGraphDestroy(graph_);
+        if (plan_) qwen3_decode_plan_destroy(plan_);
     }
+    // true when one-token steps run as the single resident kernel (qwen3_decode_layers)
+    bool resident_decode() const { return plan_ != nullptr; }
     const Qwen3Config &config() const { return c_; }
 
     // Queues one forward pass of ws.rows rows: `ids` holds their token ids (the control buffer in decode, whose word
@@ -223,6 +228,10 @@ class Qwen3Model {
         cudaStream_t s = gpu_.stream();
         const int rows = ws.rows, H = c_.hidden;
         ensure(qwen3_embedding(ids, embedding_.ptr(), rows, H, c_.vocab, ws.hidden.ptr(), W8A8_F32, s), "embedding");
+        if (rows == 1 && plan_) {  // every layer of the step inside one kernel; the same bits as the launches below
+            ensure(qwen3_decode_layers(plan_, ws.hidden.ptr(), control_.ptr(), s), "decode layers");
+            return head(ws);
+        }
         for (auto &lp : layers_) {
             Layer &l = *lp;
             gpu_.norm_quantize(ws.hidden, l.norm1, nullptr, ws.quant4, ws.scales, &ws.maxima);
@@ -251,7 +260,14 @@ class Qwen3Model {
                                W8A8_F32, s),
                    "down projection");
         }
-        const float *last = ws.hidden.ptr() + (size_t)(rows - 1) * H;
+        head(ws);
+    }
+
+    // Final norm of the last row, output head and greedy selection; the token lands in next_.
+    void head(Qwen3Workspace &ws) {
+        cudaStream_t s = gpu_.stream();
+        const int H = c_.hidden;
+        const float *last = ws.hidden.ptr() + (size_t)(ws.rows - 1) * H;
         const bool bf16_head = head_ == nullptr;
         // the final norm; with the bf16 head its output row is what the head multiplies (`norm`, src/gpu.rs:798)
         ensure(w8a8_rmsnorm_quantize(last, final_gain_.ptr(), W8A8_F32, c_.eps, 1, H, H, head_q_.ptr(), head_scale_.ptr(),
@@ -308,6 +324,26 @@ class Qwen3Model {
               up(t.up, t.up_scale, c.intermediate, c.hidden), down(t.down, t.down_scale, c.hidden, c.intermediate) {}
     };
 
+    // The resident decode kernel's plan, where the library supports the shape and the device (W8A8_RESIDENT_DECODE=0
+    // keeps the launch-per-operator step).
+    void make_plan() {
+        const char *off = std::getenv("W8A8_RESIDENT_DECODE");
+        if (off && off[0] == '0') return;
+        std::vector<qwen3_layer_desc> table;
+        for (auto &lp : layers_) {
+            Layer &l = *lp;
+            qwen3_layer_desc d{};
+            d.norm1 = l.norm1.ptr(); d.norm2 = l.norm2.ptr(); d.q_gain = l.qnorm.ptr(); d.k_gain = l.knorm.ptr();
+            d.qkv = l.qkv.handle; d.o = l.o.handle; d.gate = l.gate.handle; d.up = l.up.handle; d.down = l.down.handle;
+            d.k_cache = l.k_cache.ptr(); d.v_cache = l.v_cache.ptr();
+            table.push_back(d);
+        }
+        const int st = qwen3_decode_plan_create(table.data(), (int)table.size(), c_.hidden, c_.q_heads, c_.kv_heads, c_.intermediate,
+                                                c_.context, c_.eps, rope_.ptr(), W8A8_F32, &plan_);
+        if (st == W8A8_ERR_UNSUPPORTED) plan_ = nullptr;
+        else ensure(st, "decode plan");
+    }
+
     // One decode step as a graph (src/gpu.rs:303-333, src/graph.rs:63-127): a warm-up launch outside the capture, then
     // the capture with every kernel on a programmatic edge.
     void capture_decode() {
@@ -344,6 +380,7 @@ class Qwen3Model {
     Qwen3Workspace decode_;
     cudaGraph_t graph_ = nullptr;
     cudaGraphExec_t exec_ = nullptr;
+    qwen3_decode_plan_t plan_ = nullptr;
 };
 
 }  // namespace w8a8

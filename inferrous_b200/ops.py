@@ -337,3 +337,42 @@ def head_bf16(x: torch.Tensor, w: torch.Tensor, logits: torch.Tensor | None = No
     assert w.dtype == torch.bfloat16 and w.is_contiguous() and x.numel() == hidden
     capi.check(capi.load().qwen3_head_bf16(_ptr(x), _dtype_code(x), _ptr(w), vocab, hidden, _ptr(logits), _ptr(token), _ptr(value),
                                            _stream()), "qwen3_head_bf16")
+
+
+class DecodePlan:
+    """qwen3_decode_plan (include/qwen3_glue.h): one decode step of the whole decoder stack as a single resident kernel.
+    `layers` is a sequence of objects with norm1, qkv, qnorm, knorm, o, norm2, gate, up, down (Matrix handles and gain
+    tensors); k_caches / v_caches the per-layer [capacity, kv_heads, 128] bf16 caches.  The plan keeps references to
+    everything it names.  Raises W8A8Error (status 3) where the shape or the device is not supported."""
+
+    def __init__(self, layers, k_caches, v_caches, hidden: int, q_heads: int, kv_heads: int, intermediate: int, eps: float,
+                 rope: torch.Tensor, dtype: torch.dtype = torch.bfloat16):
+        init(rope.device.index)
+        assert rope.dtype == torch.float32 and rope.is_contiguous() and rope.shape[1] == 128
+        self._keep = (list(layers), list(k_caches), list(v_caches), rope)
+        table = (capi.LayerDesc * len(layers))()
+        for d, layer, k, v in zip(table, layers, k_caches, v_caches):
+            assert layer.norm1.dtype == dtype and layer.norm2.dtype == dtype and layer.qnorm.dtype == torch.float32
+            assert k.is_contiguous() and v.is_contiguous() and k.shape == v.shape and tuple(k.shape[1:]) == (kv_heads, 128)
+            d.norm1, d.norm2, d.q_gain, d.k_gain = (_ptr(t).value for t in (layer.norm1, layer.norm2, layer.qnorm, layer.knorm))
+            d.qkv, d.o, d.gate, d.up, d.down = (m.handle.value for m in (layer.qkv, layer.o, layer.gate, layer.up, layer.down))
+            d.k_cache, d.v_cache = _ptr(k).value, _ptr(v).value
+        capacity = k_caches[0].shape[0]
+        handle = C.c_void_p()
+        capi.check(capi.load().qwen3_decode_plan_create(C.cast(table, C.c_void_p), len(layers), hidden, q_heads, kv_heads, intermediate,
+                                                        capacity, eps, _ptr(rope), 0 if dtype == torch.bfloat16 else 1,
+                                                        C.byref(handle)), "qwen3_decode_plan_create")
+        self.handle = handle
+        self.hidden = hidden
+
+    def run(self, hidden_row: torch.Tensor, control: torch.Tensor) -> None:
+        """hidden_row ([hidden] or [1, hidden]): the token's embedding in, the last layer's output out; control = {token,
+        position} on the device."""
+        assert hidden_row.numel() == self.hidden and hidden_row.is_contiguous()
+        capi.check(capi.load().qwen3_decode_layers(self.handle, _ptr(hidden_row), _ptr(control), _stream()), "qwen3_decode_layers")
+
+    def __del__(self):
+        h = getattr(self, "handle", None)
+        if h and capi is not None:
+            capi.load().qwen3_decode_plan_destroy(h)
+            self.handle = None

@@ -210,7 +210,7 @@ class Qwen3Runner:
     def __init__(self, weights: Qwen3Weights, unfused: bool = False, device="cuda", fold_quantizers: str = "none",
                  prefetch_rows: int = 0, prefetch_down_at: str = "quant", prefetch_o: bool = False, group=None,
                  fused_allreduce: bool = True, fold_attention_quantizer: bool = False, batch: int = 1,
-                 peer_rows_times_ranks: int = 128):
+                 peer_rows_times_ranks: int = 128, resident: bool | None = None):
         ops.init()
         if batch < 1:
             raise ValueError("batch must be at least 1")
@@ -258,6 +258,18 @@ class Qwen3Runner:
             self.local_best = torch.zeros(2, dtype=torch.int32, device=device)         # {token within the shard, value bits}
             self.all_best = torch.zeros(weights.tp, 2, dtype=torch.int32, device=device)
         self.graph = None
+        # One-token decode on one GPU: all layers of a step inside one resident kernel (ops.DecodePlan) instead of ten
+        # launches per layer; bit-identical.  resident=None: on wherever the library supports the shape and the device.
+        self.plan = None
+        if resident is None:
+            resident = os.environ.get("W8A8_RESIDENT_DECODE", "1") != "0"
+        if resident and weights.tp == 1 and not unfused and fold_quantizers == "none":
+            try:
+                self.plan = ops.DecodePlan(weights.layers, self.k_cache, self.v_cache, c.hidden, c.q_heads, c.kv_heads, c.intermediate,
+                                           c.eps, weights.rope)
+            except capi.W8A8Error as error:
+                if error.status != 3:  # W8A8_ERR_UNSUPPORTED: this shape stays on the launch-per-operator path
+                    raise
         self._host_control = torch.zeros(2, dtype=torch.int32).pin_memory()
         self._host_next = torch.zeros(1, dtype=torch.int32).pin_memory()
         # batched decode: one row per sequence
@@ -299,6 +311,9 @@ class Qwen3Runner:
         inter = c.intermediate
         single = rows == 1 and not batched  # the reference's decode step: hints and folded quantizers apply
         ops.embedding(ids, w.embedding, ws.hidden)
+        if single and self.plan is not None and slot == 0:
+            self.plan.run(ws.hidden, self.control)
+            return self._head(ws)
         if single and self.fold_quantizers != "none" and not self.unfused:
             self._decode_layers(ws)
             return self._head(ws)

@@ -1,7 +1,8 @@
 // Greedy generation through the C++ host harness (inferrous_b200/host/qwen3_model.hpp) from an on-disk bundle.
 // usage: generate <bundle dir> <max tokens> <use graph 0|1> <prompt id>...      (W8A8_HEAD=w8a8 in the environment
 //        runs the head as a W8A8 projection instead of the reference's bf16 head)
-// Prints one line "tokens: t0 t1 ..." and exits 0; any failure is a message on stderr and exit code 1.
+// Prints one line "tokens: t0 t1 ...", one line "resident decode: 0|1" (whether one-token steps ran as the single resident
+// kernel; W8A8_RESIDENT_DECODE=0 turns it off) and exits 0; any failure is a message on stderr and exit code 1.
 #include <cstdio>
 #include <cstdlib>
 
@@ -25,6 +26,7 @@ int main(int argc, char **argv) {
         printf("tokens:");
         for (uint32_t t : out.token_ids) printf(" %u", t);
         printf("\n");
+        printf("resident decode: %d\n", model.resident_decode() ? 1 : 0);
         // a second request on the same model reuses caches, graph and workspaces
         const auto again = model.generate(prompt, max_tokens, use_graph);
         if (again.token_ids != out.token_ids) {

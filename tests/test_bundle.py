@@ -107,11 +107,14 @@ def test_generation_from_a_bundle_python_cpp_and_cpu_agree(tmp_path, prompt_len,
         weights = load_bundle(tmp_path / "b", head=head)
         prompt = [int(t) for t in rng.integers(0, weights.config.vocab, prompt_len)]
         tokens, _ = Qwen3Runner(weights).generate(prompt, steps)
-        for use_graph in (1, 0):
+        # graph and eager; the decode step as one resident kernel (f32 carrier) and as one launch per operator
+        for use_graph, resident in ((1, 1), (0, 1), (1, 0)):
             r = subprocess.run([str(build("generate")), str(tmp_path / "b"), str(steps), str(use_graph), *map(str, prompt)],
-                               capture_output=True, text=True, timeout=600, env=dict(os.environ, W8A8_HEAD=head))
+                               capture_output=True, text=True, timeout=600,
+                               env=dict(os.environ, W8A8_HEAD=head, W8A8_RESIDENT_DECODE=str(resident)))
             assert r.returncode == 0, r.stdout + r.stderr
-            assert [int(t) for t in r.stdout.split("tokens:")[1].split()] == tokens
+            assert [int(t) for t in r.stdout.split("tokens:")[1].split("\n")[0].split()] == tokens
+            assert f"resident decode: {resident}" in r.stdout
         if prompt_len <= 16:
             assert OracleModel(export(weights)).generate(prompt, steps) == tokens
 

@@ -15,7 +15,8 @@ C_TO_RUST = {
     "const uint32_t *": "*const u32", "uint32_t *": "*mut u32", "const uint16_t *": "*const u16", "uint16_t *": "*mut u16",
     "int32_t *": "*mut i32", "int *": "*mut c_int", "w8a8_weight_t": "*mut W8a8Weight", "w8a8_weight_t *": "*mut *mut W8a8Weight",
     "const w8a8_weight_t *": "*const *mut W8a8Weight", "void *const *": "*const *mut c_void", "uint32_t *const *": "*const *mut u32",
-    "const char *": "*const c_char",
+    "const char *": "*const c_char", "const qwen3_layer_desc *": "*const Qwen3LayerDesc", "qwen3_decode_plan_t": "*mut Qwen3DecodePlan",
+    "qwen3_decode_plan_t *": "*mut *mut Qwen3DecodePlan", "const struct w8a8_weight *": "*const W8a8Weight",
 }
 
 
@@ -49,6 +50,21 @@ def test_every_header_function_is_declared_with_matching_types():
         rret, rtypes = rust[name]
         assert rret == C_TO_RUST[ret], name
         assert rtypes == [C_TO_RUST[t] for t in types], name
+
+
+def test_layer_struct_matches_the_header():
+    header = re.sub(r"/\*.*?\*/", "", (ROOT / "include" / "qwen3_glue.h").read_text(), flags=re.S)
+    body = re.search(r"typedef struct qwen3_layer_desc \{(.*?)\} qwen3_layer_desc;", header, flags=re.S).group(1)
+    fields = []
+    for decl in body.split(";"):
+        decl = " ".join(decl.split())
+        if decl:
+            first, *rest = [d.strip() for d in decl.split(",")]
+            ty, name = re.match(r"(.*?)(\w+)$", first).groups()
+            fields += [(name, C_TO_RUST[ty.strip()])] + [(more.lstrip("* "), C_TO_RUST[ty.strip()]) for more in rest]
+    rust = LIB_RS.read_text()
+    block = re.search(r"pub struct Qwen3LayerDesc \{(.*?)\}", rust, flags=re.S).group(1)
+    assert re.findall(r"pub (\w+): ([^,]+),", block) == fields and len(fields) == 11
 
 
 def test_constants_match_the_header():
