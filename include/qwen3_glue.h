@@ -158,6 +158,13 @@ int qwen3_decode_plan_destroy(qwen3_decode_plan_t plan);
  * `hidden` undefined and code 7 in the device status word (w8a8_device_status). */
 int qwen3_decode_layers(qwen3_decode_plan_t plan, void *hidden, const uint32_t *control, void *stream);
 
+/* Measurement aid: a plan created while W8A8_DECODE_TRACE=1 is in the environment makes thread 0 of every CTA note its
+ * SM's cycle counter at `points` boundaries of every layer (start, after each quantizer, projection, barrier and the
+ * attention step).  This call synchronises the device and copies the last step's counts to the HOST array `cycles`
+ * ([ctas][layers][points] int64; counters of different CTAs are not synchronised with each other, differences within one
+ * CTA are exact).  cycles == NULL only reports the three extents.  W8A8_ERR_UNSUPPORTED when the plan has no trace. */
+int qwen3_decode_plan_trace(qwen3_decode_plan_t plan, int64_t *cycles, size_t capacity, int *ctas, int *layers, int *points);
+
 /* Launches of 32 rows or more (prefill) run both attention products on the tensor cores (bf16 warp-level MMA, float32
  * accumulation, softmax weights carried as two bf16 parts); 0 keeps them on the CUDA-core kernel that shorter launches
  * use, for comparison.  Process-wide; default 1. */

@@ -92,6 +92,8 @@ int w8a8_prefetch_hint(const void *weights, size_t bytes);
 int w8a8_set_programmatic_launch(int enabled);
 /* Reads (and clears) the device-side status words of the current device: 0, or
  * W8A8_ERR_DEVICE_TIMEOUT with *detail = code of the wait that gave up (code << 24 | low bits of its argument).
+ * Codes: 1-4 a stage of a TMA / tensor-core pipeline, 5 another rank's partial outputs (tensor parallel), 6 a token id
+ * or cache position out of range (not a wait: the access was skipped), 7 a grid-wide barrier of qwen3_decode_layers.
  * Synchronises `stream`.  It covers both the status word w8a8_init() allocated and the one inside the fixed array of
  * w8a8_linear_no_alloc, so it also works on a device where only that entry point has run.  Scratch that launches
  * share and leave at zero (stream-K partial tiles and arrival counters of w8a8_linear for 9..128 tokens, the

@@ -77,6 +77,8 @@ unsigned long long *argmax_scratch() {
     int dev = current_ready_device();
     return dev < 0 ? nullptr : g_dev[dev].argmax;
 }
+int attention_splits(int units) { return std::max(1, std::min(kAttnMaxSplits, (2 * sm_count()) / std::max(1, units))); }
+
 float *attention_scratch() {
     int dev = current_ready_device();
     return dev < 0 ? nullptr : g_dev[dev].attn_scratch;

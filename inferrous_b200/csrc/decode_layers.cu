@@ -8,12 +8,18 @@
 // graph with programmatic edges and next-weight prefetch CTAs, src/graph.rs:63-127, src/kernels.rs:173-237).  Here
 // one CTA per SM stays resident for the whole stack:
 //   * the activation quantizers run as a prologue of the projection that consumes them, once per SM (not once per
-//     launch-sized CTA), while that CTA's first weight lines are already on their way;
-//   * before a CTA arrives at a barrier it asks L2 for the first part of its share of the NEXT matrix (weights are
-//     immutable), and inside a projection every warp keeps such requests a fixed distance ahead of its loads, so
-//     the HBM stream does not stop at a barrier;
+//     launch-sized CTA);
+//   * while thread 0 of a CTA polls a barrier, the other warps ask L2 for the first part of the CTA's share of the NEXT
+//     matrix (weights are immutable), and inside a projection every warp keeps such requests one batch of rows ahead
+//     of its loads, so the HBM stream does not stop dead at a barrier.  64 KiB per CTA and matrix is the measured
+//     optimum: deeper requests cost more than they hide;
 //   * head norm + rotary embedding are done by the attention units themselves (each recomputes its query head and,
 //     where its key range holds the newest position, that key), which removes one dependent step per layer.
+// Measured on a B200 (Qwen3-8B shapes, context 130..260): 58 us per layer, of which streaming the 193 MB of weights
+// 28.6 us, the four quantizer prologues 9.2 us, attention about 8 us and the five barriers with the skew in front of
+// them the rest; 2.13 ms per token against 2.47 ms for the same step as ten launches per layer.  Things that were tried
+// and measured slower are noted where they would go (bulk L2 requests, more rows in flight per warp, the steps as
+// separate non-inlined functions).
 // Arithmetic: exactly that of the separate kernels (quantize.cu, gemv.cu, forward_glue.cu), so a step gives the
 // same bits as the launch-per-operator path: int32 sums are exact, every float operation is element-wise or follows
 // the same fixed association, and attention is the shared device function of attention_unit.cuh.
@@ -68,8 +74,16 @@ struct StepDev {
     uint32_t *counters;         // attention: per head arrival counters (zero between launches)
     uint32_t *sync;             // {arrivals, abort}: zeroed by the host before every launch
     uint32_t *status;
-    int ahead_bytes;            // per CTA: bytes of the next matrix requested from L2 before a barrier
+    long long ahead_bytes;      // per CTA: bytes of the next matrix requested from L2 while waiting at the barrier in front of it
+    long long ahead_more;       // per CTA: further bytes of gate and up requested one barrier earlier still (the O projection is short)
     int ahead_rows;             // inside a projection: L2 requests run this many row batches ahead of the loads
+    long long *trace;           // optional: [CTA][layer][kTracePoints] SM cycle counts at the step boundaries of a layer
+};
+
+// Points of a layer at which thread 0 of every CTA notes its SM's cycle counter when the plan carries a trace buffer.
+enum TracePoint {
+    TP_START = 0, TP_NORM1, TP_QKV, TP_ARRIVE1, TP_PASS1, TP_ATTENTION, TP_PASS2, TP_QUANT_O, TP_O, TP_PASS3, TP_NORM2, TP_GATE_UP,
+    TP_PASS4, TP_QUANT_DOWN, TP_DOWN, TP_PASS5, kTracePoints
 };
 
 // ---- loads of values another CTA wrote during this kernel: from L2, never from this SM's L1 ----------------
@@ -82,13 +96,17 @@ template <> __device__ __forceinline__ float load_one_cg<Bf16>(const uint16_t *p
 template <> __device__ __forceinline__ float load_one_cg<F32>(const float *p) { return __ldcg(p); }
 
 // ---- grid-wide barrier ---------------------------------------------------------------------------------------
-// sync[0] counts arrivals since the launch (the host zeroes it), so the n-th barrier is passed when it reaches
-// n * gridDim.x.  Returns false when the wait was abandoned; the caller leaves the kernel.
-__device__ __forceinline__ bool grid_barrier(const StepDev &a, uint32_t &passed, uint32_t *ok_smem) {
+// sync[0] counts arrivals since the launch (the host zeroes it), so the n-th barrier of the step (n = 1, 2, ...) is
+// passed when it reaches n * gridDim.x.  Returns false when the wait was abandoned; the caller leaves the kernel.
+// `meanwhile(i, n)` is run by the other fifteen warps (thread i of n) after the CTA has arrived and while thread 0 polls:
+// the L2 requests for the next matrix go there, off the path on which the other CTAs wait for this one.
+template <class Meanwhile>
+__device__ __forceinline__ bool grid_barrier(const StepDev &a, uint32_t ordinal, uint32_t *ok_smem, Meanwhile meanwhile) {
     __syncthreads();
+    if (threadIdx.x >= 32) meanwhile((int)threadIdx.x - 32, kThreads - 32);
     if (threadIdx.x == 0) {
-        passed += 1;
-        const uint32_t target = passed * gridDim.x;
+        const uint32_t target = ordinal * gridDim.x;
+        // release: everything this CTA wrote (ordered before by the barrier above) is visible to whoever sees the count
         __threadfence();
         atomicAdd(a.sync, 1u);
         uint32_t good = 1;
@@ -116,6 +134,9 @@ __device__ __forceinline__ bool grid_barrier(const StepDev &a, uint32_t &passed,
     __syncthreads();
     return *ok_smem != 0;
 }
+// The barriers of layer l in step order: in front of Q|K|V (layers after the first), attention, O, gate|up, down.
+enum { BAR_QKV = 0, BAR_ATTENTION = 1, BAR_O = 2, BAR_GATE_UP = 3, BAR_DOWN = 4, kBarriersPerLayer = 5 };
+__device__ __forceinline__ uint32_t barrier_ordinal(int l, int which) { return (uint32_t)(l * kBarriersPerLayer + which); }
 
 // This CTA's rows [r0, r1) of an N-row matrix.
 __device__ __forceinline__ void cta_rows(int N, int &r0, int &r1) {
@@ -123,15 +144,18 @@ __device__ __forceinline__ void cta_rows(int N, int &r0, int &r1) {
     r1 = (int)(((long long)N * (blockIdx.x + 1)) / gridDim.x);
 }
 
-// Ask L2 for the first `limit` bytes of rows [r0, r1) of a [N][K] matrix (whole 128-byte lines inside the range).
-__device__ __forceinline__ void request_rows(const int8_t *w, int K, int r0, int r1, int limit) {
-    if (r1 <= r0) return;
+// Ask L2 for bytes [from, to) of this CTA's rows of an [N][K] matrix, one 128-byte line per prefetch instruction, thread
+// i of n.  (Bulk requests of 16 KiB per instruction, cp.async.bulk.prefetch.L2, are cheaper to issue and were measured
+// slower overall: 2.53 against 2.44 ms per token.)
+__device__ __forceinline__ void request_rows(const int8_t *w, int K, int N, long long from, long long to, int i, int n) {
+    int r0, r1;
+    cta_rows(N, r0, r1);
+    const long long share = (long long)(r1 - r0) * K;
+    if (to > share) to = share;
+    if (to <= from) return;
     const unsigned long long base = reinterpret_cast<unsigned long long>(w) + (unsigned long long)r0 * K;
-    unsigned long long bytes = (unsigned long long)(r1 - r0) * K;
-    if (bytes > (unsigned long long)limit) bytes = (unsigned long long)limit;
-    const unsigned long long begin = (base + 127ull) & ~127ull, end = (base + bytes) & ~127ull;
-    for (unsigned long long p = begin + 128ull * threadIdx.x; p < end; p += 128ull * kThreads)
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+    const unsigned long long begin = (base + (unsigned long long)from + 127ull) & ~127ull, end = (base + (unsigned long long)to) & ~127ull;
+    for (unsigned long long p = begin + 128ull * i; p < end; p += 128ull * n) asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
 // ---- quantizing prologues: the unquantized row -> int8 codes in shared memory, returns the scale --------------
@@ -236,7 +260,9 @@ __device__ void project(const StepDev &a, const int8_t *__restrict__ w0, const i
                         const float *__restrict__ ws0, const float *__restrict__ ws1, int N, int K, float a_scale,
                         const int8_t *sq, int *red, const typename T::storage *residual, typename T::storage *out, int tid) {
     constexpr int R = (EPI == PRJ_SWIGLU) ? 2 : 1;
-    constexpr int U = (R * J == 1) ? 8 : (R * J == 2) ? 4 : (R * J == 3) ? 3 : (R * J == 4) ? 2 : 1;  // row units per batch
+    // row units per batch: eight 16-byte loads in flight per lane.  Twelve or sixteen fit the registers too and were
+    // measured 5-10 % slower per token.
+    constexpr int U = (R * J == 1) ? 8 : (R * J == 2) ? 4 : (R * J == 3) ? 3 : (R * J == 4) ? 2 : 1;
     const int lane = tid & 31, warp = tid >> 5;
     const int g = warp / kGroupWarps, slot = warp % kGroupWarps;
     int r0, r1;
@@ -376,8 +402,8 @@ __device__ __forceinline__ void unit_of(const StepDev &a, int u, int &head, int 
 }
 
 // Before the barrier in front of the attention step: ask L2 for the cache lines of this half-CTA's first unit.
-__device__ __forceinline__ void request_cache(const StepDev &a, const LayerDev &L, int end, int tid) {
-    const int half = tid >> 8, t = tid & 255;
+__device__ __forceinline__ void request_cache(const StepDev &a, const LayerDev &L, int end, int i, int n) {
+    const int half = i >= n / 2, t = half ? i - n / 2 : i, per_half = n / 2;
     const int u = blockIdx.x * 2 + half;
     if (u >= a.q_heads * a.splits) return;
     int head, split, splits, begin, stop;
@@ -388,8 +414,8 @@ __device__ __forceinline__ void request_cache(const StepDev &a, const LayerDev &
     const size_t stride_bytes = (size_t)a.kv_heads * kHeadDim * sizeof(uint16_t);
     const char *kline = reinterpret_cast<const char *>(L.k_cache) + (size_t)kv * kHeadDim * sizeof(uint16_t);
     const char *vline = reinterpret_cast<const char *>(L.v_cache) + (size_t)kv * kHeadDim * sizeof(uint16_t);
-    for (int i = t; i < 2 * (stop - begin); i += 256) {  // two 128-byte lines per key and per cache
-        const size_t off = (size_t)(begin + (i >> 1)) * stride_bytes + (size_t)(i & 1) * 128;
+    for (int line = t; line < 2 * (stop - begin); line += per_half) {  // two 128-byte lines per key and per cache
+        const size_t off = (size_t)(begin + (line >> 1)) * stride_bytes + (size_t)(line & 1) * 128;
         asm volatile("prefetch.global.L2 [%0];" ::"l"(kline + off));
         asm volatile("prefetch.global.L2 [%0];" ::"l"(vline + off));
     }
@@ -458,7 +484,9 @@ struct StepShared {
     };
 };
 
-template <class T>
+// The five steps of a layer are inlined into the layer loop on purpose: as separate (not inlined) functions each call
+// spilled the registers that live across it, inside the streaming loops too, and a token took 4.9 ms instead of 2.2.
+template <class T, bool TRACE>
 __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const StepDev a) {
     typedef typename T::storage S;
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -472,50 +500,76 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const StepDe
     const int end = (int)pos + 1;
     const int q_width = a.q_heads * kHeadDim, qkv_width = (a.q_heads + 2 * a.kv_heads) * kHeadDim;
     S *hidden = static_cast<S *>(a.hidden_io), *residual = static_cast<S *>(a.residual);
-    uint32_t passed = 0;
-    int r0, r1;
+    // TRACE is a separate instantiation: the marks cost 1 % of the step even when nothing is recorded
+    long long *trace = TRACE && a.trace && tid == 0 ? a.trace + (size_t)blockIdx.x * a.n_layers * kTracePoints : nullptr;
     for (int l = 0; l < a.n_layers; ++l) {
-        const LayerDev L = a.layers[l];
+        const LayerDev L = a.layers[l];  // all seventeen pointers at once: fetched one by one where they are used, each costs an L2 round trip on the critical path
+        auto mark = [&](int point) {
+            if (TRACE && trace) trace[l * kTracePoints + point] = clock64();
+        };
+        mark(TP_START);
         // norm1 + quantize -> Q|K|V
         float s = prologue_rmsnorm<T>(hidden, static_cast<const S *>(L.norm1), a.eps, a.hidden, sh.codes, sh.row, sh.ps, tid);
         __syncthreads();
+        mark(TP_NORM1);
         project_any<T, PRJ_PLAIN>(a, L.qkv, nullptr, L.qkv_s, nullptr, qkv_width, a.hidden, s, sh.codes, sh.red, nullptr,
                                   static_cast<S *>(a.qkv), tid);
-        cta_rows(a.hidden, r0, r1);
-        request_rows(L.o, q_width, r0, r1, 1 << 30);  // attention leaves HBM idle: the whole share of O
-        request_cache(a, L, end, tid);
-        if (!grid_barrier(a, passed, &sh.ok)) return;
+        mark(TP_QKV);
+        mark(TP_ARRIVE1);
+        if (!grid_barrier(a, barrier_ordinal(l, BAR_ATTENTION), &sh.ok, [&](int i, int n) {
+                request_cache(a, L, end, i, n);
+                request_rows(L.o, q_width, a.hidden, 0, 1ll << 40, i, n);  // attention leaves HBM idle: the whole share of O
+            }))
+            return;
+        mark(TP_PASS1);
 
         attention_phase<T>(a, L, sh.units, end, tid);
-        cta_rows(a.inter, r0, r1);
-        request_rows(L.gate, a.hidden, r0, r1, a.ahead_bytes);
-        request_rows(L.up, a.hidden, r0, r1, a.ahead_bytes);
-        if (!grid_barrier(a, passed, &sh.ok)) return;
+        mark(TP_ATTENTION);
+        if (!grid_barrier(a, barrier_ordinal(l, BAR_O), &sh.ok, [&](int i, int n) {
+                request_rows(L.gate, a.hidden, a.inter, 0, a.ahead_bytes, i, n);
+                request_rows(L.up, a.hidden, a.inter, 0, a.ahead_bytes, i, n);
+            }))
+            return;
+        mark(TP_PASS2);
 
         // quantize(attention row) -> O + residual
         s = prologue_plain<T>(static_cast<const S *>(a.attn), q_width, sh.codes, sh.row, sh.ps, tid);
         __syncthreads();
+        mark(TP_QUANT_O);
         project_any<T, PRJ_RESIDUAL>(a, L.o, nullptr, L.o_s, nullptr, a.hidden, q_width, s, sh.codes, sh.red, hidden, residual, tid);
-        if (!grid_barrier(a, passed, &sh.ok)) return;
+        mark(TP_O);
+        if (!grid_barrier(a, barrier_ordinal(l, BAR_GATE_UP), &sh.ok, [&](int i, int n) {
+                request_rows(L.gate, a.hidden, a.inter, a.ahead_bytes, a.ahead_bytes + a.ahead_more, i, n);
+                request_rows(L.up, a.hidden, a.inter, a.ahead_bytes, a.ahead_bytes + a.ahead_more, i, n);
+            }))
+            return;
+        mark(TP_PASS3);
 
         // norm2 + quantize -> gate|up + SwiGLU
         s = prologue_rmsnorm<T>(residual, static_cast<const S *>(L.norm2), a.eps, a.hidden, sh.codes, sh.row, sh.ps, tid);
         __syncthreads();
+        mark(TP_NORM2);
         project_any<T, PRJ_SWIGLU>(a, L.gate, L.up, L.gate_s, L.up_s, a.inter, a.hidden, s, sh.codes, sh.red, nullptr,
                                    static_cast<S *>(a.act), tid);
-        cta_rows(a.hidden, r0, r1);
-        request_rows(L.down, a.inter, r0, r1, a.ahead_bytes);
-        if (!grid_barrier(a, passed, &sh.ok)) return;
+        mark(TP_GATE_UP);
+        if (!grid_barrier(a, barrier_ordinal(l, BAR_DOWN), &sh.ok,
+                          [&](int i, int n) { request_rows(L.down, a.inter, a.hidden, 0, a.ahead_bytes, i, n); }))
+            return;
+        mark(TP_PASS4);
 
         // quantize(act) -> down + residual
         s = prologue_plain<T>(static_cast<const S *>(a.act), a.inter, sh.codes, sh.row, sh.ps, tid);
         __syncthreads();
+        mark(TP_QUANT_DOWN);
         project_any<T, PRJ_RESIDUAL>(a, L.down, nullptr, L.down_s, nullptr, a.hidden, a.inter, s, sh.codes, sh.red, residual, hidden, tid);
+        mark(TP_DOWN);
         if (l + 1 < a.n_layers) {
-            cta_rows(qkv_width, r0, r1);
-            request_rows(a.layers[l + 1].qkv, a.hidden, r0, r1, a.ahead_bytes);
-            if (!grid_barrier(a, passed, &sh.ok)) return;
+            const int8_t *next = a.layers[l + 1].qkv;
+            if (!grid_barrier(a, barrier_ordinal(l + 1, BAR_QKV), &sh.ok,
+                              [&](int i, int n) { request_rows(next, a.hidden, qkv_width, 0, a.ahead_bytes, i, n); }))
+                return;
         }
+        mark(TP_PASS5);
     }
 }
 
@@ -531,6 +585,7 @@ struct qwen3_decode_plan {
     void *layers_dev;
     void *work;           // residual | qkv | attention | act | scratch | {barrier words, attention counters}, one allocation
     size_t clear_bytes;   // barrier words + counters: zeroed in stream order before every step
+    void *trace;          // W8A8_DECODE_TRACE=1 at creation: cycle counts of the last step (qwen3_decode_plan_trace)
 };
 
 namespace {
@@ -556,8 +611,10 @@ int env_int(const char *name, int fallback) {
 namespace w8a8 {
 cudaError_t init_decode_layers() {
     const int smem = (int)sizeof(StepShared);
-    cudaError_t e = cudaFuncSetAttribute(decode_layers_kernel<Bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_kernel<F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_layers_kernel<Bf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_kernel<F32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_kernel<Bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_kernel<F32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     return e;
 }
 }  // namespace w8a8
@@ -583,8 +640,8 @@ int qwen3_decode_plan_create(const qwen3_layer_desc *layers, int n_layers, int h
     REQUIRE(cooperative, W8A8_ERR_UNSUPPORTED);
     int per_sm = 0;
     cudaError_t e = dtype == W8A8_BF16
-                        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_layers_kernel<Bf16>, kThreads, sizeof(StepShared))
-                        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_layers_kernel<F32>, kThreads, sizeof(StepShared));
+                        ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_layers_kernel<Bf16, false>, kThreads, sizeof(StepShared))
+                        : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_layers_kernel<F32, false>, kThreads, sizeof(StepShared));
     if (e != cudaSuccess) return fail_cuda(e, "occupancy of the decode kernel");
     REQUIRE(per_sm >= 1, W8A8_ERR_UNSUPPORTED);
     int grid = sm_count();  // one CTA per SM
@@ -618,10 +675,10 @@ int qwen3_decode_plan_create(const qwen3_layer_desc *layers, int n_layers, int h
 
     qwen3_decode_plan *p = new (std::nothrow) qwen3_decode_plan();
     REQUIRE(p, W8A8_ERR_CUDA);
-    p->device = device; p->dtype = dtype; p->grid = grid;
+    p->device = device; p->dtype = dtype; p->grid = grid; p->trace = nullptr;
     const size_t el = dtype == W8A8_BF16 ? 2 : 4;
     // the same split count qwen3_attention launches for one row (forward_glue.cu), so that both give the same bits
-    const int splits = std::min(kAttnMaxSplits, (2 * sm_count() + q_heads - 1) / q_heads);
+    const int splits = attention_splits(q_heads);
     const size_t b_hidden = round_up((size_t)hidden * el, 256), b_qkv = round_up((size_t)qkv_width * el, 256);
     const size_t b_attn = round_up((size_t)q_width * el, 256), b_act = round_up((size_t)intermediate * el, 256);
     const size_t b_scratch = round_up((size_t)q_heads * splits * kUnitRecord * sizeof(float), 256);
@@ -650,8 +707,20 @@ int qwen3_decode_plan_create(const qwen3_layer_desc *layers, int n_layers, int h
     s.sync = reinterpret_cast<uint32_t *>(at);
     s.counters = s.sync + 4;
     s.status = device_status_ptr();
-    s.ahead_bytes = env_int("W8A8_DECODE_AHEAD_KB", 128) * 1024;
-    s.ahead_rows = env_int("W8A8_DECODE_AHEAD_BATCHES", 2);
+    s.trace = nullptr;
+    if (env_int("W8A8_DECODE_TRACE", 0)) {
+        const size_t words = (size_t)grid * n_layers * kTracePoints;
+        if (cudaMalloc(&p->trace, words * sizeof(long long)) == cudaSuccess) {
+            cudaMemset(p->trace, 0, words * sizeof(long long));
+            s.trace = static_cast<long long *>(p->trace);
+        } else {
+            p->trace = nullptr;
+            (void)cudaGetLastError();
+        }
+    }
+    s.ahead_bytes = (long long)env_int("W8A8_DECODE_AHEAD_KB", 64) * 1024;
+    s.ahead_more = (long long)env_int("W8A8_DECODE_AHEAD_MORE_KB", 0) * 1024;
+    s.ahead_rows = env_int("W8A8_DECODE_AHEAD_BATCHES", 1);
     p->magic = kPlanMagic;
     *plan_out = p;
     return W8A8_OK;
@@ -663,8 +732,22 @@ int qwen3_decode_plan_destroy(qwen3_decode_plan_t plan) {
     plan->magic = 0;
     cudaFree(plan->work);
     cudaFree(plan->layers_dev);
+    cudaFree(plan->trace);
     delete plan;
     return W8A8_OK;
+}
+
+int qwen3_decode_plan_trace(qwen3_decode_plan_t plan, int64_t *cycles, size_t capacity, int *ctas, int *layers, int *points) {
+    REQUIRE(valid_plan(plan) && ctas && layers && points, W8A8_ERR_BAD_ARG);
+    *ctas = plan->grid;
+    *layers = plan->dev.n_layers;
+    *points = kTracePoints;
+    REQUIRE(plan->trace, W8A8_ERR_UNSUPPORTED);
+    const size_t words = (size_t)plan->grid * plan->dev.n_layers * kTracePoints;
+    if (!cycles) return W8A8_OK;
+    REQUIRE(capacity >= words, W8A8_ERR_BAD_ARG);
+    cudaError_t e = cudaMemcpy(cycles, plan->trace, words * sizeof(long long), cudaMemcpyDeviceToHost);
+    return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "decode trace read-back");
 }
 
 int qwen3_decode_layers(qwen3_decode_plan_t plan, void *hidden, const uint32_t *control, void *stream) {
@@ -686,8 +769,11 @@ int qwen3_decode_layers(qwen3_decode_plan_t plan, void *hidden, const uint32_t *
     attr.val.cooperative = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    e = plan->dtype == W8A8_BF16 ? cudaLaunchKernelEx(&cfg, decode_layers_kernel<Bf16>, args)
-                                 : cudaLaunchKernelEx(&cfg, decode_layers_kernel<F32>, args);
+    const bool bf16 = plan->dtype == W8A8_BF16;
+    if (plan->trace)
+        e = bf16 ? cudaLaunchKernelEx(&cfg, decode_layers_kernel<Bf16, true>, args) : cudaLaunchKernelEx(&cfg, decode_layers_kernel<F32, true>, args);
+    else
+        e = bf16 ? cudaLaunchKernelEx(&cfg, decode_layers_kernel<Bf16, false>, args) : cudaLaunchKernelEx(&cfg, decode_layers_kernel<F32, false>, args);
     return e == cudaSuccess ? W8A8_OK : fail_cuda(e, "decode step launch");
 }
 

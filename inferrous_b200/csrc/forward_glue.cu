@@ -724,10 +724,10 @@ static int attention_impl(const void *q, int dtype, int64_t ldq, int rows, int q
     REQUIRE(ldq >= (int64_t)q_heads * kHeadDim && ldo >= (int64_t)q_heads * kHeadDim, W8A8_ERR_BAD_ARG);
     REQUIRE(aligned(k_cache, 16) && aligned(v_cache, 16), W8A8_ERR_ALIGNMENT);
     if (rows == 0) return W8A8_OK;
-    // Few (row, head) units: split the keys of each over several CTAs, about two CTAs per SM in all.
+    // Few (row, head) units: split the keys of each over several CTAs, at most two CTAs per SM in all.
     const int units = rows * q_heads;
     int splits = 1;
-    if (units < sm_count() && units <= kAttnSplitMaxUnits) splits = std::min(kAttnMaxSplits, (2 * sm_count() + units - 1) / units);
+    if (units < sm_count() && units <= kAttnSplitMaxUnits) splits = attention_splits(units);
     // the folded quantizer exists in the few-row kernel only
     REQUIRE(q_out == nullptr || (rows * q_heads < sm_count() && rows * q_heads <= kAttnSplitMaxUnits), W8A8_ERR_UNSUPPORTED);
     if (rows >= kMmaMinRows && (ldq % 2) == 0 && (ldo % 2) == 0 && aligned(q, 8) && aligned(out, 8) && !g_attention_no_mma) {

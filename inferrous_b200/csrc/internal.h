@@ -151,6 +151,9 @@ constexpr int kAttnMaxSplits = 16;
 constexpr size_t kAttnScratchFloats = (size_t)kAttnSplitMaxUnits * kAttnMaxSplits * 132;
 float *attention_scratch();
 uint32_t *attention_counters();
+// Key splits launched for `units` (row, head) pairs: as many as keep units * splits within two CTAs per SM.  The resident
+// decode kernel uses the same number, so that both give the same bits.
+int attention_splits(int units);
 
 // L2 prefetch hint for immutable weights (w8a8_prefetch_hint): consumed by the next launch that carries prefetch CTAs.
 constexpr int kMaxPrefetchRanges = 4;

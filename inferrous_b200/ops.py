@@ -376,3 +376,17 @@ class DecodePlan:
         if h and capi is not None:
             capi.load().qwen3_decode_plan_destroy(h)
             self.handle = None
+
+    def trace(self):
+        """Cycle counts of the last step, [ctas, layers, points] (numpy int64), when the plan was created with
+        W8A8_DECODE_TRACE=1 in the environment (qwen3_decode_plan_trace)."""
+        import numpy as np
+
+        ctas, layers, points = C.c_int(), C.c_int(), C.c_int()
+        lib = capi.load()
+        capi.check(lib.qwen3_decode_plan_trace(self.handle, None, 0, C.byref(ctas), C.byref(layers), C.byref(points)),
+                   "qwen3_decode_plan_trace")
+        out = np.zeros((ctas.value, layers.value, points.value), dtype=np.int64)
+        capi.check(lib.qwen3_decode_plan_trace(self.handle, out.ctypes.data_as(C.c_void_p), out.size, C.byref(ctas), C.byref(layers),
+                                               C.byref(points)), "qwen3_decode_plan_trace")
+        return out

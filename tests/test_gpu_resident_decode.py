@@ -26,8 +26,8 @@ CASES = [
     # down projection rows of two and three 4096-byte rounds (intermediate 4608 and 8448), hidden rows shorter than a round
     (dict(layers=1, intermediate=4608, context=64), 3, 20),
     (dict(layers=1, intermediate=8448, context=64), 3, 20),
-    # one key/value head for eight query heads; a hidden width that is not a multiple of the 512-byte warp slice
-    (dict(layers=2, hidden=1168, q_heads=8, kv_heads=1, intermediate=2064, vocab=1000, context=96), 17, 60),
+    # one key/value head for eight query heads; widths that are not multiples of the 512-byte warp slice
+    (dict(layers=2, hidden=1152, q_heads=8, kv_heads=1, intermediate=2176, vocab=1000, context=96), 17, 60),
 ]
 
 
@@ -77,7 +77,7 @@ def test_resident_step_on_fewer_ctas(monkeypatch):
 def test_unsupported_shapes_keep_the_separate_launches():
     from inferrous_b200.qwen3 import Qwen3Runner, Qwen3Weights
 
-    c = config(layers=1, intermediate=12288 + 16, context=32)  # a down-projection row longer than three rounds
+    c = config(layers=1, intermediate=12288 + 128, context=32)  # a down-projection row longer than three rounds
     weights = Qwen3Weights.random(c, seed=2)
     runner = Qwen3Runner(weights)
     assert runner.plan is None
