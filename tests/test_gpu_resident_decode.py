@@ -104,3 +104,26 @@ def test_plan_arguments_are_checked():
     assert lib.qwen3_decode_plan_create(None, 1, 256, 4, 2, 512, 64, 1e-6, None, 0, C.byref(out)) == 1
     assert lib.qwen3_decode_layers(None, None, None, None) == 1
     assert lib.qwen3_decode_plan_destroy(None) == 0
+
+
+def test_cycle_trace_of_the_last_step(monkeypatch):
+    """W8A8_DECODE_TRACE=1 at plan creation: every CTA notes its cycle counter at the boundaries of each layer's steps; the
+    counts rise along a layer and from layer to layer, and the tokens are those of the kernel without marks."""
+    from inferrous_b200 import capi
+    from inferrous_b200.qwen3 import Qwen3Runner, Qwen3Weights
+
+    c = config(layers=3, context=96)
+    weights = Qwen3Weights.random(c, seed=8)
+    prompt = [5, 6, 7]
+    plain = Qwen3Runner(weights, resident=True)
+    expected, _ = plain.generate(prompt, 20)
+    with pytest.raises(capi.W8A8Error) as none:
+        plain.plan.trace()
+    assert none.value.status == 3
+    monkeypatch.setenv("W8A8_DECODE_TRACE", "1")
+    traced = Qwen3Runner(weights, resident=True)
+    assert traced.generate(prompt, 20)[0] == expected
+    t = traced.plan.trace()
+    assert t.shape[1] == 3 and t.shape[2] == 16 and (t > 0).all()
+    flat = t.reshape(t.shape[0], -1)
+    assert (np.diff(flat, axis=1) >= 0).all()
