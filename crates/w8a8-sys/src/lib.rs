@@ -111,6 +111,7 @@ extern "C" {
     pub fn qwen3_decode_plan_create(layers: *const Qwen3LayerDesc, n_layers: c_int, hidden: c_int, q_heads: c_int, kv_heads: c_int, intermediate: c_int, capacity: c_int, eps: f32, rope_table: *const f32, dtype: c_int, plan: *mut *mut Qwen3DecodePlan) -> c_int;
     pub fn qwen3_decode_plan_destroy(plan: *mut Qwen3DecodePlan) -> c_int;
     pub fn qwen3_decode_layers(plan: *mut Qwen3DecodePlan, hidden: *mut c_void, control: *const u32, stream: *mut c_void) -> c_int;
+    pub fn qwen3_decode_plan_set_peers(plan: *mut Qwen3DecodePlan, packet_buffers: *const *mut c_void, seq: *mut u32, rank: c_int, tp: c_int) -> c_int;
     pub fn qwen3_decode_plan_trace(plan: *mut Qwen3DecodePlan, cycles: *mut i64, capacity: usize, ctas: *mut c_int, layers: *mut c_int, points: *mut c_int) -> c_int;
     pub fn qwen3_attention_use_tensor_cores(enabled: c_int) -> c_int;
 }

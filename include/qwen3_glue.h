@@ -158,6 +158,17 @@ int qwen3_decode_plan_destroy(qwen3_decode_plan_t plan);
  * `hidden` undefined and code 7 in the device status word (w8a8_device_status). */
 int qwen3_decode_layers(qwen3_decode_plan_t plan, void *hidden, const uint32_t *control, void *stream);
 
+/* Tensor parallel form of the step (no counterpart in the reference, which is single-GPU): the plan describes THIS rank's
+ * shard (its query / key / value heads and the matching rows of Q|K|V, its slice of the input channels of O, its gate /
+ * up channels and the matching input channels of down; hidden unchanged), and after this call qwen3_decode_layers runs
+ * the kernel in which O and down send their partial outputs to every rank as 8-byte packets {float32 bits of the bf16
+ * value, tag} with plain peer stores and every rank sums them in rank order (float32, bf16, + residual, bf16: the
+ * arithmetic of w8a8_linear_allreduce).  `packet_buffers[r]` is rank r's buffer as seen from this device (symmetric /
+ * peer-mapped memory, 2 * tp * hidden packets of 8 bytes, zeroed once), `seq` one local zeroed word the step advances.
+ * All ranks must run the same steps in the same order; a wait for another rank's packets is bounded (about two seconds,
+ * code 5 in the device status word).  tp = 1 with the rank's own buffer is valid and gives the single-GPU result. */
+int qwen3_decode_plan_set_peers(qwen3_decode_plan_t plan, void *const *packet_buffers, uint32_t *seq, int rank, int tp);
+
 /* Measurement aid: a plan created while W8A8_DECODE_TRACE=1 is in the environment makes thread 0 of every CTA note its
  * SM's cycle counter at `points` boundaries of every layer (start, after each quantizer, projection, barrier and the
  * attention step).  This call synchronises the device and copies the last step's counts to the HOST array `cycles`

@@ -57,6 +57,7 @@ SIGNATURES = {
     "qwen3_decode_plan_create": (_i, [_vp, _i, _i, _i, _i, _i, _i, _f, _vp, _i, C.POINTER(_vp)]),
     "qwen3_decode_plan_destroy": (_i, [_vp]),
     "qwen3_decode_layers": (_i, [_vp, _vp, _vp, _vp]),
+    "qwen3_decode_plan_set_peers": (_i, [_vp, C.POINTER(_vp), _vp, _i, _i]),
     "qwen3_decode_plan_trace": (_i, [_vp, _vp, _sz, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     "qwen3_attention_use_tensor_cores": (_i, [_i]),
     "qwen3_attention_quantize": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp, _vp, _vp, _i64, _i, _vp, _vp, _vp]),

@@ -78,6 +78,11 @@ struct StepDev {
     long long ahead_more;       // per CTA: further bytes of gate and up requested one barrier earlier still (the O projection is short)
     int ahead_rows;             // inside a projection: L2 requests run this many row batches ahead of the loads
     long long *trace;           // optional: [CTA][layer][kTracePoints] SM cycle counts at the step boundaries of a layer
+    // tensor parallel (decode_layers_tp_kernel): O and down own a slice of the input channels, their partial outputs are
+    // summed over the ranks through packet buffers in peer memory
+    uint2 *ll[kTpMaxRanks];     // packet buffer of every rank: [2 halves][tp sources][hidden] packets {value bits, tag}
+    uint32_t *seq;              // local: [0] = exchanges completed by earlier steps (the tag base of this step)
+    int rank, tp;
 };
 
 // Points of a layer at which thread 0 of every CTA notes its SM's cycle counter when the plan carries a trace buffer.
@@ -190,17 +195,11 @@ __device__ __forceinline__ float prologue_plain(const typename T::storage *x, in
 
 // norm_quantize (src/kernels.rs:479-576): the reference's summation tree (256 strided partial sums, distances
 // 128..1), y = bf16((x * rsqrt(mean + eps)) * gain), m = max(1e-8, max|y|), s = m / 127
+// The part of norm_quantize behind the load: `row` holds the K values of x.
 template <class T>
-__device__ __forceinline__ float prologue_rmsnorm(const typename T::storage *x, const typename T::storage *gain, float eps, int K,
-                                                  int8_t *sq, float *row, PrologueShared &ps, int tid) {
+__device__ __forceinline__ float rmsnorm_row(const typename T::storage *gain, float eps, int K, int8_t *sq, float *row,
+                                             PrologueShared &ps, int tid) {
     constexpr int V = T::kVec;
-    for (int j = tid * V; j < K; j += kThreads * V) {
-        float v[V];
-        load_vec_cg<T>(x + j, v);
-#pragma unroll
-        for (int i = 0; i < V; i += 4) *reinterpret_cast<float4 *>(row + j + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-    }
-    __syncthreads();
     if (tid < 256) {
         float p = 0.0f;
         for (int j = tid; j < K; j += 256) p = __fadd_rn(p, __fmul_rn(row[j], row[j]));
@@ -239,13 +238,38 @@ __device__ __forceinline__ float prologue_rmsnorm(const typename T::storage *x, 
     return s;
 }
 
+// norm_quantize (src/kernels.rs:479-576): the reference's summation tree (256 strided partial sums, distances
+// 128..1), y = bf16((x * rsqrt(mean + eps)) * gain), m = max(1e-8, max|y|), s = m / 127
+template <class T>
+__device__ __forceinline__ float prologue_rmsnorm(const typename T::storage *x, const typename T::storage *gain, float eps, int K,
+                                                  int8_t *sq, float *row, PrologueShared &ps, int tid) {
+    constexpr int V = T::kVec;
+    for (int j = tid * V; j < K; j += kThreads * V) {
+        float v[V];
+        load_vec_cg<T>(x + j, v);
+#pragma unroll
+        for (int i = 0; i < V; i += 4) *reinterpret_cast<float4 *>(row + j + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    }
+    __syncthreads();
+    return rmsnorm_row<T>(gain, eps, K, sq, row, ps, tid);
+}
+
 // ---- one projection, this CTA's share ------------------------------------------------------------------------
 // The CTA owns the weight rows [r0, r1) (row pairs (gate c, up c) for the SwiGLU form).  Its sixteen warps form two
 // groups of eight; a group takes every other row and spreads the row's K bytes over its 256 lanes, 16 bytes each per
 // round of 4096 bytes, so the lane's slice of the activation codes stays in registers for the whole projection.
 // Per row and warp: J loads, 4 J dp4a, one warp-wide integer add; the eight partial sums of a row meet in shared
 // memory and one thread per row finishes it (exact: int32).
-enum { PRJ_PLAIN = 0, PRJ_RESIDUAL = 1, PRJ_SWIGLU = 2 };
+enum { PRJ_PLAIN = 0, PRJ_RESIDUAL = 1, PRJ_SWIGLU = 2, PRJ_PUSH = 3 };
+
+// Tensor parallel: one 8-byte packet {value bits, tag of the exchange} to the same slot of every rank (plain peer stores
+// over NVLink); value and tag travel in one store, so the reader needs no fence, only to see the tag.
+__device__ __forceinline__ void push_packet(const StepDev &a, uint32_t exchange, uint32_t tag, int element, float value) {
+    const size_t at = ((size_t)(exchange & 1u) * a.tp + a.rank) * a.hidden + element;
+    const uint32_t bits = __float_as_uint(value);
+    for (int p = 0; p < a.tp; ++p)
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(a.ll[p] + at), "r"(bits), "r"(tag) : "memory");
+}
 
 __device__ __forceinline__ int dp4a_16(const uint4 &w, const uint4 &x, int acc) {
     acc = __dp4a((int)w.x, (int)x.x, acc);
@@ -258,7 +282,8 @@ __device__ __forceinline__ int dp4a_16(const uint4 &w, const uint4 &x, int acc) 
 template <class T, int EPI, int J>
 __device__ void project(const StepDev &a, const int8_t *__restrict__ w0, const int8_t *__restrict__ w1,
                         const float *__restrict__ ws0, const float *__restrict__ ws1, int N, int K, float a_scale,
-                        const int8_t *sq, int *red, const typename T::storage *residual, typename T::storage *out, int tid) {
+                        const int8_t *sq, int *red, const typename T::storage *residual, typename T::storage *out, int tid,
+                        uint32_t exchange = 0, uint32_t tag = 0) {
     constexpr int R = (EPI == PRJ_SWIGLU) ? 2 : 1;
     // row units per batch: eight 16-byte loads in flight per lane.  Twelve or sixteen fit the registers too and were
     // measured 5-10 % slower per token.
@@ -349,6 +374,8 @@ __device__ void project(const StepDev &a, const int8_t *__restrict__ w0, const i
             const float gv = dequant(sum[0], a_scale, pre_s0);
             const float uv = dequant(sum[R - 1], a_scale, pre_s1);
             T::store(out + c, swiglu_value(gv, uv));
+        } else if (EPI == PRJ_PUSH) {
+            push_packet(a, exchange, tag, c, dequant(sum[0], a_scale, pre_s0));
         } else if (EPI == PRJ_RESIDUAL) {
             T::store(out + c, bf16_rne(__fadd_rn(pre_res, dequant(sum[0], a_scale, pre_s0))));
         } else {
@@ -360,10 +387,11 @@ __device__ void project(const StepDev &a, const int8_t *__restrict__ w0, const i
 template <class T, int EPI>
 __device__ __forceinline__ void project_any(const StepDev &a, const int8_t *w0, const int8_t *w1, const float *ws0, const float *ws1,
                                             int N, int K, float a_scale, const int8_t *sq, int *red,
-                                            const typename T::storage *residual, typename T::storage *out, int tid) {
-    if (K <= kGroupBytes) project<T, EPI, 1>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid);
-    else if (K <= 2 * kGroupBytes) project<T, EPI, 2>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid);
-    else project<T, EPI, 3>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid);
+                                            const typename T::storage *residual, typename T::storage *out, int tid,
+                                            uint32_t exchange = 0, uint32_t tag = 0) {
+    if (K <= kGroupBytes) project<T, EPI, 1>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid, exchange, tag);
+    else if (K <= 2 * kGroupBytes) project<T, EPI, 2>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid, exchange, tag);
+    else project<T, EPI, 3>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid, exchange, tag);
 }
 
 // ---- attention: two units side by side per CTA ------------------------------------------------------------------
@@ -573,6 +601,138 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const StepDe
     }
 }
 
+
+// ---- the step under tensor parallelism ------------------------------------------------------------------------------
+// Every rank runs this kernel on its shard (its query / key / value heads, its gate / up channels, its slice of the
+// input channels of O and down).  The residual stream is replicated: every CTA of every rank keeps the whole hidden
+// row and the whole residual row in its shared memory.  O and down send their partial outputs to every rank as tagged
+// packets; the wait for the packets of an exchange takes the place of the grid-wide barrier behind those projections,
+// and the reduction (sum in rank order in float32, bf16, + residual, bf16: what tp_reduce_kernel computes after
+// w8a8_linear_allreduce) is the first part of the prologue that follows.  Two packet-buffer halves alternate; a rank
+// can only run two exchanges ahead of another once that one has read the older half.
+struct StepSharedTp {
+    StepShared base;
+    float hidden[kMaxK];    // the hidden row (the layer's input), every CTA its own copy
+    float residual[kMaxK];  // hidden + attention block
+};
+
+// Waits (bounded) for the packets of `exchange` from every rank and leaves out[e] = bf16(in[e] + bf16(sum_r y_r[e])).
+__device__ __forceinline__ bool gather_exchange(const StepDev &a, uint32_t exchange, uint32_t tag, const float *in, float *out,
+                                                uint32_t *ok_smem, int tid) {
+    const uint2 *base = a.ll[a.rank] + (size_t)(exchange & 1u) * a.tp * a.hidden;
+    bool good = true;
+    for (int e = tid; e < a.hidden && good; e += kThreads) {
+        float sum = 0.0f;
+        for (int r = 0; r < a.tp && good; ++r) {
+            const uint2 *p = base + (size_t)r * a.hidden + e;
+            uint2 v;
+            unsigned long long t0 = 0;
+            for (uint32_t spin = 1;; ++spin) {
+                asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+                if (v.y == tag) break;
+                if ((spin & 255u) == 0) {
+                    uint32_t stop;
+                    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(stop) : "l"(a.sync + 1) : "memory");
+                    const unsigned long long now = global_ns();
+                    if (t0 == 0) t0 = now;
+                    if (stop || now - t0 > kWaitLimitNs) {
+                        if (!stop) {
+                            atomicExch(a.sync + 1, 1u);
+                            if (a.status && atomicCAS(a.status, 0u, (uint32_t)WAIT_PEER) == 0u) a.status[1] = (uint32_t)r;
+                        }
+                        good = false;
+                        break;
+                    }
+                }
+            }
+            sum = __fadd_rn(sum, __uint_as_float(v.x));
+        }
+        if (good) out[e] = bf16_rne(__fadd_rn(in[e], bf16_rne(sum)));
+    }
+    if (tid == 0) *ok_smem = 1;
+    __syncthreads();
+    if (!good) *ok_smem = 0;
+    __syncthreads();
+    return *ok_smem != 0;
+}
+
+// norm_quantize of a row that is already in shared memory
+template <class T>
+__device__ __forceinline__ float prologue_rmsnorm_shared(const float *x, const typename T::storage *gain, float eps, int K, int8_t *sq,
+                                                         float *row, PrologueShared &ps, int tid) {
+    for (int j = tid * 4; j < K; j += kThreads * 4) *reinterpret_cast<float4 *>(row + j) = *reinterpret_cast<const float4 *>(x + j);
+    __syncthreads();
+    return rmsnorm_row<T>(gain, eps, K, sq, row, ps, tid);
+}
+
+enum { BAR_TP_ATTENTION = 1, BAR_TP_O = 2, BAR_TP_DOWN = 3, kBarriersPerLayerTp = 3 };
+
+template <class T>
+__global__ void __launch_bounds__(kThreads, 1) decode_layers_tp_kernel(const StepDev a) {
+    typedef typename T::storage S;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    StepSharedTp &tp = *reinterpret_cast<StepSharedTp *>(smem_raw);
+    StepShared &sh = tp.base;
+    const int tid = threadIdx.x;
+    const uint32_t pos = a.control[1];
+    if (pos >= (uint32_t)a.capacity) {  // every CTA of every rank takes this branch: nobody waits for anybody
+        if (blockIdx.x == 0 && tid == 0 && a.status && atomicCAS(a.status, 0u, (uint32_t)FAULT_CACHE_RANGE) == 0u) a.status[1] = pos;
+        return;
+    }
+    const int end = (int)pos + 1;
+    const int q_width = a.q_heads * kHeadDim, qkv_width = (a.q_heads + 2 * a.kv_heads) * kHeadDim;  // this rank's share
+    const uint32_t tag0 = *reinterpret_cast<const volatile uint32_t *>(a.seq) + 1u;  // tag of this step's first exchange
+    for (int j = tid; j < a.hidden; j += kThreads) tp.hidden[j] = load_one_cg<T>(static_cast<const S *>(a.hidden_io) + j);
+    __syncthreads();
+    const auto ordinal = [](int l, int which) { return (uint32_t)(l * kBarriersPerLayerTp + which); };
+    for (int l = 0; l < a.n_layers; ++l) {
+        const LayerDev L = a.layers[l];
+        const uint32_t x_o = 2u * l, x_down = 2u * l + 1u;  // the layer's two exchanges
+        // norm1 + quantize -> this rank's Q|K|V heads
+        float s = prologue_rmsnorm_shared<T>(tp.hidden, static_cast<const S *>(L.norm1), a.eps, a.hidden, sh.codes, sh.row, sh.ps, tid);
+        __syncthreads();
+        project_any<T, PRJ_PLAIN>(a, L.qkv, nullptr, L.qkv_s, nullptr, qkv_width, a.hidden, s, sh.codes, sh.red, nullptr,
+                                  static_cast<S *>(a.qkv), tid);
+        if (!grid_barrier(a, ordinal(l, BAR_TP_ATTENTION), &sh.ok, [&](int i, int n) {
+                request_cache(a, L, end, i, n);
+                request_rows(L.o, q_width, a.hidden, 0, 1ll << 40, i, n);
+            }))
+            return;
+        attention_phase<T>(a, L, sh.units, end, tid);
+        if (!grid_barrier(a, ordinal(l, BAR_TP_O), &sh.ok, [&](int i, int n) {
+                request_rows(L.gate, a.hidden, a.inter, 0, a.ahead_bytes, i, n);
+                request_rows(L.up, a.hidden, a.inter, 0, a.ahead_bytes, i, n);
+            }))
+            return;
+        // quantize(this rank's attention heads) -> partial O, sent to every rank
+        s = prologue_plain<T>(static_cast<const S *>(a.attn), q_width, sh.codes, sh.row, sh.ps, tid);
+        __syncthreads();
+        project_any<T, PRJ_PUSH>(a, L.o, nullptr, L.o_s, nullptr, a.hidden, q_width, s, sh.codes, sh.red, nullptr, nullptr, tid, x_o,
+                                 tag0 + x_o);
+        if (!gather_exchange(a, x_o, tag0 + x_o, tp.hidden, tp.residual, &sh.ok, tid)) return;
+        // norm2 + quantize -> this rank's gate|up channels + SwiGLU
+        s = prologue_rmsnorm_shared<T>(tp.residual, static_cast<const S *>(L.norm2), a.eps, a.hidden, sh.codes, sh.row, sh.ps, tid);
+        __syncthreads();
+        project_any<T, PRJ_SWIGLU>(a, L.gate, L.up, L.gate_s, L.up_s, a.inter, a.hidden, s, sh.codes, sh.red, nullptr,
+                                   static_cast<S *>(a.act), tid);
+        if (!grid_barrier(a, ordinal(l, BAR_TP_DOWN), &sh.ok,
+                          [&](int i, int n) { request_rows(L.down, a.inter, a.hidden, 0, a.ahead_bytes, i, n); }))
+            return;
+        // quantize(this rank's act channels) -> partial down, sent to every rank
+        s = prologue_plain<T>(static_cast<const S *>(a.act), a.inter, sh.codes, sh.row, sh.ps, tid);
+        __syncthreads();
+        project_any<T, PRJ_PUSH>(a, L.down, nullptr, L.down_s, nullptr, a.hidden, a.inter, s, sh.codes, sh.red, nullptr, nullptr, tid,
+                                 x_down, tag0 + x_down);
+        if (l + 1 < a.n_layers) request_rows(a.layers[l + 1].qkv, a.hidden, qkv_width, 0, a.ahead_bytes, tid, kThreads);
+        if (!gather_exchange(a, x_down, tag0 + x_down, tp.residual, tp.hidden, &sh.ok, tid)) return;
+    }
+    if (blockIdx.x == 0) {
+        for (int j = tid; j < a.hidden; j += kThreads) T::store(static_cast<S *>(a.hidden_io) + j, tp.hidden[j]);
+        // every CTA of this rank read the tag base before it sent its first packet, and this CTA has seen all packets
+        if (tid == 0) a.seq[0] = tag0 - 1u + 2u * (uint32_t)a.n_layers;
+    }
+}
+
 }  // namespace
 }  // namespace w8a8
 
@@ -615,6 +775,9 @@ cudaError_t init_decode_layers() {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_kernel<F32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_kernel<Bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_kernel<F32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    const int smem_tp = (int)sizeof(StepSharedTp);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_tp_kernel<Bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tp);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_tp_kernel<F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tp);
     return e;
 }
 }  // namespace w8a8
@@ -707,6 +870,8 @@ int qwen3_decode_plan_create(const qwen3_layer_desc *layers, int n_layers, int h
     s.sync = reinterpret_cast<uint32_t *>(at);
     s.counters = s.sync + 4;
     s.status = device_status_ptr();
+    s.seq = nullptr; s.rank = 0; s.tp = 0;
+    for (int r = 0; r < kTpMaxRanks; ++r) s.ll[r] = nullptr;
     s.trace = nullptr;
     if (env_int("W8A8_DECODE_TRACE", 0)) {
         const size_t words = (size_t)grid * n_layers * kTracePoints;
@@ -734,6 +899,16 @@ int qwen3_decode_plan_destroy(qwen3_decode_plan_t plan) {
     cudaFree(plan->layers_dev);
     cudaFree(plan->trace);
     delete plan;
+    return W8A8_OK;
+}
+
+int qwen3_decode_plan_set_peers(qwen3_decode_plan_t plan, void *const *packet_buffers, uint32_t *seq, int rank, int tp) {
+    REQUIRE(valid_plan(plan) && packet_buffers && seq, W8A8_ERR_BAD_ARG);
+    REQUIRE(tp >= 1 && tp <= kTpMaxRanks && rank >= 0 && rank < tp, W8A8_ERR_BAD_ARG);
+    for (int r = 0; r < tp; ++r) REQUIRE(packet_buffers[r] && (reinterpret_cast<uintptr_t>(packet_buffers[r]) & 7u) == 0, W8A8_ERR_BAD_ARG);
+    StepDev &s = plan->dev;
+    for (int r = 0; r < kTpMaxRanks; ++r) s.ll[r] = r < tp ? static_cast<uint2 *>(packet_buffers[r]) : nullptr;
+    s.seq = seq; s.rank = rank; s.tp = tp;
     return W8A8_OK;
 }
 
@@ -770,7 +945,10 @@ int qwen3_decode_layers(qwen3_decode_plan_t plan, void *hidden, const uint32_t *
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     const bool bf16 = plan->dtype == W8A8_BF16;
-    if (plan->trace)
+    if (plan->dev.tp > 0) {
+        cfg.dynamicSmemBytes = sizeof(StepSharedTp);
+        e = bf16 ? cudaLaunchKernelEx(&cfg, decode_layers_tp_kernel<Bf16>, args) : cudaLaunchKernelEx(&cfg, decode_layers_tp_kernel<F32>, args);
+    } else if (plan->trace)
         e = bf16 ? cudaLaunchKernelEx(&cfg, decode_layers_kernel<Bf16, true>, args) : cudaLaunchKernelEx(&cfg, decode_layers_kernel<F32, true>, args);
     else
         e = bf16 ? cudaLaunchKernelEx(&cfg, decode_layers_kernel<Bf16, false>, args) : cudaLaunchKernelEx(&cfg, decode_layers_kernel<F32, false>, args);

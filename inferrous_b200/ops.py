@@ -365,6 +365,13 @@ class DecodePlan:
         self.handle = handle
         self.hidden = hidden
 
+    def set_peers(self, packet_buffers, seq: torch.Tensor, rank: int, tp: int) -> None:
+        """Tensor parallel (qwen3_decode_plan_set_peers): `packet_buffers` are the device addresses of every rank's packet
+        buffer (2 * tp * hidden packets of 8 bytes, zeroed), `seq` a zeroed int32 word of this rank."""
+        table = (C.c_void_p * tp)(*[int(p) for p in packet_buffers])
+        self._keep = self._keep + (seq,)
+        capi.check(capi.load().qwen3_decode_plan_set_peers(self.handle, table, _ptr(seq), rank, tp), "qwen3_decode_plan_set_peers")
+
     def run(self, hidden_row: torch.Tensor, control: torch.Tensor) -> None:
         """hidden_row ([hidden] or [1, hidden]): the token's embedding in, the last layer's output out; control = {token,
         position} on the device."""

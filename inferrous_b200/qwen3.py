@@ -210,7 +210,7 @@ class Qwen3Runner:
     def __init__(self, weights: Qwen3Weights, unfused: bool = False, device="cuda", fold_quantizers: str = "none",
                  prefetch_rows: int = 0, prefetch_down_at: str = "quant", prefetch_o: bool = False, group=None,
                  fused_allreduce: bool = True, fold_attention_quantizer: bool = False, batch: int = 1,
-                 peer_rows_times_ranks: int = 128, resident: bool | None = None):
+                 peer_rows_times_ranks: int = 128, resident: bool | None = None, resident_exchange: bool = False):
         ops.init()
         if batch < 1:
             raise ValueError("batch must be at least 1")
@@ -258,18 +258,27 @@ class Qwen3Runner:
             self.local_best = torch.zeros(2, dtype=torch.int32, device=device)         # {token within the shard, value bits}
             self.all_best = torch.zeros(weights.tp, 2, dtype=torch.int32, device=device)
         self.graph = None
-        # One-token decode on one GPU: all layers of a step inside one resident kernel (ops.DecodePlan) instead of ten
-        # launches per layer; bit-identical.  resident=None: on wherever the library supports the shape and the device.
+        # One-token decode: all layers of a step inside one resident kernel (ops.DecodePlan) instead of ten launches per
+        # layer; bit-identical.  resident=None: on wherever the library supports the shape and the device.  Tensor parallel:
+        # the same kernel on every rank's shard, O and down exchanging their partial outputs as packets over peer memory
+        # inside it (needs fused_allreduce: the arithmetic is that of the fused exchange).  resident_exchange=True runs
+        # that form on one GPU as a group of one (a test of the exchange code without a second device).
         self.plan = None
+        self._exchange = None
         if resident is None:
             resident = os.environ.get("W8A8_RESIDENT_DECODE", "1") != "0"
-        if resident and weights.tp == 1 and not unfused and fold_quantizers == "none":
+        exchange = (weights.tp > 1 and fused_allreduce) or (weights.tp == 1 and resident_exchange)
+        if resident and not unfused and fold_quantizers == "none" and (weights.tp == 1 or fused_allreduce):
             try:
                 self.plan = ops.DecodePlan(weights.layers, self.k_cache, self.v_cache, c.hidden, c.q_heads, c.kv_heads, c.intermediate,
                                            c.eps, weights.rope)
+                if exchange:
+                    self._exchange = self._make_exchange(weights.tp, weights.rank, c.hidden)
+                    self.plan.set_peers(*self._exchange[:2], weights.rank, weights.tp)
             except capi.W8A8Error as error:
                 if error.status != 3:  # W8A8_ERR_UNSUPPORTED: this shape stays on the launch-per-operator path
                     raise
+                self.plan = None
         self._host_control = torch.zeros(2, dtype=torch.int32).pin_memory()
         self._host_next = torch.zeros(1, dtype=torch.int32).pin_memory()
         # batched decode: one row per sequence
@@ -279,6 +288,24 @@ class Qwen3Runner:
             self._make_batch_buffers()
 
     PEER_MAX_ROWS = 64  # w8a8_linear_allreduce takes decode-sized launches only
+
+    def _make_exchange(self, tp: int, rank: int, hidden: int):
+        """Packet buffers of the resident decode kernel's exchanges: [2 halves][tp sources][hidden] packets of 8 bytes per
+        rank, in symmetric memory when there are peers.  Returns (addresses by rank, seq word, what must stay alive)."""
+        device = torch.device("cuda", torch.cuda.current_device())
+        seq = torch.zeros(4, dtype=torch.int32, device=device)
+        if tp == 1:
+            buf = torch.zeros(2 * hidden * 2, dtype=torch.int32, device=device)
+            return [buf.data_ptr()], seq, buf
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        buf = symm.empty(2 * tp * hidden * 2, dtype=torch.int32, device=device)
+        handle = symm.rendezvous(buf, self.group.group_name if hasattr(self.group, "group_name") else self.group)
+        buf.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        return [int(p) for p in handle.buffer_ptrs], seq, (buf, handle)
 
     def _make_batch_buffers(self) -> None:
         c, w, device, rows = self.c, self.w, self.device, self.batch

@@ -127,3 +127,29 @@ def test_cycle_trace_of_the_last_step(monkeypatch):
     assert t.shape[1] == 3 and t.shape[2] == 16 and (t > 0).all()
     flat = t.reshape(t.shape[0], -1)
     assert (np.diff(flat, axis=1) >= 0).all()
+
+
+@pytest.mark.parametrize("cfg,prompt_len,steps", [CASES[1], CASES[3]])
+def test_resident_step_with_the_exchange_as_a_group_of_one(cfg, prompt_len, steps):
+    """The tensor-parallel form of the kernel (partial outputs of O and down sent as tagged packets, summed over the ranks
+    in the next prologue, hidden and residual rows kept in shared memory) run on one GPU with itself as the only rank:
+    the sum over one rank is the value itself, so the result must equal the single-GPU kernels' bit for bit."""
+    import torch
+
+    from inferrous_b200 import ops
+    from inferrous_b200.qwen3 import Qwen3Runner, Qwen3Weights
+
+    c = config(**cfg)
+    weights = Qwen3Weights.random(c, seed=13)
+    prompt = [int(t) for t in np.random.default_rng(1).integers(0, c.vocab, prompt_len)]
+    separate = Qwen3Runner(weights, resident=False)
+    expected, _ = separate.generate(prompt, steps, use_graph=False)
+    runner = Qwen3Runner(weights, resident=True, resident_exchange=True)
+    assert runner.plan is not None and runner._exchange is not None
+    for use_graph in (False, True):
+        assert runner.generate(prompt, steps, use_graph=use_graph)[0] == expected
+        assert torch.equal(runner.decode.hidden, separate.decode.hidden)
+        n = prompt_len + steps - 1
+        for layer in range(c.layers):
+            assert torch.equal(runner.k_cache[layer][:n], separate.k_cache[layer][:n]), layer
+    assert ops.device_status() == (0, 0)

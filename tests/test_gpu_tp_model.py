@@ -85,6 +85,8 @@ def test_two_rank_generation_against_one_gpu():
     assert ranks[0]["tokens_tp"] == ranks[0]["tokens_tp_eager"]           # graph replay == eager launches
     assert ranks[0]["tokens_tp"] == ranks[0]["tokens_nccl"]               # fused projection + all-reduce == NCCL + residual (2 ranks)
     assert all(r["fused_exact"] for r in ranks)                           # ... and bit-exact against a sum in rank order
+    # the resident decode kernel with the exchange inside == one launch per operator with the fused projection + all-reduce
+    assert all(r["tokens_launches"] == r["tokens_tp"] and r["resident_exact"] for r in ranks)
     assert all(0 <= t < 1024 for t in ranks[0]["tokens_tp"])
     # the reference's whole-model gate for a changed summation: relative L2 <= 5 %, cosine >= 0.999 (tools/reference.py)
     assert ranks[0]["logit_rel_l2"] <= 0.05 and ranks[0]["logit_cosine"] >= 0.999

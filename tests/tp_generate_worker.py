@@ -33,8 +33,15 @@ def main() -> None:
     steps = int(sys.argv[2])
     group = dist.group.WORLD
 
-    tokens_tp, _ = Qwen3Runner(shard, group=group).generate(prompt, steps)                     # fused projection + all-reduce
+    # the decode step as one resident kernel per rank, the partial outputs of O and down exchanged as packets inside it
+    resident = Qwen3Runner(shard, group=group)
+    tokens_tp, _ = resident.generate(prompt, steps)
+    hidden_resident = resident.decode.hidden.clone()
     tokens_eager, _ = Qwen3Runner(shard, group=group).generate(prompt, steps, use_graph=False)
+    # the same step as one launch per operator, O and down with the all-reduce fused into the projection: same bits
+    launches = Qwen3Runner(shard, group=group, resident=False)
+    tokens_launches, _ = launches.generate(prompt, steps)
+    resident_exact = resident.plan is not None and launches.plan is None and bool(torch.equal(hidden_resident, launches.decode.hidden))
     tokens_nccl, _ = Qwen3Runner(shard, group=group, fused_allreduce=False).generate(prompt, steps)
 
     # the fused projection + all-reduce against projection, gathered partials and a sum in rank order, bit for bit
@@ -86,7 +93,7 @@ def main() -> None:
 
     logits_tp = prompt_logits(shard, group)
     result = {"rank": rank, "tp": tp, "tokens_tp": tokens_tp, "tokens_tp_eager": tokens_eager, "tokens_nccl": tokens_nccl,
-              "fused_exact": fused_exact, "batch_tokens": batch_tokens, "batch_eager": batch_eager, "batch_nccl": batch_nccl,
+              "fused_exact": fused_exact, "tokens_launches": tokens_launches, "resident_exact": resident_exact, "batch_tokens": batch_tokens, "batch_eager": batch_eager, "batch_nccl": batch_nccl,
               "batch_alone": batch_alone}
     if rank == 0:
         tokens_single, _ = Qwen3Runner(full).generate(prompt, steps)
