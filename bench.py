@@ -772,14 +772,20 @@ def model_generation_table(torch, hbm_peak, rank=0, world=1, group=None, fused_a
     torch.cuda.empty_cache()
     table = {"model": "Qwen3-8B architecture, random-init W8A8 weights (body and head int8), batch 1, greedy",
              "parallelism": f"tp{world}" if world > 1 else "single", "all_reduce": exchange,
-             "decode_step": ("one resident cooperative kernel for all layers (qwen3_decode_layers) + head" if resident
+             "decode_step": (("one resident cooperative kernel for all layers (qwen3_decode_layers) + head"
+                              + (", the O / down partial outputs exchanged as packets over peer memory inside it" if world > 1 else ""))
+                             if resident
                              else "one launch per operator, CUDA graph with programmatic edges"),
              "weight_bytes_per_token": config.weight_bytes(), "runs": rows}
     if resident:  # the same step as one launch per operator, for comparison
-        other = Qwen3Runner(weights, resident=False)
+        other = Qwen3Runner(weights, group=group, fused_allreduce=fused_allreduce and not exchange.startswith("NCCL"), resident=False)
         prompt = [int(t) for t in np.random.default_rng(0).integers(0, config.vocab, 129)]
         other.generate(prompt, 32)
         _, seconds = other.generate(prompt, 32)
+        if world > 1:
+            slowest = torch.tensor(seconds, dtype=torch.float64, device="cuda")
+            dist.all_reduce(slowest, op=dist.ReduceOp.MAX, group=group)
+            seconds = slowest.tolist()
         median = float(np.median(seconds[1:]))
         table["separate_launches"] = {"prompt": 129, "generated": 32, "decode_ms_per_token_median": round(median * 1e3, 4),
                                       "decode_tok_s": round(len(seconds[1:]) / sum(seconds[1:]), 1)}

@@ -617,37 +617,62 @@ struct StepSharedTp {
 };
 
 // Waits (bounded) for the packets of `exchange` from every rank and leaves out[e] = bf16(in[e] + bf16(sum_r y_r[e])).
+// Thread t owns elements t, t + 512, ...; its packets (element-major, rank fastest) are taken sixteen at a time: all that
+// are still missing are requested together, again and again until every tag is the exchange's, so the wait costs the
+// time the last packet needs to arrive plus one round trip, not one round trip per packet.
 __device__ __forceinline__ bool gather_exchange(const StepDev &a, uint32_t exchange, uint32_t tag, const float *in, float *out,
                                                 uint32_t *ok_smem, int tid) {
     const uint2 *base = a.ll[a.rank] + (size_t)(exchange & 1u) * a.tp * a.hidden;
+    constexpr int kBatch = 16;
+    const int packets = ((a.hidden + kThreads - 1) / kThreads) * a.tp;
     bool good = true;
-    for (int e = tid; e < a.hidden && good; e += kThreads) {
-        float sum = 0.0f;
-        for (int r = 0; r < a.tp && good; ++r) {
-            const uint2 *p = base + (size_t)r * a.hidden + e;
-            uint2 v;
-            unsigned long long t0 = 0;
-            for (uint32_t spin = 1;; ++spin) {
-                asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-                if (v.y == tag) break;
-                if ((spin & 255u) == 0) {
-                    uint32_t stop;
-                    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(stop) : "l"(a.sync + 1) : "memory");
-                    const unsigned long long now = global_ns();
-                    if (t0 == 0) t0 = now;
-                    if (stop || now - t0 > kWaitLimitNs) {
-                        if (!stop) {
-                            atomicExch(a.sync + 1, 1u);
-                            if (a.status && atomicCAS(a.status, 0u, (uint32_t)WAIT_PEER) == 0u) a.status[1] = (uint32_t)r;
-                        }
-                        good = false;
-                        break;
+    float sum = 0.0f;
+    for (int first = 0; first < packets && good; first += kBatch) {
+        uint2 v[kBatch];
+        uint32_t missing = 0;
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            const int idx = first + b, k = idx / a.tp;
+            if (idx < packets && tid + k * kThreads < a.hidden) missing |= 1u << b;
+        }
+        unsigned long long t0 = 0;
+        for (uint32_t spin = 1; missing; ++spin) {
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+                const int idx = first + b, k = idx / a.tp, r = idx - k * a.tp, e = tid + k * kThreads;
+                if (missing >> b & 1u)
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
+                                 : "=r"(v[b].x), "=r"(v[b].y)
+                                 : "l"(base + (size_t)r * a.hidden + e)
+                                 : "memory");
+            }
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b)
+                if ((missing >> b & 1u) && v[b].y == tag) missing &= ~(1u << b);
+            if (missing && (spin & 63u) == 0) {
+                uint32_t stop;
+                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(stop) : "l"(a.sync + 1) : "memory");
+                const unsigned long long now = global_ns();
+                if (t0 == 0) t0 = now;
+                if (stop || now - t0 > kWaitLimitNs) {
+                    if (!stop) {
+                        atomicExch(a.sync + 1, 1u);
+                        if (a.status && atomicCAS(a.status, 0u, (uint32_t)WAIT_PEER) == 0u) a.status[1] = missing;
                     }
+                    good = false;
+                    break;
                 }
             }
-            sum = __fadd_rn(sum, __uint_as_float(v.x));
         }
-        if (good) out[e] = bf16_rne(__fadd_rn(in[e], bf16_rne(sum)));
+        if (!good) break;
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            const int idx = first + b, k = idx / a.tp, r = idx - k * a.tp, e = tid + k * kThreads;
+            if (idx < packets && e < a.hidden) {
+                sum = r == 0 ? __uint_as_float(v[b].x) : __fadd_rn(sum, __uint_as_float(v[b].x));  // rank order; 0 + y0 = y0
+                if (r == a.tp - 1) out[e] = bf16_rne(__fadd_rn(in[e], bf16_rne(sum)));
+            }
+        }
     }
     if (tid == 0) *ok_smem = 1;
     __syncthreads();
@@ -667,7 +692,7 @@ __device__ __forceinline__ float prologue_rmsnorm_shared(const float *x, const t
 
 enum { BAR_TP_ATTENTION = 1, BAR_TP_O = 2, BAR_TP_DOWN = 3, kBarriersPerLayerTp = 3 };
 
-template <class T>
+template <class T, bool TRACE>
 __global__ void __launch_bounds__(kThreads, 1) decode_layers_tp_kernel(const StepDev a) {
     typedef typename T::storage S;
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -685,46 +710,66 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_tp_kernel(const Ste
     for (int j = tid; j < a.hidden; j += kThreads) tp.hidden[j] = load_one_cg<T>(static_cast<const S *>(a.hidden_io) + j);
     __syncthreads();
     const auto ordinal = [](int l, int which) { return (uint32_t)(l * kBarriersPerLayerTp + which); };
+    long long *trace = TRACE && a.trace && tid == 0 ? a.trace + (size_t)blockIdx.x * a.n_layers * kTracePoints : nullptr;
     for (int l = 0; l < a.n_layers; ++l) {
         const LayerDev L = a.layers[l];
+        auto mark = [&](int point) {
+            if (TRACE && trace) trace[l * kTracePoints + point] = clock64();
+        };
         const uint32_t x_o = 2u * l, x_down = 2u * l + 1u;  // the layer's two exchanges
+        mark(TP_START);
         // norm1 + quantize -> this rank's Q|K|V heads
         float s = prologue_rmsnorm_shared<T>(tp.hidden, static_cast<const S *>(L.norm1), a.eps, a.hidden, sh.codes, sh.row, sh.ps, tid);
         __syncthreads();
+        mark(TP_NORM1);
         project_any<T, PRJ_PLAIN>(a, L.qkv, nullptr, L.qkv_s, nullptr, qkv_width, a.hidden, s, sh.codes, sh.red, nullptr,
                                   static_cast<S *>(a.qkv), tid);
+        mark(TP_QKV);
+        mark(TP_ARRIVE1);
         if (!grid_barrier(a, ordinal(l, BAR_TP_ATTENTION), &sh.ok, [&](int i, int n) {
                 request_cache(a, L, end, i, n);
                 request_rows(L.o, q_width, a.hidden, 0, 1ll << 40, i, n);
             }))
             return;
+        mark(TP_PASS1);
         attention_phase<T>(a, L, sh.units, end, tid);
+        mark(TP_ATTENTION);
         if (!grid_barrier(a, ordinal(l, BAR_TP_O), &sh.ok, [&](int i, int n) {
                 request_rows(L.gate, a.hidden, a.inter, 0, a.ahead_bytes, i, n);
                 request_rows(L.up, a.hidden, a.inter, 0, a.ahead_bytes, i, n);
             }))
             return;
+        mark(TP_PASS2);
         // quantize(this rank's attention heads) -> partial O, sent to every rank
         s = prologue_plain<T>(static_cast<const S *>(a.attn), q_width, sh.codes, sh.row, sh.ps, tid);
         __syncthreads();
+        mark(TP_QUANT_O);
         project_any<T, PRJ_PUSH>(a, L.o, nullptr, L.o_s, nullptr, a.hidden, q_width, s, sh.codes, sh.red, nullptr, nullptr, tid, x_o,
                                  tag0 + x_o);
+        mark(TP_O);
         if (!gather_exchange(a, x_o, tag0 + x_o, tp.hidden, tp.residual, &sh.ok, tid)) return;
+        mark(TP_PASS3);
         // norm2 + quantize -> this rank's gate|up channels + SwiGLU
         s = prologue_rmsnorm_shared<T>(tp.residual, static_cast<const S *>(L.norm2), a.eps, a.hidden, sh.codes, sh.row, sh.ps, tid);
         __syncthreads();
+        mark(TP_NORM2);
         project_any<T, PRJ_SWIGLU>(a, L.gate, L.up, L.gate_s, L.up_s, a.inter, a.hidden, s, sh.codes, sh.red, nullptr,
                                    static_cast<S *>(a.act), tid);
+        mark(TP_GATE_UP);
         if (!grid_barrier(a, ordinal(l, BAR_TP_DOWN), &sh.ok,
                           [&](int i, int n) { request_rows(L.down, a.inter, a.hidden, 0, a.ahead_bytes, i, n); }))
             return;
+        mark(TP_PASS4);
         // quantize(this rank's act channels) -> partial down, sent to every rank
         s = prologue_plain<T>(static_cast<const S *>(a.act), a.inter, sh.codes, sh.row, sh.ps, tid);
         __syncthreads();
+        mark(TP_QUANT_DOWN);
         project_any<T, PRJ_PUSH>(a, L.down, nullptr, L.down_s, nullptr, a.hidden, a.inter, s, sh.codes, sh.red, nullptr, nullptr, tid,
                                  x_down, tag0 + x_down);
+        mark(TP_DOWN);
         if (l + 1 < a.n_layers) request_rows(a.layers[l + 1].qkv, a.hidden, qkv_width, 0, a.ahead_bytes, tid, kThreads);
         if (!gather_exchange(a, x_down, tag0 + x_down, tp.residual, tp.hidden, &sh.ok, tid)) return;
+        mark(TP_PASS5);
     }
     if (blockIdx.x == 0) {
         for (int j = tid; j < a.hidden; j += kThreads) T::store(static_cast<S *>(a.hidden_io) + j, tp.hidden[j]);
@@ -776,8 +821,10 @@ cudaError_t init_decode_layers() {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_kernel<Bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_kernel<F32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     const int smem_tp = (int)sizeof(StepSharedTp);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_tp_kernel<Bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tp);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_tp_kernel<F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tp);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_tp_kernel<Bf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tp);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_tp_kernel<F32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tp);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_tp_kernel<Bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tp);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_layers_tp_kernel<F32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tp);
     return e;
 }
 }  // namespace w8a8
@@ -947,7 +994,12 @@ int qwen3_decode_layers(qwen3_decode_plan_t plan, void *hidden, const uint32_t *
     const bool bf16 = plan->dtype == W8A8_BF16;
     if (plan->dev.tp > 0) {
         cfg.dynamicSmemBytes = sizeof(StepSharedTp);
-        e = bf16 ? cudaLaunchKernelEx(&cfg, decode_layers_tp_kernel<Bf16>, args) : cudaLaunchKernelEx(&cfg, decode_layers_tp_kernel<F32>, args);
+        if (plan->trace)
+            e = bf16 ? cudaLaunchKernelEx(&cfg, decode_layers_tp_kernel<Bf16, true>, args)
+                     : cudaLaunchKernelEx(&cfg, decode_layers_tp_kernel<F32, true>, args);
+        else
+            e = bf16 ? cudaLaunchKernelEx(&cfg, decode_layers_tp_kernel<Bf16, false>, args)
+                     : cudaLaunchKernelEx(&cfg, decode_layers_tp_kernel<F32, false>, args);
     } else if (plan->trace)
         e = bf16 ? cudaLaunchKernelEx(&cfg, decode_layers_kernel<Bf16, true>, args) : cudaLaunchKernelEx(&cfg, decode_layers_kernel<F32, true>, args);
     else
