@@ -82,7 +82,8 @@ struct StepDev {
     // summed over the ranks through packet buffers in peer memory
     uint2 *ll[kTpMaxRanks];     // packet buffer of every rank: [2 halves][tp sources][hidden] packets {value bits, tag}
     uint32_t *seq;              // local: [0] = exchanges completed by earlier steps (the tag base of this step)
-    int rank, tp;
+    float *reduced;             // [hidden]: the summed row of an exchange, sliced form (below)
+    int rank, tp, sliced;
 };
 
 // Points of a layer at which thread 0 of every CTA notes its SM's cycle counter when the plan carries a trace buffer.
@@ -681,6 +682,61 @@ __device__ __forceinline__ bool gather_exchange(const StepDev &a, uint32_t excha
     return *ok_smem != 0;
 }
 
+// The same exchange in two stages, for many ranks: read directly, every CTA fetches hidden x tp packets from L2 (256 KiB
+// at 8 ranks, 38 MB per exchange over the GPU).  Here a CTA sums only its slice of the row (one thread per element, the
+// element's tp packets requested together), writes the result to `reduced`, the GPU's CTAs meet at a grid-wide barrier and
+// everyone reads the finished row: one more barrier, an eighth of the reads.
+__device__ __forceinline__ bool gather_exchange_sliced(const StepDev &a, uint32_t exchange, uint32_t tag, const float *in, float *out,
+                                                       uint32_t barrier, uint32_t *ok_smem, int tid) {
+    const uint2 *base = a.ll[a.rank] + (size_t)(exchange & 1u) * a.tp * a.hidden;
+    int e0, e1;
+    cta_rows(a.hidden, e0, e1);
+    bool good = true;
+    for (int e = e0 + tid; e < e1; e += kThreads) {
+        uint2 v[kTpMaxRanks];
+        uint32_t missing = (1u << a.tp) - 1u;
+        unsigned long long t0 = 0;
+        for (uint32_t spin = 1; missing; ++spin) {
+#pragma unroll
+            for (int r = 0; r < kTpMaxRanks; ++r)
+                if (missing >> r & 1u)
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
+                                 : "=r"(v[r].x), "=r"(v[r].y)
+                                 : "l"(base + (size_t)r * a.hidden + e)
+                                 : "memory");
+#pragma unroll
+            for (int r = 0; r < kTpMaxRanks; ++r)
+                if ((missing >> r & 1u) && v[r].y == tag) missing &= ~(1u << r);
+            if (missing && (spin & 63u) == 0) {
+                uint32_t stop;
+                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(stop) : "l"(a.sync + 1) : "memory");
+                const unsigned long long now = global_ns();
+                if (t0 == 0) t0 = now;
+                if (stop || now - t0 > kWaitLimitNs) {
+                    if (!stop) {
+                        atomicExch(a.sync + 1, 1u);
+                        if (a.status && atomicCAS(a.status, 0u, (uint32_t)WAIT_PEER) == 0u) a.status[1] = missing;
+                    }
+                    good = false;
+                    break;
+                }
+            }
+        }
+        if (!good) break;
+        float sum = __uint_as_float(v[0].x);  // rank order; 0 + y0 = y0
+#pragma unroll
+        for (int r = 1; r < kTpMaxRanks; ++r)
+            if (r < a.tp) sum = __fadd_rn(sum, __uint_as_float(v[r].x));
+        a.reduced[e] = bf16_rne(__fadd_rn(in[e], bf16_rne(sum)));
+    }
+    if (__syncthreads_or(!good)) return false;  // the abort word is up: the other CTAs leave at the barrier
+    if (!grid_barrier(a, barrier, ok_smem, [](int, int) {})) return false;
+    for (int j = tid * 4; j < a.hidden; j += kThreads * 4)
+        *reinterpret_cast<float4 *>(out + j) = __ldcg(reinterpret_cast<const float4 *>(a.reduced + j));
+    __syncthreads();
+    return true;
+}
+
 // norm_quantize of a row that is already in shared memory
 template <class T>
 __device__ __forceinline__ float prologue_rmsnorm_shared(const float *x, const typename T::storage *gain, float eps, int K, int8_t *sq,
@@ -690,7 +746,6 @@ __device__ __forceinline__ float prologue_rmsnorm_shared(const float *x, const t
     return rmsnorm_row<T>(gain, eps, K, sq, row, ps, tid);
 }
 
-enum { BAR_TP_ATTENTION = 1, BAR_TP_O = 2, BAR_TP_DOWN = 3, kBarriersPerLayerTp = 3 };
 
 template <class T, bool TRACE>
 __global__ void __launch_bounds__(kThreads, 1) decode_layers_tp_kernel(const StepDev a) {
@@ -709,7 +764,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_tp_kernel(const Ste
     const uint32_t tag0 = *reinterpret_cast<const volatile uint32_t *>(a.seq) + 1u;  // tag of this step's first exchange
     for (int j = tid; j < a.hidden; j += kThreads) tp.hidden[j] = load_one_cg<T>(static_cast<const S *>(a.hidden_io) + j);
     __syncthreads();
-    const auto ordinal = [](int l, int which) { return (uint32_t)(l * kBarriersPerLayerTp + which); };
+    // the layer's barriers in step order: attention, O, (sliced exchange of O), down, (sliced exchange of down)
+    const int per_layer = a.sliced ? 5 : 3;
+    const int BAR_TP_ATTENTION = 1, BAR_TP_O = 2, BAR_TP_XO = 3, BAR_TP_DOWN = a.sliced ? 4 : 3, BAR_TP_XDOWN = 5;
+    const auto ordinal = [per_layer](int l, int which) { return (uint32_t)(l * per_layer + which); };
     long long *trace = TRACE && a.trace && tid == 0 ? a.trace + (size_t)blockIdx.x * a.n_layers * kTracePoints : nullptr;
     for (int l = 0; l < a.n_layers; ++l) {
         const LayerDev L = a.layers[l];
@@ -747,7 +805,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_tp_kernel(const Ste
         project_any<T, PRJ_PUSH>(a, L.o, nullptr, L.o_s, nullptr, a.hidden, q_width, s, sh.codes, sh.red, nullptr, nullptr, tid, x_o,
                                  tag0 + x_o);
         mark(TP_O);
-        if (!gather_exchange(a, x_o, tag0 + x_o, tp.hidden, tp.residual, &sh.ok, tid)) return;
+        if (a.sliced ? !gather_exchange_sliced(a, x_o, tag0 + x_o, tp.hidden, tp.residual, ordinal(l, BAR_TP_XO), &sh.ok, tid)
+                     : !gather_exchange(a, x_o, tag0 + x_o, tp.hidden, tp.residual, &sh.ok, tid))
+            return;
         mark(TP_PASS3);
         // norm2 + quantize -> this rank's gate|up channels + SwiGLU
         s = prologue_rmsnorm_shared<T>(tp.residual, static_cast<const S *>(L.norm2), a.eps, a.hidden, sh.codes, sh.row, sh.ps, tid);
@@ -768,7 +828,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_tp_kernel(const Ste
                                  x_down, tag0 + x_down);
         mark(TP_DOWN);
         if (l + 1 < a.n_layers) request_rows(a.layers[l + 1].qkv, a.hidden, qkv_width, 0, a.ahead_bytes, tid, kThreads);
-        if (!gather_exchange(a, x_down, tag0 + x_down, tp.residual, tp.hidden, &sh.ok, tid)) return;
+        if (a.sliced ? !gather_exchange_sliced(a, x_down, tag0 + x_down, tp.residual, tp.hidden, ordinal(l, BAR_TP_XDOWN), &sh.ok, tid)
+                     : !gather_exchange(a, x_down, tag0 + x_down, tp.residual, tp.hidden, &sh.ok, tid))
+            return;
         mark(TP_PASS5);
     }
     if (blockIdx.x == 0) {
@@ -893,7 +955,8 @@ int qwen3_decode_plan_create(const qwen3_layer_desc *layers, int n_layers, int h
     const size_t b_attn = round_up((size_t)q_width * el, 256), b_act = round_up((size_t)intermediate * el, 256);
     const size_t b_scratch = round_up((size_t)q_heads * splits * kUnitRecord * sizeof(float), 256);
     p->clear_bytes = round_up(16 + (size_t)q_heads * sizeof(uint32_t), 16);  // barrier words, then the attention counters
-    const size_t total = b_hidden + b_qkv + b_attn + b_act + b_scratch + round_up(p->clear_bytes, 256);
+    const size_t b_reduced = round_up((size_t)hidden * sizeof(float), 256);
+    const size_t total = b_hidden + b_qkv + b_attn + b_act + b_scratch + b_reduced + round_up(p->clear_bytes, 256);
     e = cudaMalloc(&p->work, total);
     if (e == cudaSuccess) e = cudaMemset(p->work, 0, total);
     if (e == cudaSuccess) e = cudaMalloc(&p->layers_dev, table.size() * sizeof(LayerDev));
@@ -914,10 +977,11 @@ int qwen3_decode_plan_create(const qwen3_layer_desc *layers, int n_layers, int h
     s.attn = at; at += b_attn;
     s.act = at; at += b_act;
     s.scratch = reinterpret_cast<float *>(at); at += b_scratch;
+    s.reduced = reinterpret_cast<float *>(at); at += b_reduced;
     s.sync = reinterpret_cast<uint32_t *>(at);
     s.counters = s.sync + 4;
     s.status = device_status_ptr();
-    s.seq = nullptr; s.rank = 0; s.tp = 0;
+    s.seq = nullptr; s.rank = 0; s.tp = 0; s.sliced = 0;
     for (int r = 0; r < kTpMaxRanks; ++r) s.ll[r] = nullptr;
     s.trace = nullptr;
     if (env_int("W8A8_DECODE_TRACE", 0)) {
@@ -956,6 +1020,8 @@ int qwen3_decode_plan_set_peers(qwen3_decode_plan_t plan, void *const *packet_bu
     StepDev &s = plan->dev;
     for (int r = 0; r < kTpMaxRanks; ++r) s.ll[r] = r < tp ? static_cast<uint2 *>(packet_buffers[r]) : nullptr;
     s.seq = seq; s.rank = rank; s.tp = tp;
+    // from four ranks on a CTA sums only its slice of an exchanged row (gather_exchange_sliced); W8A8_DECODE_SLICED=0/1 forces either
+    s.sliced = env_int("W8A8_DECODE_SLICED", tp >= 4 ? 1 : 0) != 0;
     return W8A8_OK;
 }
 

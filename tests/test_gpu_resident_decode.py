@@ -129,12 +129,16 @@ def test_cycle_trace_of_the_last_step(monkeypatch):
     assert (np.diff(flat, axis=1) >= 0).all()
 
 
+@pytest.mark.parametrize("sliced", [0, 1])
 @pytest.mark.parametrize("cfg,prompt_len,steps", [CASES[1], CASES[3]])
-def test_resident_step_with_the_exchange_as_a_group_of_one(cfg, prompt_len, steps):
+def test_resident_step_with_the_exchange_as_a_group_of_one(cfg, prompt_len, steps, sliced, monkeypatch):
     """The tensor-parallel form of the kernel (partial outputs of O and down sent as tagged packets, summed over the ranks
     in the next prologue, hidden and residual rows kept in shared memory) run on one GPU with itself as the only rank:
-    the sum over one rank is the value itself, so the result must equal the single-GPU kernels' bit for bit."""
+    the sum over one rank is the value itself, so the result must equal the single-GPU kernels' bit for bit.  sliced = 1:
+    the form used from four ranks on (a CTA sums its slice of the row, a barrier, everyone reads the summed row)."""
     import torch
+
+    monkeypatch.setenv("W8A8_DECODE_SLICED", str(sliced))
 
     from inferrous_b200 import ops
     from inferrous_b200.qwen3 import Qwen3Runner, Qwen3Weights
