@@ -128,7 +128,7 @@ def test_norm_quantize_fixtures(ops, fixtures, carrier):
         assert torch.equal(q, q2) and torch.equal(s, s2)
 
 
-@pytest.mark.parametrize("M,K", [(1, 4096), (16, 4096), (129, 4096), (512, 4096)])
+@pytest.mark.parametrize("M,K", [(1, 4096), (16, 4096), (129, 4096), (512, 4096), (4096, 4096)])
 def test_norm_quantize_synthetic(ops, M, K):
     import torch
 
@@ -166,7 +166,7 @@ def test_swiglu_fixture_and_maxima(ops, fixtures, carrier):
 
 
 @pytest.mark.parametrize("carrier", CARRIERS)
-@pytest.mark.parametrize("M,I", [(1, 12288), (5, 12288), (129, 12288), (3, 128)])
+@pytest.mark.parametrize("M,I", [(1, 12288), (5, 12288), (129, 12288), (3, 128), (512, 12288), (4096, 12288)])
 def test_swiglu_quantize_equals_separate(ops, carrier, M, I):
     """Fused SwiGLU+quantize == `swiglu` then `quantize` bit for bit; act within the numeric gate of the oracle;
     also with gate|up interleaved as one [M,2I] buffer."""
