@@ -71,6 +71,14 @@ def test_argument_validation_needs_no_gpu(lib):
     # the operators around the linear layers refuse to run before w8a8_init()
     assert lib.qwen3_embedding(None, None, 1, 4096, 10, None, 0, None) == 6
     assert lib.qwen3_attention(None, 0, 4096, 1, 32, 8, None, None, None, None, 4096, 4096, None, None) == 6
+    # the resident decode kernel's plan: nothing without w8a8_init(), no plan from a null handle
+    out = ctypes.c_void_p()
+    assert lib.qwen3_decode_plan_create(None, 1, 256, 4, 2, 512, 64, 1e-6, None, 0, ctypes.byref(out)) == 6
+    assert lib.qwen3_decode_layers(None, None, None, None) == 1
+    assert lib.qwen3_decode_plan_set_peers(None, None, None, 0, 1) == 1
+    n = ctypes.c_int()
+    assert lib.qwen3_decode_plan_trace(None, None, 0, ctypes.byref(n), ctypes.byref(n), ctypes.byref(n)) == 1
+    assert lib.qwen3_decode_plan_destroy(None) == 0
 
 
 def test_overlapping_operands_are_rejected_on_the_host(lib):
