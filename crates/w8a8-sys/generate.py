@@ -11,7 +11,7 @@ TYPES = {
  'const uint16_t *': '*const u16', 'uint16_t *': '*mut u16', 'int32_t *': '*mut i32', 'int *': '*mut c_int',
  'w8a8_weight_t': '*mut W8a8Weight', 'w8a8_weight_t *': '*mut *mut W8a8Weight', 'const w8a8_weight_t *': '*const *mut W8a8Weight',
  'void *const *': '*const *mut c_void', 'uint32_t *const *': '*const *mut u32', 'const char *': '*const c_char',
- 'int64_t *': '*mut i64',
+ 'int64_t *': '*mut i64', 'size_t *': '*mut usize',
  'const qwen3_layer_desc *': '*const Qwen3LayerDesc', 'qwen3_decode_plan_t': '*mut Qwen3DecodePlan',
  'qwen3_decode_plan_t *': '*mut *mut Qwen3DecodePlan', 'const struct w8a8_weight *': '*const W8a8Weight',
 }

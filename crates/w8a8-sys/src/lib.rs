@@ -79,6 +79,7 @@ extern "C" {
     pub fn w8a8_weight_create(w: *const i8, w_scale: *const f32, n: c_int, k: c_int, out: *mut *mut W8a8Weight) -> c_int;
     pub fn w8a8_weight_destroy(weight: *mut W8a8Weight) -> c_int;
     pub fn w8a8_weight_shape(weight: *mut W8a8Weight, n: *mut c_int, k: *mut c_int) -> c_int;
+    pub fn w8a8_workspace_bytes(max_rows: c_int, hidden: c_int, q_width: c_int, intermediate: c_int, offsets: *mut usize) -> usize;
     pub fn w8a8_quantize(x: *const c_void, dtype: c_int, m: c_int, k: c_int, ldx: i64, q: *mut i8, scale: *mut f32, stream: *mut c_void) -> c_int;
     pub fn w8a8_quantize_with_max(x: *const c_void, dtype: c_int, maxima: *const u32, m: c_int, k: c_int, ldx: i64, q: *mut i8, scale: *mut f32, stream: *mut c_void) -> c_int;
     pub fn w8a8_rmsnorm_quantize(x: *const c_void, gamma: *const c_void, dtype: c_int, eps: f32, m: c_int, k: c_int, ldx: i64, q: *mut i8, scale: *mut f32, y_out: *mut c_void, maxima_reset: *mut u32, stream: *mut c_void) -> c_int;

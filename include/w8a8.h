@@ -112,6 +112,14 @@ int w8a8_weight_create(const int8_t *w, const float *w_scale, int N, int K, w8a8
 int w8a8_weight_destroy(w8a8_weight_t weight);
 int w8a8_weight_shape(w8a8_weight_t weight, int *N, int *K);
 
+/* Bytes of the hot path's share of the reference's Workspace (src/gpu.rs:76-143) for launches of up to `max_rows` rows:
+ * the int8 codes of the three activation widths (hidden, q_width = query heads x 128, intermediate), one f32 scale and
+ * one u32 absolute-maximum word per row, each region rounded up to 256 bytes, in that order.  `offsets` (optional, 5
+ * entries) receives the byte offset of each region in a single allocation of that size: codes[hidden], codes[q_width],
+ * codes[intermediate], scales, maxima.  Host arithmetic only: no CUDA call, no w8a8_init() needed.  0 on a non-positive
+ * argument. */
+size_t w8a8_workspace_bytes(int max_rows, int hidden, int q_width, int intermediate, size_t *offsets);
+
 /* ---- activation quantizers ---------------------------------------------------------- */
 
 /* `quantize` (src/kernels.rs:415-452; host wrapper src/gpu.rs:424-449):

@@ -24,6 +24,7 @@ SIGNATURES = {
     "w8a8_set_programmatic_launch": (_i, [_i]),
     "w8a8_prefetch_hint": (_i, [_vp, _sz]),
     "w8a8_device_status": (_i, [_vp, C.POINTER(C.c_uint32)]),
+    "w8a8_workspace_bytes": (_sz, [_i, _i, _i, _i, C.POINTER(_sz)]),
     "w8a8_weight_create": (_i, [_vp, _vp, _i, _i, C.POINTER(_vp)]),
     "w8a8_weight_destroy": (_i, [_vp]),
     "w8a8_weight_shape": (_i, [_vp, C.POINTER(_i), C.POINTER(_i)]),

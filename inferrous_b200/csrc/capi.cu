@@ -145,6 +145,19 @@ const char *w8a8_status_string(int status) {
 
 const char *w8a8_last_cuda_error(void) { return g_err; }
 
+size_t w8a8_workspace_bytes(int max_rows, int hidden, int q_width, int intermediate, size_t *offsets) {
+    if (max_rows <= 0 || hidden <= 0 || q_width <= 0 || intermediate <= 0) return 0;
+    const size_t rows = (size_t)max_rows;
+    const size_t region[5] = {rows * (size_t)hidden, rows * (size_t)q_width, rows * (size_t)intermediate, rows * sizeof(float),
+                              rows * sizeof(uint32_t)};
+    size_t at = 0;
+    for (int i = 0; i < 5; ++i) {
+        if (offsets) offsets[i] = at;
+        at += (region[i] + 255) / 256 * 256;
+    }
+    return at;
+}
+
 int w8a8_prefetch_hint(const void *weights, size_t bytes) {
     REQUIRE((weights != nullptr) == (bytes != 0), W8A8_ERR_BAD_ARG);
     if (!weights) {

@@ -71,6 +71,11 @@ def test_argument_validation_needs_no_gpu(lib):
     # the operators around the linear layers refuse to run before w8a8_init()
     assert lib.qwen3_embedding(None, None, 1, 4096, 10, None, 0, None) == 6
     assert lib.qwen3_attention(None, 0, 4096, 1, 32, 8, None, None, None, None, 4096, 4096, None, None) == 6
+    # workspace sizing is host arithmetic
+    offsets = (ctypes.c_size_t * 5)()
+    total = lib.w8a8_workspace_bytes(129, 4096, 4096, 12288, offsets)
+    assert list(offsets) == [0, 528384, 1056768, 2641920, 2642688] and total == 2643456
+    assert lib.w8a8_workspace_bytes(0, 4096, 4096, 12288, None) == 0
     # the resident decode kernel's plan: nothing without w8a8_init(), no plan from a null handle
     out = ctypes.c_void_p()
     assert lib.qwen3_decode_plan_create(None, 1, 256, 4, 2, 512, 64, 1e-6, None, 0, ctypes.byref(out)) == 6
