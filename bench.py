@@ -708,6 +708,15 @@ def decode_fused_table(torch, ops, hbm_peak):
              ("linear_residual O (16.8 MB)", lambda: ops.linear_residual(q4, s, wo, y, res, comb), 4096 * 4096, 11.94),
              ("linear_residual down (50.3 MB)", lambda: ops.linear_residual(q12, s, wd, y, res, comb), 4096 * 12288, 33.94),
              ("linear_triple QKV (25.2 MB)", lambda: ops.linear_grouped(q4, s, [wq, wk, wv], [oq, ok_, ov]), 6144 * 4096, 16.91)]
+    # the reference's own output head (bf16 weights, its summation order) with the greedy selection fused in, and the
+    # W8A8 head that BASELINE.json names: one row against [151936, 4096]
+    vocab = 151936
+    head_w = torch.empty((vocab, 4096), dtype=torch.bfloat16, device="cuda").normal_(0.0, 0.02)
+    head_x = torch.randn((1, 4096), device="cuda").to(torch.bfloat16)
+    token = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cases.append(("head, bf16 weights (1245 MB) + select_token", lambda: ops.head_bf16(head_x, head_w, token=token), 2 * vocab * 4096, None))
+    wh = mk(4096, vocab, 8)
+    cases.append(("head, W8A8 (622 MB) + select_token", lambda: ops.linear_argmax(q4, s, wh, token), vocab * 4096, None))
     rows = []
     for name, fn, wbytes, ref_us in cases:
         fn()

@@ -9,9 +9,14 @@
 // products of columns L, L + 32, L + 64, ... in that order (separately rounded multiply and add), then the 32 partial
 // sums meet in a shuffle-down tree of distances 16, 8, 4, 2, 1; the logit is bf16(sum).  The result is bit-identical to
 // `head` / `head_packed` on the same inputs.
-// What differs is how the bytes move: a warp works on two rows at once with 16 two-byte loads per row in flight per lane
-// (a warp-wide load covers 64 contiguous bytes; consecutive loads finish the 128-byte line), the activation row is
-// parked in shared memory once per CTA, and the greedy selection is fused in: a CTA of 8 warps leaves the best
+// What differs is who computes which partial sum.  The order only fixes how each of the 32 partial sums of a row is built
+// and how they are added up, not which thread holds them: here four threads share a row, each loads 16 bytes (eight
+// consecutive columns) per step of 32 columns and keeps the eight partial sums of those columns in registers, so a warp
+// works on eight rows per load instruction; the tree over the 32 partial sums is two exchanges between the four threads
+// and three levels inside a thread.  (One two-byte load per element and lane, the direct transcription, is bound by
+// instruction issue: 57.8 % of the issue slots and 43 % of the load/store pipe busy at 4.5 TB/s; widths that are not a
+// multiple of 32 still take that form.)  The activation row is parked in shared memory once per CTA, and the greedy
+// selection is fused in: a CTA of 8 warps leaves the best
 // (value, index) of its 16 rows as one packed key, which the reduction kernel of the W8A8 head finishes
 // (launch_argmax_finish), so the 151 936 logits need not be written.  Bound by the 1.24 GB stream of weights from HBM.
 #include "../../include/qwen3_glue.h"
@@ -104,13 +109,86 @@ __global__ void __launch_bounds__(kThreads) head_bf16_kernel(const typename T::s
     }
 }
 
+// K % 32 == 0, w 16-byte aligned: four threads per row (quad lane q holds the partial sums of columns 8 q .. 8 q + 7 of
+// every 32-column step), eight rows per warp, 64 per CTA.
+constexpr int kQuadRowsPerCta = 64;
+constexpr int kQuadLoads = 8;  // 16-byte loads in flight per thread
+
+template <class T>
+__global__ void __launch_bounds__(kThreads) head_bf16_quad_kernel(const typename T::storage *__restrict__ x, const uint16_t *__restrict__ w,
+                                                                  int K, int vocab, typename T::storage *__restrict__ logits,
+                                                                  unsigned long long *__restrict__ partial_best) {
+    extern __shared__ __align__(16) float xs[];  // [K]
+    __shared__ unsigned long long cand[kQuadRowsPerCta];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int q = lane & 3, in_warp = lane >> 2;
+    const int local = warp * 8 + in_warp;
+    const int row = blockIdx.x * kQuadRowsPerCta + local;
+    const uint16_t *wr = w + (size_t)min(row, vocab - 1) * K + 8 * q;  // rows beyond the vocabulary are computed and dropped
+    const int steps = K / 32;
+    uint4 v[kQuadLoads];
+    auto issue = [&](int first) {
+#pragma unroll
+        for (int u = 0; u < kQuadLoads; ++u) v[u] = first + u < steps ? ld_stream_16(wr + 32 * (first + u)) : make_uint4(0, 0, 0, 0);
+    };
+    issue(0);  // the first batch of weights does not depend on the preceding kernel
+    dependency_wait();
+    for (int j = tid; j < K; j += kThreads) xs[j] = T::load(x + j);
+    __syncthreads();
+    float p[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    for (int first = 0; first < steps; first += kQuadLoads) {
+#pragma unroll
+        for (int u = 0; u < kQuadLoads; ++u) {
+            if (first + u < steps) {  // partial sum of column c: products of c, c + 32, ... in that order (src/kernels.rs:2245-2249)
+                const float4 xa = *reinterpret_cast<const float4 *>(xs + 32 * (first + u) + 8 * q);
+                const float4 xb = *reinterpret_cast<const float4 *>(xs + 32 * (first + u) + 8 * q + 4);
+                p[0] = __fadd_rn(p[0], __fmul_rn(xa.x, __uint_as_float(v[u].x << 16)));
+                p[1] = __fadd_rn(p[1], __fmul_rn(xa.y, __uint_as_float(v[u].x & 0xffff0000u)));
+                p[2] = __fadd_rn(p[2], __fmul_rn(xa.z, __uint_as_float(v[u].y << 16)));
+                p[3] = __fadd_rn(p[3], __fmul_rn(xa.w, __uint_as_float(v[u].y & 0xffff0000u)));
+                p[4] = __fadd_rn(p[4], __fmul_rn(xb.x, __uint_as_float(v[u].z << 16)));
+                p[5] = __fadd_rn(p[5], __fmul_rn(xb.y, __uint_as_float(v[u].z & 0xffff0000u)));
+                p[6] = __fadd_rn(p[6], __fmul_rn(xb.z, __uint_as_float(v[u].w << 16)));
+                p[7] = __fadd_rn(p[7], __fmul_rn(xb.w, __uint_as_float(v[u].w & 0xffff0000u)));
+            }
+        }
+        if (first + kQuadLoads < steps) issue(first + kQuadLoads);
+    }
+    // the reference's tree over the 32 partial sums P[0..31] (src/kernels.rs:2250-2253): distances 16 and 8 pair
+    // partial sums of different quad lanes (q ^ 2, then q ^ 1), distances 4, 2, 1 pair sums inside quad lane 0
+#pragma unroll
+    for (int k = 0; k < 8; ++k) p[k] = __fadd_rn(p[k], __shfl_xor_sync(0xffffffffu, p[k], 2));
+#pragma unroll
+    for (int k = 0; k < 8; ++k) p[k] = __fadd_rn(p[k], __shfl_xor_sync(0xffffffffu, p[k], 1));
+    const float c0 = __fadd_rn(p[0], p[4]), c1 = __fadd_rn(p[1], p[5]), c2 = __fadd_rn(p[2], p[6]), c3 = __fadd_rn(p[3], p[7]);
+    const float sum = __fadd_rn(__fadd_rn(c0, c2), __fadd_rn(c1, c3));
+    if (q == 0) {
+        const float value = bf16_rne(sum);
+        if (logits && row < vocab) T::store(logits + row, value);
+        cand[local] = row < vocab ? argmax_key(value, (uint32_t)row) : 0ull;
+    }
+    if (partial_best == nullptr) return;
+    __syncthreads();
+    if (tid < 16) {  // slot layout of the W8A8 head's candidates: 16 keys per CTA
+        unsigned long long best = 0;
+        if (tid == 0) {
+#pragma unroll 8
+            for (int r = 0; r < kQuadRowsPerCta; ++r) best = max(best, cand[r]);
+        }
+        partial_best[(size_t)blockIdx.x * 16 + tid] = best;
+    }
+}
+
 bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 }  // namespace
 
 cudaError_t init_head_bf16() {
     cudaError_t e = cudaFuncSetAttribute(head_bf16_kernel<Bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    return e == cudaSuccess ? cudaFuncSetAttribute(head_bf16_kernel<F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) : e;
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(head_bf16_kernel<F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(head_bf16_quad_kernel<Bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(head_bf16_quad_kernel<F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    return e;
 }
 
 }  // namespace w8a8
@@ -128,16 +206,24 @@ extern "C" int qwen3_head_bf16(const void *x, int dtype, const uint16_t *w, int 
     REQUIRE(x && w && vocab > 0 && hidden > 0 && (logits || token), W8A8_ERR_BAD_ARG);
     REQUIRE(dtype == W8A8_BF16 || dtype == W8A8_F32, W8A8_ERR_BAD_ARG);
     REQUIRE(aligned(w, 2) && hidden <= 24576, W8A8_ERR_ALIGNMENT);
-    const int blocks = (vocab + kRowsPerCta - 1) / kRowsPerCta;
+    const bool quad = hidden % 32 == 0 && aligned(w, 16);  // four threads per row, 16-byte loads
+    const int per_cta = quad ? kQuadRowsPerCta : kRowsPerCta;
+    const int blocks = (vocab + per_cta - 1) / per_cta;
     REQUIRE(token == nullptr || blocks <= kArgmaxMaxBlocks, W8A8_ERR_UNSUPPORTED);
     unsigned long long *partial = token ? argmax_scratch() : nullptr;
     const size_t smem = (size_t)hidden * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    cudaError_t e = dtype == W8A8_BF16
-                        ? launch_kernel(head_bf16_kernel<Bf16>, dim3(blocks), dim3(kThreads), smem, s, (const uint16_t *)x, w, hidden, vocab,
-                                        (uint16_t *)logits, partial)
-                        : launch_kernel(head_bf16_kernel<F32>, dim3(blocks), dim3(kThreads), smem, s, (const float *)x, w, hidden, vocab,
-                                        (float *)logits, partial);
+    cudaError_t e;
+    if (quad)
+        e = dtype == W8A8_BF16 ? launch_kernel(head_bf16_quad_kernel<Bf16>, dim3(blocks), dim3(kThreads), smem, s, (const uint16_t *)x, w, hidden,
+                                               vocab, (uint16_t *)logits, partial)
+                               : launch_kernel(head_bf16_quad_kernel<F32>, dim3(blocks), dim3(kThreads), smem, s, (const float *)x, w, hidden,
+                                               vocab, (float *)logits, partial);
+    else
+        e = dtype == W8A8_BF16 ? launch_kernel(head_bf16_kernel<Bf16>, dim3(blocks), dim3(kThreads), smem, s, (const uint16_t *)x, w, hidden,
+                                               vocab, (uint16_t *)logits, partial)
+                               : launch_kernel(head_bf16_kernel<F32>, dim3(blocks), dim3(kThreads), smem, s, (const float *)x, w, hidden,
+                                               vocab, (float *)logits, partial);
     if (e != cudaSuccess) return fail_cuda(e, "head_bf16 launch");
     if (token) {
         e = launch_argmax_finish(partial, blocks, 1, token, value, s);

@@ -336,7 +336,7 @@ def test_head_bf16_fixture_and_reference_order(ops, fixtures, dtype):
     assert ops.device_status() == (0, 0)
 
 
-@pytest.mark.parametrize("vocab,hidden", [(1000, 4096), (151936, 4096), (17, 256), (640, 1024)])
+@pytest.mark.parametrize("vocab,hidden", [(1000, 4096), (151936, 4096), (17, 256), (640, 1024), (50, 992), (33, 288)])
 def test_head_bf16_shapes_ties_and_bad_rows(ops, vocab, hidden):
     """Ragged vocabulary sizes (a last CTA with fewer than 16 rows), the full Qwen3 vocabulary, other widths: logits bit-identical
     to the CPU restatement; equal maxima go to the lowest index; an infinite logit gives 0xffffffff."""
