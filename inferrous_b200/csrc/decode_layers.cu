@@ -450,8 +450,51 @@ __device__ __forceinline__ void request_cache(const StepDev &a, const LayerDev &
     }
 }
 
+// Shared-memory copy of the keys and values of one unit (at most kStageKeys of them: contexts up to 9 x 64 keys).
+constexpr int kStageKeys = 64;
+struct UnitStage {
+    uint16_t k[kStageKeys][kHeadDim];
+    uint16_t v[kStageKeys][kHeadDim];
+};
+__device__ __forceinline__ bool unit_staged(int begin, int stop) { return stop - begin <= kStageKeys; }
+
+// Before the barrier in front of the attention step: start the asynchronous copies of the cached keys and values of
+// this half-CTA's first unit into shared memory (they were final before the launch; the key and value of this step's
+// token are not among them), so that they arrive while the CTA waits for the others.  A unit of more than kStageKeys
+// keys only gets its cache lines requested into L2.
+__device__ __forceinline__ void stage_cache(const StepDev &a, const LayerDev &L, UnitStage *both, int end, int i) {
+    // thread i + 32 of the CTA: the copies of a unit are started by threads of that unit's half, which wait for them
+    const int tid = i + 32, half = tid >> 8, t = half ? tid - kUnitThreads : i, per_half = half ? kUnitThreads : kUnitThreads - 32;
+    const int u = blockIdx.x * 2 + half;
+    if (u >= a.q_heads * a.splits) return;
+    int head, split, splits, begin, stop;
+    unit_of(a, u, head, split);
+    unit_range(end, a.splits, split, splits, begin, stop);
+    if (split >= splits) return;
+    const int kv = head / (a.q_heads / a.kv_heads);
+    const size_t key_stride = (size_t)a.kv_heads * kHeadDim;
+    const uint16_t *ks = L.k_cache + (size_t)kv * kHeadDim + (size_t)begin * key_stride;
+    const uint16_t *vs = L.v_cache + (size_t)kv * kHeadDim + (size_t)begin * key_stride;
+    if (!unit_staged(begin, stop)) {
+        for (int line = t; line < 2 * (stop - begin); line += per_half) {  // two 128-byte lines per key and per cache
+            const size_t off = (size_t)(line >> 1) * key_stride + (size_t)(line & 1) * 64;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(ks + off));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(vs + off));
+        }
+        return;
+    }
+    const int cached = min(stop, end - 1) - begin;  // key end - 1 is written during this step
+    for (int c = t; c < cached * (kHeadDim / 8); c += per_half) {  // 16-byte pieces, sixteen per key
+        const int key = c >> 4, piece = c & 15;
+        const uint32_t kd = (uint32_t)__cvta_generic_to_shared(&both[half].k[key][8 * piece]);
+        const uint32_t vd = (uint32_t)__cvta_generic_to_shared(&both[half].v[key][8 * piece]);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(kd), "l"(ks + (size_t)key * key_stride + 8 * piece) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vd), "l"(vs + (size_t)key * key_stride + 8 * piece) : "memory");
+    }
+}
+
 template <class T>
-__device__ void attention_phase(const StepDev &a, const LayerDev &L, UnitShared *both, int end, int tid) {
+__device__ void attention_phase(const StepDev &a, const LayerDev &L, UnitShared *both, UnitStage *stage, int end, int tid) {
     typedef typename T::storage S;
     const int half = tid >> 8, t = tid & 255, warp = t >> 5, lane = t & 31;
     UnitShared &sh = both[half];
@@ -492,8 +535,13 @@ __device__ void attention_phase(const StepDev &a, const LayerDev &L, UnitShared 
                 }
             }
         }
+        // the first unit of the half reads the copies that stage_cache started (`stage`: null where nothing was staged)
+        const bool staged = stage && u < 2 * (int)gridDim.x && unit_staged(begin, stop);
+        if (staged) asm volatile("cp.async.wait_all;" ::: "memory");
         sync();
-        attention_unit<T, true>(sh, sync, t, L.k_cache + (size_t)kv * kHeadDim, L.v_cache + (size_t)kv * kHeadDim, key_stride, end,
+        const uint16_t *keys = staged ? &stage[half].k[0][0] - (size_t)begin * kHeadDim : L.k_cache + (size_t)kv * kHeadDim;
+        const uint16_t *values = staged ? &stage[half].v[0][0] - (size_t)begin * kHeadDim : L.v_cache + (size_t)kv * kHeadDim;
+        attention_unit<T, true>(sh, sync, t, keys, values, staged ? (size_t)kHeadDim : key_stride, end,
                                 splits, split, begin, stop, a.splits, head, a.scratch, a.counters,
                                 static_cast<S *>(a.attn) + (size_t)head * kHeadDim, nullptr);
         sync();  // sh is reused by this half's next unit
@@ -501,7 +549,14 @@ __device__ void attention_phase(const StepDev &a, const LayerDev &L, UnitShared 
 }
 
 // ---- the step -------------------------------------------------------------------------------------------------
-struct StepShared {
+template <bool STAGE> struct AttentionShared {
+    UnitShared units[2];
+    UnitStage stage[2];  // behind `row` in the union below: filled while the barrier after the Q|K|V step is waited for
+};
+template <> struct AttentionShared<false> {
+    UnitShared units[2];
+};
+template <bool STAGE> struct StepSharedOf {
     int8_t codes[kMaxK];                       // the quantized activation row of the current projection
     int red[kMaxCtaRows * kGroupWarps];        // per weight row: the eight partial sums of its group
     PrologueShared ps;
@@ -509,9 +564,11 @@ struct StepShared {
     uint32_t pad[3];
     union {
         float row[kMaxK];                      // prologues: the unquantized / normalised row
-        UnitShared units[2];                   // attention
+        AttentionShared<STAGE> att;
     };
 };
+typedef StepSharedOf<true> StepShared;
+static_assert(sizeof(StepShared) <= 227 * 1024, "shared memory of the decode kernel");
 
 // The five steps of a layer are inlined into the layer loop on purpose: as separate (not inlined) functions each call
 // spilled the registers that live across it, inside the streaming loops too, and a token took 4.9 ms instead of 2.2.
@@ -546,13 +603,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const StepDe
         mark(TP_QKV);
         mark(TP_ARRIVE1);
         if (!grid_barrier(a, barrier_ordinal(l, BAR_ATTENTION), &sh.ok, [&](int i, int n) {
-                request_cache(a, L, end, i, n);
+                stage_cache(a, L, sh.att.stage, end, i);
                 request_rows(L.o, q_width, a.hidden, 0, 1ll << 40, i, n);  // attention leaves HBM idle: the whole share of O
             }))
             return;
         mark(TP_PASS1);
 
-        attention_phase<T>(a, L, sh.units, end, tid);
+        attention_phase<T>(a, L, sh.att.units, sh.att.stage, end, tid);
         mark(TP_ATTENTION);
         if (!grid_barrier(a, barrier_ordinal(l, BAR_O), &sh.ok, [&](int i, int n) {
                 request_rows(L.gate, a.hidden, a.inter, 0, a.ahead_bytes, i, n);
@@ -612,10 +669,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const StepDe
 // w8a8_linear_allreduce) is the first part of the prologue that follows.  Two packet-buffer halves alternate; a rank
 // can only run two exchanges ahead of another once that one has read the older half.
 struct StepSharedTp {
-    StepShared base;
+    StepSharedOf<false> base;  // the two rows below leave no room for staged keys and values
     float hidden[kMaxK];    // the hidden row (the layer's input), every CTA its own copy
     float residual[kMaxK];  // hidden + attention block
 };
+static_assert(sizeof(StepSharedTp) <= 227 * 1024, "shared memory of the tensor-parallel decode kernel");
 
 // Waits (bounded) for the packets of `exchange` from every rank and leaves out[e] = bf16(in[e] + bf16(sum_r y_r[e])).
 // Thread t owns elements t, t + 512, ...; its packets (element-major, rank fastest) are taken sixteen at a time: all that
@@ -752,7 +810,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_tp_kernel(const Ste
     typedef typename T::storage S;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     StepSharedTp &tp = *reinterpret_cast<StepSharedTp *>(smem_raw);
-    StepShared &sh = tp.base;
+    StepSharedOf<false> &sh = tp.base;
     const int tid = threadIdx.x;
     const uint32_t pos = a.control[1];
     if (pos >= (uint32_t)a.capacity) {  // every CTA of every rank takes this branch: nobody waits for anybody
@@ -790,7 +848,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_tp_kernel(const Ste
             }))
             return;
         mark(TP_PASS1);
-        attention_phase<T>(a, L, sh.units, end, tid);
+        attention_phase<T>(a, L, sh.att.units, nullptr, end, tid);
         mark(TP_ATTENTION);
         if (!grid_barrier(a, ordinal(l, BAR_TP_O), &sh.ok, [&](int i, int n) {
                 request_rows(L.gate, a.hidden, a.inter, 0, a.ahead_bytes, i, n);
