@@ -72,6 +72,7 @@ struct StepDev {
     void *act;                  // [inter]
     float *scratch;             // attention: per (head, split) records
     uint32_t *counters;         // attention: per head arrival counters (zero between launches)
+    uint32_t *maxima;           // [layer][2]: max |v| of the attention row and of the SwiGLU row as absmax_key, zeroed with `sync`
     uint32_t *sync;             // {arrivals, abort}: zeroed by the host before every launch
     uint32_t *status;
     long long ahead_bytes;      // per CTA: bytes of the next matrix requested from L2 while waiting at the barrier in front of it
@@ -194,6 +195,25 @@ __device__ __forceinline__ float prologue_plain(const typename T::storage *x, in
     return s;
 }
 
+// quantize() of a row whose producers left max |x| in `*published` (absmax_key; quantize_with_max, src/kernels.rs:
+// 134-172): one pass, nothing parked in shared memory and no block-wide reduction.
+template <class T>
+__device__ __forceinline__ float prologue_published(const typename T::storage *x, int K, const uint32_t *published, int8_t *sq, int tid) {
+    constexpr int V = T::kVec;
+    const float m = fmaxf(1e-8f, __uint_as_float(__ldcg(published)));
+    const float s = __fdiv_rn(m, 127.0f);
+    const float inv = __frcp_rn(s);
+    for (int j = tid * V; j < K; j += kThreads * V) {
+        float v[V];
+        load_vec_cg<T>(x + j, v);
+        int c[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) c[i] = quant_code(v[i], s, inv);
+        store_codes<V>(sq + j, c);
+    }
+    return s;
+}
+
 // norm_quantize (src/kernels.rs:479-576): the reference's summation tree (256 strided partial sums, distances
 // 128..1), y = bf16((x * rsqrt(mean + eps)) * gain), m = max(1e-8, max|y|), s = m / 127
 // The part of norm_quantize behind the load: `row` holds the K values of x.
@@ -284,7 +304,7 @@ template <class T, int EPI, int J>
 __device__ void project(const StepDev &a, const int8_t *__restrict__ w0, const int8_t *__restrict__ w1,
                         const float *__restrict__ ws0, const float *__restrict__ ws1, int N, int K, float a_scale,
                         const int8_t *sq, int *red, const typename T::storage *residual, typename T::storage *out, int tid,
-                        uint32_t exchange = 0, uint32_t tag = 0) {
+                        uint32_t exchange = 0, uint32_t tag = 0, uint32_t *maxima = nullptr) {
     constexpr int R = (EPI == PRJ_SWIGLU) ? 2 : 1;
     // row units per batch: eight 16-byte loads in flight per lane.  Twelve or sixteen fit the registers too and were
     // measured 5-10 % slower per token.
@@ -362,6 +382,7 @@ __device__ void project(const StepDev &a, const int8_t *__restrict__ w0, const i
             }
     }
     __syncthreads();
+    uint32_t key = 0;  // PRJ_SWIGLU with `maxima`: max |value| of the rows this thread finished
     if (tid < units) {
         int sum[R];
 #pragma unroll
@@ -374,7 +395,9 @@ __device__ void project(const StepDev &a, const int8_t *__restrict__ w0, const i
         if (EPI == PRJ_SWIGLU) {
             const float gv = dequant(sum[0], a_scale, pre_s0);
             const float uv = dequant(sum[R - 1], a_scale, pre_s1);
-            T::store(out + c, swiglu_value(gv, uv));
+            const float value = swiglu_value(gv, uv);
+            T::store(out + c, value);
+            key = absmax_key(value);
         } else if (EPI == PRJ_PUSH) {
             push_packet(a, exchange, tag, c, dequant(sum[0], a_scale, pre_s0));
         } else if (EPI == PRJ_RESIDUAL) {
@@ -383,16 +406,20 @@ __device__ void project(const StepDev &a, const int8_t *__restrict__ w0, const i
             T::store(out + c, dequant(sum[0], a_scale, pre_s0));
         }
     }
+    if (EPI == PRJ_SWIGLU && maxima) {  // the quantizer in front of `down` takes the row's maximum from here
+        key = warp_max_u32(key);
+        if (lane == 0 && key) atomicMax(maxima, key);
+    }
 }
 
 template <class T, int EPI>
 __device__ __forceinline__ void project_any(const StepDev &a, const int8_t *w0, const int8_t *w1, const float *ws0, const float *ws1,
                                             int N, int K, float a_scale, const int8_t *sq, int *red,
                                             const typename T::storage *residual, typename T::storage *out, int tid,
-                                            uint32_t exchange = 0, uint32_t tag = 0) {
-    if (K <= kGroupBytes) project<T, EPI, 1>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid, exchange, tag);
-    else if (K <= 2 * kGroupBytes) project<T, EPI, 2>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid, exchange, tag);
-    else project<T, EPI, 3>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid, exchange, tag);
+                                            uint32_t exchange = 0, uint32_t tag = 0, uint32_t *maxima = nullptr) {
+    if (K <= kGroupBytes) project<T, EPI, 1>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid, exchange, tag, maxima);
+    else if (K <= 2 * kGroupBytes) project<T, EPI, 2>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid, exchange, tag, maxima);
+    else project<T, EPI, 3>(a, w0, w1, ws0, ws1, N, K, a_scale, sq, red, residual, out, tid, exchange, tag, maxima);
 }
 
 // ---- attention: two units side by side per CTA ------------------------------------------------------------------
@@ -494,7 +521,8 @@ __device__ __forceinline__ void stage_cache(const StepDev &a, const LayerDev &L,
 }
 
 template <class T>
-__device__ void attention_phase(const StepDev &a, const LayerDev &L, UnitShared *both, UnitStage *stage, int end, int tid) {
+__device__ void attention_phase(const StepDev &a, const LayerDev &L, UnitShared *both, UnitStage *stage, int end, int tid,
+                                uint32_t *maxima_row) {
     typedef typename T::storage S;
     const int half = tid >> 8, t = tid & 255, warp = t >> 5, lane = t & 31;
     UnitShared &sh = both[half];
@@ -543,7 +571,7 @@ __device__ void attention_phase(const StepDev &a, const LayerDev &L, UnitShared 
         const uint16_t *values = staged ? &stage[half].v[0][0] - (size_t)begin * kHeadDim : L.v_cache + (size_t)kv * kHeadDim;
         attention_unit<T, true>(sh, sync, t, keys, values, staged ? (size_t)kHeadDim : key_stride, end,
                                 splits, split, begin, stop, a.splits, head, a.scratch, a.counters,
-                                static_cast<S *>(a.attn) + (size_t)head * kHeadDim, nullptr);
+                                static_cast<S *>(a.attn) + (size_t)head * kHeadDim, maxima_row);
         sync();  // sh is reused by this half's next unit
     }
 }
@@ -609,7 +637,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const StepDe
             return;
         mark(TP_PASS1);
 
-        attention_phase<T>(a, L, sh.att.units, sh.att.stage, end, tid);
+        attention_phase<T>(a, L, sh.att.units, sh.att.stage, end, tid, a.maxima + 2 * l);
         mark(TP_ATTENTION);
         if (!grid_barrier(a, barrier_ordinal(l, BAR_O), &sh.ok, [&](int i, int n) {
                 request_rows(L.gate, a.hidden, a.inter, 0, a.ahead_bytes, i, n);
@@ -619,7 +647,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const StepDe
         mark(TP_PASS2);
 
         // quantize(attention row) -> O + residual
-        s = prologue_plain<T>(static_cast<const S *>(a.attn), q_width, sh.codes, sh.row, sh.ps, tid);
+        s = prologue_published<T>(static_cast<const S *>(a.attn), q_width, a.maxima + 2 * l, sh.codes, tid);
         __syncthreads();
         mark(TP_QUANT_O);
         project_any<T, PRJ_RESIDUAL>(a, L.o, nullptr, L.o_s, nullptr, a.hidden, q_width, s, sh.codes, sh.red, hidden, residual, tid);
@@ -636,7 +664,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const StepDe
         __syncthreads();
         mark(TP_NORM2);
         project_any<T, PRJ_SWIGLU>(a, L.gate, L.up, L.gate_s, L.up_s, a.inter, a.hidden, s, sh.codes, sh.red, nullptr,
-                                   static_cast<S *>(a.act), tid);
+                                   static_cast<S *>(a.act), tid, 0, 0, a.maxima + 2 * l + 1);
         mark(TP_GATE_UP);
         if (!grid_barrier(a, barrier_ordinal(l, BAR_DOWN), &sh.ok,
                           [&](int i, int n) { request_rows(L.down, a.inter, a.hidden, 0, a.ahead_bytes, i, n); }))
@@ -644,7 +672,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_kernel(const StepDe
         mark(TP_PASS4);
 
         // quantize(act) -> down + residual
-        s = prologue_plain<T>(static_cast<const S *>(a.act), a.inter, sh.codes, sh.row, sh.ps, tid);
+        s = prologue_published<T>(static_cast<const S *>(a.act), a.inter, a.maxima + 2 * l + 1, sh.codes, tid);
         __syncthreads();
         mark(TP_QUANT_DOWN);
         project_any<T, PRJ_RESIDUAL>(a, L.down, nullptr, L.down_s, nullptr, a.hidden, a.inter, s, sh.codes, sh.red, residual, hidden, tid);
@@ -848,7 +876,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_layers_tp_kernel(const Ste
             }))
             return;
         mark(TP_PASS1);
-        attention_phase<T>(a, L, sh.att.units, nullptr, end, tid);
+        attention_phase<T>(a, L, sh.att.units, nullptr, end, tid, nullptr);
         mark(TP_ATTENTION);
         if (!grid_barrier(a, ordinal(l, BAR_TP_O), &sh.ok, [&](int i, int n) {
                 request_rows(L.gate, a.hidden, a.inter, 0, a.ahead_bytes, i, n);
@@ -1012,7 +1040,8 @@ int qwen3_decode_plan_create(const qwen3_layer_desc *layers, int n_layers, int h
     const size_t b_hidden = round_up((size_t)hidden * el, 256), b_qkv = round_up((size_t)qkv_width * el, 256);
     const size_t b_attn = round_up((size_t)q_width * el, 256), b_act = round_up((size_t)intermediate * el, 256);
     const size_t b_scratch = round_up((size_t)q_heads * splits * kUnitRecord * sizeof(float), 256);
-    p->clear_bytes = round_up(16 + (size_t)q_heads * sizeof(uint32_t), 16);  // barrier words, then the attention counters
+    // barrier words, then the attention counters, then the published row maxima
+    p->clear_bytes = round_up(16 + ((size_t)q_heads + 2 * (size_t)n_layers) * sizeof(uint32_t), 16);
     const size_t b_reduced = round_up((size_t)hidden * sizeof(float), 256);
     const size_t total = b_hidden + b_qkv + b_attn + b_act + b_scratch + b_reduced + round_up(p->clear_bytes, 256);
     e = cudaMalloc(&p->work, total);
@@ -1038,6 +1067,7 @@ int qwen3_decode_plan_create(const qwen3_layer_desc *layers, int n_layers, int h
     s.reduced = reinterpret_cast<float *>(at); at += b_reduced;
     s.sync = reinterpret_cast<uint32_t *>(at);
     s.counters = s.sync + 4;
+    s.maxima = s.counters + q_heads;
     s.status = device_status_ptr();
     s.seq = nullptr; s.rank = 0; s.tp = 0; s.sliced = 0;
     for (int r = 0; r < kTpMaxRanks; ++r) s.ll[r] = nullptr;
