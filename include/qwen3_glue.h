@@ -153,9 +153,10 @@ int qwen3_decode_plan_destroy(qwen3_decode_plan_t plan);
 
 /* hidden: [hidden] in the plan's carrier, the embedding row of the token on entry and the last layer's output on return.
  * control[1] is the token's position (read on the device, as in qwen3_prepare_qk); the step appends that position's key
- * and value to every layer's caches.  Queues one memset of under 1 KiB (barrier words, attention counters, row maxima) and one kernel on `stream`; capturable.  Two steps of one
- * plan must not overlap on the device.  A grid-wide wait that runs out (about two seconds) ends the kernel early, leaves
- * `hidden` undefined and code 7 in the device status word (w8a8_device_status). */
+ * and value to every layer's caches.  Queues one memset of under 1 KiB (barrier words, attention counters, row maxima)
+ * and one kernel on `stream`; capturable.  Two steps of one plan must not overlap on the device.  A grid-wide wait that
+ * runs out (about two seconds) ends the kernel early, leaves `hidden` undefined and code 7 in the device status word
+ * (w8a8_device_status). */
 int qwen3_decode_layers(qwen3_decode_plan_t plan, void *hidden, const uint32_t *control, void *stream);
 
 /* Tensor parallel form of the step (no counterpart in the reference, which is single-GPU): the plan describes THIS rank's
