@@ -28,6 +28,9 @@ CASES = [
     (dict(layers=1, intermediate=8448, context=64), 3, 20),
     # one key/value head for eight query heads; widths that are not multiples of the 512-byte warp slice
     (dict(layers=2, hidden=1152, q_heads=8, kv_heads=1, intermediate=2176, vocab=1000, context=96), 17, 60),
+    # more keys than sixteen splits of 64: the units read their keys and values from the cache, not from the copies
+    # in shared memory, and decoding crosses the step from 64- to 96-key splits (1024 keys)
+    (dict(context=1100), 1000, 60),
 ]
 
 
